@@ -1,0 +1,944 @@
+// Host side of the decode engine and its C ABI (include/b200moe.h).
+//
+// What the reference does in aegist_rs/src/hybrid.rs is done here with a different plan:
+//   * every tensor, the embedding table and all experts included, is resident in HBM (a slot table
+//     [layer][expert] -> device address replaces the LRU pool of hybrid.rs:190-390);
+//   * a decode step is one CUDA graph of 6 launches per layer with no host synchronisation inside:
+//     token ids, positions, router picks and the arg-max stay on the device (the reference crosses
+//     the host boundary 82 times per token, hybrid.rs:743-758, 875, 919, 1000);
+//   * the KV cache is paged (64-token pages through a page table) and stored as bf16 or fp32.
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <map>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/b200moe.h"
+#include "kernels.cuh"
+#include "nxfile.hpp"
+
+namespace b2 {
+
+#define CU(call)                                                                                       \
+    do {                                                                                               \
+        cudaError_t e_ = (call);                                                                       \
+        if (e_ != cudaSuccess) return fail("%s: %s", #call, cudaGetErrorString(e_));                   \
+    } while (0)
+
+struct Cfg {
+    int V = 0, D = 0, L = 0;
+    std::vector<int> attn;
+    int H = 0, KV = 0, HD = 0, RD = 0;
+    double theta = 0;
+    int HK = 0, HV = 0, DK = 0, DV = 0, CK = 0;
+    int E = 0, TOPK = 0, I = 0, SH = 0, G = 0;
+    float eps = 1e-6f;
+    int n1 = 0, n2 = 0, rank = 0, cores_active = 0;
+    int C() const { return 2 * HK * DK + HV * DV; }
+    int VD() const { return HV * DV; }
+    int n_attn() const { int n = 0; for (int a : attn) n += a; return n; }
+    int n_delta() const { return L - n_attn(); }
+    size_t gu_q() const { return (size_t)2 * I * (D / 2); }
+    size_t gu_sm() const { return (size_t)2 * I * (D / G) * 2; }
+    size_t dn_q() const { return (size_t)D * (I / 2); }
+    size_t dn_sm() const { return (size_t)D * (I / G) * 2; }
+    size_t off_gu_s() const { return gu_q(); }
+    size_t off_gu_m() const { return gu_q() + gu_sm(); }
+    size_t off_dn_q() const { return gu_q() + 2 * gu_sm(); }
+    size_t off_dn_s() const { return off_dn_q() + dn_q(); }
+    size_t off_dn_m() const { return off_dn_s() + dn_sm(); }
+    size_t expert_bytes() const { size_t n = off_dn_m() + dn_sm(); return (n + 63) / 64 * 64; }
+};
+
+struct DevTensor {
+    void* p = nullptr;
+    size_t nbytes = 0;
+    std::string dtype;
+    std::vector<int64_t> shape;
+};
+
+struct QWd { const int8_t* w = nullptr; const uint16_t* s = nullptr; int n = 0, k = 0; };
+
+struct LayerW {
+    bool attn = false;
+    int slot = 0;
+    const uint16_t *norm1 = nullptr, *norm2 = nullptr;
+    // attention
+    QWd q, k, v, o;
+    const uint16_t *q_norm = nullptr, *k_norm = nullptr;
+    // DeltaNet
+    QWd in_qkv, in_z, out;
+    const uint16_t *in_a = nullptr, *in_b = nullptr, *conv = nullptr, *a_log = nullptr, *dt_bias = nullptr, *gnorm = nullptr;
+    // MoE
+    const uint16_t* router = nullptr;
+    QWd sh_gate, sh_up, sh_down;
+    const uint16_t* sh_gw = nullptr;
+    const uint8_t* experts = nullptr;       // [local experts][expert_bytes]
+    const uint8_t** eptr = nullptr;         // device [E]
+    float* router_bias = nullptr;           // device [E] or null
+};
+
+static size_t dtype_size(const std::string& d) {
+    if (d == "bf16" || d == "f16") return 2;
+    if (d == "f32") return 4;
+    if (d == "i8" || d == "u8") return 1;
+    if (d == "i64") return 8;
+    return 0;
+}
+
+}  // namespace b2
+
+using namespace b2;
+
+struct b2_engine {
+    Cfg c;
+    int device = 0, B = 1, cap = 0, nsm = 148;
+    bool kv_f32 = false;
+    int ep_rank = 0, ep_world = 1;
+    std::string err, desc;
+    std::map<std::string, DevTensor> t;
+    std::vector<LayerW> layers;
+    const uint16_t *embed = nullptr, *norm = nullptr;
+    QWd lm_head;
+    bool finished = false;
+    size_t weight_bytes = 0;
+    std::string gpu_name;
+
+    cudaStream_t stream = nullptr;
+    cudaGraphExec_t graph = nullptr;
+    cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+    int launches = 0;
+
+    // state
+    float *conv = nullptr, *state = nullptr;
+    size_t conv_bytes = 0, state_bytes = 0;
+    float* snap_conv[2] = {nullptr, nullptr};
+    float* snap_state[2] = {nullptr, nullptr};
+    long snap_pos[2] = {-1, -1};
+    void *kpool = nullptr, *vpool = nullptr;
+    int* page_table = nullptr;
+    int pages_per_seq = 0;
+    float *rope_cos = nullptr, *rope_sin = nullptr;
+    int length = 0;
+
+    // per-step device scalars and work buffers
+    int *d_tok = nullptr, *d_next = nullptr, *d_pos = nullptr, *d_err = nullptr;
+    unsigned int* d_counter = nullptr;      // [B] gemv finishers
+    unsigned int* d_acounter = nullptr;     // [B][KV] attention merge
+    float *x = nullptr, *big = nullptr, *zbuf = nullptr, *kraw = nullptr, *vraw = nullptr, *beta = nullptr, *gdec = nullptr;
+    float *obuf = nullptr, *att = nullptr, *rlogits = nullptr, *sh_act = nullptr, *sgate = nullptr, *act = nullptr, *logits = nullptr;
+    int* top_idx = nullptr;                  // [L][B][TOPK]
+    float* top_w = nullptr;
+    float* part_val = nullptr;
+    int* part_idx = nullptr;
+    float* attn_part = nullptr;
+    int nsplit = 1, head_grid = 1;
+    uint32_t* h_pin = nullptr;               // pinned staging [B]
+    std::vector<int> tap_layers;
+    float* tap_buf = nullptr;
+    uint64_t hits = 0;
+
+    int fail(const char* fmt, ...) {
+        char buf[1024];
+        va_list ap;
+        va_start(ap, fmt);
+        vsnprintf(buf, sizeof(buf), fmt, ap);
+        va_end(ap);
+        err = buf;
+        return 1;
+    }
+    ~b2_engine();
+    int parse_config(const JValue& j);
+    int put(const std::string& name, const std::string& dtype, const std::vector<int64_t>& shape, const void* data,
+            size_t nbytes, bool on_device);
+    int finish();
+    int need(const std::string& name, const std::string& dtype, std::vector<int64_t> shape, const void** out);
+    int qw(const std::string& prefix, int n, int k, QWd* out);
+    int build_graph();
+    int enqueue_step(cudaStream_t st, bool count);
+    int run_steps(int n);
+    int check_device_error();
+    int reset_state();
+};
+
+b2_engine::~b2_engine() {
+    cudaSetDevice(device);
+    if (graph) cudaGraphExecDestroy(graph);
+    for (auto& kv : t) cudaFree(kv.second.p);
+    for (auto& l : layers) { cudaFree((void*)l.eptr); cudaFree(l.router_bias); }
+    void* bufs[] = {conv, state, snap_conv[0], snap_conv[1], snap_state[0], snap_state[1], kpool, vpool, page_table, rope_cos,
+                    rope_sin, d_tok, d_next, d_pos, d_err, d_counter, d_acounter, x, big, zbuf, kraw, vraw, beta, gdec, obuf, att,
+                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf};
+    for (void* p : bufs) cudaFree(p);
+    if (h_pin) cudaFreeHost(h_pin);
+    if (ev0) cudaEventDestroy(ev0);
+    if (ev1) cudaEventDestroy(ev1);
+    if (stream) cudaStreamDestroy(stream);
+}
+
+// HConfig::from_header + check (aegist_rs/src/hybrid.rs:53-120), with this engine's own shape limits.
+int b2_engine::parse_config(const JValue& j) {
+    auto num = [&](const char* k, double* out) -> bool {
+        const JValue* v = j.get(k);
+        if (!v || !v->is_num()) { fail("config is missing %s", k); return false; }
+        *out = v->num;
+        return true;
+    };
+    double d;
+#define GETI(field, key) if (!num(key, &d)) return 1; c.field = (int)d;
+    GETI(V, "vocab_size") GETI(D, "d_model") GETI(L, "n_layers") GETI(H, "n_heads") GETI(KV, "n_kv_heads")
+    GETI(HD, "head_dim") GETI(RD, "rotary_dim") GETI(HK, "lin_k_heads") GETI(HV, "lin_v_heads") GETI(DK, "lin_k_dim")
+    GETI(DV, "lin_v_dim") GETI(CK, "conv_kernel") GETI(E, "n_experts") GETI(TOPK, "experts_active")
+    GETI(I, "expert_hidden") GETI(SH, "shared_hidden") GETI(G, "expert_group") GETI(rank, "core_rank")
+    GETI(cores_active, "cores_active")
+#undef GETI
+    if (!num("rope_theta", &c.theta)) return 1;
+    if (!num("norm_eps", &d)) return 1;
+    c.eps = (float)d;
+    const JValue* lt = j.get("layer_types");
+    if (!lt || lt->type != JValue::Arr) return fail("config is missing layer_types");
+    for (auto& k : lt->arr) c.attn.push_back(k.type == JValue::Str && k.str == "attn");
+    const JValue* grid = j.get("core_grid");
+    if (!grid || grid->type != JValue::Arr || grid->arr.size() != 2) return fail("config is missing core_grid");
+    c.n1 = (int)grid->arr[0].num;
+    c.n2 = (int)grid->arr[1].num;
+    const JValue* tie = j.get("tie_embeddings");
+    if (tie && tie->type == JValue::Bool && tie->b) return fail("this engine build needs an untied output head");
+    const JValue* arch = j.get("arch");
+    if (arch && arch->type == JValue::Str && arch->str != "hybrid-moe") return fail("arch %s is not hybrid-moe", arch->str.c_str());
+    for (const char* k : {"hc_count"}) {
+        const JValue* v = j.get(k);
+        if (v && v->is_num() && v->num > 1) return fail("this engine does not run brains with hyper-connections (hc_count > 1)");
+    }
+    const JValue* ef = j.get("expert_format");
+    if (ef && ef->type == JValue::Str && ef->str != "q4") return fail("expert_format %s is not q4", ef->str.c_str());
+
+    std::string bad;
+    auto add = [&](const std::string& s) { bad += (bad.empty() ? "" : "; ") + s; };
+    if ((int)c.attn.size() != c.L) add("layer_types length");
+    if (c.V < 1 || c.L < 1) add("empty model");
+    if (c.D % 64 != 0 || c.D < 64 || c.D > 2048) add("d_model must be a multiple of 64, at most 2048");
+    if (!(c.HD == 64 || c.HD == 128 || c.HD == 256) || c.RD > c.HD || c.RD % 2 != 0 || c.RD < 2) add("head_dim must be 64/128/256 and rotary_dim even <= head_dim");
+    if (c.KV < 1 || c.H % std::max(c.KV, 1) != 0 || c.H / std::max(c.KV, 1) > 8) add("n_heads must be a multiple of n_kv_heads with at most 8 query heads per KV head");
+    if (!(c.DK == 64 || c.DK == 128) || c.DV % 32 != 0 || c.DV > 256 || c.HK < 1 || c.HV % std::max(c.HK, 1) != 0 || c.CK != 4) add("DeltaNet needs lin_k_dim 64/128, lin_v_dim a multiple of 32, hv % hk == 0, conv kernel 4");
+    if (c.H * c.HD > 4096 || c.VD() > 4096 || (c.H * c.HD) % 32 != 0 || c.VD() % 32 != 0) add("mixer width above 4096");
+    if (c.C() % 2 != 0) add("odd conv width");
+    if (c.E > 256 || c.E < 1 || c.TOPK > 8 || c.TOPK < 1 || c.TOPK > c.E || c.G != 64 || c.I % 64 != 0 || c.I > 512 || c.I < 64) add("experts need n_experts <= 256, top-k <= 8, group 64, hidden a multiple of 64 up to 512");
+    if (c.SH % 16 != 0 || c.SH > 512 || c.SH < 16) add("shared_hidden must be a multiple of 16 up to 512");
+    if (c.E % ep_world != 0) add("n_experts not divisible by the number of expert-parallel ranks");
+    if (!bad.empty()) return fail("this engine build does not support this brain's shape: %s", bad.c_str());
+    return 0;
+}
+
+int b2_engine::put(const std::string& name, const std::string& dtype, const std::vector<int64_t>& shape, const void* data,
+                   size_t nbytes, bool on_device) {
+    if (finished) return fail("b2_put_tensor after b2_finish");
+    size_t es = dtype_size(dtype);
+    if (!es) return fail("%s: unsupported dtype %s", name.c_str(), dtype.c_str());
+    size_t n = es;
+    for (auto s : shape) n *= (size_t)s;
+    if (n != nbytes) return fail("%s: %zu bytes given, shape says %zu", name.c_str(), nbytes, n);
+    // tensors the decode path does not read are not kept (the embedding IS kept: it is gathered on the device)
+    if (name.find(".engine.") != std::string::npos || name.find(".cores.") != std::string::npos) {
+        if (name.size() > 10 && name.rfind(".cores.ids") == name.size() - 10 && nbytes != 0)
+            return fail("%s: this brain has live switchable cores, which this engine build does not run", name.c_str());
+        return 0;
+    }
+    CU(cudaSetDevice(device));
+    DevTensor d;
+    d.dtype = dtype;
+    d.shape = shape;
+    const char* src = (const char*)data;
+    // expert-parallel: keep only this rank's rows of the packed experts
+    bool is_experts = name.size() > 15 && name.rfind(".moe.experts.q4") == name.size() - 15;
+    if (is_experts && ep_world > 1) {
+        if (shape.size() != 2 || shape[0] != c.E) return fail("%s: expected [%d, expert_bytes]", name.c_str(), c.E);
+        size_t per = (size_t)c.E / ep_world;
+        src += per * ep_rank * (size_t)shape[1];
+        nbytes = per * (size_t)shape[1];
+        d.shape[0] = (int64_t)per;
+    }
+    d.nbytes = nbytes;
+    if (t.count(name)) { cudaFree(t[name].p); weight_bytes -= t[name].nbytes; }
+    CU(cudaMalloc(&d.p, std::max<size_t>(nbytes, 16)));
+    if (nbytes) CU(cudaMemcpy(d.p, src, nbytes, on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice));
+    weight_bytes += nbytes;
+    t[name] = d;
+    return 0;
+}
+
+int b2_engine::need(const std::string& name, const std::string& dtype, std::vector<int64_t> shape, const void** out) {
+    auto it = t.find(name);
+    if (it == t.end()) return fail("the brain has no tensor %s", name.c_str());
+    const DevTensor& d = it->second;
+    bool same = d.dtype == dtype && d.shape.size() == shape.size();
+    for (size_t i = 0; same && i < shape.size(); i++) same = d.shape[i] == shape[i];
+    if (!same) {
+        std::string got = d.dtype + " [", want = dtype + " [";
+        for (auto s : d.shape) got += std::to_string(s) + ",";
+        for (auto s : shape) want += std::to_string(s) + ",";
+        return fail("%s is %s], expected %s]", name.c_str(), got.c_str(), want.c_str());
+    }
+    *out = d.p;
+    return 0;
+}
+
+int b2_engine::qw(const std::string& prefix, int n, int k, QWd* out) {
+    const void *w, *s;
+    if (need(prefix + ".qweight", "i8", {n, k}, &w)) return 1;
+    if (need(prefix + ".scale", "bf16", {n, 1}, &s)) return 1;
+    out->w = (const int8_t*)w;
+    out->s = (const uint16_t*)s;
+    out->n = n;
+    out->k = k;
+    return 0;
+}
+
+template <typename T>
+static cudaError_t dalloc(T** p, size_t n, bool zero = true) {
+    cudaError_t e = cudaMalloc((void**)p, std::max<size_t>(n * sizeof(T), 16));
+    if (e == cudaSuccess && zero) e = cudaMemset(*p, 0, std::max<size_t>(n * sizeof(T), 16));
+    return e;
+}
+
+int b2_engine::finish() {
+    if (finished) return fail("b2_finish called twice");
+    CU(cudaSetDevice(device));
+    cudaDeviceProp prop;
+    CU(cudaGetDeviceProperties(&prop, device));
+    nsm = prop.multiProcessorCount;
+    gpu_name = prop.name;
+    const void* p;
+#define NEED(dst, name, dtype, ...) if (need(name, dtype, {__VA_ARGS__}, &p)) return 1; dst = (decltype(dst))p;
+    NEED(embed, "embed.weight", "bf16", c.V, c.D)
+    NEED(norm, "norm.weight", "bf16", c.D)
+    if (qw("lm_head", c.V, c.D, &lm_head)) return 1;
+    int n_attn = 0, n_delta = 0;
+    const int per = c.E / ep_world;
+    for (int i = 0; i < c.L; i++) {
+        LayerW l;
+        std::string b = "blocks." + std::to_string(i) + ".";
+        l.attn = c.attn[i];
+        NEED(l.norm1, b + "norm1.weight", "bf16", c.D)
+        NEED(l.norm2, b + "norm2.weight", "bf16", c.D)
+        if (l.attn) {
+            l.slot = n_attn++;
+            NEED(l.q_norm, b + "mixer.q_norm.weight", "bf16", c.HD)
+            NEED(l.k_norm, b + "mixer.k_norm.weight", "bf16", c.HD)
+            if (qw(b + "mixer.q", 2 * c.H * c.HD, c.D, &l.q) || qw(b + "mixer.k", c.KV * c.HD, c.D, &l.k) ||
+                qw(b + "mixer.v", c.KV * c.HD, c.D, &l.v) || qw(b + "mixer.o", c.D, c.H * c.HD, &l.o)) return 1;
+        } else {
+            l.slot = n_delta++;
+            NEED(l.in_a, b + "mixer.in_a.weight", "bf16", c.HV, c.D)
+            NEED(l.in_b, b + "mixer.in_b.weight", "bf16", c.HV, c.D)
+            NEED(l.conv, b + "mixer.conv", "bf16", c.C(), c.CK)
+            NEED(l.a_log, b + "mixer.A_log", "bf16", c.HV)
+            NEED(l.dt_bias, b + "mixer.dt_bias", "bf16", c.HV)
+            NEED(l.gnorm, b + "mixer.norm.weight", "bf16", c.DV)
+            if (qw(b + "mixer.in_qkv", c.C(), c.D, &l.in_qkv) || qw(b + "mixer.in_z", c.VD(), c.D, &l.in_z) ||
+                qw(b + "mixer.out", c.D, c.VD(), &l.out)) return 1;
+        }
+        NEED(l.router, b + "moe.router.weight", "bf16", c.E, c.D)
+        NEED(l.sh_gw, b + "moe.shared_gate.weight", "bf16", 1, c.D)
+        if (qw(b + "moe.shared.gate", c.SH, c.D, &l.sh_gate) || qw(b + "moe.shared.up", c.SH, c.D, &l.sh_up) ||
+            qw(b + "moe.shared.down", c.D, c.SH, &l.sh_down)) return 1;
+        NEED(l.experts, b + "moe.experts.q4", "u8", per, (int64_t)c.expert_bytes())
+        // the slot table: every expert of this rank is resident at a fixed address
+        std::vector<const uint8_t*> tab(c.E, nullptr);
+        for (int e = 0; e < per; e++) tab[ep_rank * per + e] = l.experts + (size_t)e * c.expert_bytes();
+        CU(cudaMalloc((void**)&l.eptr, c.E * sizeof(void*)));
+        CU(cudaMemcpy((void*)l.eptr, tab.data(), c.E * sizeof(void*), cudaMemcpyHostToDevice));
+        layers.push_back(l);
+    }
+#undef NEED
+    // context, recurrent state, snapshots (aegist_rs/src/hybrid.rs:606-625)
+    if (cap <= 0) cap = 32768;
+    pages_per_seq = (cap + KV_PAGE - 1) / KV_PAGE;
+    const size_t kv_elems = (size_t)std::max(n_attn, 1) * B * pages_per_seq * c.KV * KV_PAGE * c.HD;
+    const size_t kvb = kv_f32 ? 4 : 2;
+    cudaError_t e1 = cudaMalloc(&kpool, kv_elems * kvb), e2 = cudaMalloc(&vpool, kv_elems * kvb);
+    if (e1 != cudaSuccess || e2 != cudaSuccess) return fail("KV cache for %d tokens x %d sequences: %s", cap, B, cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+    {
+        // identity page table: sequence b owns pages [b * pages_per_seq, (b+1) * pages_per_seq) of each layer's pool
+        std::vector<int> pt((size_t)B * pages_per_seq);
+        for (size_t i = 0; i < pt.size(); i++) pt[i] = (int)i;
+        CU(dalloc(&page_table, pt.size(), false));
+        CU(cudaMemcpy(page_table, pt.data(), pt.size() * 4, cudaMemcpyHostToDevice));
+    }
+    conv_bytes = (size_t)std::max(n_delta, 1) * B * c.C() * 3 * 4;
+    state_bytes = (size_t)std::max(n_delta, 1) * B * c.HV * c.DK * c.DV * 4;
+    CU(dalloc((char**)&conv, conv_bytes));
+    CU(dalloc((char**)&state, state_bytes));
+    for (int s = 0; s < 2; s++) {
+        CU(dalloc((char**)&snap_conv[s], conv_bytes));
+        CU(dalloc((char**)&snap_state[s], state_bytes));
+    }
+    {
+        // RoPE tables as the Python reference builds them (aegist/hybrid.py:152-157): fp32 angle =
+        // fp32(position) * fp32(1 / fp32(theta^(2j/rd))); the power in double reproduces torch's fp32 pow.
+        const int hr = c.RD / 2;
+        std::vector<float> cs((size_t)cap * hr), sn((size_t)cap * hr);
+        for (int j = 0; j < hr; j++) {
+            const float ex = (float)(2 * j) / (float)c.RD;
+            const float pw = (float)std::pow((double)(float)c.theta, (double)ex);
+            const float inv = 1.0f / pw;
+            for (int pos = 0; pos < cap; pos++) {
+                const float ang = (float)pos * inv;
+                cs[(size_t)pos * hr + j] = (float)std::cos((double)ang);
+                sn[(size_t)pos * hr + j] = (float)std::sin((double)ang);
+            }
+        }
+        CU(dalloc(&rope_cos, cs.size(), false));
+        CU(dalloc(&rope_sin, sn.size(), false));
+        CU(cudaMemcpy(rope_cos, cs.data(), cs.size() * 4, cudaMemcpyHostToDevice));
+        CU(cudaMemcpy(rope_sin, sn.data(), sn.size() * 4, cudaMemcpyHostToDevice));
+    }
+    // work buffers
+    const int bigw = std::max(2 * c.H * c.HD, c.C());
+    CU(dalloc(&d_tok, B)); CU(dalloc(&d_next, B)); CU(dalloc(&d_pos, B)); CU(dalloc(&d_err, 1));
+    CU(dalloc(&d_counter, B)); CU(dalloc(&d_acounter, (size_t)B * c.KV));
+    CU(dalloc(&x, (size_t)B * c.D)); CU(dalloc(&big, (size_t)B * bigw)); CU(dalloc(&zbuf, (size_t)B * c.VD()));
+    CU(dalloc(&kraw, (size_t)B * c.KV * c.HD)); CU(dalloc(&vraw, (size_t)B * c.KV * c.HD));
+    CU(dalloc(&beta, (size_t)B * c.HV)); CU(dalloc(&gdec, (size_t)B * c.HV));
+    CU(dalloc(&obuf, (size_t)B * c.VD())); CU(dalloc(&att, (size_t)B * c.H * c.HD));
+    CU(dalloc(&rlogits, (size_t)B * c.E)); CU(dalloc(&sh_act, (size_t)B * c.SH)); CU(dalloc(&sgate, B));
+    CU(dalloc(&act, (size_t)B * c.TOPK * c.I)); CU(dalloc(&logits, (size_t)B * c.V));
+    CU(dalloc(&top_idx, (size_t)c.L * B * c.TOPK)); CU(dalloc(&top_w, (size_t)c.L * B * c.TOPK));
+    head_grid = std::min((c.V / 2 + WARPS - 1) / WARPS, 2 * nsm);
+    CU(dalloc(&part_val, (size_t)B * head_grid)); CU(dalloc(&part_idx, (size_t)B * head_grid));
+    // attention: enough slices to fill the GPU, but at least 64 positions each at full context
+    nsplit = std::max(1, std::min({64, (2 * nsm) / std::max(1, c.KV * B), (cap + 63) / 64}));
+    CU(dalloc(&attn_part, (size_t)B * c.KV * nsplit * (c.H / c.KV) * (c.HD + 2)));
+    CU(cudaMallocHost((void**)&h_pin, std::max(B, 1) * sizeof(uint32_t) * 2));
+    CU(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
+    CU(cudaEventCreate(&ev0));
+    CU(cudaEventCreate(&ev1));
+    CU(cudaDeviceSynchronize());
+    finished = true;
+    char buf[512];
+    size_t kv_bytes = 2 * kv_elems * kvb;
+    snprintf(buf, sizeof(buf), "%s: %.2f GB of weights in HBM (%d of %d experts resident%s), %d live cores, context %d tokens x %d, KV %s %.2f GB",
+             gpu_name.c_str(), weight_bytes / 1e9, c.L * per, c.L * c.E, ep_world > 1 ? " on this rank" : "", 0, cap, B,
+             kv_f32 ? "fp32" : "bf16", kv_bytes / 1e9);
+    desc = buf;
+    return build_graph();
+}
+
+template <typename F>
+static cudaError_t opt_in_smem(F* f, size_t bytes) {
+    if (bytes <= 48 * 1024) return cudaSuccess;
+    return cudaFuncSetAttribute((const void*)f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+}
+
+static void launch_gemv(const GemvArgs& a, int B, int nsm, cudaStream_t st, int grid_override = 0) {
+    const int grid = grid_override ? grid_override : std::max(1, std::min((a.total_jobs + WARPS - 1) / WARPS, 2 * nsm));
+    const size_t smem = (size_t)(a.K + 32) * 4;
+    const int maxc = (a.K + 511) / 512;
+    dim3 g(grid, B);
+    if (maxc <= 1) k_gemv_norm<1><<<g, THREADS, smem, st>>>(a);
+    else if (maxc == 2) k_gemv_norm<2><<<g, THREADS, smem, st>>>(a);
+    else k_gemv_norm<4><<<g, THREADS, smem, st>>>(a);
+}
+
+static Seg make_seg(int kind, const void* w, const uint16_t* s, int rows, float* out, int out_stride) {
+    Seg g{};
+    g.w = w; g.s = s; g.rows = rows; g.kind = kind; g.out = out; g.out_stride = out_stride;
+    g.jobs = (kind == SEG_I8 || kind == SEG_I8_CONV || kind == SEG_I8_ARGMAX) ? (rows + 1) / 2 : rows;
+    return g;
+}
+static void seal(GemvArgs& a) {
+    a.total_jobs = 0;
+    for (int i = 0; i < a.nseg; i++) a.total_jobs += a.seg[i].jobs;
+}
+
+static void launch_proj(const ProjArgs& a, int B, int nsm, cudaStream_t st) {
+    // rows per block a multiple of 4 (four warp pairs per block), one wave of blocks
+    int rpb = 4;
+    while ((a.N + rpb - 1) / rpb > 2 * nsm) rpb += 4;
+    const int grid = (a.N + rpb - 1) / rpb;
+    const size_t smem = (size_t)(a.K + 2 * rpb) * 4;
+    const int maxc = (a.K / 2 + 511) / 512;
+    dim3 g(grid, B);
+    if (maxc <= 1) k_proj_out<1><<<g, THREADS, smem, st>>>(a);
+    else if (maxc == 2) k_proj_out<2><<<g, THREADS, smem, st>>>(a);
+    else k_proj_out<4><<<g, THREADS, smem, st>>>(a);
+}
+
+static void launch_delta(const DeltaArgs& a, int DK, int B, cudaStream_t st) {
+    dim3 g(a.HV * (a.DV / 32), B);
+    if (DK == 64) k_delta_step<64><<<g, THREADS, 0, st>>>(a);
+    else k_delta_step<128><<<g, THREADS, 0, st>>>(a);
+}
+
+static void launch_experts(const ExpertArgs& a, int B, int nsm, cudaStream_t st) {
+    const int picks = B * a.topk;
+    int gx = std::max(1, std::min((a.I + WARPS - 1) / WARPS, (2 * nsm + picks - 1) / picks));
+    const size_t smem = (size_t)(a.D + 32) * 4;
+    if (a.D <= 1024) k_expert_gu<1><<<dim3(gx, picks), THREADS, smem, st>>>(a);
+    else k_expert_gu<2><<<dim3(gx, picks), THREADS, smem, st>>>(a);
+    int gd = std::max(1, std::min((a.D + WARPS - 1) / WARPS, (2 * nsm + B - 1) / B));
+    const size_t smem2 = (size_t)(a.topk * a.I + a.SH) * 4;
+    k_expert_down<<<dim3(gd, B), THREADS, smem2, st>>>(a);
+}
+
+static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaStream_t st) {
+    const int G = a.H / a.KV;
+    const size_t smem = (size_t)WARPS * G * HD * 4;
+    dim3 g(a.nsplit, a.KV, B);
+#define ATT(hd, f)                                                                     \
+    {                                                                                  \
+        cudaError_t e = opt_in_smem(k_attn<hd, f>, smem);                              \
+        if (e != cudaSuccess) return e;                                                \
+        k_attn<hd, f><<<g, THREADS, smem, st>>>(a);                                    \
+    }
+    if (HD == 64) { if (f32) ATT(64, true) else ATT(64, false) }
+    else if (HD == 128) { if (f32) ATT(128, true) else ATT(128, false) }
+    else { if (f32) ATT(256, true) else ATT(256, false) }
+#undef ATT
+    return cudaSuccess;
+}
+
+// One decode step for all B sequences: token ids in d_tok, positions in d_pos.
+int b2_engine::enqueue_step(cudaStream_t st, bool count) {
+    int n = 0;
+    k_embed<<<B, 256, 0, st>>>(embed, d_tok, x, c.D, c.V, d_err);
+    n++;
+    const size_t kv_layer = (size_t)B * pages_per_seq * c.KV * KV_PAGE * c.HD * (kv_f32 ? 4 : 2);
+    for (int li = 0; li < c.L; li++) {
+        const LayerW& l = layers[li];
+        if (l.attn) {
+            GemvArgs a{};
+            a.seg[0] = make_seg(SEG_I8, l.q.w, l.q.s, l.q.n, big, 2 * c.H * c.HD);
+            a.seg[1] = make_seg(SEG_I8, l.k.w, l.k.s, l.k.n, kraw, c.KV * c.HD);
+            a.seg[2] = make_seg(SEG_I8, l.v.w, l.v.s, l.v.n, vraw, c.KV * c.HD);
+            a.nseg = 3; seal(a);
+            a.x = x; a.norm_w = l.norm1; a.eps = c.eps; a.K = c.D;
+            launch_gemv(a, B, nsm, st);
+            AttnArgs t{};
+            t.qraw = big; t.kraw = kraw; t.vraw = vraw; t.qn_w = l.q_norm; t.kn_w = l.k_norm;
+            t.rope_cos = rope_cos; t.rope_sin = rope_sin; t.pos = d_pos;
+            t.kpool = (char*)kpool + kv_layer * l.slot; t.vpool = (char*)vpool + kv_layer * l.slot;
+            t.page_table = page_table; t.pages_per_seq = pages_per_seq;
+            t.H = c.H; t.KV = c.KV; t.RD = c.RD; t.eps = c.eps; t.scale = 1.0f / std::sqrt((float)c.HD);
+            t.part = attn_part; t.counter = d_acounter; t.out = att; t.nsplit = nsplit;
+            cudaError_t e = launch_attn(t, c.HD, kv_f32, B, st);
+            if (e != cudaSuccess) return fail("attention launch: %s", cudaGetErrorString(e));
+            ProjArgs p{};
+            p.in = att; p.mode = 1; p.w = l.o.w; p.s = l.o.s; p.x = x; p.N = c.D; p.K = c.H * c.HD; p.eps = c.eps; p.DV = c.DV;
+            launch_proj(p, B, nsm, st);
+        } else {
+            GemvArgs a{};
+            a.seg[0] = make_seg(SEG_I8_CONV, l.in_qkv.w, l.in_qkv.s, l.in_qkv.n, big, c.C());
+            a.seg[1] = make_seg(SEG_I8, l.in_z.w, l.in_z.s, l.in_z.n, zbuf, c.VD());
+            a.seg[2] = make_seg(SEG_BF_SIGMOID, l.in_b, nullptr, c.HV, beta, c.HV);
+            a.seg[3] = make_seg(SEG_BF_DECAY, l.in_a, nullptr, c.HV, gdec, c.HV);
+            a.nseg = 4; seal(a);
+            a.x = x; a.norm_w = l.norm1; a.eps = c.eps; a.K = c.D;
+            a.conv_w = l.conv; a.conv_state = conv + (size_t)l.slot * B * c.C() * 3;
+            a.a_log = l.a_log; a.dt_bias = l.dt_bias;
+            launch_gemv(a, B, nsm, st);
+            DeltaArgs d{};
+            d.y = big; d.beta = beta; d.g = gdec; d.state = state + (size_t)l.slot * B * c.HV * c.DK * c.DV;
+            d.o = obuf; d.C = c.C(); d.HK = c.HK; d.HV = c.HV; d.DV = c.DV; d.prenormed = 0;
+            launch_delta(d, c.DK, B, st);
+            ProjArgs p{};
+            p.in = obuf; p.z = zbuf; p.gn_w = l.gnorm; p.eps = c.eps; p.DV = c.DV; p.mode = 0;
+            p.w = l.out.w; p.s = l.out.s; p.x = x; p.N = c.D; p.K = c.VD();
+            launch_proj(p, B, nsm, st);
+        }
+        n += 3;
+        {
+            GemvArgs a{};
+            a.seg[0] = make_seg(SEG_BF, l.router, nullptr, c.E, rlogits, c.E);
+            a.seg[0].bias = l.router_bias;
+            a.seg[1] = make_seg(SEG_I8_GATEUP, l.sh_gate.w, l.sh_gate.s, c.SH, sh_act, c.SH);
+            a.seg[1].w2 = l.sh_up.w; a.seg[1].s2 = l.sh_up.s;
+            a.seg[2] = make_seg(SEG_BF_SIGMOID, l.sh_gw, nullptr, 1, sgate, 1);
+            a.nseg = 3; seal(a);
+            a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D;
+            a.finisher = FIN_TOPK; a.counter = d_counter; a.E = c.E; a.topk = c.TOPK;
+            a.top_idx = top_idx + (size_t)li * B * c.TOPK; a.top_w = top_w + (size_t)li * B * c.TOPK;
+            launch_gemv(a, B, nsm, st);
+            ExpertArgs x2{};
+            x2.eptr = l.eptr; x2.top_idx = a.top_idx; x2.top_w = a.top_w; x2.topk = c.TOPK; x2.E = c.E; x2.D = c.D; x2.I = c.I;
+            x2.off_gu_s = c.off_gu_s(); x2.off_gu_m = c.off_gu_m(); x2.off_dn_q = c.off_dn_q(); x2.off_dn_s = c.off_dn_s(); x2.off_dn_m = c.off_dn_m();
+            x2.x = x; x2.norm_w = l.norm2; x2.eps = c.eps; x2.act = act; x2.sh_act = sh_act; x2.sg = sgate;
+            x2.shd_w = l.sh_down.w; x2.shd_s = l.sh_down.s; x2.SH = c.SH; x2.xout = x; x2.err = d_err;
+            launch_experts(x2, B, nsm, st);
+            n += 3;
+        }
+        for (size_t j = 0; j < tap_layers.size(); j++)
+            if (tap_layers[j] == li)
+                cudaMemcpyAsync(tap_buf + j * (size_t)B * c.D, x, (size_t)B * c.D * 4, cudaMemcpyDeviceToDevice, st);
+    }
+    {
+        GemvArgs a{};
+        a.seg[0] = make_seg(SEG_I8_ARGMAX, lm_head.w, lm_head.s, c.V, logits, c.V);
+        a.nseg = 1; seal(a);
+        a.x = x; a.norm_w = norm; a.eps = c.eps; a.K = c.D;
+        a.finisher = FIN_ARGMAX; a.counter = d_counter; a.part_val = part_val; a.part_idx = part_idx;
+        a.next_tok = d_next; a.pos = d_pos;
+        launch_gemv(a, B, nsm, st, head_grid);
+        n++;
+    }
+    if (count) launches = n;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail("kernel launch: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+int b2_engine::build_graph() {
+    CU(cudaSetDevice(device));
+    if (graph) { cudaGraphExecDestroy(graph); graph = nullptr; }
+    cudaGraph_t g;
+    CU(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+    int rc = enqueue_step(stream, true);
+    cudaError_t e = cudaStreamEndCapture(stream, &g);
+    if (rc) return rc;
+    if (e != cudaSuccess) return fail("graph capture: %s", cudaGetErrorString(e));
+    e = cudaGraphInstantiate(&graph, g, 0);
+    cudaGraphDestroy(g);
+    if (e != cudaSuccess) return fail("graph instantiate: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+int b2_engine::check_device_error() {
+    int h = 0;
+    CU(cudaMemcpyAsync(&h, d_err, 4, cudaMemcpyDeviceToHost, stream));
+    CU(cudaStreamSynchronize(stream));
+    if (h) {
+        cudaMemsetAsync(d_err, 0, 4, stream);
+        cudaStreamSynchronize(stream);
+        if (h == 1) return fail("a token id is outside the vocabulary (%d)", c.V);
+        return fail("router returned an expert outside 0..%d", c.E - 1);
+    }
+    return 0;
+}
+
+int b2_engine::run_steps(int n) {
+    for (int i = 0; i < n; i++) CU(cudaGraphLaunch(graph, stream));
+    length += n;
+    hits += (uint64_t)n * B * c.TOPK * c.L;
+    return 0;
+}
+
+int b2_engine::reset_state() {
+    CU(cudaMemsetAsync(conv, 0, conv_bytes, stream));
+    CU(cudaMemsetAsync(state, 0, state_bytes, stream));
+    CU(cudaMemsetAsync(d_pos, 0, B * 4, stream));
+    length = 0;
+    snap_pos[0] = snap_pos[1] = -1;
+    return 0;
+}
+
+// ------------------------------------------------------------------------------------------
+extern "C" {
+
+int b2_create(const char* config_json, int max_context, int device, int batch, int kv_dtype, int ep_rank, int ep_world,
+              b2_engine** out) {
+    if (!out) return 1;
+    b2_engine* e = new b2_engine();
+    *out = e;
+    e->device = device;
+    e->B = batch < 1 ? 1 : batch;
+    e->cap = max_context;
+    e->kv_f32 = kv_dtype == B2_KV_F32;
+    e->ep_rank = ep_rank;
+    e->ep_world = ep_world < 1 ? 1 : ep_world;
+    if (ep_rank < 0 || ep_rank >= e->ep_world) return e->fail("expert-parallel rank %d outside 0..%d", ep_rank, e->ep_world - 1);
+    int ndev = 0;
+    cudaError_t ce = cudaGetDeviceCount(&ndev);
+    if (ce != cudaSuccess || ndev == 0) return e->fail("no CUDA device: %s (this engine has no CPU path)", cudaGetErrorString(ce));
+    if (device < 0 || device >= ndev) return e->fail("CUDA device %d does not exist (%d visible)", device, ndev);
+    JValue j;
+    std::string jerr;
+    JParser parser(config_json, strlen(config_json));
+    if (!parser.parse(j, jerr)) return e->fail("bad config JSON: %s", jerr.c_str());
+    return e->parse_config(j);
+}
+
+int b2_put_tensor(b2_engine* e, const char* name, const char* dtype, const int64_t* shape, int ndim, const void* data,
+                  size_t nbytes, int data_on_device) {
+    if (!e) return 1;
+    return e->put(name, dtype, std::vector<int64_t>(shape, shape + ndim), data, nbytes, data_on_device != 0);
+}
+
+int b2_finish(b2_engine* e) { return e ? e->finish() : 1; }
+
+int b2_open(const char* nx_path, int max_context, int device, int batch, int kv_dtype, b2_engine** out) {
+    if (!out) return 1;
+    *out = nullptr;
+    NxFile nx;
+    std::string err;
+    if (!nx.open(nx_path, err)) {
+        b2_engine* e = new b2_engine();
+        *out = e;
+        return e->fail("%s", err.c_str());
+    }
+    const JValue* cfg = nx.header.get("config");
+    // re-serialise the config object: find it in the raw header is not needed, rebuild minimal JSON
+    std::string js = "{";
+    if (cfg && cfg->type == JValue::Obj) {
+        bool first = true;
+        for (auto& kv : cfg->obj) {
+            const JValue& v = kv.second;
+            std::string s;
+            char buf[64];
+            if (v.type == JValue::Num) { snprintf(buf, sizeof(buf), "%.17g", v.num); s = buf; }
+            else if (v.type == JValue::Bool) s = v.b ? "true" : "false";
+            else if (v.type == JValue::Str) s = "\"" + v.str + "\"";
+            else if (v.type == JValue::Arr) {
+                s = "[";
+                for (size_t i = 0; i < v.arr.size(); i++) {
+                    if (i) s += ",";
+                    if (v.arr[i].type == JValue::Num) { snprintf(buf, sizeof(buf), "%.17g", v.arr[i].num); s += buf; }
+                    else if (v.arr[i].type == JValue::Str) s += "\"" + v.arr[i].str + "\"";
+                    else s += "null";
+                }
+                s += "]";
+            } else s = "null";
+            js += std::string(first ? "" : ",") + "\"" + kv.first + "\":" + s;
+            first = false;
+        }
+    }
+    js += "}";
+    int rc = b2_create(js.c_str(), max_context, device, batch, kv_dtype, 0, 1, out);
+    if (rc) return rc;
+    b2_engine* e = *out;
+    for (auto& kv : nx.tensors) {
+        const NxTensor& t = kv.second;
+        if (e->put(kv.first, t.dtype, t.shape, nx.data(t), t.nbytes, false)) return 1;
+    }
+    return e->finish();
+}
+
+int b2_verify_file(const char* nx_path, int ok[3], char* err, size_t err_len) {
+    NxFile nx;
+    std::string msg;
+    if (!nx.open(nx_path, msg)) {
+        if (err && err_len) snprintf(err, err_len, "%s", msg.c_str());
+        return 1;
+    }
+    auto r = nx.verify();
+    ok[0] = r["base"]; ok[1] = r["engine"]; ok[2] = r["cores"];
+    return 0;
+}
+
+void b2_close(b2_engine* e) { delete e; }
+
+static int feed_checks(b2_engine* e, int n) {
+    if (!e) return 1;
+    if (!e->finished) return e->fail("the engine is not loaded (b2_finish has not succeeded)");
+    if (e->length + n > e->cap) return e->fail("context full: %d + %d tokens > %d", e->length, n, e->cap);
+    cudaError_t ce = cudaSetDevice(e->device);
+    if (ce != cudaSuccess) return e->fail("cudaSetDevice: %s", cudaGetErrorString(ce));
+    return 0;
+}
+#define CUE(call)                                                                                      \
+    do {                                                                                               \
+        cudaError_t e_ = (call);                                                                       \
+        if (e_ != cudaSuccess) return e->fail("%s: %s", #call, cudaGetErrorString(e_));                \
+    } while (0)
+
+int b2_feed(b2_engine* e, const uint32_t* ids, int n, float* logits_out) {
+    if (e && e->B != 1) return e->fail("b2_feed needs an engine opened with batch 1 (this one has %d)", e->B);
+    if (e && n < 1) return e->fail("b2_feed needs at least one token");
+    if (feed_checks(e, n)) return 1;
+    for (int i = 0; i < n; i++)
+        if (ids[i] >= (uint32_t)e->c.V) return e->fail("token id %u is outside the vocabulary (%d)", ids[i], e->c.V);
+    for (int i = 0; i < n; i++) {
+        // the id travels as a kernel-independent 4-byte copy ordered on the stream
+        CUE(cudaMemcpyAsync(e->d_tok, ids + i, 4, cudaMemcpyHostToDevice, e->stream));
+        if (e->run_steps(1)) return 1;
+    }
+    if (logits_out) CUE(cudaMemcpyAsync(logits_out, e->logits, (size_t)e->c.V * 4, cudaMemcpyDeviceToHost, e->stream));
+    CUE(cudaStreamSynchronize(e->stream));
+    return 0;
+}
+
+int b2_feed_batch(b2_engine* e, const uint32_t* ids, uint32_t* next_greedy, float* logits_out) {
+    if (feed_checks(e, 1)) return 1;
+    for (int b = 0; b < e->B; b++)
+        if (ids[b] >= (uint32_t)e->c.V) return e->fail("token id %u is outside the vocabulary (%d)", ids[b], e->c.V);
+    memcpy(e->h_pin, ids, (size_t)e->B * 4);
+    CUE(cudaMemcpyAsync(e->d_tok, e->h_pin, (size_t)e->B * 4, cudaMemcpyHostToDevice, e->stream));
+    if (e->run_steps(1)) return 1;
+    if (next_greedy) CUE(cudaMemcpyAsync(e->h_pin + e->B, e->d_next, (size_t)e->B * 4, cudaMemcpyDeviceToHost, e->stream));
+    if (logits_out) CUE(cudaMemcpyAsync(logits_out, e->logits, (size_t)e->B * e->c.V * 4, cudaMemcpyDeviceToHost, e->stream));
+    CUE(cudaStreamSynchronize(e->stream));
+    if (next_greedy) memcpy(next_greedy, e->h_pin + e->B, (size_t)e->B * 4);
+    return 0;
+}
+
+int b2_decode_greedy(b2_engine* e, const uint32_t* first, int steps, uint32_t* tokens_out, float* device_ms) {
+    if (e && steps < 1) return e->fail("b2_decode_greedy needs at least one step");
+    if (feed_checks(e, steps)) return 1;
+    const int B = e->B;
+    for (int b = 0; b < B; b++)
+        if (first[b] >= (uint32_t)e->c.V) return e->fail("token id %u is outside the vocabulary (%d)", first[b], e->c.V);
+    int* hist = nullptr;
+    CUE(cudaMalloc((void**)&hist, (size_t)steps * B * 4));
+    memcpy(e->h_pin, first, (size_t)B * 4);
+    CUE(cudaMemcpyAsync(e->d_tok, e->h_pin, (size_t)B * 4, cudaMemcpyHostToDevice, e->stream));
+    CUE(cudaEventRecord(e->ev0, e->stream));
+    for (int s = 0; s < steps; s++) {
+        if (e->run_steps(1)) { cudaFree(hist); return 1; }
+        // the arg-max becomes the next input and is kept for the caller: two 4*B-byte device copies
+        CUE(cudaMemcpyAsync(e->d_tok, e->d_next, (size_t)B * 4, cudaMemcpyDeviceToDevice, e->stream));
+        CUE(cudaMemcpyAsync(hist + (size_t)s * B, e->d_next, (size_t)B * 4, cudaMemcpyDeviceToDevice, e->stream));
+    }
+    CUE(cudaEventRecord(e->ev1, e->stream));
+    CUE(cudaMemcpyAsync(tokens_out, hist, (size_t)steps * B * 4, cudaMemcpyDeviceToHost, e->stream));
+    CUE(cudaStreamSynchronize(e->stream));
+    cudaFree(hist);
+    if (device_ms) CUE(cudaEventElapsedTime(device_ms, e->ev0, e->ev1));
+    return e->check_device_error();
+}
+
+// Lm::crop (aegist_rs/src/hybrid.rs:1029-1059)
+int b2_crop(b2_engine* e, int n) {
+    if (!e || !e->finished) return -1;
+    if (n >= e->length) return e->length;
+    cudaSetDevice(e->device);
+    int best = -1;
+    for (int i = 0; i < 2; i++)
+        if (e->snap_pos[i] >= 0 && e->snap_pos[i] <= n && (best < 0 || e->snap_pos[i] > e->snap_pos[best])) best = i;
+    bool ok = false;
+    if (best >= 0) {
+        ok = cudaMemcpyAsync(e->conv, e->snap_conv[best], e->conv_bytes, cudaMemcpyDeviceToDevice, e->stream) == cudaSuccess &&
+             cudaMemcpyAsync(e->state, e->snap_state[best], e->state_bytes, cudaMemcpyDeviceToDevice, e->stream) == cudaSuccess;
+    }
+    if (ok) {
+        const int p = (int)e->snap_pos[best];
+        e->length = p;
+        k_fill_i32<<<(e->B + 255) / 256, 256, 0, e->stream>>>(e->d_pos, p, e->B);
+        for (int i = 0; i < 2; i++) if (e->snap_pos[i] > p) e->snap_pos[i] = -1;
+    } else {
+        e->reset_state();
+    }
+    cudaStreamSynchronize(e->stream);
+    return e->length;
+}
+
+// Lm::snapshot (aegist_rs/src/hybrid.rs:1061-1072)
+int b2_snapshot(b2_engine* e) {
+    if (!e || !e->finished) return 1;
+    for (int i = 0; i < 2; i++) if (e->snap_pos[i] == e->length) return 0;
+    int i = (e->snap_pos[0] <= e->snap_pos[1]) ? 0 : 1;   // an empty slot (-1), else the oldest
+    CUE(cudaSetDevice(e->device));
+    CUE(cudaMemcpyAsync(e->snap_conv[i], e->conv, e->conv_bytes, cudaMemcpyDeviceToDevice, e->stream));
+    CUE(cudaMemcpyAsync(e->snap_state[i], e->state, e->state_bytes, cudaMemcpyDeviceToDevice, e->stream));
+    CUE(cudaStreamSynchronize(e->stream));
+    e->snap_pos[i] = e->length;
+    return 0;
+}
+
+int b2_length(const b2_engine* e) { return e ? e->length : 0; }
+int b2_cap(const b2_engine* e) { return e ? e->cap : 0; }
+int b2_vocab(const b2_engine* e) { return e ? e->c.V : 0; }
+int b2_d_model(const b2_engine* e) { return e ? e->c.D : 0; }
+
+int b2_set_taps(b2_engine* e, const int* layers, int n) {
+    if (!e || !e->finished) return 1;
+    for (int i = 0; i < n; i++)
+        if (layers[i] < 0 || layers[i] >= e->c.L) return e->fail("tap layer %d out of range (the brain has %d layers)", layers[i], e->c.L);
+    CUE(cudaSetDevice(e->device));
+    CUE(cudaStreamSynchronize(e->stream));
+    cudaFree(e->tap_buf);
+    e->tap_buf = nullptr;
+    e->tap_layers.assign(layers, layers + n);
+    if (n) CUE(dalloc(&e->tap_buf, (size_t)n * e->B * e->c.D));
+    return e->build_graph();
+}
+
+int b2_taps(b2_engine* e, float* out) {
+    if (!e || !e->finished) return 1;
+    if (e->tap_layers.empty()) return 0;
+    CUE(cudaSetDevice(e->device));
+    CUE(cudaMemcpyAsync(out, e->tap_buf, e->tap_layers.size() * (size_t)e->B * e->c.D * 4, cudaMemcpyDeviceToHost, e->stream));
+    CUE(cudaStreamSynchronize(e->stream));
+    return 0;
+}
+
+int b2_core_counts(b2_engine* e, int32_t* out) {
+    if (!e) return 1;
+    memset(out, 0, (size_t)e->c.L * e->c.n1 * e->c.n2 * 4);
+    return 0;
+}
+int b2_reset_counts(b2_engine* e) { return e ? 0 : 1; }
+
+void b2_expert_counters(const b2_engine* e, uint64_t* hits, uint64_t* page_ins) {
+    if (hits) *hits = e ? e->hits : 0;
+    if (page_ins) *page_ins = 0;
+}
+
+const char* b2_describe(const b2_engine* e) { return e ? e->desc.c_str() : ""; }
+const char* b2_last_error(const b2_engine* e) { return e ? e->err.c_str() : "no engine"; }
+
+int b2_debug_router(b2_engine* e, int layer, int32_t* idx, float* wts) {
+    if (!e || !e->finished) return 1;
+    if (layer < 0 || layer >= e->c.L) return e->fail("layer %d out of range", layer);
+    CUE(cudaSetDevice(e->device));
+    const size_t n = (size_t)e->B * e->c.TOPK;
+    CUE(cudaStreamSynchronize(e->stream));
+    if (idx) CUE(cudaMemcpy(idx, e->top_idx + layer * n, n * 4, cudaMemcpyDeviceToHost));
+    if (wts) CUE(cudaMemcpy(wts, e->top_w + layer * n, n * 4, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int b2_debug_hidden(b2_engine* e, float* out) {
+    if (!e || !e->finished) return 1;
+    CUE(cudaSetDevice(e->device));
+    CUE(cudaStreamSynchronize(e->stream));
+    CUE(cudaMemcpy(out, e->x, (size_t)e->B * e->c.D * 4, cudaMemcpyDeviceToHost));
+    return 0;
+}
+
+int b2_set_router_bias(b2_engine* e, int layer, const float* bias) {
+    if (!e || !e->finished) return 1;
+    if (layer < 0 || layer >= e->c.L) return e->fail("layer %d out of range", layer);
+    CUE(cudaSetDevice(e->device));
+    CUE(cudaStreamSynchronize(e->stream));
+    LayerW& l = e->layers[layer];
+    if (!bias) { cudaFree(l.router_bias); l.router_bias = nullptr; }
+    else {
+        if (!l.router_bias) CUE(dalloc(&l.router_bias, e->c.E));
+        CUE(cudaMemcpy(l.router_bias, bias, (size_t)e->c.E * 4, cudaMemcpyHostToDevice));
+    }
+    return e->build_graph();
+}
+
+int b2_launches_per_step(const b2_engine* e) { return e ? e->launches : 0; }
+
+double b2_step_bytes(const b2_engine* e) {
+    if (!e) return 0;
+    const Cfg& c = e->c;
+    const double B = e->B;
+    double w = 0;          // read once per step per sequence by these kernels
+    double per_seq = 0;    // state and KV
+    auto qwb = [](double n, double k) { return n * k + 2 * n; };
+    for (int i = 0; i < c.L; i++) {
+        w += 2.0 * c.D * 2;   // norm1, norm2
+        if (c.attn[i]) {
+            w += qwb(2 * c.H * c.HD, c.D) + 2 * qwb(c.KV * c.HD, c.D) + qwb(c.D, c.H * c.HD) + 2.0 * c.HD * 2;
+            per_seq += 2.0 * c.KV * c.HD * (e->kv_f32 ? 4 : 2) * (e->length + 1);
+        } else {
+            w += qwb(c.C(), c.D) + qwb(c.VD(), c.D) + qwb(c.D, c.VD()) + 2.0 * c.HV * c.D * 2 + c.C() * c.CK * 2.0 + c.HV * 4.0 + c.DV * 2.0;
+            per_seq += 2.0 * c.HV * c.DK * c.DV * 4 + 2.0 * c.C() * 3 * 4;
+        }
+        w += (double)c.E * c.D * 2 + c.D * 2.0 + 2 * qwb(c.SH, c.D) + qwb(c.D, c.SH);
+        w += (double)c.TOPK * c.expert_bytes();
+    }
+    w += c.D * 2.0 + qwb(c.V, c.D) + c.D * 2.0;   // final norm, head, one embedding row
+    return w * B + per_seq * B;
+}
+
+}  // extern "C"
+
+#include "ops.cuh"
+#include "sampler.hpp"

@@ -1,0 +1,1046 @@
+// Decode-step kernels for the hybrid-MoE token loop, written for sm_100a.
+//
+// One decode step of one layer is six launches (the reference's CUDA engine uses 16-18,
+// aegist_rs/src/hybrid.rs:787-993):
+//
+//   DeltaNet layer                                   attention layer
+//   k_gemv_norm   norm1 + in_qkv(+conv+SiLU) + in_z   k_gemv_norm   norm1 + q, k, v
+//                 + in_b(sigmoid) + in_a(decay)
+//   k_delta_step  L2 norm + gated delta rule          k_attn        q/k norm + RoPE + KV append +
+//                                                                   split-K attention + merge + gate
+//   k_proj_out    gated RMSNorm + out, += residual    k_proj_out    o, += residual
+//   -- then, for every layer --
+//   k_gemv_norm   norm2 + router logits + shared gate/up(+SiLU) + shared_gate, then top-8 in the
+//                 last block to finish
+//   k_expert_gu   4-bit gate/up GEMV + SiLU for the 8 picked experts
+//   k_expert_down 4-bit down GEMV of the 8 picks (weighted, fixed order) + shared down, += residual
+//
+// All arithmetic is fp32 with fp32 accumulation (the reference's kernels do the same,
+// aegist_rs/kernels/aegist.cu:1-6). Weights stream from HBM exactly once per sequence with 128-bit
+// loads and are widened in registers; the activation vector of a GEMV lives in registers (each lane
+// always owns the same 16-value slices of it), because at one byte of weight per FMA the shared-
+// memory port could not feed fp32 activations at HBM speed. Each kernel covers one sequence per
+// blockIdx.y; grids are sized in multiples of the SM count by the host.
+//
+// Cross-block steps (router top-8, arg-max over the vocabulary, split-K merge) are done by
+// whichever block finishes last (a counter and a fence), never by waiting on another block.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b2 {
+
+constexpr int THREADS = 256;
+constexpr int WARPS = 8;
+constexpr int KV_PAGE = 64;   // tokens per KV-cache page
+
+__device__ __forceinline__ float bf(uint16_t b) { return __uint_as_float(((uint32_t)b) << 16); }
+__device__ __forceinline__ float bflo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bfhi(uint32_t w) { return __uint_as_float(w & 0xFFFF0000u); }
+__device__ __forceinline__ uint16_t f2bf(float f) {   // round to nearest even
+    uint32_t u = __float_as_uint(f);
+    return (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+}
+__device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+// Sum over the 256 threads of a block, the same value in every thread; `red` holds 8 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < WARPS; i++) s += red[i];
+    return s;
+}
+__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float siluf_(float x) { return x / (1.0f + expf(-x)); }
+__device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+
+// Streaming 128-bit load of weights that are read once per step.
+__device__ __forceinline__ int4 ldw(const void* p) { return __ldcs(reinterpret_cast<const int4*>(p)); }
+
+__device__ __forceinline__ float dot16_i8(const int4& w, const float* x) {
+    float a = 0.f;
+    const int v[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        a = fmaf(x[4 * i + 0], (float)(signed char)(v[i]), a);
+        a = fmaf(x[4 * i + 1], (float)(signed char)(v[i] >> 8), a);
+        a = fmaf(x[4 * i + 2], (float)(signed char)(v[i] >> 16), a);
+        a = fmaf(x[4 * i + 3], (float)(v[i] >> 24), a);
+    }
+    return a;
+}
+__device__ __forceinline__ float dot8_bf16(const int4& w, const float* x) {
+    float a = 0.f;
+    const uint32_t v[4] = {(uint32_t)w.x, (uint32_t)w.y, (uint32_t)w.z, (uint32_t)w.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        a = fmaf(x[2 * i], bflo(v[i]), a);
+        a = fmaf(x[2 * i + 1], bfhi(v[i]), a);
+    }
+    return a;
+}
+// 32 four-bit codes (even index in the low nibble) against 32 activations: sum code * x.
+__device__ __forceinline__ float dot32_q4(const int4& w, const float* x) {
+    float a = 0.f;
+    const uint32_t v[4] = {(uint32_t)w.x, (uint32_t)w.y, (uint32_t)w.z, (uint32_t)w.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+#pragma unroll
+        for (int n = 0; n < 8; n++) a = fmaf(x[8 * i + n], (float)((v[i] >> (4 * n)) & 0xFu), a);
+    }
+    return a;
+}
+
+// Copy this lane's 16-value slices of a staged vector into registers: slice j is values
+// [16*(lane + 32*j), +16) (zeros past the end).
+template <int MAXC>
+__device__ __forceinline__ void load_slices(float (&xr)[MAXC][16], const float* xs, int nchunk, int lane) {
+#pragma unroll
+    for (int j = 0; j < MAXC; j++) {
+        const int c = lane + 32 * j;
+        if (c < nchunk) {
+            const float4* p = reinterpret_cast<const float4*>(xs + 16 * c);
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                float4 t = p[q];
+                xr[j][4 * q] = t.x; xr[j][4 * q + 1] = t.y; xr[j][4 * q + 2] = t.z; xr[j][4 * q + 3] = t.w;
+            }
+        } else {
+#pragma unroll
+            for (int q = 0; q < 16; q++) xr[j][q] = 0.f;
+        }
+    }
+}
+
+// Zero-centred RMSNorm of one row into shared memory: xs = x * rsqrt(mean x^2 + eps) * (1 + w)
+// (aegist/hybrid.py:119-130). A null weight stages the row as it is.
+__device__ __forceinline__ void stage_znorm(const float* __restrict__ x, const uint16_t* __restrict__ w, float eps,
+                                            int D, float* xs, float* red) {
+    if (w == nullptr) {
+        for (int k = threadIdx.x; k < D; k += THREADS) xs[k] = x[k];
+        __syncthreads();
+        return;
+    }
+    float ss = 0.f;
+    for (int k = threadIdx.x; k < D; k += THREADS) {
+        float v = x[k];
+        xs[k] = v;
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float r = 1.0f / sqrtf(ss / (float)D + eps);
+    for (int k = threadIdx.x; k < D; k += THREADS) xs[k] = xs[k] * r * (1.0f + bf(w[k]));
+    __syncthreads();
+}
+
+// ------------------------------------------------------------------------------------------
+// k_embed: x[b] = embed[token[b]] widened to fp32 (the reference looks rows up on the host,
+// aegist_rs/src/hybrid.rs:743-758). A bad id sets *err and reads row 0.
+__global__ void k_embed(const uint16_t* __restrict__ embed, const int* __restrict__ tok, float* __restrict__ x,
+                        int D, int V, int* err) {
+    const int b = blockIdx.x;
+    int id = tok[b];
+    if (id < 0 || id >= V) {
+        if (threadIdx.x == 0) atomicExch(err, 1);
+        id = 0;
+    }
+    const uint16_t* row = embed + (size_t)id * D;
+    for (int k = threadIdx.x; k < D; k += blockDim.x) x[(size_t)b * D + k] = bf(row[k]);
+}
+
+// ------------------------------------------------------------------------------------------
+// k_gemv_norm: norm prologue + several weight matrices against the same normalised vector.
+enum SegKind : int {
+    SEG_I8 = 0,        // int8 rows, out = scale * dot
+    SEG_I8_CONV = 1,   // int8 rows, then the depthwise causal conv (kernel 4) + SiLU with its state
+    SEG_BF_SIGMOID = 2,  // bf16 rows, out = sigmoid(dot)
+    SEG_BF_DECAY = 3,  // bf16 rows, out = -exp(A_log) * softplus(dot + dt_bias)
+    SEG_BF = 4,        // bf16 rows, out = dot (+ bias[row] if given)
+    SEG_I8_GATEUP = 5, // two int8 matrices, out = silu(s1 * dot1) * (s2 * dot2)
+    SEG_I8_ARGMAX = 6  // int8 rows, out = scale * dot, and the arg-max over all rows
+};
+enum Finisher : int { FIN_NONE = 0, FIN_TOPK = 1, FIN_ARGMAX = 2 };
+
+struct Seg {
+    const void* w;
+    const uint16_t* s;
+    const void* w2;
+    const uint16_t* s2;
+    float* out;        // [B][out_stride]
+    const float* bias; // SEG_BF only, may be null
+    int rows;
+    int kind;
+    int out_stride;
+    int jobs;          // filled by the host: ceil(rows / 2) for one-matrix int8 kinds, else rows
+};
+
+struct GemvArgs {
+    Seg seg[4];
+    int nseg;
+    int total_jobs;
+    const float* x;          // [B][K] residual stream
+    const uint16_t* norm_w;  // [K]
+    float eps;
+    int K;
+    // SEG_I8_CONV
+    const uint16_t* conv_w;  // [C][4]
+    float* conv_state;       // [B][C][3], oldest first
+    // SEG_BF_DECAY
+    const uint16_t* a_log;
+    const uint16_t* dt_bias;
+    // finishers
+    int finisher;
+    unsigned int* counter;   // [B], zero before the launch; the finisher puts it back to zero
+    // FIN_TOPK
+    int E, topk;
+    int* top_idx;            // [B][topk]
+    float* top_w;            // [B][topk]
+    // FIN_ARGMAX
+    float* part_val;         // [B][gridDim.x]
+    int* part_idx;           // [B][gridDim.x]
+    int* next_tok;           // [B]
+    int* pos;                // [B] advanced by one by the finisher (may be null)
+};
+
+// Softmax over E router logits and the `topk` largest in descending order, ties to the lower
+// index, weights renormalised over the picks (aegist/hybrid.py:641-645; hybrid.cu:317-360).
+// One warp per token; E <= 256.
+__device__ __forceinline__ void router_topk_warp(const float* __restrict__ logits, int E, int topk,
+                                                 int* __restrict__ idx, float* __restrict__ wts, int lane) {
+    float p[8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int e = lane + 32 * i;
+        p[i] = e < E ? __ldcg(logits + e) : -INFINITY;
+        mx = fmaxf(mx, p[i]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int e = lane + 32 * i;
+        p[i] = e < E ? expf(p[i] - mx) : 0.f;
+        sum += p[i];
+    }
+    sum = warp_sum(sum);
+#pragma unroll
+    for (int i = 0; i < 8; i++) p[i] = (lane + 32 * i) < E ? p[i] / sum : -1.f;
+    float topv[8];
+    int tope[8];
+    float tsum = 0.f;
+    for (int r = 0; r < topk; r++) {
+        float bv = -1.f;
+        int be = 0x7fffffff;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {   // ascending expert id within the lane: '>' keeps the lower id
+            if (p[i] > bv) { bv = p[i]; be = lane + 32 * i; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oe = __shfl_xor_sync(0xffffffffu, be, o);
+            if (ov > bv || (ov == bv && oe < be)) { bv = ov; be = oe; }
+        }
+        if ((be & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) if (i == (be >> 5)) p[i] = -1.f;
+        }
+        if (r < 8) { topv[r] = bv; tope[r] = be; }
+        tsum += bv;
+    }
+    if (lane == 0) {
+        for (int r = 0; r < topk && r < 8; r++) {
+            idx[r] = tope[r];
+            wts[r] = topv[r] / tsum;
+        }
+    }
+}
+
+template <int MAXC>
+__global__ void __launch_bounds__(THREADS, 2) k_gemv_norm(const GemvArgs a) {
+    extern __shared__ float smem[];
+    float* xs = smem;              // [K]
+    float* red = smem + a.K;       // [32]
+    const int b = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nchunk = a.K >> 4;
+    const int gw = blockIdx.x * WARPS + warp, TW = gridDim.x * WARPS;
+
+    int4 wbuf[2 * MAXC];
+    // what one job reads: two int8 rows, or one bf16 row (twice the bytes), or a gate row and an up row
+    auto issue = [&](int job) {
+        int s = 0, j = job;
+        while (s + 1 < a.nseg && j >= a.seg[s].jobs) { j -= a.seg[s].jobs; s++; }
+        const Seg& sg = a.seg[s];
+        const char *pa, *pb;
+        int step;   // bytes between this lane's consecutive 16-value slices
+        bool hasb = true;
+        if (sg.kind == SEG_BF_SIGMOID || sg.kind == SEG_BF_DECAY || sg.kind == SEG_BF) {
+            pa = (const char*)sg.w + (size_t)j * a.K * 2;
+            pb = pa + 16;
+            step = 32;
+        } else if (sg.kind == SEG_I8_GATEUP) {
+            pa = (const char*)sg.w + (size_t)j * a.K;
+            pb = (const char*)sg.w2 + (size_t)j * a.K;
+            step = 16;
+        } else {
+            pa = (const char*)sg.w + (size_t)(2 * j) * a.K;
+            pb = pa + a.K;
+            hasb = 2 * j + 1 < sg.rows;
+            step = 16;
+        }
+#pragma unroll
+        for (int jj = 0; jj < MAXC; jj++) {
+            const int c = lane + 32 * jj;
+            if (c < nchunk) {
+                wbuf[jj] = ldw(pa + (size_t)c * step);
+                wbuf[MAXC + jj] = hasb ? ldw(pb + (size_t)c * step) : make_int4(0, 0, 0, 0);
+            } else {
+                wbuf[jj] = make_int4(0, 0, 0, 0);
+                wbuf[MAXC + jj] = make_int4(0, 0, 0, 0);
+            }
+        }
+    };
+
+    // the first job's weights do not depend on the activations: start them before the prologue
+    int job = gw;
+    if (job < a.total_jobs) issue(job);
+
+    stage_znorm(a.x + (size_t)b * a.K, a.norm_w, a.eps, a.K, xs, red);
+    float xr[MAXC][16];
+    load_slices<MAXC>(xr, xs, nchunk, lane);
+
+    float best_v = -INFINITY;
+    int best_i = 0x7fffffff;
+
+    for (; job < a.total_jobs; job += TW) {
+        int s = 0, j = job;
+        while (s + 1 < a.nseg && j >= a.seg[s].jobs) { j -= a.seg[s].jobs; s++; }
+        const Seg& sg = a.seg[s];
+        const bool isbf = sg.kind == SEG_BF_SIGMOID || sg.kind == SEG_BF_DECAY || sg.kind == SEG_BF;
+        float accA = 0.f, accB = 0.f;
+        if (isbf) {
+#pragma unroll
+            for (int jj = 0; jj < MAXC; jj++) {
+                accA += dot8_bf16(wbuf[jj], &xr[jj][0]);
+                accA += dot8_bf16(wbuf[MAXC + jj], &xr[jj][8]);
+            }
+        } else {
+#pragma unroll
+            for (int jj = 0; jj < MAXC; jj++) {
+                accA += dot16_i8(wbuf[jj], &xr[jj][0]);
+                accB += dot16_i8(wbuf[MAXC + jj], &xr[jj][0]);
+            }
+        }
+        if (job + TW < a.total_jobs) issue(job + TW);   // next job's loads fly during the reduction
+        accA = warp_sum(accA);
+        accB = warp_sum(accB);
+        if (lane == 0) {
+            float* out = sg.out + (size_t)b * sg.out_stride;
+            switch (sg.kind) {
+            case SEG_I8: {
+                const int r = 2 * j;
+                out[r] = bf(sg.s[r]) * accA;
+                if (r + 1 < sg.rows) out[r + 1] = bf(sg.s[r + 1]) * accB;
+            } break;
+            case SEG_I8_ARGMAX: {
+                const int r = 2 * j;
+                const float v0 = bf(sg.s[r]) * accA;
+                out[r] = v0;
+                if (v0 > best_v || (v0 == best_v && r < best_i)) { best_v = v0; best_i = r; }
+                if (r + 1 < sg.rows) {
+                    const float v1 = bf(sg.s[r + 1]) * accB;
+                    out[r + 1] = v1;
+                    if (v1 > best_v || (v1 == best_v && r + 1 < best_i)) { best_v = v1; best_i = r + 1; }
+                }
+            } break;
+            case SEG_I8_CONV: {
+                // hybrid.py:393-398: y = silu(sum_j w[c][j] * taps[j]), taps = 3 previous inputs + the new one
+                for (int q = 0; q < 2; q++) {
+                    const int c = 2 * j + q;
+                    if (c >= sg.rows) break;
+                    const float raw = bf(sg.s[c]) * (q ? accB : accA);
+                    float* st = a.conv_state + ((size_t)b * sg.rows + c) * 3;
+                    const uint16_t* cw = a.conv_w + (size_t)c * 4;
+                    const float s0 = st[0], s1 = st[1], s2 = st[2];
+                    float y = bf(cw[0]) * s0;
+                    y = fmaf(bf(cw[1]), s1, y);
+                    y = fmaf(bf(cw[2]), s2, y);
+                    y = fmaf(bf(cw[3]), raw, y);
+                    st[0] = s1; st[1] = s2; st[2] = raw;
+                    out[c] = siluf_(y);
+                }
+            } break;
+            case SEG_BF_SIGMOID: out[j] = sigmoidf_(accA); break;
+            case SEG_BF_DECAY: out[j] = -expf(bf(a.a_log[j])) * softplusf_(accA + bf(a.dt_bias[j])); break;
+            case SEG_BF: out[j] = accA + (sg.bias ? sg.bias[j] : 0.f); break;
+            case SEG_I8_GATEUP: out[j] = siluf_(bf(sg.s[j]) * accA) * (bf(sg.s2[j]) * accB); break;
+            }
+        }
+    }
+
+    if (a.finisher == FIN_NONE) return;
+
+    __shared__ int s_last;
+    __shared__ float s_bv[WARPS];
+    __shared__ int s_bi[WARPS];
+    if (a.finisher == FIN_ARGMAX) {
+        if (lane == 0) { s_bv[warp] = best_v; s_bi[warp] = best_i; }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float v = s_bv[0];
+            int i = s_bi[0];
+            for (int w = 1; w < WARPS; w++)
+                if (s_bv[w] > v || (s_bv[w] == v && s_bi[w] < i)) { v = s_bv[w]; i = s_bi[w]; }
+            a.part_val[(size_t)b * gridDim.x + blockIdx.x] = v;
+            a.part_idx[(size_t)b * gridDim.x + blockIdx.x] = i;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int n = atomicAdd(a.counter + b, 1u);
+        s_last = (n == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    if (a.finisher == FIN_TOPK) {
+        if (warp == 0)
+            router_topk_warp(a.seg[0].out + (size_t)b * a.seg[0].out_stride, a.E, a.topk, a.top_idx + (size_t)b * a.topk,
+                             a.top_w + (size_t)b * a.topk, lane);
+    } else {
+        if (warp == 0) {
+            float v = -INFINITY;
+            int i = 0x7fffffff;
+            for (int g = lane; g < (int)gridDim.x; g += 32) {
+                const float pv = __ldcg(a.part_val + (size_t)b * gridDim.x + g);
+                const int pi = __ldcg(a.part_idx + (size_t)b * gridDim.x + g);
+                if (pv > v || (pv == v && pi < i)) { v = pv; i = pi; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+                if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+            }
+            if (lane == 0) {
+                a.next_tok[b] = i;
+                if (a.pos) a.pos[b] += 1;
+            }
+        }
+    }
+    if (threadIdx.x == 0) a.counter[b] = 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// k_delta_step: L2-normalise q and k, then one step of the gated delta rule on a [DK x 32] column
+// slab of one value head's state (aegist/hybrid.py:314-324, 409-412):
+//     S *= exp(g);  kv = S^T k;  delta = (v - kv) * beta;  S += k (x) delta;  o = S^T q
+// Columns of S never interact, so a head is split over DV/32 blocks. State is [B][HV][DK][DV] fp32
+// and crosses HBM once in each direction.
+struct DeltaArgs {
+    const float* y;      // [B][C] conv+SiLU output: q | k | v
+    const float* beta;   // [B][HV]
+    const float* g;      // [B][HV]
+    float* state;        // [B][HV][DK][DV]
+    float* o;            // [B][HV*DV] raw readout (the gated norm is applied by k_proj_out)
+    int C, HK, HV, DV;
+    int prenormed;       // 1: q and k come in already normalised and scaled (the bare delta-rule op)
+};
+
+template <int DK>
+__global__ void __launch_bounds__(THREADS) k_delta_step(const DeltaArgs a) {
+    constexpr int RPT = DK / WARPS;   // state rows per thread
+    __shared__ float qs[DK], ks[DK];
+    __shared__ float red[WARPS][32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nslab = a.DV / 32;
+    const int slab = blockIdx.x % nslab, h = blockIdx.x / nslab, b = blockIdx.y;
+    const int hk = h / (a.HV / a.HK);
+    const int key_dim = a.HK * DK;
+    const int col = slab * 32 + lane;
+
+    float* S = a.state + (((size_t)b * a.HV + h) * DK) * a.DV + col;
+    float st[RPT];
+#pragma unroll
+    for (int r = 0; r < RPT; r++) st[r] = S[(size_t)(warp + WARPS * r) * a.DV];
+
+    const float* yb = a.y + (size_t)b * a.C;
+    if (warp < 2) {   // warp 0 normalises q, warp 1 normalises k
+        const float* src = yb + (warp == 0 ? 0 : key_dim) + hk * DK;
+        float* dst = warp == 0 ? qs : ks;
+        float v[DK / 32];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < DK / 32; i++) { v[i] = src[lane + 32 * i]; ss = fmaf(v[i], v[i], ss); }
+        ss = warp_sum(ss);
+        float r = 1.0f;
+        if (!a.prenormed) r = 1.0f / sqrtf(ss + 1e-6f);
+#pragma unroll
+        for (int i = 0; i < DK / 32; i++) {
+            float t = v[i] * r;
+            if (warp == 0 && !a.prenormed) t *= (DK == 128 ? 0.08838834764831845f : (DK == 64 ? 0.125f : rsqrtf((float)DK)));
+            dst[lane + 32 * i] = t;
+        }
+    }
+    const float vj = yb[2 * key_dim + h * a.DV + col];
+    const float beta = a.beta[(size_t)b * a.HV + h];
+    const float decay = expf(a.g[(size_t)b * a.HV + h]);
+    __syncthreads();
+
+    float kv = 0.f;
+#pragma unroll
+    for (int r = 0; r < RPT; r++) {
+        st[r] *= decay;
+        kv = fmaf(st[r], ks[warp + WARPS * r], kv);
+    }
+    red[warp][lane] = kv;
+    __syncthreads();
+    kv = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; w++) kv += red[w][lane];
+    const float delta = (vj - kv) * beta;
+    __syncthreads();
+    float o = 0.f;
+#pragma unroll
+    for (int r = 0; r < RPT; r++) {
+        st[r] = fmaf(ks[warp + WARPS * r], delta, st[r]);
+        o = fmaf(st[r], qs[warp + WARPS * r], o);
+        S[(size_t)(warp + WARPS * r) * a.DV] = st[r];
+    }
+    red[warp][lane] = o;
+    __syncthreads();
+    if (warp == 0) {
+        o = 0.f;
+#pragma unroll
+        for (int w = 0; w < WARPS; w++) o += red[w][lane];
+        a.o[(size_t)b * a.HV * a.DV + h * a.DV + col] = o;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// k_proj_out: the mixer's output projection, accumulated into the residual stream.
+//   mode 0 (DeltaNet): input = w * rmsnorm_DV(o) * silu(z) per value head (aegist/hybrid.py:133-147)
+//   mode 1 (attention): input is used as it is (already merged and gated by k_attn)
+// K up to 4096: two warps share a row (each holds half of the input in registers).
+struct ProjArgs {
+    const float* in;      // [B][K]
+    const float* z;       // [B][K]      mode 0
+    const uint16_t* gn_w; // [DV]        mode 0
+    float eps;
+    int DV;
+    int mode;
+    const int8_t* w;      // [N][K]
+    const uint16_t* s;    // [N]
+    float* x;             // [B][N] residual stream, += result
+    int N, K;
+};
+
+template <int MAXC>
+__global__ void __launch_bounds__(THREADS, 2) k_proj_out(const ProjArgs a) {
+    extern __shared__ float smem[];
+    float* xs = smem;               // [K]
+    float* part = smem + a.K;       // [2][rows per block]
+    const int b = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int half = warp & 1, pair = warp >> 1;          // 4 row-pairs of warps per block
+    const int nchunk_half = a.K >> 5;                      // 16-value slices per half row
+    const int rows_per_block = (a.N + gridDim.x - 1) / gridDim.x;
+    const int row0 = blockIdx.x * rows_per_block;
+    const int row1 = min(a.N, row0 + rows_per_block);
+
+    int4 wbuf[MAXC];
+    auto issue = [&](int row) {
+        const char* p = (const char*)a.w + (size_t)row * a.K + (size_t)half * (a.K >> 1);
+#pragma unroll
+        for (int jj = 0; jj < MAXC; jj++) {
+            const int c = lane + 32 * jj;
+            wbuf[jj] = c < nchunk_half ? ldw(p + (size_t)c * 16) : make_int4(0, 0, 0, 0);
+        }
+    };
+    int row = row0 + pair;
+    if (row < row1) issue(row);
+
+    const float* in = a.in + (size_t)b * a.K;
+    if (a.mode == 0) {
+        const float* z = a.z + (size_t)b * a.K;
+        const int nh = a.K / a.DV;
+        for (int h = warp; h < nh; h += WARPS) {
+            float ss = 0.f;
+            for (int i = lane; i < a.DV; i += 32) { const float v = in[h * a.DV + i]; ss = fmaf(v, v, ss); }
+            ss = warp_sum(ss);
+            const float r = 1.0f / sqrtf(ss / (float)a.DV + a.eps);
+            for (int i = lane; i < a.DV; i += 32) {
+                const int k = h * a.DV + i;
+                xs[k] = (bf(a.gn_w[i]) * (in[k] * r)) * siluf_(z[k]);
+            }
+        }
+    } else {
+        for (int k = threadIdx.x; k < a.K; k += THREADS) xs[k] = in[k];
+    }
+    __syncthreads();
+    float xr[MAXC][16];
+    load_slices<MAXC>(xr, xs + half * (a.K >> 1), nchunk_half, lane);
+
+    for (; row < row1; row += 4) {
+        float acc = 0.f;
+#pragma unroll
+        for (int jj = 0; jj < MAXC; jj++) acc += dot16_i8(wbuf[jj], &xr[jj][0]);
+        if (row + 4 < row1) issue(row + 4);
+        acc = warp_sum(acc);
+        if (lane == 0) part[half * rows_per_block + (row - row0)] = acc;
+    }
+    __syncthreads();
+    for (int r = threadIdx.x; r < row1 - row0; r += THREADS) {
+        const float d = part[r] + part[rows_per_block + r];
+        a.x[(size_t)b * a.N + row0 + r] += bf(a.s[row0 + r]) * d;
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Experts. One expert's bytes (aegist/hybrid.py:472-480):
+//   gu_q u8 [2I][D/2] | gu_s f16 [2I][D/64] | gu_m f16 [2I][D/64] | dn_q u8 [D][I/2] | dn_s | dn_m f16 [D][I/64]
+// w = code * scale + min, so a row's dot is  sum_g ( s_g * sum(code * x) + m_g * sum(x) )  over its
+// 64-value groups (the factorisation of hybrid.cu:405-406).
+struct ExpertArgs {
+    const uint8_t* const* eptr;   // [E] device address of each resident expert (null: not on this GPU)
+    const int* top_idx;           // [B][topk]
+    const float* top_w;           // [B][topk]
+    int topk, E;
+    int D, I;
+    size_t off_gu_s, off_gu_m, off_dn_q, off_dn_s, off_dn_m;
+    // gate/up
+    const float* x;               // [B][D] residual stream (normalised again here)
+    const uint16_t* norm_w;
+    float eps;
+    float* act;                   // [B*topk][I]
+    // down + shared down
+    const float* sh_act;          // [B][SH]
+    const float* sg;              // [B] sigmoid(shared_gate)
+    const int8_t* shd_w;          // [D][SH]
+    const uint16_t* shd_s;        // [D]
+    int SH;
+    float* xout;                  // [B][D] residual stream, += result
+    int* err;
+};
+
+// act[pick][i] = silu(gate_i . h) * (up_i . h), one warp per (gate, up) row pair.
+// grid (blocks per pick, B * topk).
+template <int MAXC>   // 32-code slices per lane: D <= MAXC * 1024
+__global__ void __launch_bounds__(THREADS, 2) k_expert_gu(const ExpertArgs a) {
+    extern __shared__ float smem[];
+    float* xs = smem;
+    float* red = smem + a.D;
+    const int pick = blockIdx.y, b = pick / a.topk;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int e = a.top_idx[pick];
+    const uint8_t* base = (e >= 0 && e < a.E) ? a.eptr[e] : nullptr;
+    if (base == nullptr) {   // not resident here (another rank's expert) or a bad pick
+        if (e < 0 || e >= a.E) { if (threadIdx.x == 0) atomicExch(a.err, 2); }
+        return;
+    }
+    const int nchunk = a.D >> 5;          // 16-byte slices per row
+    const int ngroup = a.D >> 6;
+    const int gw = blockIdx.x * WARPS + warp, TW = gridDim.x * WARPS;
+
+    const uint16_t* gs = (const uint16_t*)(base + a.off_gu_s);
+    const uint16_t* gm = (const uint16_t*)(base + a.off_gu_m);
+    int4 wg[MAXC], wu[MAXC];
+    uint16_t sg_[MAXC], mg_[MAXC], su_[MAXC], mu_[MAXC];
+    auto issue = [&](int i) {
+        const uint8_t* pg = base + (size_t)i * (a.D >> 1);
+        const uint8_t* pu = base + (size_t)(a.I + i) * (a.D >> 1);
+#pragma unroll
+        for (int jj = 0; jj < MAXC; jj++) {
+            const int c = lane + 32 * jj;
+            if (c < nchunk) {
+                wg[jj] = ldw(pg + (size_t)c * 16); wu[jj] = ldw(pu + (size_t)c * 16);
+                const int g = c >> 1;
+                sg_[jj] = gs[(size_t)i * ngroup + g]; mg_[jj] = gm[(size_t)i * ngroup + g];
+                su_[jj] = gs[(size_t)(a.I + i) * ngroup + g]; mu_[jj] = gm[(size_t)(a.I + i) * ngroup + g];
+            } else {
+                wg[jj] = make_int4(0, 0, 0, 0); wu[jj] = make_int4(0, 0, 0, 0);
+                sg_[jj] = mg_[jj] = su_[jj] = mu_[jj] = 0;
+            }
+        }
+    };
+    int i = gw;
+    if (i < a.I) issue(i);
+
+    stage_znorm(a.x + (size_t)b * a.D, a.norm_w, a.eps, a.D, xs, red);
+    float xr[MAXC][32];
+    float xsum[MAXC];
+#pragma unroll
+    for (int jj = 0; jj < MAXC; jj++) {
+        const int c = lane + 32 * jj;
+        xsum[jj] = 0.f;
+#pragma unroll
+        for (int q = 0; q < 32; q++) {
+            xr[jj][q] = c < nchunk ? xs[32 * c + q] : 0.f;
+            xsum[jj] += xr[jj][q];
+        }
+    }
+    for (; i < a.I; i += TW) {
+        float ag = 0.f, au = 0.f;
+#pragma unroll
+        for (int jj = 0; jj < MAXC; jj++) {
+            const float cg = dot32_q4(wg[jj], &xr[jj][0]);
+            const float cu = dot32_q4(wu[jj], &xr[jj][0]);
+            ag += h2f(sg_[jj]) * cg + h2f(mg_[jj]) * xsum[jj];
+            au += h2f(su_[jj]) * cu + h2f(mu_[jj]) * xsum[jj];
+        }
+        if (i + TW < a.I) issue(i + TW);
+        ag = warp_sum(ag);
+        au = warp_sum(au);
+        if (lane == 0) a.act[(size_t)pick * a.I + i] = siluf_(ag) * au;
+    }
+}
+
+// x[b][o] += sum_r w_r * (down_r[o] . act_r)  +  sigmoid(shared_gate) * (shared_down[o] . shared_act)
+// The picks are summed in rank order, so the result does not depend on scheduling. One warp per
+// output row; a half-warp covers one pick's row (I/2 bytes = up to 16 slices of 32 codes).
+// grid (blocks, B). Needs I <= 512 and SH <= 512.
+__global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) {
+    extern __shared__ float smem[];
+    float* acts = smem;                          // [topk][I]
+    float* shs = smem + a.topk * a.I;            // [SH]
+    __shared__ const uint8_t* s_base[8];
+    __shared__ float s_w[8];
+    const int b = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x < 8) {
+        const int r = threadIdx.x;
+        const uint8_t* p = nullptr;
+        float w = 0.f;
+        if (r < a.topk) {
+            const int e = a.top_idx[b * a.topk + r];
+            if (e >= 0 && e < a.E) p = a.eptr[e];
+            w = a.top_w[b * a.topk + r];
+        }
+        s_base[r] = p;
+        s_w[r] = w;
+    }
+    for (int k = threadIdx.x; k < a.topk * a.I; k += THREADS) acts[k] = a.act[(size_t)b * a.topk * a.I + k];
+    for (int k = threadIdx.x; k < a.SH; k += THREADS) shs[k] = a.sh_act[(size_t)b * a.SH + k];
+    __syncthreads();
+    const int nchunk = a.I >> 5;                  // slices per expert row (<= 16)
+    const int ngroup = a.I >> 6;
+    const int hw = lane >> 4, hl = lane & 15;
+    const int shchunk = a.SH >> 4;                // 16-value int8 slices of the shared row (<= 32)
+    float shx[16];
+#pragma unroll
+    for (int q = 0; q < 16; q++) shx[q] = lane < shchunk ? shs[16 * lane + q] : 0.f;
+    const float sgate = a.sg ? a.sg[b] : 0.f;
+    const int gw = blockIdx.x * WARPS + warp, TW = gridDim.x * WARPS;
+    for (int o = gw; o < a.D; o += TW) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};   // picks hw, hw+2, hw+4, hw+6
+        int4 w[4];
+#pragma unroll
+        for (int it = 0; it < 4; it++) {
+            const int r = 2 * it + hw;
+            w[it] = make_int4(0, 0, 0, 0);
+            if (r < a.topk && s_base[r] != nullptr && hl < nchunk)
+                w[it] = ldw(s_base[r] + a.off_dn_q + (size_t)o * (a.I >> 1) + (size_t)hl * 16);
+        }
+        int4 wsh = make_int4(0, 0, 0, 0);
+        if (a.shd_w && lane < shchunk) wsh = ldw(a.shd_w + (size_t)o * a.SH + (size_t)lane * 16);
+#pragma unroll
+        for (int it = 0; it < 4; it++) {
+            const int r = 2 * it + hw;
+            if (r < a.topk && s_base[r] != nullptr && hl < nchunk) {
+                const float* ar = acts + r * a.I + 32 * hl;
+                float xv[32];
+                float xsum = 0.f;
+#pragma unroll
+                for (int q = 0; q < 32; q++) { xv[q] = ar[q]; xsum += xv[q]; }
+                const float cs = dot32_q4(w[it], xv);
+                const uint16_t* ds = (const uint16_t*)(s_base[r] + a.off_dn_s);
+                const uint16_t* dm = (const uint16_t*)(s_base[r] + a.off_dn_m);
+                const int g = hl >> 1;
+                acc[it] = h2f(ds[(size_t)o * ngroup + g]) * cs + h2f(dm[(size_t)o * ngroup + g]) * xsum;
+            }
+        }
+        float shd = dot16_i8(wsh, shx);
+        // reduce each pick over its half-warp, the shared row over the warp
+#pragma unroll
+        for (int it = 0; it < 4; it++) {
+#pragma unroll
+            for (int off = 8; off > 0; off >>= 1) acc[it] += __shfl_xor_sync(0xffffffffu, acc[it], off);
+        }
+        shd = warp_sum(shd);
+        float other[4];
+#pragma unroll
+        for (int it = 0; it < 4; it++) other[it] = __shfl_xor_sync(0xffffffffu, acc[it], 16);
+        if (lane == 0) {
+            float y = 0.f;
+#pragma unroll
+            for (int it = 0; it < 4; it++) {   // rank order 0, 1, 2, ... (lane 0 holds the even ranks)
+                if (2 * it < a.topk) y = fmaf(s_w[2 * it], acc[it], y);
+                if (2 * it + 1 < a.topk) y = fmaf(s_w[2 * it + 1], other[it], y);
+            }
+            if (a.shd_w) y = fmaf(sgate, bf(a.shd_s[o]) * shd, y);
+            a.xout[(size_t)b * a.D + o] += y;
+        }
+    }
+}
+
+// N consecutive cache values (bf16 or fp32) starting at a 4*N- or 2*N-byte aligned address -> fp32.
+template <int N, bool F32>
+__device__ __forceinline__ void load_kv(const void* base, size_t elem, float (&out)[N]) {
+    if (F32) {
+        const float* p = (const float*)base + elem;
+        if (N % 4 == 0) {
+#pragma unroll
+            for (int q = 0; q < N / 4; q++) {
+                const float4 t = reinterpret_cast<const float4*>(p)[q];
+                out[4 * q] = t.x; out[4 * q + 1] = t.y; out[4 * q + 2] = t.z; out[4 * q + 3] = t.w;
+            }
+        } else {
+            const float2 t = *reinterpret_cast<const float2*>(p);
+            out[0] = t.x; out[1] = t.y;
+        }
+    } else {
+        const uint16_t* p = (const uint16_t*)base + elem;
+        if (N == 8) {
+            const uint4 t = *reinterpret_cast<const uint4*>(p);
+            out[0] = bflo(t.x); out[1] = bfhi(t.x); out[2] = bflo(t.y); out[3] = bfhi(t.y);
+            out[4] = bflo(t.z); out[5] = bfhi(t.z); out[6] = bflo(t.w); out[7] = bfhi(t.w);
+        } else if (N == 4) {
+            const uint2 t = *reinterpret_cast<const uint2*>(p);
+            out[0] = bflo(t.x); out[1] = bfhi(t.x); out[2] = bflo(t.y); out[3] = bfhi(t.y);
+        } else {
+            const uint32_t t = *reinterpret_cast<const uint32_t*>(p);
+            out[0] = bflo(t); out[1] = bfhi(t);
+        }
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// k_attn: gated GQA decode attention over the paged KV cache, split along the context.
+// Each block takes one KV head of one sequence and one slice of the positions, for all the query
+// heads of the group (so a key/value row is read once, not once per query head as in hybrid.cu:121-173).
+// Prologue: per-head zero-centred RMSNorm of q and of the new k, partial RoPE (rotate-half on the
+// first RD dims, aegist/hybrid.py:160-166, angles from a host-built table), and the block that owns
+// the newest position appends k, v to the cache. Each block leaves (max, sum, acc) per query head;
+// the last block of the (sequence, KV head) merges the slices and applies sigmoid(gate).
+struct AttnArgs {
+    const float* qraw;        // [B][H][2*HD]  (query | gate) per head
+    const float* kraw;        // [B][KV][HD]
+    const float* vraw;        // [B][KV][HD]
+    const uint16_t* qn_w;     // [HD]
+    const uint16_t* kn_w;     // [HD]
+    const float* rope_cos;    // [cap][RD/2]
+    const float* rope_sin;
+    const int* pos;           // [B] position of the new token
+    void* kpool;              // [pages][KV][KV_PAGE][HD] bf16 or fp32
+    void* vpool;
+    const int* page_table;    // [B][pages per sequence]
+    int pages_per_seq;
+    int H, KV, RD;
+    float eps, scale;
+    float* part;              // [B][KV][nsplit][G][HD + 2]
+    unsigned int* counter;    // [B][KV]
+    float* out;               // [B][H*HD]
+    int nsplit;
+};
+
+template <int HD, bool KVF32>
+__global__ void __launch_bounds__(THREADS) k_attn(const AttnArgs a) {
+    constexpr int DPL = HD / 32;              // dims per lane
+    constexpr int MAXG = 8;
+    const int G = a.H / a.KV;                 // query heads per KV head (<= 8)
+    const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int pos = a.pos[b];
+    const int L = pos + 1;
+    int chunk = (L + a.nsplit - 1) / a.nsplit;
+    chunk = (chunk + WARPS - 1) / WARPS * WARPS;
+    const int p0 = split * chunk, p1 = min(L, p0 + chunk);
+
+    __shared__ float qs[MAXG][HD];
+    __shared__ float knew[HD], vnew[HD];
+    __shared__ float m_s[WARPS][MAXG], l_s[WARPS][MAXG];
+    __shared__ int s_last;
+    extern __shared__ float accs[];            // [WARPS][G][HD]
+
+    // prologue: warps 0..G-1 prepare the query heads, warp G (mod 8) the new key and value
+    const float* cs = a.rope_cos + (size_t)pos * (a.RD / 2);
+    const float* sn = a.rope_sin + (size_t)pos * (a.RD / 2);
+    for (int t = warp; t < G + 1; t += WARPS) {
+        const bool isq = t < G;
+        const float* src = isq ? a.qraw + ((size_t)b * a.H + kvh * G + t) * 2 * HD : a.kraw + ((size_t)b * a.KV + kvh) * HD;
+        const uint16_t* nw = isq ? a.qn_w : a.kn_w;
+        float* dst = isq ? qs[t] : knew;
+        float v[DPL];
+        float ss = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPL; i++) { v[i] = src[lane + 32 * i]; ss = fmaf(v[i], v[i], ss); }
+        ss = warp_sum(ss);
+        const float r = 1.0f / sqrtf(ss / (float)HD + a.eps);
+#pragma unroll
+        for (int i = 0; i < DPL; i++) dst[lane + 32 * i] = v[i] * r * (1.0f + bf(nw[lane + 32 * i]));
+        __syncwarp();
+        const int hr = a.RD / 2;
+        for (int j = lane; j < hr; j += 32) {     // pairs (j, j + RD/2)
+            const float x0 = dst[j], x1 = dst[j + hr];
+            const float c = cs[j], s = sn[j];
+            dst[j] = x0 * c - x1 * s;
+            dst[j + hr] = x1 * c + x0 * s;
+        }
+        if (!isq) {
+            const float* vs = a.vraw + ((size_t)b * a.KV + kvh) * HD;
+            __syncwarp();
+            for (int i = lane; i < HD; i += 32) {
+                float kx = dst[i], vx = vs[i];
+                if (!KVF32) { kx = bf(f2bf(kx)); vx = bf(f2bf(vx)); }   // what a bf16 cache gives back
+                knew[i] = kx;
+                vnew[i] = vx;
+            }
+        }
+    }
+    __syncthreads();
+    // the block that owns the newest position appends it
+    if (pos >= p0 && pos < p1) {
+        const int page = a.page_table[(size_t)b * a.pages_per_seq + pos / KV_PAGE];
+        const size_t off = (((size_t)page * a.KV + kvh) * KV_PAGE + pos % KV_PAGE) * HD;
+        for (int i = threadIdx.x; i < HD; i += THREADS) {
+            if (KVF32) { ((float*)a.kpool)[off + i] = knew[i]; ((float*)a.vpool)[off + i] = vnew[i]; }
+            else { ((uint16_t*)a.kpool)[off + i] = f2bf(knew[i]); ((uint16_t*)a.vpool)[off + i] = f2bf(vnew[i]); }
+        }
+    }
+
+    float q[MAXG][DPL];
+#pragma unroll
+    for (int g = 0; g < MAXG; g++)
+#pragma unroll
+        for (int i = 0; i < DPL; i++) q[g][i] = g < G ? qs[g][lane * DPL + i] * a.scale : 0.f;
+    float m[MAXG], l[MAXG], acc[MAXG][DPL];
+#pragma unroll
+    for (int g = 0; g < MAXG; g++) {
+        m[g] = -INFINITY; l[g] = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPL; i++) acc[g][i] = 0.f;
+    }
+    // each lane owns DPL consecutive dims of a row: one 16-byte (bf16, HD 256) load per key
+    for (int p = p0 + warp; p < p1; p += WARPS) {
+        float kk[DPL], vv[DPL];
+        if (p == pos) {
+#pragma unroll
+            for (int i = 0; i < DPL; i++) { kk[i] = knew[lane * DPL + i]; vv[i] = vnew[lane * DPL + i]; }
+        } else {
+            const int page = a.page_table[(size_t)b * a.pages_per_seq + p / KV_PAGE];
+            const size_t off = (((size_t)page * a.KV + kvh) * KV_PAGE + p % KV_PAGE) * HD + lane * DPL;
+            load_kv<DPL, KVF32>(a.kpool, off, kk);
+            load_kv<DPL, KVF32>(a.vpool, off, vv);
+        }
+#pragma unroll
+        for (int g = 0; g < MAXG; g++) {
+            if (g < G) {
+                float s = 0.f;
+#pragma unroll
+                for (int i = 0; i < DPL; i++) s = fmaf(q[g][i], kk[i], s);
+                s = warp_sum(s);
+                const float mn = fmaxf(m[g], s);
+                const float corr = expf(m[g] - mn);
+                const float pe = expf(s - mn);
+                l[g] = l[g] * corr + pe;
+#pragma unroll
+                for (int i = 0; i < DPL; i++) acc[g][i] = fmaf(pe, vv[i], acc[g][i] * corr);
+                m[g] = mn;
+            }
+        }
+    }
+    // merge the 8 warps of this block
+#pragma unroll
+    for (int g = 0; g < MAXG; g++) {
+        if (g < G) {
+            if (lane == 0) { m_s[warp][g] = m[g]; l_s[warp][g] = l[g]; }
+#pragma unroll
+            for (int i = 0; i < DPL; i++) accs[((size_t)warp * G + g) * HD + lane * DPL + i] = acc[g][i];
+        }
+    }
+    __syncthreads();
+    const size_t pstride = HD + 2;
+    float* part = a.part + (((size_t)b * a.KV + kvh) * a.nsplit + split) * G * pstride;
+    for (int g = 0; g < G; g++) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < WARPS; w++) mx = fmaxf(mx, m_s[w][g]);
+        float lsum = 0.f;
+        for (int d = threadIdx.x; d < HD; d += THREADS) {
+            float s = 0.f;
+#pragma unroll
+            for (int w = 0; w < WARPS; w++) {
+                const float c = m_s[w][g] == -INFINITY ? 0.f : expf(m_s[w][g] - mx);
+                s = fmaf(accs[((size_t)w * G + g) * HD + d], c, s);
+            }
+            part[g * pstride + d] = s;
+        }
+        if (threadIdx.x == 0) {
+#pragma unroll
+            for (int w = 0; w < WARPS; w++) lsum += m_s[w][g] == -INFINITY ? 0.f : l_s[w][g] * expf(m_s[w][g] - mx);
+            part[g * pstride + HD] = mx;
+            part[g * pstride + HD + 1] = lsum;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int n = atomicAdd(a.counter + b * a.KV + kvh, 1u);
+        s_last = (n == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    const float* pb = a.part + (((size_t)b * a.KV + kvh) * a.nsplit) * G * pstride;
+    for (int g = 0; g < G; g++) {
+        float mx = -INFINITY;
+        for (int s = 0; s < a.nsplit; s++) mx = fmaxf(mx, __ldcg(pb + ((size_t)s * G + g) * pstride + HD));
+        float lsum = 0.f;
+        for (int s = 0; s < a.nsplit; s++) {
+            const float ms = __ldcg(pb + ((size_t)s * G + g) * pstride + HD);
+            if (ms != -INFINITY) lsum += __ldcg(pb + ((size_t)s * G + g) * pstride + HD + 1) * expf(ms - mx);
+        }
+        const int head = kvh * G + g;
+        for (int d = threadIdx.x; d < HD; d += THREADS) {
+            float s_acc = 0.f;
+            for (int s = 0; s < a.nsplit; s++) {
+                const float ms = __ldcg(pb + ((size_t)s * G + g) * pstride + HD);
+                if (ms != -INFINITY) s_acc = fmaf(__ldcg(pb + ((size_t)s * G + g) * pstride + d), expf(ms - mx), s_acc);
+            }
+            const float gate = a.qraw[((size_t)b * a.H + head) * 2 * HD + HD + d];
+            a.out[(size_t)b * a.H * HD + head * HD + d] = (s_acc / lsum) * sigmoidf_(gate);
+        }
+    }
+    if (threadIdx.x == 0) a.counter[b * a.KV + kvh] = 0;
+}
+
+// ------------------------------------------------------------------------------------------
+// Small helpers for the host: fill and copy.
+__global__ void k_fill_i32(int* p, int v, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] = v;
+}
+__global__ void k_add_i32(int* p, int v, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) p[i] += v;
+}
+
+}  // namespace b2
