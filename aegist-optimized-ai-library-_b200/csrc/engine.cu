@@ -142,6 +142,18 @@ struct b2_engine {
     std::vector<int> tap_layers;
     float* tap_buf = nullptr;
     uint64_t hits = 0;
+    // per-kernel timing (b2_profile_step): one event after every launch of an un-graphed step
+    bool profiling = false;
+    std::vector<cudaEvent_t> prof_ev;
+    std::vector<int> prof_class;
+    size_t prof_used = 0;
+    void mark(int cls, cudaStream_t st) {
+        if (!profiling) return;
+        if (prof_used == prof_ev.size()) { cudaEvent_t e; cudaEventCreate(&e); prof_ev.push_back(e); prof_class.push_back(0); }
+        prof_class[prof_used] = cls;
+        cudaEventRecord(prof_ev[prof_used++], st);
+    }
+    void class_bytes(double out[8]) const;
 
     int fail(const char* fmt, ...) {
         char buf[1024];
@@ -167,6 +179,7 @@ struct b2_engine {
 };
 
 b2_engine::~b2_engine() {
+    if (t.empty() && !finished) return;   // nothing was ever allocated (e.g. creation was refused)
     cudaSetDevice(device);
     if (graph) cudaGraphExecDestroy(graph);
     for (auto& kv : t) cudaFree(kv.second.p);
@@ -178,6 +191,7 @@ b2_engine::~b2_engine() {
     if (h_pin) cudaFreeHost(h_pin);
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
+    for (cudaEvent_t e : prof_ev) cudaEventDestroy(e);
     if (stream) cudaStreamDestroy(stream);
 }
 
@@ -363,6 +377,8 @@ int b2_engine::finish() {
     const size_t kvb = kv_f32 ? 4 : 2;
     cudaError_t e1 = cudaMalloc(&kpool, kv_elems * kvb), e2 = cudaMalloc(&vpool, kv_elems * kvb);
     if (e1 != cudaSuccess || e2 != cudaSuccess) return fail("KV cache for %d tokens x %d sequences: %s", cap, B, cudaGetErrorString(e1 != cudaSuccess ? e1 : e2));
+    CU(cudaMemset(kpool, 0, kv_elems * kvb));
+    CU(cudaMemset(vpool, 0, kv_elems * kvb));
     {
         // identity page table: sequence b owns pages [b * pages_per_seq, (b+1) * pages_per_seq) of each layer's pool
         std::vector<int> pt((size_t)B * pages_per_seq);
@@ -475,15 +491,17 @@ static void launch_delta(const DeltaArgs& a, int DK, int B, cudaStream_t st) {
     else k_delta_step<128><<<g, THREADS, 0, st>>>(a);
 }
 
-static void launch_experts(const ExpertArgs& a, int B, int nsm, cudaStream_t st) {
+static void launch_experts(const ExpertArgs& a, int B, int nsm, cudaStream_t st, b2_engine* prof = nullptr) {
     const int picks = B * a.topk;
     int gx = std::max(1, std::min((a.I + WARPS - 1) / WARPS, (2 * nsm + picks - 1) / picks));
     const size_t smem = (size_t)(a.D + 32) * 4;
     if (a.D <= 1024) k_expert_gu<1><<<dim3(gx, picks), THREADS, smem, st>>>(a);
     else k_expert_gu<2><<<dim3(gx, picks), THREADS, smem, st>>>(a);
+    if (prof) prof->mark(5, st);
     int gd = std::max(1, std::min((a.D + WARPS - 1) / WARPS, (2 * nsm + B - 1) / B));
     const size_t smem2 = (size_t)(a.topk * a.I + a.SH) * 4;
     k_expert_down<<<dim3(gd, B), THREADS, smem2, st>>>(a);
+    if (prof) prof->mark(6, st);
 }
 
 static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaStream_t st) {
@@ -506,7 +524,10 @@ static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaS
 // One decode step for all B sequences: token ids in d_tok, positions in d_pos.
 int b2_engine::enqueue_step(cudaStream_t st, bool count) {
     int n = 0;
+    cudaGetLastError();   // a stale error of an earlier, unrelated call must not be blamed on these launches
+    mark(-1, st);
     k_embed<<<B, 256, 0, st>>>(embed, d_tok, x, c.D, c.V, d_err);
+    mark(0, st);
     n++;
     const size_t kv_layer = (size_t)B * pages_per_seq * c.KV * KV_PAGE * c.HD * (kv_f32 ? 4 : 2);
     for (int li = 0; li < c.L; li++) {
@@ -519,6 +540,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.nseg = 3; seal(a);
             a.x = x; a.norm_w = l.norm1; a.eps = c.eps; a.K = c.D;
             launch_gemv(a, B, nsm, st);
+            mark(1, st);
             AttnArgs t{};
             t.qraw = big; t.kraw = kraw; t.vraw = vraw; t.qn_w = l.q_norm; t.kn_w = l.k_norm;
             t.rope_cos = rope_cos; t.rope_sin = rope_sin; t.pos = d_pos;
@@ -528,6 +550,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             t.part = attn_part; t.counter = d_acounter; t.out = att; t.nsplit = nsplit;
             cudaError_t e = launch_attn(t, c.HD, kv_f32, B, st);
             if (e != cudaSuccess) return fail("attention launch: %s", cudaGetErrorString(e));
+            mark(3, st);
             ProjArgs p{};
             p.in = att; p.mode = 1; p.w = l.o.w; p.s = l.o.s; p.x = x; p.N = c.D; p.K = c.H * c.HD; p.eps = c.eps; p.DV = c.DV;
             launch_proj(p, B, nsm, st);
@@ -542,15 +565,18 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.conv_w = l.conv; a.conv_state = conv + (size_t)l.slot * B * c.C() * 3;
             a.a_log = l.a_log; a.dt_bias = l.dt_bias;
             launch_gemv(a, B, nsm, st);
+            mark(1, st);
             DeltaArgs d{};
             d.y = big; d.beta = beta; d.g = gdec; d.state = state + (size_t)l.slot * B * c.HV * c.DK * c.DV;
             d.o = obuf; d.C = c.C(); d.HK = c.HK; d.HV = c.HV; d.DV = c.DV; d.prenormed = 0;
             launch_delta(d, c.DK, B, st);
+            mark(2, st);
             ProjArgs p{};
             p.in = obuf; p.z = zbuf; p.gn_w = l.gnorm; p.eps = c.eps; p.DV = c.DV; p.mode = 0;
             p.w = l.out.w; p.s = l.out.s; p.x = x; p.N = c.D; p.K = c.VD();
             launch_proj(p, B, nsm, st);
         }
+        mark(4, st);
         n += 3;
         {
             GemvArgs a{};
@@ -564,12 +590,13 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.finisher = FIN_TOPK; a.counter = d_counter; a.E = c.E; a.topk = c.TOPK;
             a.top_idx = top_idx + (size_t)li * B * c.TOPK; a.top_w = top_w + (size_t)li * B * c.TOPK;
             launch_gemv(a, B, nsm, st);
+            mark(1, st);
             ExpertArgs x2{};
             x2.eptr = l.eptr; x2.top_idx = a.top_idx; x2.top_w = a.top_w; x2.topk = c.TOPK; x2.E = c.E; x2.D = c.D; x2.I = c.I;
             x2.off_gu_s = c.off_gu_s(); x2.off_gu_m = c.off_gu_m(); x2.off_dn_q = c.off_dn_q(); x2.off_dn_s = c.off_dn_s(); x2.off_dn_m = c.off_dn_m();
             x2.x = x; x2.norm_w = l.norm2; x2.eps = c.eps; x2.act = act; x2.sh_act = sh_act; x2.sg = sgate;
             x2.shd_w = l.sh_down.w; x2.shd_s = l.sh_down.s; x2.SH = c.SH; x2.xout = x; x2.err = d_err;
-            launch_experts(x2, B, nsm, st);
+            launch_experts(x2, B, nsm, st, this);
             n += 3;
         }
         for (size_t j = 0; j < tap_layers.size(); j++)
@@ -584,6 +611,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
         a.finisher = FIN_ARGMAX; a.counter = d_counter; a.part_val = part_val; a.part_idx = part_idx;
         a.next_tok = d_next; a.pos = d_pos;
         launch_gemv(a, B, nsm, st, head_grid);
+        mark(7, st);
         n++;
     }
     if (count) launches = n;
@@ -634,6 +662,34 @@ int b2_engine::reset_state() {
     length = 0;
     snap_pos[0] = snap_pos[1] = -1;
     return 0;
+}
+
+// Algorithmic bytes of one decode step by kernel class (0 embed, 1 norm+GEMV groups, 2 delta step,
+// 3 attention, 4 output projections, 5 expert gate/up, 6 expert down + shared down, 7 head):
+// every weight byte once per step, recurrent state read and written, KV read up to the current length,
+// min(B * top-k, E) experts per layer. Activations are not counted.
+void b2_engine::class_bytes(double out[8]) const {
+    for (int i = 0; i < 8; i++) out[i] = 0;
+    auto qwb = [](double n, double k) { return n * k + 2 * n; };
+    const double nb = B;
+    const double uniq = std::min<double>(nb * c.TOPK, c.E / ep_world);
+    out[0] = nb * c.D * 2.0;
+    for (int i = 0; i < c.L; i++) {
+        if (c.attn[i]) {
+            out[1] += c.D * 2.0 + qwb(2 * c.H * c.HD, c.D) + 2 * qwb(c.KV * c.HD, c.D);
+            out[3] += 2.0 * c.HD * 2 + nb * 2.0 * c.KV * c.HD * (kv_f32 ? 4 : 2) * (length + 1);
+            out[4] += qwb(c.D, c.H * c.HD);
+        } else {
+            out[1] += c.D * 2.0 + qwb(c.C(), c.D) + qwb(c.VD(), c.D) + 2.0 * c.HV * c.D * 2 + c.C() * c.CK * 2.0 + c.HV * 4.0 +
+                      nb * 2.0 * c.C() * 3 * 4;
+            out[2] += nb * 2.0 * c.HV * c.DK * c.DV * 4;
+            out[4] += qwb(c.D, c.VD()) + c.DV * 2.0;
+        }
+        out[1] += c.D * 2.0 + (double)c.E * c.D * 2 + c.D * 2.0 + 2 * qwb(c.SH, c.D);
+        out[5] += uniq * (double)(c.gu_q() + 2 * c.gu_sm()) + c.D * 2.0;
+        out[6] += uniq * (double)(c.dn_q() + 2 * c.dn_sm()) + qwb(c.D, c.SH);
+    }
+    out[7] = c.D * 2.0 + qwb(c.V, c.D);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -915,27 +971,47 @@ int b2_set_router_bias(b2_engine* e, int layer, const float* bias) {
 
 int b2_launches_per_step(const b2_engine* e) { return e ? e->launches : 0; }
 
+int b2_debug_seek(b2_engine* e, int n) {
+    if (!e || !e->finished) return 1;
+    if (n < 0 || n > e->cap) return e->fail("cannot seek to %d (context holds %d)", n, e->cap);
+    CUE(cudaSetDevice(e->device));
+    k_fill_i32<<<(e->B + 255) / 256, 256, 0, e->stream>>>(e->d_pos, n, e->B);
+    CUE(cudaStreamSynchronize(e->stream));
+    e->length = n;
+    return 0;
+}
+
 double b2_step_bytes(const b2_engine* e) {
     if (!e) return 0;
-    const Cfg& c = e->c;
-    const double B = e->B;
-    double w = 0;          // read once per step per sequence by these kernels
-    double per_seq = 0;    // state and KV
-    auto qwb = [](double n, double k) { return n * k + 2 * n; };
-    for (int i = 0; i < c.L; i++) {
-        w += 2.0 * c.D * 2;   // norm1, norm2
-        if (c.attn[i]) {
-            w += qwb(2 * c.H * c.HD, c.D) + 2 * qwb(c.KV * c.HD, c.D) + qwb(c.D, c.H * c.HD) + 2.0 * c.HD * 2;
-            per_seq += 2.0 * c.KV * c.HD * (e->kv_f32 ? 4 : 2) * (e->length + 1);
-        } else {
-            w += qwb(c.C(), c.D) + qwb(c.VD(), c.D) + qwb(c.D, c.VD()) + 2.0 * c.HV * c.D * 2 + c.C() * c.CK * 2.0 + c.HV * 4.0 + c.DV * 2.0;
-            per_seq += 2.0 * c.HV * c.DK * c.DV * 4 + 2.0 * c.C() * 3 * 4;
+    double cls[8];
+    e->class_bytes(cls);
+    double s = 0;
+    for (double v : cls) s += v;
+    return s;
+}
+
+int b2_profile_step(b2_engine* e, int iters, float ms[8], double bytes[8], int launches[8]) {
+    if (feed_checks(e, iters)) return 1;
+    for (int i = 0; i < 8; i++) { ms[i] = 0; launches[i] = 0; }
+    e->class_bytes(bytes);
+    e->profiling = true;
+    for (int it = 0; it < iters; it++) {
+        e->prof_used = 0;
+        if (e->enqueue_step(e->stream, false)) { e->profiling = false; return 1; }
+        cudaMemcpyAsync(e->d_tok, e->d_next, (size_t)e->B * 4, cudaMemcpyDeviceToDevice, e->stream);
+        cudaError_t ce = cudaStreamSynchronize(e->stream);
+        if (ce != cudaSuccess) { e->profiling = false; return e->fail("profile step: %s", cudaGetErrorString(ce)); }
+        e->length += 1;
+        for (size_t k = 1; k < e->prof_used; k++) {
+            float t = 0;
+            cudaEventElapsedTime(&t, e->prof_ev[k - 1], e->prof_ev[k]);
+            ms[e->prof_class[k]] += t;
+            launches[e->prof_class[k]] += 1;
         }
-        w += (double)c.E * c.D * 2 + c.D * 2.0 + 2 * qwb(c.SH, c.D) + qwb(c.D, c.SH);
-        w += (double)c.TOPK * c.expert_bytes();
     }
-    w += c.D * 2.0 + qwb(c.V, c.D) + c.D * 2.0;   // final norm, head, one embedding row
-    return w * B + per_seq * B;
+    e->profiling = false;
+    for (int i = 0; i < 8; i++) { ms[i] /= iters; launches[i] /= iters; }
+    return 0;
 }
 
 }  // extern "C"

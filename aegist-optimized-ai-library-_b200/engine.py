@@ -62,8 +62,10 @@ SYMBOLS = {
     "b2_debug_router": (_I, [_P, _I, _P, _P]),
     "b2_debug_hidden": (_I, [_P, _P]),
     "b2_set_router_bias": (_I, [_P, _I, _P]),
+    "b2_debug_seek": (_I, [_P, _I]),
     "b2_launches_per_step": (_I, [_P]),
     "b2_step_bytes": (C.c_double, [_P]),
+    "b2_profile_step": (_I, [_P, _I, C.POINTER(_F), C.POINTER(C.c_double), C.POINTER(_I)]),
     "b2_op_linear_i8": (_I, [_I, _P, _P, _I, _I, _P, _I, _P]),
     "b2_moe_create": (_I, [_I, C.POINTER(MoeWeights), _I, C.POINTER(_P)]),
     "b2_moe_forward": (_I, [_P, _P, _I, _P, _P, _P, C.POINTER(_F)]),
@@ -254,11 +256,24 @@ class HybridEngine:
             b = np.ascontiguousarray(np.asarray(bias, dtype=np.float32))
             self._check(self._lib.b2_set_router_bias(self._h, layer, _ptr(b)))
 
+    def seek(self, n: int):
+        """Set the context length without feeding (timing hook; see b2_debug_seek)."""
+        self._check(self._lib.b2_debug_seek(self._h, n))
+
     def launches_per_step(self) -> int:
         return self._lib.b2_launches_per_step(self._h)
 
     def step_bytes(self) -> float:
         return self._lib.b2_step_bytes(self._h)
+
+    KERNEL_CLASSES = ("k_embed", "k_gemv_norm", "k_delta_step", "k_attn", "k_proj_out", "k_expert_gu",
+                      "k_expert_down", "k_gemv_norm[head]")
+
+    def profile_step(self, iters: int = 8) -> dict:
+        """Per kernel class: mean ms per step, algorithmic bytes per step, launches per step."""
+        ms, by, ln = (C.c_float * 8)(), (C.c_double * 8)(), (C.c_int * 8)()
+        self._check(self._lib.b2_profile_step(self._h, iters, ms, by, ln))
+        return {n: {"ms": ms[i], "bytes": by[i], "launches": ln[i]} for i, n in enumerate(self.KERNEL_CLASSES)}
 
 
 # --- sampler (aegist_rs/src/chat.rs:221-272) ----------------------------------------------------

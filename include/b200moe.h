@@ -109,11 +109,22 @@ int b2_debug_hidden(b2_engine* e, float* out);
 /* Add `bias` (f32[n_experts], host; NULL removes it) to one layer's router logits before the
  * softmax: shapes expert popularity for load-balance measurements. No reference counterpart. */
 int b2_set_router_bias(b2_engine* e, int layer, const float* bias);
+/* Set the context length without feeding tokens: positions 0..n-1 of the KV cache keep whatever they
+ * hold (zeros after loading) and the recurrent state is untouched. For timing a step at a given
+ * context length; the logits that follow are not those of any real prompt. No reference counterpart. */
+int b2_debug_seek(b2_engine* e, int n);
 /* Number of kernel launches in one decode step (all sequences). */
 int b2_launches_per_step(const b2_engine* e);
 /* Algorithmic bytes one decode step moves (weights once, recurrent state read + written, KV read
  * up to the current length), for roofline arithmetic. */
 double b2_step_bytes(const b2_engine* e);
+
+/* Run `iters` decode steps (each sequence is fed its own arg-max) outside the CUDA graph with an
+ * event after every launch, and report per kernel class the mean device time per step (ms), the
+ * algorithmic bytes per step and the launches per step. Classes: 0 embedding gather, 1 norm + GEMV
+ * groups, 2 DeltaNet step, 3 attention, 4 output projections, 5 expert gate/up, 6 expert down +
+ * shared down, 7 head. */
+int b2_profile_step(b2_engine* e, int iters, float ms[8], double bytes[8], int launches[8]);
 
 /* -- single operators, host buffers in and out (the reference's per-op semantics) ----------- */
 
