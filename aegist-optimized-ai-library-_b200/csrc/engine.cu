@@ -91,6 +91,8 @@ static size_t dtype_size(const std::string& d) {
     return 0;
 }
 
+static int down_row_blocks(int D) { return (D + DOWN_ROWS - 1) / DOWN_ROWS; }
+
 }  // namespace b2
 
 using namespace b2;
@@ -137,6 +139,8 @@ struct b2_engine {
     float* part_val = nullptr;
     int* part_idx = nullptr;
     float* attn_part = nullptr;
+    float* ypart = nullptr;                  // [B][TOPK + 1][D]
+    unsigned int* d_dcounter = nullptr;      // [B][row blocks of the expert down projection]
     int nsplit = 1, head_grid = 1;
     uint32_t* h_pin = nullptr;               // pinned staging [B]
     std::vector<int> tap_layers;
@@ -186,7 +190,7 @@ b2_engine::~b2_engine() {
     for (auto& l : layers) { cudaFree((void*)l.eptr); cudaFree(l.router_bias); }
     void* bufs[] = {conv, state, snap_conv[0], snap_conv[1], snap_state[0], snap_state[1], kpool, vpool, page_table, rope_cos,
                     rope_sin, d_tok, d_next, d_pos, d_err, d_counter, d_acounter, x, big, zbuf, kraw, vraw, beta, gdec, obuf, att,
-                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf};
+                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter};
     for (void* p : bufs) cudaFree(p);
     if (h_pin) cudaFreeHost(h_pin);
     if (ev0) cudaEventDestroy(ev0);
@@ -430,6 +434,8 @@ int b2_engine::finish() {
     // attention: enough slices to fill the GPU, but at least 64 positions each at full context
     nsplit = std::max(1, std::min({64, (2 * nsm) / std::max(1, c.KV * B), (cap + 63) / 64}));
     CU(dalloc(&attn_part, (size_t)B * c.KV * nsplit * (c.H / c.KV) * (c.HD + 2)));
+    CU(dalloc(&ypart, (size_t)B * (c.TOPK + 1) * c.D));
+    CU(dalloc(&d_dcounter, (size_t)B * down_row_blocks(c.D)));
     CU(cudaMallocHost((void**)&h_pin, std::max(B, 1) * sizeof(uint32_t) * 2));
     CU(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
     CU(cudaEventCreate(&ev0));
@@ -445,6 +451,24 @@ int b2_engine::finish() {
     return build_graph();
 }
 
+// Programmatic dependent launch for every kernel of a step (B2_PDL=0 turns it off).
+static bool g_pdl = [] { const char* v = getenv("B2_PDL"); return !(v && v[0] == '0'); }();
+
+template <typename... KArgs, typename... Args>
+static cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 template <typename F>
 static cudaError_t opt_in_smem(F* f, size_t bytes) {
     if (bytes <= 48 * 1024) return cudaSuccess;
@@ -453,12 +477,11 @@ static cudaError_t opt_in_smem(F* f, size_t bytes) {
 
 static void launch_gemv(const GemvArgs& a, int B, int nsm, cudaStream_t st, int grid_override = 0) {
     const int grid = grid_override ? grid_override : std::max(1, std::min((a.total_jobs + WARPS - 1) / WARPS, 2 * nsm));
-    const size_t smem = (size_t)(a.K + 32) * 4;
     const int maxc = (a.K + 511) / 512;
     dim3 g(grid, B);
-    if (maxc <= 1) k_gemv_norm<1><<<g, THREADS, smem, st>>>(a);
-    else if (maxc == 2) k_gemv_norm<2><<<g, THREADS, smem, st>>>(a);
-    else k_gemv_norm<4><<<g, THREADS, smem, st>>>(a);
+    if (maxc <= 1) launch_k(k_gemv_norm<1>, g, THREADS, 0, st, a);
+    else if (maxc == 2) launch_k(k_gemv_norm<2>, g, THREADS, 0, st, a);
+    else launch_k(k_gemv_norm<4>, g, THREADS, 0, st, a);
 }
 
 static Seg make_seg(int kind, const void* w, const uint16_t* s, int rows, float* out, int out_stride) {
@@ -477,34 +500,32 @@ static void launch_proj(const ProjArgs& a, int B, int nsm, cudaStream_t st) {
     int rpb = 4;
     while ((a.N + rpb - 1) / rpb > 2 * nsm) rpb += 4;
     const int grid = (a.N + rpb - 1) / rpb;
-    const size_t smem = (size_t)(a.K + 2 * rpb) * 4;
+    const size_t smem = (size_t)(2 * rpb) * 4;
     const int maxc = (a.K / 2 + 511) / 512;
     dim3 g(grid, B);
-    if (maxc <= 1) k_proj_out<1><<<g, THREADS, smem, st>>>(a);
-    else if (maxc == 2) k_proj_out<2><<<g, THREADS, smem, st>>>(a);
-    else k_proj_out<4><<<g, THREADS, smem, st>>>(a);
+    if (maxc <= 1) launch_k(k_proj_out<1>, g, THREADS, smem, st, a);
+    else if (maxc == 2) launch_k(k_proj_out<2>, g, THREADS, smem, st, a);
+    else launch_k(k_proj_out<4>, g, THREADS, smem, st, a);
 }
 
 static void launch_delta(const DeltaArgs& a, int DK, int B, cudaStream_t st) {
     dim3 g(a.HV * (a.DV / 32), B);
-    if (DK == 64) k_delta_step<64><<<g, THREADS, 0, st>>>(a);
-    else k_delta_step<128><<<g, THREADS, 0, st>>>(a);
+    if (DK == 64) launch_k(k_delta_step<64>, g, THREADS, 0, st, a);
+    else launch_k(k_delta_step<128>, g, THREADS, 0, st, a);
 }
 
 static void launch_experts(const ExpertArgs& a, int B, int nsm, cudaStream_t st, b2_engine* prof = nullptr) {
     const int picks = B * a.topk;
-    int gx = std::max(1, std::min((a.I + WARPS - 1) / WARPS, (2 * nsm + picks - 1) / picks));
-    const size_t smem = (size_t)(a.D + 32) * 4;
-    if (a.D <= 1024) k_expert_gu<1><<<dim3(gx, picks), THREADS, smem, st>>>(a);
-    else k_expert_gu<2><<<dim3(gx, picks), THREADS, smem, st>>>(a);
+    // whole rows per warp: I / 8 warps / blocks; 32 blocks give two rows per warp at I = 512
+    int gx = std::max(1, std::min((a.I + 2 * WARPS - 1) / (2 * WARPS), (2 * nsm + picks - 1) / picks));
+    if (a.D <= 1024) launch_k(k_expert_gu<1>, dim3(gx, picks), THREADS, 0, st, a);
+    else launch_k(k_expert_gu<2>, dim3(gx, picks), THREADS, 0, st, a);
     if (prof) prof->mark(5, st);
-    int gd = std::max(1, std::min((a.D + WARPS - 1) / WARPS, (2 * nsm + B - 1) / B));
-    const size_t smem2 = (size_t)(a.topk * a.I + a.SH) * 4;
-    k_expert_down<<<dim3(gd, B), THREADS, smem2, st>>>(a);
+    launch_k(k_expert_down, dim3(down_row_blocks(a.D), a.topk + 1, B), THREADS, 0, st, a);
     if (prof) prof->mark(6, st);
 }
 
-static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaStream_t st) {
+static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaStream_t st, b2_engine* prof = nullptr) {
     const int G = a.H / a.KV;
     const size_t smem = (size_t)WARPS * G * HD * 4;
     dim3 g(a.nsplit, a.KV, B);
@@ -512,12 +533,13 @@ static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaS
     {                                                                                  \
         cudaError_t e = opt_in_smem(k_attn<hd, f>, smem);                              \
         if (e != cudaSuccess) return e;                                                \
-        k_attn<hd, f><<<g, THREADS, smem, st>>>(a);                                    \
+        launch_k(k_attn<hd, f>, g, THREADS, smem, st, a);                              \
     }
     if (HD == 64) { if (f32) ATT(64, true) else ATT(64, false) }
     else if (HD == 128) { if (f32) ATT(128, true) else ATT(128, false) }
     else { if (f32) ATT(256, true) else ATT(256, false) }
 #undef ATT
+    launch_k(k_attn_merge, dim3(a.H, B), THREADS, 0, st, a, HD);
     return cudaSuccess;
 }
 
@@ -526,7 +548,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
     int n = 0;
     cudaGetLastError();   // a stale error of an earlier, unrelated call must not be blamed on these launches
     mark(-1, st);
-    k_embed<<<B, 256, 0, st>>>(embed, d_tok, x, c.D, c.V, d_err);
+    launch_k(k_embed, dim3(B), dim3(256), 0, st, embed, (const int*)d_tok, x, c.D, c.V, d_err);
     mark(0, st);
     n++;
     const size_t kv_layer = (size_t)B * pages_per_seq * c.KV * KV_PAGE * c.HD * (kv_f32 ? 4 : 2);
@@ -547,7 +569,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             t.kpool = (char*)kpool + kv_layer * l.slot; t.vpool = (char*)vpool + kv_layer * l.slot;
             t.page_table = page_table; t.pages_per_seq = pages_per_seq;
             t.H = c.H; t.KV = c.KV; t.RD = c.RD; t.eps = c.eps; t.scale = 1.0f / std::sqrt((float)c.HD);
-            t.part = attn_part; t.counter = d_acounter; t.out = att; t.nsplit = nsplit;
+            t.part = attn_part; t.out = att; t.nsplit = nsplit;
             cudaError_t e = launch_attn(t, c.HD, kv_f32, B, st);
             if (e != cudaSuccess) return fail("attention launch: %s", cudaGetErrorString(e));
             mark(3, st);
@@ -577,7 +599,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             launch_proj(p, B, nsm, st);
         }
         mark(4, st);
-        n += 3;
+        n += l.attn ? 4 : 3;
         {
             GemvArgs a{};
             a.seg[0] = make_seg(SEG_BF, l.router, nullptr, c.E, rlogits, c.E);
@@ -596,6 +618,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             x2.off_gu_s = c.off_gu_s(); x2.off_gu_m = c.off_gu_m(); x2.off_dn_q = c.off_dn_q(); x2.off_dn_s = c.off_dn_s(); x2.off_dn_m = c.off_dn_m();
             x2.x = x; x2.norm_w = l.norm2; x2.eps = c.eps; x2.act = act; x2.sh_act = sh_act; x2.sg = sgate;
             x2.shd_w = l.sh_down.w; x2.shd_s = l.sh_down.s; x2.SH = c.SH; x2.xout = x; x2.err = d_err;
+            x2.ypart = ypart; x2.counter = d_dcounter;
             launch_experts(x2, B, nsm, st, this);
             n += 3;
         }

@@ -18,12 +18,19 @@
 // All arithmetic is fp32 with fp32 accumulation (the reference's kernels do the same,
 // aegist_rs/kernels/aegist.cu:1-6). Weights stream from HBM exactly once per sequence with 128-bit
 // loads and are widened in registers; the activation vector of a GEMV lives in registers (each lane
-// always owns the same 16-value slices of it), because at one byte of weight per FMA the shared-
-// memory port could not feed fp32 activations at HBM speed. Each kernel covers one sequence per
-// blockIdx.y; grids are sized in multiples of the SM count by the host.
+// always owns the same 16-value slices of it, read straight from L2, normalised per warp), because
+// at one byte of weight per FMA the shared-memory port could not feed fp32 activations at HBM
+// speed. Integer-to-float conversion instructions run at a sixteenth of the FMA rate on this part,
+// so weights are widened with byte permutes into the mantissa of a magic constant instead
+// (i8_to_f32x4, q4 codes as 1 + code/16). Each kernel covers one sequence per blockIdx.y; grids
+// are sized in multiples of the SM count by the host.
 //
-// Cross-block steps (router top-8, arg-max over the vocabulary, split-K merge) are done by
-// whichever block finishes last (a counter and a fence), never by waiting on another block.
+// Cross-block steps (router top-8, arg-max over the vocabulary, summing the expert picks) are done
+// by whichever block finishes last (a counter and a fence), never by waiting on another block.
+//
+// Every kernel is written for programmatic dependent launch: it first asks for its successor to be
+// scheduled and starts loading its own first weights (which no kernel writes), and only then waits
+// for its predecessor's results (grid_dep_wait). Launched without the attribute these are no-ops.
 #pragma once
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
@@ -43,6 +50,12 @@ __device__ __forceinline__ uint16_t f2bf(float f) {   // round to nearest even
     return (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
 }
 __device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_as_half(h)); }
+
+// Programmatic dependent launch: let the next kernel of the stream be scheduled now; and block until
+// the previous kernel has completed and its writes are visible. Everything a kernel reads that an
+// earlier kernel wrote, and everything it writes, comes after grid_dep_wait().
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
@@ -72,15 +85,18 @@ __device__ __forceinline__ float softplusf_(float x) { return x > 20.f ? x : log
 // Streaming 128-bit load of weights that are read once per step.
 __device__ __forceinline__ int4 ldw(const void* p) { return __ldcs(reinterpret_cast<const int4*>(p)); }
 
+// Four int8 -> fp32 without conversion instructions: flip the sign bit (q + 128 in 0..255), drop the
+// byte into the low mantissa of 2^23 with a byte permute, subtract 2^23 + 128. Exact.
 __device__ __forceinline__ float dot16_i8(const int4& w, const float* x) {
     float a = 0.f;
     const int v[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
     for (int i = 0; i < 4; i++) {
-        a = fmaf(x[4 * i + 0], (float)(signed char)(v[i]), a);
-        a = fmaf(x[4 * i + 1], (float)(signed char)(v[i] >> 8), a);
-        a = fmaf(x[4 * i + 2], (float)(signed char)(v[i] >> 16), a);
-        a = fmaf(x[4 * i + 3], (float)(v[i] >> 24), a);
+        const uint32_t u = (uint32_t)v[i] ^ 0x80808080u;
+        a = fmaf(x[4 * i + 0], __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f, a);
+        a = fmaf(x[4 * i + 1], __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f, a);
+        a = fmaf(x[4 * i + 2], __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f, a);
+        a = fmaf(x[4 * i + 3], __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f, a);
     }
     return a;
 }
@@ -94,58 +110,69 @@ __device__ __forceinline__ float dot8_bf16(const int4& w, const float* x) {
     }
     return a;
 }
-// 32 four-bit codes (even index in the low nibble) against 32 activations: sum code * x.
-__device__ __forceinline__ float dot32_q4(const int4& w, const float* x) {
+// 32 four-bit codes (even index in the low nibble) against 32 activations. Each code is placed in
+// the top four mantissa bits of 1.0 (a shift and one logic op), giving f = 1 + code/16 exactly; the
+// function returns sum f * x, and the caller recovers sum code * x = 16 * (result - sum x).
+__device__ __forceinline__ float dot32_q4f(const int4& w, const float* x) {
     float a = 0.f;
     const uint32_t v[4] = {(uint32_t)w.x, (uint32_t)w.y, (uint32_t)w.z, (uint32_t)w.w};
 #pragma unroll
     for (int i = 0; i < 4; i++) {
 #pragma unroll
-        for (int n = 0; n < 8; n++) a = fmaf(x[8 * i + n], (float)((v[i] >> (4 * n)) & 0xFu), a);
+        for (int n = 0; n < 8; n++) {
+            const int sh = 19 - 4 * n;
+            const uint32_t t = sh >= 0 ? (v[i] << sh) : (v[i] >> (-sh));
+            a = fmaf(x[8 * i + n], __uint_as_float((t & 0x00780000u) | 0x3F800000u), a);
+        }
     }
     return a;
 }
 
-// Copy this lane's 16-value slices of a staged vector into registers: slice j is values
-// [16*(lane + 32*j), +16) (zeros past the end).
+// This lane's 16-value slices of a vector in global memory: slice j is values [16*(lane + 32*j), +16)
+// of `x` (zeros past the end), optionally followed by the zero-centred RMSNorm of the whole vector
+// (aegist/hybrid.py:119-130: x * rsqrt(mean x^2 + eps) * (1 + w)). One warp covers K <= 512 * MAXC
+// values, so the mean needs one shuffle reduction and no shared memory.
 template <int MAXC>
-__device__ __forceinline__ void load_slices(float (&xr)[MAXC][16], const float* xs, int nchunk, int lane) {
+__device__ __forceinline__ void load_x_znorm(float (&xr)[MAXC][16], const float* __restrict__ x,
+                                             const uint16_t* __restrict__ w, float eps, int K, int lane) {
+    const int nchunk = K >> 4;
+    float ss = 0.f;
 #pragma unroll
     for (int j = 0; j < MAXC; j++) {
         const int c = lane + 32 * j;
         if (c < nchunk) {
-            const float4* p = reinterpret_cast<const float4*>(xs + 16 * c);
+            const float4* p = reinterpret_cast<const float4*>(x + 16 * c);
 #pragma unroll
             for (int q = 0; q < 4; q++) {
-                float4 t = p[q];
+                const float4 t = p[q];
                 xr[j][4 * q] = t.x; xr[j][4 * q + 1] = t.y; xr[j][4 * q + 2] = t.z; xr[j][4 * q + 3] = t.w;
+                ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
             }
         } else {
 #pragma unroll
             for (int q = 0; q < 16; q++) xr[j][q] = 0.f;
         }
     }
-}
-
-// Zero-centred RMSNorm of one row into shared memory: xs = x * rsqrt(mean x^2 + eps) * (1 + w)
-// (aegist/hybrid.py:119-130). A null weight stages the row as it is.
-__device__ __forceinline__ void stage_znorm(const float* __restrict__ x, const uint16_t* __restrict__ w, float eps,
-                                            int D, float* xs, float* red) {
-    if (w == nullptr) {
-        for (int k = threadIdx.x; k < D; k += THREADS) xs[k] = x[k];
-        __syncthreads();
-        return;
+    if (w == nullptr) return;
+    ss = warp_sum(ss);
+    const float r = 1.0f / sqrtf(ss / (float)K + eps);
+#pragma unroll
+    for (int j = 0; j < MAXC; j++) {
+        const int c = lane + 32 * j;
+        if (c < nchunk) {
+            const uint4* pw = reinterpret_cast<const uint4*>(w + 16 * c);
+#pragma unroll
+            for (int q = 0; q < 2; q++) {
+                const uint4 t = pw[q];
+                const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++) {
+                    xr[j][8 * q + 2 * i] = xr[j][8 * q + 2 * i] * r * (1.0f + bflo(u[i]));
+                    xr[j][8 * q + 2 * i + 1] = xr[j][8 * q + 2 * i + 1] * r * (1.0f + bfhi(u[i]));
+                }
+            }
+        }
     }
-    float ss = 0.f;
-    for (int k = threadIdx.x; k < D; k += THREADS) {
-        float v = x[k];
-        xs[k] = v;
-        ss = fmaf(v, v, ss);
-    }
-    ss = block_sum(ss, red);
-    const float r = 1.0f / sqrtf(ss / (float)D + eps);
-    for (int k = threadIdx.x; k < D; k += THREADS) xs[k] = xs[k] * r * (1.0f + bf(w[k]));
-    __syncthreads();
 }
 
 // ------------------------------------------------------------------------------------------
@@ -154,6 +181,8 @@ __device__ __forceinline__ void stage_znorm(const float* __restrict__ x, const u
 __global__ void k_embed(const uint16_t* __restrict__ embed, const int* __restrict__ tok, float* __restrict__ x,
                         int D, int V, int* err) {
     const int b = blockIdx.x;
+    grid_dep_launch();
+    grid_dep_wait();
     int id = tok[b];
     if (id < 0 || id >= V) {
         if (threadIdx.x == 0) atomicExch(err, 1);
@@ -274,13 +303,11 @@ __device__ __forceinline__ void router_topk_warp(const float* __restrict__ logit
 
 template <int MAXC>
 __global__ void __launch_bounds__(THREADS, 2) k_gemv_norm(const GemvArgs a) {
-    extern __shared__ float smem[];
-    float* xs = smem;              // [K]
-    float* red = smem + a.K;       // [32]
     const int b = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nchunk = a.K >> 4;
     const int gw = blockIdx.x * WARPS + warp, TW = gridDim.x * WARPS;
+    grid_dep_launch();
 
     int4 wbuf[2 * MAXC];
     // what one job reads: two int8 rows, or one bf16 row (twice the bytes), or a gate row and an up row
@@ -318,13 +345,14 @@ __global__ void __launch_bounds__(THREADS, 2) k_gemv_norm(const GemvArgs a) {
         }
     };
 
-    // the first job's weights do not depend on the activations: start them before the prologue
+    // the first job's weights do not depend on the activations: they are in flight while the previous
+    // kernel finishes
     int job = gw;
     if (job < a.total_jobs) issue(job);
+    grid_dep_wait();
 
-    stage_znorm(a.x + (size_t)b * a.K, a.norm_w, a.eps, a.K, xs, red);
     float xr[MAXC][16];
-    load_slices<MAXC>(xr, xs, nchunk, lane);
+    load_x_znorm<MAXC>(xr, a.x + (size_t)b * a.K, a.norm_w, a.eps, a.K, lane);
 
     float best_v = -INFINITY;
     int best_i = 0x7fffffff;
@@ -476,6 +504,8 @@ __global__ void __launch_bounds__(THREADS) k_delta_step(const DeltaArgs a) {
     const int hk = h / (a.HV / a.HK);
     const int key_dim = a.HK * DK;
     const int col = slab * 32 + lane;
+    grid_dep_launch();
+    grid_dep_wait();        // the state itself is written by this kernel's previous launch
 
     float* S = a.state + (((size_t)b * a.HV + h) * DK) * a.DV + col;
     float st[RPT];
@@ -538,14 +568,16 @@ __global__ void __launch_bounds__(THREADS) k_delta_step(const DeltaArgs a) {
 // ------------------------------------------------------------------------------------------
 // k_proj_out: the mixer's output projection, accumulated into the residual stream.
 //   mode 0 (DeltaNet): input = w * rmsnorm_DV(o) * silu(z) per value head (aegist/hybrid.py:133-147)
-//   mode 1 (attention): input is used as it is (already merged and gated by k_attn)
-// K up to 4096: two warps share a row (each holds half of the input in registers).
+//   mode 1 (attention): input is used as it is (already merged and gated by k_attn_merge)
+// K up to 4096: two warps share a row, each holding its half of the input in registers. A value
+// head (DV values) is DV/16 neighbouring lanes' slices, so its mean square is a short shuffle
+// reduction.
 struct ProjArgs {
     const float* in;      // [B][K]
     const float* z;       // [B][K]      mode 0
     const uint16_t* gn_w; // [DV]        mode 0
     float eps;
-    int DV;
+    int DV;               // 32, 64, 128 or 256
     int mode;
     const int8_t* w;      // [N][K]
     const uint16_t* s;    // [N]
@@ -556,8 +588,7 @@ struct ProjArgs {
 template <int MAXC>
 __global__ void __launch_bounds__(THREADS, 2) k_proj_out(const ProjArgs a) {
     extern __shared__ float smem[];
-    float* xs = smem;               // [K]
-    float* part = smem + a.K;       // [2][rows per block]
+    float* part = smem;             // [2][rows per block]
     const int b = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int half = warp & 1, pair = warp >> 1;          // 4 row-pairs of warps per block
@@ -565,6 +596,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_proj_out(const ProjArgs a) {
     const int rows_per_block = (a.N + gridDim.x - 1) / gridDim.x;
     const int row0 = blockIdx.x * rows_per_block;
     const int row1 = min(a.N, row0 + rows_per_block);
+    grid_dep_launch();
 
     int4 wbuf[MAXC];
     auto issue = [&](int row) {
@@ -577,27 +609,38 @@ __global__ void __launch_bounds__(THREADS, 2) k_proj_out(const ProjArgs a) {
     };
     int row = row0 + pair;
     if (row < row1) issue(row);
+    grid_dep_wait();
 
-    const float* in = a.in + (size_t)b * a.K;
+    const int koff = half * (a.K >> 1);
+    const float* in = a.in + (size_t)b * a.K + koff;
+    float xr[MAXC][16];
+    load_x_znorm<MAXC>(xr, in, nullptr, 0.f, a.K >> 1, lane);
     if (a.mode == 0) {
-        const float* z = a.z + (size_t)b * a.K;
-        const int nh = a.K / a.DV;
-        for (int h = warp; h < nh; h += WARPS) {
+        const float* z = a.z + (size_t)b * a.K + koff;
+        const int lanes_per_head = a.DV >> 4;
+#pragma unroll
+        for (int jj = 0; jj < MAXC; jj++) {
+            const int c = lane + 32 * jj;
             float ss = 0.f;
-            for (int i = lane; i < a.DV; i += 32) { const float v = in[h * a.DV + i]; ss = fmaf(v, v, ss); }
-            ss = warp_sum(ss);
-            const float r = 1.0f / sqrtf(ss / (float)a.DV + a.eps);
-            for (int i = lane; i < a.DV; i += 32) {
-                const int k = h * a.DV + i;
-                xs[k] = (bf(a.gn_w[i]) * (in[k] * r)) * siluf_(z[k]);
+#pragma unroll
+            for (int q = 0; q < 16; q++) ss = fmaf(xr[jj][q], xr[jj][q], ss);
+            for (int o = 1; o < lanes_per_head; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (c < nchunk_half) {
+                const float r = 1.0f / sqrtf(ss / (float)a.DV + a.eps);
+                const int k0 = 16 * c;                       // offset inside this half
+                const int d0 = (koff + k0) % a.DV;           // position inside the value head
+                const float4* pz = reinterpret_cast<const float4*>(z + k0);
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const float4 t = pz[q];
+                    const float zz[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                    for (int i = 0; i < 4; i++)
+                        xr[jj][4 * q + i] = (bf(a.gn_w[d0 + 4 * q + i]) * (xr[jj][4 * q + i] * r)) * siluf_(zz[i]);
+                }
             }
         }
-    } else {
-        for (int k = threadIdx.x; k < a.K; k += THREADS) xs[k] = in[k];
     }
-    __syncthreads();
-    float xr[MAXC][16];
-    load_slices<MAXC>(xr, xs + half * (a.K >> 1), nchunk_half, lane);
 
     for (; row < row1; row += 4) {
         float acc = 0.f;
@@ -637,6 +680,8 @@ struct ExpertArgs {
     const int8_t* shd_w;          // [D][SH]
     const uint16_t* shd_s;        // [D]
     int SH;
+    float* ypart;                 // [B][topk + 1][D] per-pick down outputs (+ the shared expert's)
+    unsigned int* counter;        // [B][row blocks]
     float* xout;                  // [B][D] residual stream, += result
     int* err;
 };
@@ -645,11 +690,10 @@ struct ExpertArgs {
 // grid (blocks per pick, B * topk).
 template <int MAXC>   // 32-code slices per lane: D <= MAXC * 1024
 __global__ void __launch_bounds__(THREADS, 2) k_expert_gu(const ExpertArgs a) {
-    extern __shared__ float smem[];
-    float* xs = smem;
-    float* red = smem + a.D;
     const int pick = blockIdx.y, b = pick / a.topk;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    grid_dep_launch();
+    grid_dep_wait();              // which expert to read is the previous kernel's result
     const int e = a.top_idx[pick];
     const uint8_t* base = (e >= 0 && e < a.E) ? a.eptr[e] : nullptr;
     if (base == nullptr) {   // not resident here (another rank's expert) or a bad pick
@@ -684,121 +728,166 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_gu(const ExpertArgs a) {
     int i = gw;
     if (i < a.I) issue(i);
 
-    stage_znorm(a.x + (size_t)b * a.D, a.norm_w, a.eps, a.D, xs, red);
+    // this lane's 32-value slices of norm2(x): slice jj is values [32 * (lane + 32 jj), +32)
     float xr[MAXC][32];
     float xsum[MAXC];
+    {
+        const float* xg = a.x + (size_t)b * a.D;
+        float ss = 0.f;
 #pragma unroll
-    for (int jj = 0; jj < MAXC; jj++) {
-        const int c = lane + 32 * jj;
-        xsum[jj] = 0.f;
+        for (int jj = 0; jj < MAXC; jj++) {
+            const int c = lane + 32 * jj;
 #pragma unroll
-        for (int q = 0; q < 32; q++) {
-            xr[jj][q] = c < nchunk ? xs[32 * c + q] : 0.f;
-            xsum[jj] += xr[jj][q];
+            for (int q = 0; q < 8; q++) {
+                float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (c < nchunk) t = reinterpret_cast<const float4*>(xg + 32 * c)[q];
+                xr[jj][4 * q] = t.x; xr[jj][4 * q + 1] = t.y; xr[jj][4 * q + 2] = t.z; xr[jj][4 * q + 3] = t.w;
+                ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
+            }
+        }
+        float r = 1.0f;
+        if (a.norm_w) {
+            ss = warp_sum(ss);
+            r = 1.0f / sqrtf(ss / (float)a.D + a.eps);
+        }
+#pragma unroll
+        for (int jj = 0; jj < MAXC; jj++) {
+            const int c = lane + 32 * jj;
+            xsum[jj] = 0.f;
+            if (a.norm_w && c < nchunk) {
+                const uint4* pw = reinterpret_cast<const uint4*>(a.norm_w + 32 * c);
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    const uint4 t = pw[q];
+                    const uint32_t u[4] = {t.x, t.y, t.z, t.w};
+#pragma unroll
+                    for (int n = 0; n < 4; n++) {
+                        xr[jj][8 * q + 2 * n] = xr[jj][8 * q + 2 * n] * r * (1.0f + bflo(u[n]));
+                        xr[jj][8 * q + 2 * n + 1] = xr[jj][8 * q + 2 * n + 1] * r * (1.0f + bfhi(u[n]));
+                    }
+                }
+            }
+#pragma unroll
+            for (int q = 0; q < 32; q++) xsum[jj] += xr[jj][q];
         }
     }
     for (; i < a.I; i += TW) {
         float ag = 0.f, au = 0.f;
 #pragma unroll
         for (int jj = 0; jj < MAXC; jj++) {
-            const float cg = dot32_q4(wg[jj], &xr[jj][0]);
-            const float cu = dot32_q4(wu[jj], &xr[jj][0]);
-            ag += h2f(sg_[jj]) * cg + h2f(mg_[jj]) * xsum[jj];
-            au += h2f(su_[jj]) * cu + h2f(mu_[jj]) * xsum[jj];
+            // sum code * x = 16 * (sum f * x - sum x), f = 1 + code / 16
+            const float fg = dot32_q4f(wg[jj], &xr[jj][0]);
+            const float fu = dot32_q4f(wu[jj], &xr[jj][0]);
+            ag += h2f(sg_[jj]) * (16.0f * (fg - xsum[jj])) + h2f(mg_[jj]) * xsum[jj];
+            au += h2f(su_[jj]) * (16.0f * (fu - xsum[jj])) + h2f(mu_[jj]) * xsum[jj];
         }
+        const int done = i;
         if (i + TW < a.I) issue(i + TW);
         ag = warp_sum(ag);
         au = warp_sum(au);
-        if (lane == 0) a.act[(size_t)pick * a.I + i] = siluf_(ag) * au;
+        if (lane == 0) a.act[(size_t)pick * a.I + done] = siluf_(ag) * au;
     }
 }
 
-// x[b][o] += sum_r w_r * (down_r[o] . act_r)  +  sigmoid(shared_gate) * (shared_down[o] . shared_act)
-// The picks are summed in rank order, so the result does not depend on scheduling. One warp per
-// output row; a half-warp covers one pick's row (I/2 bytes = up to 16 slices of 32 codes).
-// grid (blocks, B). Needs I <= 512 and SH <= 512.
+// The down projections. grid (row blocks, topk + 1, B): blockIdx.y < topk computes one pick's
+//   ypart[r][o] = down_r[o] . act_r        (4-bit rows, a half-warp per row, act_r in registers)
+// and blockIdx.y == topk the shared expert's  ypart[topk][o] = scale[o] * (shared_down[o] . shared_act).
+// The block that finishes a row block last adds, in rank order so that the result does not depend
+// on scheduling,   x[o] += sum_r w_r * ypart[r][o] + sigmoid(shared_gate) * ypart[topk][o].
+// Needs I <= 512 and SH <= 512.
+constexpr int DOWN_ROWS = 64;     // output rows per block
 __global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) {
-    extern __shared__ float smem[];
-    float* acts = smem;                          // [topk][I]
-    float* shs = smem + a.topk * a.I;            // [SH]
-    __shared__ const uint8_t* s_base[8];
-    __shared__ float s_w[8];
-    const int b = blockIdx.y;
+    const int rb = blockIdx.x, r = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (threadIdx.x < 8) {
-        const int r = threadIdx.x;
-        const uint8_t* p = nullptr;
-        float w = 0.f;
-        if (r < a.topk) {
-            const int e = a.top_idx[b * a.topk + r];
-            if (e >= 0 && e < a.E) p = a.eptr[e];
-            w = a.top_w[b * a.topk + r];
+    const int row0 = rb * DOWN_ROWS, row1 = min(a.D, row0 + DOWN_ROWS);
+    __shared__ int s_last;
+    grid_dep_launch();
+    float* yp = a.ypart + ((size_t)b * (a.topk + 1) + r) * a.D;
+    if (r == a.topk) {
+        // shared expert: int8 rows of SH values, one warp per row
+        const int shchunk = a.SH >> 4;
+        int4 w = make_int4(0, 0, 0, 0);
+        int o = row0 + warp;
+        if (o < row1 && lane < shchunk) w = ldw(a.shd_w + (size_t)o * a.SH + (size_t)lane * 16);
+        grid_dep_wait();
+        float shx[16];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (lane < shchunk) t = reinterpret_cast<const float4*>(a.sh_act + (size_t)b * a.SH + 16 * lane)[q];
+            shx[4 * q] = t.x; shx[4 * q + 1] = t.y; shx[4 * q + 2] = t.z; shx[4 * q + 3] = t.w;
         }
-        s_base[r] = p;
-        s_w[r] = w;
+        for (; o < row1; o += WARPS) {
+            float d = dot16_i8(w, shx);
+            const int done = o;
+            if (o + WARPS < row1 && lane < shchunk) w = ldw(a.shd_w + (size_t)(o + WARPS) * a.SH + (size_t)lane * 16);
+            d = warp_sum(d);
+            if (lane == 0) yp[done] = bf(a.shd_s[done]) * d;
+        }
+    } else {
+        grid_dep_wait();
+        const int e = a.top_idx[b * a.topk + r];
+        const uint8_t* base = (e >= 0 && e < a.E) ? a.eptr[e] : nullptr;
+        const int nchunk = a.I >> 5;                  // 32-code slices per row (<= 16)
+        const int ngroup = a.I >> 6;
+        const int hw = lane >> 4, hl = lane & 15;
+        if (base != nullptr) {
+            const uint8_t* q4 = base + a.off_dn_q;
+            const uint16_t* ds = (const uint16_t*)(base + a.off_dn_s);
+            const uint16_t* dm = (const uint16_t*)(base + a.off_dn_m);
+            int4 w = make_int4(0, 0, 0, 0);
+            uint16_t sc = 0, mn = 0;
+            auto issue = [&](int o) {
+                if (o < row1 && hl < nchunk) {
+                    w = ldw(q4 + (size_t)o * (a.I >> 1) + (size_t)hl * 16);
+                    sc = ds[(size_t)o * ngroup + (hl >> 1)];
+                    mn = dm[(size_t)o * ngroup + (hl >> 1)];
+                } else { w = make_int4(0, 0, 0, 0); sc = 0; mn = 0; }
+            };
+            int o = row0 + 2 * warp + hw;             // a warp covers two rows at a time
+            issue(o);
+            float xv[32];
+            float xsum = 0.f;
+            const float* ar = a.act + ((size_t)b * a.topk + r) * a.I + 32 * hl;
+#pragma unroll
+            for (int q = 0; q < 8; q++) {
+                float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (hl < nchunk) t = reinterpret_cast<const float4*>(ar)[q];
+                xv[4 * q] = t.x; xv[4 * q + 1] = t.y; xv[4 * q + 2] = t.z; xv[4 * q + 3] = t.w;
+                xsum += t.x + t.y + t.z + t.w;
+            }
+            for (; o - hw < row1; o += 2 * WARPS) {
+                const float f = dot32_q4f(w, xv);
+                float d = h2f(sc) * (16.0f * (f - xsum)) + h2f(mn) * xsum;
+                const int done = o;
+                issue(o + 2 * WARPS);
+#pragma unroll
+                for (int off = 8; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
+                if (hl == 0 && done < row1) yp[done] = d;
+            }
+        } else {
+            if (e < 0 || e >= a.E) { if (threadIdx.x == 0) atomicExch(a.err, 2); }
+            for (int o = row0 + threadIdx.x; o < row1; o += THREADS) yp[o] = 0.f;   // another rank's expert
+        }
     }
-    for (int k = threadIdx.x; k < a.topk * a.I; k += THREADS) acts[k] = a.act[(size_t)b * a.topk * a.I + k];
-    for (int k = threadIdx.x; k < a.SH; k += THREADS) shs[k] = a.sh_act[(size_t)b * a.SH + k];
+    // last block of this (sequence, row block): weighted sum in rank order, into the residual stream
+    __threadfence();
     __syncthreads();
-    const int nchunk = a.I >> 5;                  // slices per expert row (<= 16)
-    const int ngroup = a.I >> 6;
-    const int hw = lane >> 4, hl = lane & 15;
-    const int shchunk = a.SH >> 4;                // 16-value int8 slices of the shared row (<= 32)
-    float shx[16];
-#pragma unroll
-    for (int q = 0; q < 16; q++) shx[q] = lane < shchunk ? shs[16 * lane + q] : 0.f;
-    const float sgate = a.sg ? a.sg[b] : 0.f;
-    const int gw = blockIdx.x * WARPS + warp, TW = gridDim.x * WARPS;
-    for (int o = gw; o < a.D; o += TW) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};   // picks hw, hw+2, hw+4, hw+6
-        int4 w[4];
-#pragma unroll
-        for (int it = 0; it < 4; it++) {
-            const int r = 2 * it + hw;
-            w[it] = make_int4(0, 0, 0, 0);
-            if (r < a.topk && s_base[r] != nullptr && hl < nchunk)
-                w[it] = ldw(s_base[r] + a.off_dn_q + (size_t)o * (a.I >> 1) + (size_t)hl * 16);
-        }
-        int4 wsh = make_int4(0, 0, 0, 0);
-        if (a.shd_w && lane < shchunk) wsh = ldw(a.shd_w + (size_t)o * a.SH + (size_t)lane * 16);
-#pragma unroll
-        for (int it = 0; it < 4; it++) {
-            const int r = 2 * it + hw;
-            if (r < a.topk && s_base[r] != nullptr && hl < nchunk) {
-                const float* ar = acts + r * a.I + 32 * hl;
-                float xv[32];
-                float xsum = 0.f;
-#pragma unroll
-                for (int q = 0; q < 32; q++) { xv[q] = ar[q]; xsum += xv[q]; }
-                const float cs = dot32_q4(w[it], xv);
-                const uint16_t* ds = (const uint16_t*)(s_base[r] + a.off_dn_s);
-                const uint16_t* dm = (const uint16_t*)(s_base[r] + a.off_dn_m);
-                const int g = hl >> 1;
-                acc[it] = h2f(ds[(size_t)o * ngroup + g]) * cs + h2f(dm[(size_t)o * ngroup + g]) * xsum;
-            }
-        }
-        float shd = dot16_i8(wsh, shx);
-        // reduce each pick over its half-warp, the shared row over the warp
-#pragma unroll
-        for (int it = 0; it < 4; it++) {
-#pragma unroll
-            for (int off = 8; off > 0; off >>= 1) acc[it] += __shfl_xor_sync(0xffffffffu, acc[it], off);
-        }
-        shd = warp_sum(shd);
-        float other[4];
-#pragma unroll
-        for (int it = 0; it < 4; it++) other[it] = __shfl_xor_sync(0xffffffffu, acc[it], 16);
-        if (lane == 0) {
-            float y = 0.f;
-#pragma unroll
-            for (int it = 0; it < 4; it++) {   // rank order 0, 1, 2, ... (lane 0 holds the even ranks)
-                if (2 * it < a.topk) y = fmaf(s_w[2 * it], acc[it], y);
-                if (2 * it + 1 < a.topk) y = fmaf(s_w[2 * it + 1], other[it], y);
-            }
-            if (a.shd_w) y = fmaf(sgate, bf(a.shd_s[o]) * shd, y);
-            a.xout[(size_t)b * a.D + o] += y;
-        }
+    if (threadIdx.x == 0) {
+        const unsigned int n = atomicAdd(a.counter + (size_t)b * gridDim.x + rb, 1u);
+        s_last = (n == (unsigned int)a.topk);
     }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    for (int o = row0 + threadIdx.x; o < row1; o += THREADS) {
+        const float* base = a.ypart + (size_t)b * (a.topk + 1) * a.D + o;
+        float y = 0.f;
+        for (int k = 0; k < a.topk; k++) y = fmaf(a.top_w[b * a.topk + k], __ldcg(base + (size_t)k * a.D), y);
+        if (a.shd_w) y = fmaf(a.sg[b], __ldcg(base + (size_t)a.topk * a.D), y);
+        a.xout[(size_t)b * a.D + o] += y;
+    }
+    if (threadIdx.x == 0) a.counter[(size_t)b * gridDim.x + rb] = 0;
 }
 
 // N consecutive cache values (bf16 or fp32) starting at a 4*N- or 2*N-byte aligned address -> fp32.
@@ -838,8 +927,9 @@ __device__ __forceinline__ void load_kv(const void* base, size_t elem, float (&o
 // heads of the group (so a key/value row is read once, not once per query head as in hybrid.cu:121-173).
 // Prologue: per-head zero-centred RMSNorm of q and of the new k, partial RoPE (rotate-half on the
 // first RD dims, aegist/hybrid.py:160-166, angles from a host-built table), and the block that owns
-// the newest position appends k, v to the cache. Each block leaves (max, sum, acc) per query head;
-// the last block of the (sequence, KV head) merges the slices and applies sigmoid(gate).
+// the newest position appends k, v to the cache. Each warp walks its positions four at a time with
+// all eight row loads in flight. A block leaves (acc, max, sum) per query head in scratch memory;
+// k_attn_merge combines the slices and applies sigmoid(gate).
 struct AttnArgs {
     const float* qraw;        // [B][H][2*HD]  (query | gate) per head
     const float* kraw;        // [B][KV][HD]
@@ -855,11 +945,12 @@ struct AttnArgs {
     int pages_per_seq;
     int H, KV, RD;
     float eps, scale;
-    float* part;              // [B][KV][nsplit][G][HD + 2]
-    unsigned int* counter;    // [B][KV]
+    float* part;              // [B][KV][nsplit][G][HD + 2]  scratch
     float* out;               // [B][H*HD]
     int nsplit;
 };
+
+constexpr int ATT_PPW = 4;    // positions a warp loads at once
 
 template <int HD, bool KVF32>
 __global__ void __launch_bounds__(THREADS) k_attn(const AttnArgs a) {
@@ -868,19 +959,26 @@ __global__ void __launch_bounds__(THREADS) k_attn(const AttnArgs a) {
     const int G = a.H / a.KV;                 // query heads per KV head (<= 8)
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    grid_dep_launch();
+    grid_dep_wait();
     const int pos = a.pos[b];
     const int L = pos + 1;
     int chunk = (L + a.nsplit - 1) / a.nsplit;
-    chunk = (chunk + WARPS - 1) / WARPS * WARPS;
+    chunk = (chunk + WARPS * ATT_PPW - 1) / (WARPS * ATT_PPW) * (WARPS * ATT_PPW);
     const int p0 = split * chunk, p1 = min(L, p0 + chunk);
+    const size_t pstride = HD + 2;
+    float* part = a.part + (((size_t)b * a.KV + kvh) * a.nsplit + split) * G * pstride;
+    if (p0 >= p1) {                           // an empty slice: say so and leave
+        for (int g = threadIdx.x; g < G; g += THREADS) { part[g * pstride + HD] = -INFINITY; part[g * pstride + HD + 1] = 0.f; }
+        return;
+    }
 
     __shared__ float qs[MAXG][HD];
     __shared__ float knew[HD], vnew[HD];
     __shared__ float m_s[WARPS][MAXG], l_s[WARPS][MAXG];
-    __shared__ int s_last;
     extern __shared__ float accs[];            // [WARPS][G][HD]
 
-    // prologue: warps 0..G-1 prepare the query heads, warp G (mod 8) the new key and value
+    // prologue: warps 0..G-1 prepare the query heads, the next one the new key and value
     const float* cs = a.rope_cos + (size_t)pos * (a.RD / 2);
     const float* sn = a.rope_sin + (size_t)pos * (a.RD / 2);
     for (int t = warp; t < G + 1; t += WARPS) {
@@ -939,31 +1037,45 @@ __global__ void __launch_bounds__(THREADS) k_attn(const AttnArgs a) {
         for (int i = 0; i < DPL; i++) acc[g][i] = 0.f;
     }
     // each lane owns DPL consecutive dims of a row: one 16-byte (bf16, HD 256) load per key
-    for (int p = p0 + warp; p < p1; p += WARPS) {
-        float kk[DPL], vv[DPL];
-        if (p == pos) {
+    const int per_warp = chunk / WARPS;
+    const int w0 = p0 + warp * per_warp, w1 = min(p1, w0 + per_warp);
+    for (int pb = w0; pb < w1; pb += ATT_PPW) {
+        float kk[ATT_PPW][DPL], vv[ATT_PPW][DPL];
 #pragma unroll
-            for (int i = 0; i < DPL; i++) { kk[i] = knew[lane * DPL + i]; vv[i] = vnew[lane * DPL + i]; }
-        } else {
-            const int page = a.page_table[(size_t)b * a.pages_per_seq + p / KV_PAGE];
-            const size_t off = (((size_t)page * a.KV + kvh) * KV_PAGE + p % KV_PAGE) * HD + lane * DPL;
-            load_kv<DPL, KVF32>(a.kpool, off, kk);
-            load_kv<DPL, KVF32>(a.vpool, off, vv);
+        for (int u = 0; u < ATT_PPW; u++) {
+            const int p = pb + u;
+            if (p < w1 && p != pos) {
+                const int page = a.page_table[(size_t)b * a.pages_per_seq + p / KV_PAGE];
+                const size_t off = (((size_t)page * a.KV + kvh) * KV_PAGE + p % KV_PAGE) * HD + lane * DPL;
+                load_kv<DPL, KVF32>(a.kpool, off, kk[u]);
+                load_kv<DPL, KVF32>(a.vpool, off, vv[u]);
+            } else {
+#pragma unroll
+                for (int i = 0; i < DPL; i++) {
+                    kk[u][i] = p == pos ? knew[lane * DPL + i] : 0.f;
+                    vv[u][i] = p == pos ? vnew[lane * DPL + i] : 0.f;
+                }
+            }
         }
 #pragma unroll
-        for (int g = 0; g < MAXG; g++) {
-            if (g < G) {
-                float s = 0.f;
+        for (int u = 0; u < ATT_PPW; u++) {
+            if (pb + u < w1) {
 #pragma unroll
-                for (int i = 0; i < DPL; i++) s = fmaf(q[g][i], kk[i], s);
-                s = warp_sum(s);
-                const float mn = fmaxf(m[g], s);
-                const float corr = expf(m[g] - mn);
-                const float pe = expf(s - mn);
-                l[g] = l[g] * corr + pe;
+                for (int g = 0; g < MAXG; g++) {
+                    if (g < G) {
+                        float s = 0.f;
 #pragma unroll
-                for (int i = 0; i < DPL; i++) acc[g][i] = fmaf(pe, vv[i], acc[g][i] * corr);
-                m[g] = mn;
+                        for (int i = 0; i < DPL; i++) s = fmaf(q[g][i], kk[u][i], s);
+                        s = warp_sum(s);
+                        const float mn = fmaxf(m[g], s);
+                        const float corr = expf(m[g] - mn);
+                        const float pe = expf(s - mn);
+                        l[g] = l[g] * corr + pe;
+#pragma unroll
+                        for (int i = 0; i < DPL; i++) acc[g][i] = fmaf(pe, vv[u][i], acc[g][i] * corr);
+                        m[g] = mn;
+                    }
+                }
             }
         }
     }
@@ -977,59 +1089,78 @@ __global__ void __launch_bounds__(THREADS) k_attn(const AttnArgs a) {
         }
     }
     __syncthreads();
-    const size_t pstride = HD + 2;
-    float* part = a.part + (((size_t)b * a.KV + kvh) * a.nsplit + split) * G * pstride;
     for (int g = 0; g < G; g++) {
         float mx = -INFINITY;
 #pragma unroll
         for (int w = 0; w < WARPS; w++) mx = fmaxf(mx, m_s[w][g]);
-        float lsum = 0.f;
+        float cw[WARPS];
+#pragma unroll
+        for (int w = 0; w < WARPS; w++) cw[w] = m_s[w][g] == -INFINITY ? 0.f : expf(m_s[w][g] - mx);
         for (int d = threadIdx.x; d < HD; d += THREADS) {
             float s = 0.f;
 #pragma unroll
-            for (int w = 0; w < WARPS; w++) {
-                const float c = m_s[w][g] == -INFINITY ? 0.f : expf(m_s[w][g] - mx);
-                s = fmaf(accs[((size_t)w * G + g) * HD + d], c, s);
-            }
+            for (int w = 0; w < WARPS; w++) s = fmaf(accs[((size_t)w * G + g) * HD + d], cw[w], s);
             part[g * pstride + d] = s;
         }
         if (threadIdx.x == 0) {
+            float lsum = 0.f;
 #pragma unroll
-            for (int w = 0; w < WARPS; w++) lsum += m_s[w][g] == -INFINITY ? 0.f : l_s[w][g] * expf(m_s[w][g] - mx);
+            for (int w = 0; w < WARPS; w++) lsum += l_s[w][g] * cw[w];
             part[g * pstride + HD] = mx;
             part[g * pstride + HD + 1] = lsum;
         }
     }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned int n = atomicAdd(a.counter + b * a.KV + kvh, 1u);
-        s_last = (n == gridDim.x - 1);
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    const float* pb = a.part + (((size_t)b * a.KV + kvh) * a.nsplit) * G * pstride;
-    for (int g = 0; g < G; g++) {
+}
+
+// out[b][head][d] = (sum_s acc_s[d] * e^(m_s - m)) / (sum_s l_s * e^(m_s - m)) * sigmoid(gate[d]).
+// grid (H, B), one thread per dim (strided when HD > blockDim).
+__global__ void __launch_bounds__(THREADS) k_attn_merge(const AttnArgs a, int HD) {
+    const int head = blockIdx.x, b = blockIdx.y;
+    const int G = a.H / a.KV, kvh = head / G, g = head % G;
+    __shared__ float sc[64];
+    __shared__ float s_inv;
+    grid_dep_launch();
+    grid_dep_wait();
+    const size_t pstride = HD + 2;
+    const float* pb = a.part + (((size_t)b * a.KV + kvh) * a.nsplit) * G * pstride + (size_t)g * pstride;
+    const size_t sstride = (size_t)G * pstride;
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float ms[2], ls[2];
         float mx = -INFINITY;
-        for (int s = 0; s < a.nsplit; s++) mx = fmaxf(mx, __ldcg(pb + ((size_t)s * G + g) * pstride + HD));
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const int s = lane + 32 * u;
+            ms[u] = s < a.nsplit ? pb[s * sstride + HD] : -INFINITY;
+            ls[u] = s < a.nsplit ? pb[s * sstride + HD + 1] : 0.f;
+            mx = fmaxf(mx, ms[u]);
+        }
+        mx = warp_max(mx);
         float lsum = 0.f;
-        for (int s = 0; s < a.nsplit; s++) {
-            const float ms = __ldcg(pb + ((size_t)s * G + g) * pstride + HD);
-            if (ms != -INFINITY) lsum += __ldcg(pb + ((size_t)s * G + g) * pstride + HD + 1) * expf(ms - mx);
+#pragma unroll
+        for (int u = 0; u < 2; u++) {
+            const float c = ms[u] == -INFINITY ? 0.f : expf(ms[u] - mx);
+            if (lane + 32 * u < 64) sc[lane + 32 * u] = c;
+            lsum += ls[u] * c;
         }
-        const int head = kvh * G + g;
-        for (int d = threadIdx.x; d < HD; d += THREADS) {
-            float s_acc = 0.f;
-            for (int s = 0; s < a.nsplit; s++) {
-                const float ms = __ldcg(pb + ((size_t)s * G + g) * pstride + HD);
-                if (ms != -INFINITY) s_acc = fmaf(__ldcg(pb + ((size_t)s * G + g) * pstride + d), expf(ms - mx), s_acc);
-            }
-            const float gate = a.qraw[((size_t)b * a.H + head) * 2 * HD + HD + d];
-            a.out[(size_t)b * a.H * HD + head * HD + d] = (s_acc / lsum) * sigmoidf_(gate);
-        }
+        lsum = warp_sum(lsum);
+        if (lane == 0) s_inv = 1.0f / lsum;
     }
-    if (threadIdx.x == 0) a.counter[b * a.KV + kvh] = 0;
+    __syncthreads();
+    for (int d = threadIdx.x; d < HD; d += THREADS) {
+        float acc = 0.f;
+        int s = 0;
+        for (; s + 8 <= a.nsplit; s += 8) {
+            float v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) v[u] = sc[s + u] != 0.f ? pb[(s + u) * sstride + d] : 0.f;
+#pragma unroll
+            for (int u = 0; u < 8; u++) acc = fmaf(v[u], sc[s + u], acc);
+        }
+        for (; s < a.nsplit; s++) if (sc[s] != 0.f) acc = fmaf(pb[s * sstride + d], sc[s], acc);
+        const float gate = a.qraw[((size_t)b * a.H + head) * 2 * HD + HD + d];
+        a.out[(size_t)b * a.H * HD + head * HD + d] = (acc * s_inv) * sigmoidf_(gate);
+    }
 }
 
 // ------------------------------------------------------------------------------------------

@@ -31,6 +31,8 @@ struct b2_moe {
     float *h = nullptr, *y = nullptr, *rlogits = nullptr, *sh_act = nullptr, *sgate = nullptr, *act = nullptr, *top_w = nullptr;
     int *top_idx = nullptr, *err = nullptr;
     unsigned int* counter = nullptr;
+    float* ypart = nullptr;
+    unsigned int* dcounter = nullptr;
     cudaStream_t st = nullptr;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
 };
@@ -101,6 +103,8 @@ int b2_moe_create(int device, const b2_moe_weights* w, int max_tokens, b2_moe** 
     OPCU(dalloc(&m->sh_act, (size_t)T * c.SH)); OPCU(dalloc(&m->sgate, T)); OPCU(dalloc(&m->act, (size_t)T * c.TOPK * c.I));
     OPCU(dalloc(&m->top_w, (size_t)T * c.TOPK)); OPCU(dalloc(&m->top_idx, (size_t)T * c.TOPK)); OPCU(dalloc(&m->err, 1));
     OPCU(dalloc(&m->counter, T));
+    OPCU(dalloc(&m->ypart, (size_t)T * (c.TOPK + 1) * c.D));
+    OPCU(dalloc(&m->dcounter, (size_t)T * down_row_blocks(c.D)));
     OPCU(cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking));
     OPCU(cudaEventCreate(&m->e0)); OPCU(cudaEventCreate(&m->e1));
     return 0;
@@ -127,6 +131,7 @@ int b2_moe_forward(b2_moe* m, const float* h, int tokens, float* y, int32_t* idx
     x.off_gu_s = c.off_gu_s(); x.off_gu_m = c.off_gu_m(); x.off_dn_q = c.off_dn_q(); x.off_dn_s = c.off_dn_s(); x.off_dn_m = c.off_dn_m();
     x.x = m->h; x.norm_w = nullptr; x.act = m->act; x.sh_act = m->sh_act; x.sg = m->sgate;
     x.shd_w = m->sd_q; x.shd_s = m->sd_s; x.SH = c.SH; x.xout = m->y; x.err = m->err;
+    x.ypart = m->ypart; x.counter = m->dcounter;
     launch_experts(x, tokens, m->nsm, m->st);
     OPCU(cudaEventRecord(m->e1, m->st));
     OPCU(cudaGetLastError());
@@ -142,7 +147,7 @@ void b2_moe_destroy(b2_moe* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     void* bufs[] = {m->router, m->sg_s, m->su_s, m->sd_s, m->shared_gate, m->experts, m->sg_q, m->su_q, m->sd_q, (void*)m->eptr, m->h, m->y,
-                    m->rlogits, m->sh_act, m->sgate, m->act, m->top_w, m->top_idx, m->err, m->counter};
+                    m->rlogits, m->sh_act, m->sgate, m->act, m->top_w, m->top_idx, m->err, m->counter, m->ypart, m->dcounter};
     for (void* p : bufs) cudaFree(p);
     if (m->e0) cudaEventDestroy(m->e0);
     if (m->e1) cudaEventDestroy(m->e1);
