@@ -91,6 +91,8 @@ static size_t dtype_size(const std::string& d) {
     return 0;
 }
 
+// Blocks per SM of the streaming GEMV kernel (B2_GEMV_CTAS overrides; for experiments).
+static int g_gemv_ctas_per_sm = [] { const char* v = getenv("B2_GEMV_CTAS"); return v ? atoi(v) : 2; }();
 static int down_row_blocks(int D) { return (D + DOWN_ROWS - 1) / DOWN_ROWS; }
 
 }  // namespace b2
@@ -429,7 +431,7 @@ int b2_engine::finish() {
     CU(dalloc(&rlogits, (size_t)B * c.E)); CU(dalloc(&sh_act, (size_t)B * c.SH)); CU(dalloc(&sgate, B));
     CU(dalloc(&act, (size_t)B * c.TOPK * c.I)); CU(dalloc(&logits, (size_t)B * c.V));
     CU(dalloc(&top_idx, (size_t)c.L * B * c.TOPK)); CU(dalloc(&top_w, (size_t)c.L * B * c.TOPK));
-    head_grid = std::min((c.V / 2 + WARPS - 1) / WARPS, 2 * nsm);
+    head_grid = std::min((c.V + 7) / 8, g_gemv_ctas_per_sm * nsm);
     CU(dalloc(&part_val, (size_t)B * head_grid)); CU(dalloc(&part_idx, (size_t)B * head_grid));
     // attention: enough slices to fill the GPU, but at least 64 positions each at full context
     nsplit = std::max(1, std::min({64, (2 * nsm) / std::max(1, c.KV * B), (cap + 63) / 64}));
@@ -475,19 +477,23 @@ static cudaError_t opt_in_smem(F* f, size_t bytes) {
     return cudaFuncSetAttribute((const void*)f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
 
-static void launch_gemv(const GemvArgs& a, int B, int nsm, cudaStream_t st, int grid_override = 0) {
-    const int grid = grid_override ? grid_override : std::max(1, std::min((a.total_jobs + WARPS - 1) / WARPS, 2 * nsm));
+static cudaError_t launch_gemv(const GemvArgs& a, int B, int nsm, cudaStream_t st, int grid_override = 0) {
+    // one block per SM (the ring of one block is 96 KB, so the next kernel of the stream fits beside it)
+    const int grid = grid_override ? grid_override : std::max(1, std::min(a.total_jobs, g_gemv_ctas_per_sm * nsm));
+    const size_t smem = (size_t)RING_STAGES * RING_STAGE_BYTES;
     const int maxc = (a.K + 511) / 512;
     dim3 g(grid, B);
-    if (maxc <= 1) launch_k(k_gemv_norm<1>, g, THREADS, 0, st, a);
-    else if (maxc == 2) launch_k(k_gemv_norm<2>, g, THREADS, 0, st, a);
-    else launch_k(k_gemv_norm<4>, g, THREADS, 0, st, a);
+    cudaError_t e;
+    if (maxc <= 1) { e = opt_in_smem(k_gemv_norm<1>, smem); if (e == cudaSuccess) e = launch_k(k_gemv_norm<1>, g, GEMV_THREADS, smem, st, a); }
+    else if (maxc == 2) { e = opt_in_smem(k_gemv_norm<2>, smem); if (e == cudaSuccess) e = launch_k(k_gemv_norm<2>, g, GEMV_THREADS, smem, st, a); }
+    else { e = opt_in_smem(k_gemv_norm<4>, smem); if (e == cudaSuccess) e = launch_k(k_gemv_norm<4>, g, GEMV_THREADS, smem, st, a); }
+    return e;
 }
 
 static Seg make_seg(int kind, const void* w, const uint16_t* s, int rows, float* out, int out_stride) {
     Seg g{};
     g.w = w; g.s = s; g.rows = rows; g.kind = kind; g.out = out; g.out_stride = out_stride;
-    g.jobs = (kind == SEG_I8 || kind == SEG_I8_CONV || kind == SEG_I8_ARGMAX) ? (rows + 1) / 2 : rows;
+    g.jobs = (kind == SEG_I8 || kind == SEG_I8_CONV || kind == SEG_I8_ARGMAX || kind == SEG_I8_SILU) ? (rows + 7) / 8 : (rows + 3) / 4;
     return g;
 }
 static void seal(GemvArgs& a) {
@@ -560,7 +566,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.seg[1] = make_seg(SEG_I8, l.k.w, l.k.s, l.k.n, kraw, c.KV * c.HD);
             a.seg[2] = make_seg(SEG_I8, l.v.w, l.v.s, l.v.n, vraw, c.KV * c.HD);
             a.nseg = 3; seal(a);
-            a.x = x; a.norm_w = l.norm1; a.eps = c.eps; a.K = c.D;
+            a.x = x; a.norm_w = l.norm1; a.eps = c.eps; a.K = c.D; a.err = d_err;
             launch_gemv(a, B, nsm, st);
             mark(1, st);
             AttnArgs t{};
@@ -579,11 +585,11 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
         } else {
             GemvArgs a{};
             a.seg[0] = make_seg(SEG_I8_CONV, l.in_qkv.w, l.in_qkv.s, l.in_qkv.n, big, c.C());
-            a.seg[1] = make_seg(SEG_I8, l.in_z.w, l.in_z.s, l.in_z.n, zbuf, c.VD());
+            a.seg[1] = make_seg(SEG_I8_SILU, l.in_z.w, l.in_z.s, l.in_z.n, zbuf, c.VD());
             a.seg[2] = make_seg(SEG_BF_SIGMOID, l.in_b, nullptr, c.HV, beta, c.HV);
             a.seg[3] = make_seg(SEG_BF_DECAY, l.in_a, nullptr, c.HV, gdec, c.HV);
             a.nseg = 4; seal(a);
-            a.x = x; a.norm_w = l.norm1; a.eps = c.eps; a.K = c.D;
+            a.x = x; a.norm_w = l.norm1; a.eps = c.eps; a.K = c.D; a.err = d_err;
             a.conv_w = l.conv; a.conv_state = conv + (size_t)l.slot * B * c.C() * 3;
             a.a_log = l.a_log; a.dt_bias = l.dt_bias;
             launch_gemv(a, B, nsm, st);
@@ -608,7 +614,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.seg[1].w2 = l.sh_up.w; a.seg[1].s2 = l.sh_up.s;
             a.seg[2] = make_seg(SEG_BF_SIGMOID, l.sh_gw, nullptr, 1, sgate, 1);
             a.nseg = 3; seal(a);
-            a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D;
+            a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D; a.err = d_err;
             a.finisher = FIN_TOPK; a.counter = d_counter; a.E = c.E; a.topk = c.TOPK;
             a.top_idx = top_idx + (size_t)li * B * c.TOPK; a.top_w = top_w + (size_t)li * B * c.TOPK;
             launch_gemv(a, B, nsm, st);
@@ -630,7 +636,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
         GemvArgs a{};
         a.seg[0] = make_seg(SEG_I8_ARGMAX, lm_head.w, lm_head.s, c.V, logits, c.V);
         a.nseg = 1; seal(a);
-        a.x = x; a.norm_w = norm; a.eps = c.eps; a.K = c.D;
+        a.x = x; a.norm_w = norm; a.eps = c.eps; a.K = c.D; a.err = d_err;
         a.finisher = FIN_ARGMAX; a.counter = d_counter; a.part_val = part_val; a.part_idx = part_idx;
         a.next_tok = d_next; a.pos = d_pos;
         launch_gemv(a, B, nsm, st, head_grid);
@@ -666,6 +672,7 @@ int b2_engine::check_device_error() {
         cudaMemsetAsync(d_err, 0, 4, stream);
         cudaStreamSynchronize(stream);
         if (h == 1) return fail("a token id is outside the vocabulary (%d)", c.V);
+        if (h == 3) return fail("a bulk copy into shared memory did not complete (bounded wait gave up)");
         return fail("router returned an expert outside 0..%d", c.E - 1);
     }
     return 0;

@@ -88,17 +88,17 @@ __device__ __forceinline__ int4 ldw(const void* p) { return __ldcs(reinterpret_c
 // Four int8 -> fp32 without conversion instructions: flip the sign bit (q + 128 in 0..255), drop the
 // byte into the low mantissa of 2^23 with a byte permute, subtract 2^23 + 128. Exact.
 __device__ __forceinline__ float dot16_i8(const int4& w, const float* x) {
-    float a = 0.f;
+    float a[4];
     const int v[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-    for (int i = 0; i < 4; i++) {
+    for (int i = 0; i < 4; i++) {       // four independent chains: a lone FMA chain is latency-bound
         const uint32_t u = (uint32_t)v[i] ^ 0x80808080u;
-        a = fmaf(x[4 * i + 0], __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f, a);
-        a = fmaf(x[4 * i + 1], __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f, a);
-        a = fmaf(x[4 * i + 2], __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f, a);
-        a = fmaf(x[4 * i + 3], __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f, a);
+        a[i] = x[4 * i + 0] * (__uint_as_float(__byte_perm(u, 0x4B000000u, 0x7650)) - 8388736.0f);
+        a[i] = fmaf(x[4 * i + 1], __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7651)) - 8388736.0f, a[i]);
+        a[i] = fmaf(x[4 * i + 2], __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7652)) - 8388736.0f, a[i]);
+        a[i] = fmaf(x[4 * i + 3], __uint_as_float(__byte_perm(u, 0x4B000000u, 0x7653)) - 8388736.0f, a[i]);
     }
-    return a;
+    return (a[0] + a[1]) + (a[2] + a[3]);
 }
 __device__ __forceinline__ float dot8_bf16(const int4& w, const float* x) {
     float a = 0.f;
@@ -114,7 +114,7 @@ __device__ __forceinline__ float dot8_bf16(const int4& w, const float* x) {
 // the top four mantissa bits of 1.0 (a shift and one logic op), giving f = 1 + code/16 exactly; the
 // function returns sum f * x, and the caller recovers sum code * x = 16 * (result - sum x).
 __device__ __forceinline__ float dot32_q4f(const int4& w, const float* x) {
-    float a = 0.f;
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
     const uint32_t v[4] = {(uint32_t)w.x, (uint32_t)w.y, (uint32_t)w.z, (uint32_t)w.w};
 #pragma unroll
     for (int i = 0; i < 4; i++) {
@@ -122,10 +122,10 @@ __device__ __forceinline__ float dot32_q4f(const int4& w, const float* x) {
         for (int n = 0; n < 8; n++) {
             const int sh = 19 - 4 * n;
             const uint32_t t = sh >= 0 ? (v[i] << sh) : (v[i] >> (-sh));
-            a = fmaf(x[8 * i + n], __uint_as_float((t & 0x00780000u) | 0x3F800000u), a);
+            a[i] = fmaf(x[8 * i + n], __uint_as_float((t & 0x00780000u) | 0x3F800000u), a[i]);
         }
     }
-    return a;
+    return (a[0] + a[1]) + (a[2] + a[3]);
 }
 
 // This lane's 16-value slices of a vector in global memory: slice j is values [16*(lane + 32*j), +16)
@@ -201,7 +201,8 @@ enum SegKind : int {
     SEG_BF_DECAY = 3,  // bf16 rows, out = -exp(A_log) * softplus(dot + dt_bias)
     SEG_BF = 4,        // bf16 rows, out = dot (+ bias[row] if given)
     SEG_I8_GATEUP = 5, // two int8 matrices, out = silu(s1 * dot1) * (s2 * dot2)
-    SEG_I8_ARGMAX = 6  // int8 rows, out = scale * dot, and the arg-max over all rows
+    SEG_I8_ARGMAX = 6, // int8 rows, out = scale * dot, and the arg-max over all rows
+    SEG_I8_SILU = 7    // int8 rows, out = silu(scale * dot)
 };
 enum Finisher : int { FIN_NONE = 0, FIN_TOPK = 1, FIN_ARGMAX = 2 };
 
@@ -215,7 +216,7 @@ struct Seg {
     int rows;
     int kind;
     int out_stride;
-    int jobs;          // filled by the host: ceil(rows / 2) for one-matrix int8 kinds, else rows
+    int jobs;          // filled by the host: tiles of 8 rows (int8 kinds) or 4 rows (bf16 rows, gate/up pairs)
 };
 
 struct GemvArgs {
@@ -244,6 +245,7 @@ struct GemvArgs {
     int* part_idx;           // [B][gridDim.x]
     int* next_tok;           // [B]
     int* pos;                // [B] advanced by one by the finisher (may be null)
+    int* err;                // set to 3 if a bulk copy never landed (bounded wait gave up)
 };
 
 // Softmax over E router logits and the `topk` largest in descending order, ties to the lower
@@ -301,135 +303,200 @@ __device__ __forceinline__ void router_topk_warp(const float* __restrict__ logit
     }
 }
 
+// ---- bulk asynchronous copies (TMA) into a shared-memory ring, tracked by mbarriers ----
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// Wait for a phase of an mbarrier of this block. The wait is bounded: if the phase has not completed
+// after a very long time (a copy that never lands), *err is set and the caller goes on with whatever
+// the buffer holds, so that the kernel always terminates.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
+    for (int spin = 0; spin < (1 << 22); spin++) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (ok) return;
+    }
+    if (err) atomicExch(err, 3);
+}
+// One contiguous copy global -> shared; src, dst 16-byte aligned, bytes a multiple of 16.
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
+                 "l"(src), "r"(bytes), "r"(smem_u32(bar))
+                 : "memory");
+}
+
+constexpr int RING_STAGE_BYTES = 16384;   // one tile: 8 int8 rows of 2048, or 4 bf16 rows, or 4 + 4 rows of a pair
+constexpr int RING_STAGES = 6;            // 96 KB per block: two kernels of a PDL pair fit one SM
+constexpr int GEMV_THREADS = THREADS + 32;   // 8 consumer warps + 1 producer warp
+
+__device__ __forceinline__ int seg_tile_rows(int kind) {
+    return (kind == SEG_BF_SIGMOID || kind == SEG_BF_DECAY || kind == SEG_BF || kind == SEG_I8_GATEUP) ? 4 : 8;
+}
+
+// The block's tiles [t0, t1) of the launch are streamed by one producer thread through the ring with
+// bulk copies; each of the 8 consumer warps takes one row of a tile (a row pair for gate/up), reads
+// its 16-byte slices from shared memory and reduces. Weights do not depend on the previous kernel, so
+// the producer starts before grid_dep_wait(): the ring fills while the predecessor is still running.
 template <int MAXC>
-__global__ void __launch_bounds__(THREADS, 2) k_gemv_norm(const GemvArgs a) {
+__global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv_norm(const GemvArgs a) {
+    extern __shared__ __align__(128) unsigned char ring[];
+    __shared__ __align__(8) uint64_t full_bar[RING_STAGES], empty_bar[RING_STAGES];
+    __shared__ int s_last;
+    __shared__ float s_bv[WARPS];
+    __shared__ int s_bi[WARPS];
     const int b = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int nchunk = a.K >> 4;
-    const int gw = blockIdx.x * WARPS + warp, TW = gridDim.x * WARPS;
+    const int t0 = (int)((long long)blockIdx.x * a.total_jobs / gridDim.x);
+    const int t1 = (int)((long long)(blockIdx.x + 1) * a.total_jobs / gridDim.x);
     grid_dep_launch();
-
-    int4 wbuf[2 * MAXC];
-    // what one job reads: two int8 rows, or one bf16 row (twice the bytes), or a gate row and an up row
-    auto issue = [&](int job) {
-        int s = 0, j = job;
-        while (s + 1 < a.nseg && j >= a.seg[s].jobs) { j -= a.seg[s].jobs; s++; }
-        const Seg& sg = a.seg[s];
-        const char *pa, *pb;
-        int step;   // bytes between this lane's consecutive 16-value slices
-        bool hasb = true;
-        if (sg.kind == SEG_BF_SIGMOID || sg.kind == SEG_BF_DECAY || sg.kind == SEG_BF) {
-            pa = (const char*)sg.w + (size_t)j * a.K * 2;
-            pb = pa + 16;
-            step = 32;
-        } else if (sg.kind == SEG_I8_GATEUP) {
-            pa = (const char*)sg.w + (size_t)j * a.K;
-            pb = (const char*)sg.w2 + (size_t)j * a.K;
-            step = 16;
-        } else {
-            pa = (const char*)sg.w + (size_t)(2 * j) * a.K;
-            pb = pa + a.K;
-            hasb = 2 * j + 1 < sg.rows;
-            step = 16;
-        }
-#pragma unroll
-        for (int jj = 0; jj < MAXC; jj++) {
-            const int c = lane + 32 * jj;
-            if (c < nchunk) {
-                wbuf[jj] = ldw(pa + (size_t)c * step);
-                wbuf[MAXC + jj] = hasb ? ldw(pb + (size_t)c * step) : make_int4(0, 0, 0, 0);
-            } else {
-                wbuf[jj] = make_int4(0, 0, 0, 0);
-                wbuf[MAXC + jj] = make_int4(0, 0, 0, 0);
-            }
-        }
-    };
-
-    // the first job's weights do not depend on the activations: they are in flight while the previous
-    // kernel finishes
-    int job = gw;
-    if (job < a.total_jobs) issue(job);
-    grid_dep_wait();
-
-    float xr[MAXC][16];
-    load_x_znorm<MAXC>(xr, a.x + (size_t)b * a.K, a.norm_w, a.eps, a.K, lane);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < RING_STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], WARPS); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
 
     float best_v = -INFINITY;
     int best_i = 0x7fffffff;
 
-    for (; job < a.total_jobs; job += TW) {
-        int s = 0, j = job;
-        while (s + 1 < a.nseg && j >= a.seg[s].jobs) { j -= a.seg[s].jobs; s++; }
-        const Seg& sg = a.seg[s];
-        const bool isbf = sg.kind == SEG_BF_SIGMOID || sg.kind == SEG_BF_DECAY || sg.kind == SEG_BF;
-        float accA = 0.f, accB = 0.f;
-        if (isbf) {
-#pragma unroll
-            for (int jj = 0; jj < MAXC; jj++) {
-                accA += dot8_bf16(wbuf[jj], &xr[jj][0]);
-                accA += dot8_bf16(wbuf[MAXC + jj], &xr[jj][8]);
-            }
-        } else {
-#pragma unroll
-            for (int jj = 0; jj < MAXC; jj++) {
-                accA += dot16_i8(wbuf[jj], &xr[jj][0]);
-                accB += dot16_i8(wbuf[MAXC + jj], &xr[jj][0]);
+    if (warp == WARPS) {
+        // ---- producer ----
+        if (lane == 0) {
+            int s = 0, tile_in_seg = t0;
+            while (s + 1 < a.nseg && tile_in_seg >= a.seg[s].jobs) { tile_in_seg -= a.seg[s].jobs; s++; }
+            for (int t = t0, i = 0; t < t1; t++, i++) {
+                const int st = i % RING_STAGES;
+                if (i >= RING_STAGES) mbar_wait(&empty_bar[st], ((i / RING_STAGES) - 1) & 1, a.err);
+                const Seg& sg = a.seg[s];
+                const int tr = seg_tile_rows(sg.kind);
+                const int row0 = tile_in_seg * tr;
+                const int nrows = min(tr, sg.rows - row0);
+                unsigned char* dst = ring + (size_t)st * RING_STAGE_BYTES;
+                if (sg.kind == SEG_I8_GATEUP) {
+                    const uint32_t bytes = (uint32_t)nrows * a.K;
+                    mbar_expect_tx(&full_bar[st], 2 * bytes);
+                    bulk_load(dst, (const char*)sg.w + (size_t)row0 * a.K, bytes, &full_bar[st]);
+                    bulk_load(dst + 4 * a.K, (const char*)sg.w2 + (size_t)row0 * a.K, bytes, &full_bar[st]);
+                } else {
+                    const int rb = (tr == 4) ? 2 * a.K : a.K;     // bytes per row
+                    const uint32_t bytes = (uint32_t)nrows * rb;
+                    mbar_expect_tx(&full_bar[st], bytes);
+                    bulk_load(dst, (const char*)sg.w + (size_t)row0 * rb, bytes, &full_bar[st]);
+                }
+                if (++tile_in_seg >= sg.jobs && s + 1 < a.nseg) { tile_in_seg = 0; s++; }
             }
         }
-        if (job + TW < a.total_jobs) issue(job + TW);   // next job's loads fly during the reduction
-        accA = warp_sum(accA);
-        accB = warp_sum(accB);
-        if (lane == 0) {
-            float* out = sg.out + (size_t)b * sg.out_stride;
-            switch (sg.kind) {
-            case SEG_I8: {
-                const int r = 2 * j;
-                out[r] = bf(sg.s[r]) * accA;
-                if (r + 1 < sg.rows) out[r + 1] = bf(sg.s[r + 1]) * accB;
-            } break;
-            case SEG_I8_ARGMAX: {
-                const int r = 2 * j;
-                const float v0 = bf(sg.s[r]) * accA;
-                out[r] = v0;
-                if (v0 > best_v || (v0 == best_v && r < best_i)) { best_v = v0; best_i = r; }
-                if (r + 1 < sg.rows) {
-                    const float v1 = bf(sg.s[r + 1]) * accB;
-                    out[r + 1] = v1;
-                    if (v1 > best_v || (v1 == best_v && r + 1 < best_i)) { best_v = v1; best_i = r + 1; }
+    } else {
+        // ---- consumers ----
+        grid_dep_wait();
+        float xr[MAXC][16];
+        load_x_znorm<MAXC>(xr, a.x + (size_t)b * a.K, a.norm_w, a.eps, a.K, lane);
+        int s = 0, tile_in_seg = t0;
+        while (s + 1 < a.nseg && tile_in_seg >= a.seg[s].jobs) { tile_in_seg -= a.seg[s].jobs; s++; }
+        for (int t = t0, i = 0; t < t1; t++, i++) {
+            const int st = i % RING_STAGES;
+            const Seg& sg = a.seg[s];
+            const int tr = seg_tile_rows(sg.kind);
+            const int row = tile_in_seg * tr + warp;
+            const bool mine = warp < tr && row < sg.rows;
+            // what the epilogue needs from global memory is requested before the tile is waited for
+            float e0 = 0.f, e1 = 0.f, e2 = 0.f, e3 = 0.f;
+            uint2 ecw = make_uint2(0u, 0u);
+            if (mine && lane == 0) {
+                switch (sg.kind) {
+                case SEG_I8: case SEG_I8_ARGMAX: case SEG_I8_SILU: e0 = bf(sg.s[row]); break;
+                case SEG_I8_GATEUP: e0 = bf(sg.s[row]); e1 = bf(sg.s2[row]); break;
+                case SEG_I8_CONV: {
+                    e0 = bf(sg.s[row]);
+                    const float* stt = a.conv_state + ((size_t)b * sg.rows + row) * 3;
+                    e1 = stt[0]; e2 = stt[1]; e3 = stt[2];
+                    ecw = *reinterpret_cast<const uint2*>(a.conv_w + (size_t)row * 4);
+                } break;
+                case SEG_BF_DECAY: e0 = bf(a.a_log[row]); e1 = bf(a.dt_bias[row]); break;
+                case SEG_BF: e0 = sg.bias ? sg.bias[row] : 0.f; break;
+                default: break;
                 }
-            } break;
-            case SEG_I8_CONV: {
-                // hybrid.py:393-398: y = silu(sum_j w[c][j] * taps[j]), taps = 3 previous inputs + the new one
-                for (int q = 0; q < 2; q++) {
-                    const int c = 2 * j + q;
-                    if (c >= sg.rows) break;
-                    const float raw = bf(sg.s[c]) * (q ? accB : accA);
-                    float* st = a.conv_state + ((size_t)b * sg.rows + c) * 3;
-                    const uint16_t* cw = a.conv_w + (size_t)c * 4;
-                    const float s0 = st[0], s1 = st[1], s2 = st[2];
-                    float y = bf(cw[0]) * s0;
-                    y = fmaf(bf(cw[1]), s1, y);
-                    y = fmaf(bf(cw[2]), s2, y);
-                    y = fmaf(bf(cw[3]), raw, y);
-                    st[0] = s1; st[1] = s2; st[2] = raw;
-                    out[c] = siluf_(y);
-                }
-            } break;
-            case SEG_BF_SIGMOID: out[j] = sigmoidf_(accA); break;
-            case SEG_BF_DECAY: out[j] = -expf(bf(a.a_log[j])) * softplusf_(accA + bf(a.dt_bias[j])); break;
-            case SEG_BF: out[j] = accA + (sg.bias ? sg.bias[j] : 0.f); break;
-            case SEG_I8_GATEUP: out[j] = siluf_(bf(sg.s[j]) * accA) * (bf(sg.s2[j]) * accB); break;
             }
+            mbar_wait(&full_bar[st], (i / RING_STAGES) & 1, a.err);
+            const unsigned char* src = ring + (size_t)st * RING_STAGE_BYTES;
+            float accA = 0.f, accB = 0.f;
+            if (mine) {
+                if (tr == 8) {
+                    const int4* p = reinterpret_cast<const int4*>(src + (size_t)warp * a.K);
+#pragma unroll
+                    for (int jj = 0; jj < MAXC; jj++) {
+                        const int c = lane + 32 * jj;
+                        if (c < nchunk) accA += dot16_i8(p[c], &xr[jj][0]);
+                    }
+                } else if (sg.kind == SEG_I8_GATEUP) {
+                    const int4* pg = reinterpret_cast<const int4*>(src + (size_t)warp * a.K);
+                    const int4* pu = reinterpret_cast<const int4*>(src + (size_t)(4 + warp) * a.K);
+#pragma unroll
+                    for (int jj = 0; jj < MAXC; jj++) {
+                        const int c = lane + 32 * jj;
+                        if (c < nchunk) { accA += dot16_i8(pg[c], &xr[jj][0]); accB += dot16_i8(pu[c], &xr[jj][0]); }
+                    }
+                } else {
+                    const int4* p = reinterpret_cast<const int4*>(src + (size_t)warp * 2 * a.K);
+#pragma unroll
+                    for (int jj = 0; jj < MAXC; jj++) {
+                        const int c = lane + 32 * jj;
+                        if (c < nchunk) { accA += dot8_bf16(p[2 * c], &xr[jj][0]); accA += dot8_bf16(p[2 * c + 1], &xr[jj][8]); }
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty_bar[st]);      // this warp is done with the stage
+            if (mine) {
+                accA = warp_sum(accA);
+                if (sg.kind == SEG_I8_GATEUP) accB = warp_sum(accB);
+                if (lane == 0) {
+                    float* out = sg.out + (size_t)b * sg.out_stride;
+                    switch (sg.kind) {
+                    case SEG_I8: out[row] = e0 * accA; break;
+                    case SEG_I8_SILU: out[row] = siluf_(e0 * accA); break;
+                    case SEG_I8_ARGMAX: {
+                        const float v0 = e0 * accA;
+                        out[row] = v0;
+                        if (v0 > best_v || (v0 == best_v && row < best_i)) { best_v = v0; best_i = row; }
+                    } break;
+                    case SEG_I8_CONV: {
+                        // hybrid.py:393-398: y = silu(sum_j w[c][j] * taps[j]), taps = 3 previous inputs + the new one
+                        const float raw = e0 * accA;
+                        float* stt = a.conv_state + ((size_t)b * sg.rows + row) * 3;
+                        float y = bflo(ecw.x) * e1;
+                        y = fmaf(bfhi(ecw.x), e2, y);
+                        y = fmaf(bflo(ecw.y), e3, y);
+                        y = fmaf(bfhi(ecw.y), raw, y);
+                        stt[0] = e2; stt[1] = e3; stt[2] = raw;
+                        out[row] = siluf_(y);
+                    } break;
+                    case SEG_BF_SIGMOID: out[row] = sigmoidf_(accA); break;
+                    case SEG_BF_DECAY: out[row] = -expf(e0) * softplusf_(accA + e1); break;
+                    case SEG_BF: out[row] = accA + e0; break;
+                    case SEG_I8_GATEUP: out[row] = siluf_(e0 * accA) * (e1 * accB); break;
+                    }
+                }
+            }
+            if (++tile_in_seg >= sg.jobs && s + 1 < a.nseg) { tile_in_seg = 0; s++; }
         }
     }
 
     if (a.finisher == FIN_NONE) return;
 
-    __shared__ int s_last;
-    __shared__ float s_bv[WARPS];
-    __shared__ int s_bi[WARPS];
     if (a.finisher == FIN_ARGMAX) {
-        if (lane == 0) { s_bv[warp] = best_v; s_bi[warp] = best_i; }
+        if (lane == 0 && warp < WARPS) { s_bv[warp] = best_v; s_bi[warp] = best_i; }
         __syncthreads();
         if (threadIdx.x == 0) {
             float v = s_bv[0];
@@ -567,14 +634,15 @@ __global__ void __launch_bounds__(THREADS) k_delta_step(const DeltaArgs a) {
 
 // ------------------------------------------------------------------------------------------
 // k_proj_out: the mixer's output projection, accumulated into the residual stream.
-//   mode 0 (DeltaNet): input = w * rmsnorm_DV(o) * silu(z) per value head (aegist/hybrid.py:133-147)
+//   mode 0 (DeltaNet): input = w * rmsnorm_DV(o) * silu(z) per value head (aegist/hybrid.py:133-147);
+//                      silu(z) arrives ready-made from the in_z rows' epilogue
 //   mode 1 (attention): input is used as it is (already merged and gated by k_attn_merge)
 // K up to 4096: two warps share a row, each holding its half of the input in registers. A value
 // head (DV values) is DV/16 neighbouring lanes' slices, so its mean square is a short shuffle
 // reduction.
 struct ProjArgs {
     const float* in;      // [B][K]
-    const float* z;       // [B][K]      mode 0
+    const float* z;       // [B][K]      mode 0: silu(z), applied by the kernel that produced z
     const uint16_t* gn_w; // [DV]        mode 0
     float eps;
     int DV;               // 32, 64, 128 or 256
@@ -636,7 +704,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_proj_out(const ProjArgs a) {
                     const float zz[4] = {t.x, t.y, t.z, t.w};
 #pragma unroll
                     for (int i = 0; i < 4; i++)
-                        xr[jj][4 * q + i] = (bf(a.gn_w[d0 + 4 * q + i]) * (xr[jj][4 * q + i] * r)) * siluf_(zz[i]);
+                        xr[jj][4 * q + i] = (bf(a.gn_w[d0 + 4 * q + i]) * (xr[jj][4 * q + i] * r)) * zz[i];
                 }
             }
         }
