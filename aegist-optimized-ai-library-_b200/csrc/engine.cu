@@ -8,6 +8,8 @@
 //     the host boundary 82 times per token, hybrid.rs:743-758, 875, 919, 1000);
 //   * the KV cache is paged (64-token pages through a page table) and stored as bf16 or fp32.
 #include <cuda_runtime.h>
+#include <dlfcn.h>
+#include <nccl.h>
 
 #include <cmath>
 #include <cstdarg>
@@ -148,6 +150,24 @@ struct b2_engine {
     std::vector<int> tap_layers;
     float* tap_buf = nullptr;
     uint64_t hits = 0;
+    // expert parallelism (ep_world > 1): NCCL is resolved at run time from the library the process
+    // already has loaded (torch's), so that one process never holds two NCCL versions
+    void* nccl_lib = nullptr;
+    ncclComm_t comm = nullptr;
+    ncclResult_t (*p_ncclGetUniqueId)(ncclUniqueId*) = nullptr;
+    ncclResult_t (*p_ncclCommInitRank)(ncclComm_t*, int, ncclUniqueId, int) = nullptr;
+    ncclResult_t (*p_ncclCommDestroy)(ncclComm_t) = nullptr;
+    ncclResult_t (*p_ncclAllGather)(const void*, void*, size_t, ncclDataType_t, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*p_ncclSend)(const void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*p_ncclRecv)(void*, size_t, ncclDataType_t, int, ncclComm_t, cudaStream_t) = nullptr;
+    ncclResult_t (*p_ncclGroupStart)() = nullptr;
+    ncclResult_t (*p_ncclGroupEnd)() = nullptr;
+    const char* (*p_ncclGetErrorString)(ncclResult_t) = nullptr;
+    float *rec_local = nullptr, *rec_all = nullptr, *recv_y = nullptr;
+    int load_nccl();
+    int ep_exchange_records(cudaStream_t st);
+    int ep_exchange_outputs(cudaStream_t st);
+
     // per-kernel timing (b2_profile_step): one event after every launch of an un-graphed step
     bool profiling = false;
     std::vector<cudaEvent_t> prof_ev;
@@ -192,12 +212,13 @@ b2_engine::~b2_engine() {
     for (auto& l : layers) { cudaFree((void*)l.eptr); cudaFree(l.router_bias); }
     void* bufs[] = {conv, state, snap_conv[0], snap_conv[1], snap_state[0], snap_state[1], kpool, vpool, page_table, rope_cos,
                     rope_sin, d_tok, d_next, d_pos, d_err, d_counter, d_acounter, x, big, zbuf, kraw, vraw, beta, gdec, obuf, att,
-                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter};
+                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y};
     for (void* p : bufs) cudaFree(p);
     if (h_pin) cudaFreeHost(h_pin);
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
     for (cudaEvent_t e : prof_ev) cudaEventDestroy(e);
+    if (comm && p_ncclCommDestroy) p_ncclCommDestroy(comm);
     if (stream) cudaStreamDestroy(stream);
 }
 
@@ -373,6 +394,7 @@ int b2_engine::finish() {
         for (int e = 0; e < per; e++) tab[ep_rank * per + e] = l.experts + (size_t)e * c.expert_bytes();
         CU(cudaMalloc((void**)&l.eptr, c.E * sizeof(void*)));
         CU(cudaMemcpy((void*)l.eptr, tab.data(), c.E * sizeof(void*), cudaMemcpyHostToDevice));
+        CU(dalloc(&l.router_bias, c.E));   // zeros: adding them changes no logit; b2_set_router_bias fills them
         layers.push_back(l);
     }
 #undef NEED
@@ -429,15 +451,22 @@ int b2_engine::finish() {
     CU(dalloc(&beta, (size_t)B * c.HV)); CU(dalloc(&gdec, (size_t)B * c.HV));
     CU(dalloc(&obuf, (size_t)B * c.VD())); CU(dalloc(&att, (size_t)B * c.H * c.HD));
     CU(dalloc(&rlogits, (size_t)B * c.E)); CU(dalloc(&sh_act, (size_t)B * c.SH)); CU(dalloc(&sgate, B));
-    CU(dalloc(&act, (size_t)B * c.TOPK * c.I)); CU(dalloc(&logits, (size_t)B * c.V));
+    const size_t Bg = (size_t)B * ep_world;   // sequences whose picks may land on this GPU's experts
+    CU(dalloc(&act, Bg * c.TOPK * c.I)); CU(dalloc(&logits, (size_t)B * c.V));
     CU(dalloc(&top_idx, (size_t)c.L * B * c.TOPK)); CU(dalloc(&top_w, (size_t)c.L * B * c.TOPK));
     head_grid = std::min((c.V + 7) / 8, g_gemv_ctas_per_sm * nsm);
     CU(dalloc(&part_val, (size_t)B * head_grid)); CU(dalloc(&part_idx, (size_t)B * head_grid));
     // attention: enough slices to fill the GPU, but at least 64 positions each at full context
     nsplit = std::max(1, std::min({64, (2 * nsm) / std::max(1, c.KV * B), (cap + 63) / 64}));
     CU(dalloc(&attn_part, (size_t)B * c.KV * nsplit * (c.H / c.KV) * (c.HD + 2)));
-    CU(dalloc(&ypart, (size_t)B * (c.TOPK + 1) * c.D));
-    CU(dalloc(&d_dcounter, (size_t)B * down_row_blocks(c.D)));
+    CU(dalloc(&ypart, Bg * (c.TOPK + 1) * c.D));
+    CU(dalloc(&d_dcounter, Bg * down_row_blocks(c.D)));
+    if (ep_world > 1) {
+        const size_t rw = c.D + 2 * c.TOPK;
+        CU(dalloc(&rec_local, (size_t)B * rw));
+        CU(dalloc(&rec_all, Bg * rw));
+        CU(dalloc(&recv_y, Bg * (c.TOPK + 1) * c.D));
+    }
     CU(cudaMallocHost((void**)&h_pin, std::max(B, 1) * sizeof(uint32_t) * 2));
     CU(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
     CU(cudaEventCreate(&ev0));
@@ -450,6 +479,7 @@ int b2_engine::finish() {
              gpu_name.c_str(), weight_bytes / 1e9, c.L * per, c.L * c.E, ep_world > 1 ? " on this rank" : "", 0, cap, B,
              kv_f32 ? "fp32" : "bf16", kv_bytes / 1e9);
     desc = buf;
+    if (ep_world > 1) return 0;   // the step graph holds NCCL calls: it is built by b2_ep_init
     return build_graph();
 }
 
@@ -620,12 +650,29 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             launch_gemv(a, B, nsm, st);
             mark(1, st);
             ExpertArgs x2{};
-            x2.eptr = l.eptr; x2.top_idx = a.top_idx; x2.top_w = a.top_w; x2.topk = c.TOPK; x2.E = c.E; x2.D = c.D; x2.I = c.I;
+            x2.eptr = l.eptr; x2.topk = c.TOPK; x2.E = c.E; x2.D = c.D; x2.I = c.I;
             x2.off_gu_s = c.off_gu_s(); x2.off_gu_m = c.off_gu_m(); x2.off_dn_q = c.off_dn_q(); x2.off_dn_s = c.off_dn_s(); x2.off_dn_m = c.off_dn_m();
-            x2.x = x; x2.norm_w = l.norm2; x2.eps = c.eps; x2.act = act; x2.sh_act = sh_act; x2.sg = sgate;
+            x2.norm_w = l.norm2; x2.eps = c.eps; x2.act = act; x2.sh_act = sh_act; x2.sg = sgate;
             x2.shd_w = l.sh_down.w; x2.shd_s = l.sh_down.s; x2.SH = c.SH; x2.xout = x; x2.err = d_err;
             x2.ypart = ypart; x2.counter = d_dcounter;
-            launch_experts(x2, B, nsm, st, this);
+            if (ep_world == 1) {
+                x2.x = x; x2.x_stride = c.D; x2.top_idx = a.top_idx; x2.top_w = a.top_w; x2.idx_stride = c.TOPK;
+                x2.combine = 1; x2.local0 = 0; x2.nlocal = B;
+                launch_experts(x2, B, nsm, st, this);
+            } else {
+                const int rw = c.D + 2 * c.TOPK;
+                EpArgs ep{};
+                ep.x = x; ep.top_idx = a.top_idx; ep.top_w = a.top_w; ep.rec = rec_local; ep.recv_y = recv_y; ep.sg = sgate; ep.xout = x;
+                ep.D = c.D; ep.topk = c.TOPK; ep.B = B; ep.E = c.E; ep.world = ep_world; ep.rank = ep_rank; ep.has_shared = 1;
+                launch_k(k_ep_pack, dim3(B), dim3(256), 0, st, ep);
+                if (ep_exchange_records(st)) return 1;
+                x2.x = rec_all; x2.x_stride = rw; x2.top_idx = (const int*)(rec_all + c.D); x2.top_w = rec_all + c.D + c.TOPK; x2.idx_stride = rw;
+                x2.combine = 0; x2.local0 = ep_rank * B; x2.nlocal = B;
+                launch_experts(x2, B * ep_world, nsm, st, this);
+                if (ep_exchange_outputs(st)) return 1;
+                launch_k(k_ep_combine, dim3(std::max(1, (c.D + 255) / 256), B), dim3(256), 0, st, ep);
+                n += 2;
+            }
             n += 3;
         }
         for (size_t j = 0; j < tap_layers.size(); j++)
@@ -694,6 +741,46 @@ int b2_engine::reset_state() {
     return 0;
 }
 
+int b2_engine::load_nccl() {
+    if (p_ncclAllGather) return 0;
+    const char* names[] = {getenv("B2_NCCL_LIB"), "libnccl.so.2", "libnccl.so"};
+    for (const char* n : names) {
+        if (!n) continue;
+        nccl_lib = dlopen(n, RTLD_NOW | RTLD_NOLOAD);        // the copy this process already uses, if any
+        if (!nccl_lib) nccl_lib = dlopen(n, RTLD_NOW | RTLD_GLOBAL);
+        if (nccl_lib) break;
+    }
+    if (!nccl_lib) return fail("cannot load NCCL (libnccl.so.2): %s", dlerror());
+#define SYM(name) *(void**)(&p_##name) = dlsym(nccl_lib, #name); if (!p_##name) return fail("NCCL has no %s", #name);
+    SYM(ncclGetUniqueId) SYM(ncclCommInitRank) SYM(ncclCommDestroy) SYM(ncclAllGather) SYM(ncclSend) SYM(ncclRecv)
+    SYM(ncclGroupStart) SYM(ncclGroupEnd) SYM(ncclGetErrorString)
+#undef SYM
+    return 0;
+}
+#define NC(call)                                                                                   \
+    do {                                                                                           \
+        ncclResult_t r_ = (call);                                                                  \
+        if (r_ != ncclSuccess) return fail("%s: %s", #call, p_ncclGetErrorString(r_));             \
+    } while (0)
+
+// every GPU's records [B][D + 2 topk] -> all records, in rank order
+int b2_engine::ep_exchange_records(cudaStream_t st) {
+    const size_t n = (size_t)B * (c.D + 2 * c.TOPK);
+    NC(p_ncclAllGather(rec_local, rec_all, n, ncclFloat32, comm, st));
+    return 0;
+}
+// block p of ypart (the picks of GPU p's sequences computed here) goes to GPU p; block q of recv_y comes from GPU q
+int b2_engine::ep_exchange_outputs(cudaStream_t st) {
+    const size_t blk = (size_t)B * (c.TOPK + 1) * c.D;
+    NC(p_ncclGroupStart());
+    for (int p = 0; p < ep_world; p++) {
+        NC(p_ncclSend(ypart + p * blk, blk, ncclFloat32, p, comm, st));
+        NC(p_ncclRecv(recv_y + p * blk, blk, ncclFloat32, p, comm, st));
+    }
+    NC(p_ncclGroupEnd());
+    return 0;
+}
+
 // Algorithmic bytes of one decode step by kernel class (0 embed, 1 norm+GEMV groups, 2 delta step,
 // 3 attention, 4 output projections, 5 expert gate/up, 6 expert down + shared down, 7 head):
 // every weight byte once per step, recurrent state read and written, KV read up to the current length,
@@ -755,6 +842,35 @@ int b2_put_tensor(b2_engine* e, const char* name, const char* dtype, const int64
 }
 
 int b2_finish(b2_engine* e) { return e ? e->finish() : 1; }
+
+int b2_ep_unique_id(b2_engine* e, void* id_out, size_t len) {
+    if (!e) return 1;
+    if (len < sizeof(ncclUniqueId)) return e->fail("the id buffer needs %zu bytes", sizeof(ncclUniqueId));
+    if (e->load_nccl()) return 1;
+    ncclUniqueId id;
+    ncclResult_t r = e->p_ncclGetUniqueId(&id);
+    if (r != ncclSuccess) return e->fail("ncclGetUniqueId: %s", e->p_ncclGetErrorString(r));
+    memcpy(id_out, &id, sizeof(id));
+    return 0;
+}
+
+int b2_ep_init(b2_engine* e, const void* id_in, size_t len) {
+    if (!e || !e->finished) return 1;
+    if (e->ep_world <= 1) return e->fail("this engine was created for a single GPU");
+    if (len < sizeof(ncclUniqueId)) return e->fail("the id buffer needs %zu bytes", sizeof(ncclUniqueId));
+    if (e->load_nccl()) return 1;
+    cudaError_t ce = cudaSetDevice(e->device);
+    if (ce != cudaSuccess) return e->fail("cudaSetDevice: %s", cudaGetErrorString(ce));
+    ncclUniqueId id;
+    memcpy(&id, id_in, sizeof(id));
+    ncclResult_t r = e->p_ncclCommInitRank(&e->comm, e->ep_world, id, e->ep_rank);
+    if (r != ncclSuccess) return e->fail("ncclCommInitRank: %s", e->p_ncclGetErrorString(r));
+    // one exchange of each kind outside the graph: NCCL sets up its channels on first use
+    if (e->ep_exchange_records(e->stream) || e->ep_exchange_outputs(e->stream)) return 1;
+    ce = cudaStreamSynchronize(e->stream);
+    if (ce != cudaSuccess) return e->fail("first exchange: %s", cudaGetErrorString(ce));
+    return e->build_graph();
+}
 
 int b2_open(const char* nx_path, int max_context, int device, int batch, int kv_dtype, b2_engine** out) {
     if (!out) return 1;
@@ -991,12 +1107,9 @@ int b2_set_router_bias(b2_engine* e, int layer, const float* bias) {
     CUE(cudaSetDevice(e->device));
     CUE(cudaStreamSynchronize(e->stream));
     LayerW& l = e->layers[layer];
-    if (!bias) { cudaFree(l.router_bias); l.router_bias = nullptr; }
-    else {
-        if (!l.router_bias) CUE(dalloc(&l.router_bias, e->c.E));
-        CUE(cudaMemcpy(l.router_bias, bias, (size_t)e->c.E * 4, cudaMemcpyHostToDevice));
-    }
-    return e->build_graph();
+    if (!bias) CUE(cudaMemset(l.router_bias, 0, (size_t)e->c.E * 4));
+    else CUE(cudaMemcpy(l.router_bias, bias, (size_t)e->c.E * 4, cudaMemcpyHostToDevice));
+    return 0;
 }
 
 int b2_launches_per_step(const b2_engine* e) { return e ? e->launches : 0; }

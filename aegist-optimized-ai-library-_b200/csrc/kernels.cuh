@@ -732,13 +732,17 @@ __global__ void __launch_bounds__(THREADS, 2) k_proj_out(const ProjArgs a) {
 // 64-value groups (the factorisation of hybrid.cu:405-406).
 struct ExpertArgs {
     const uint8_t* const* eptr;   // [E] device address of each resident expert (null: not on this GPU)
-    const int* top_idx;           // [B][topk]
-    const float* top_w;           // [B][topk]
+    const int* top_idx;           // [tokens][idx_stride] the router's picks
+    const float* top_w;           // [tokens][idx_stride]
+    int idx_stride;               // top-k on one GPU; the exchange record width under expert parallelism
+    int x_stride;                 // d_model on one GPU; the exchange record width under expert parallelism
+    int combine;                  // 1: the last block adds the picks into xout; 0: a later kernel does (expert parallel)
+    int local0, nlocal;           // tokens [local0, local0 + nlocal) are this GPU's own (they get the shared expert)
     int topk, E;
     int D, I;
     size_t off_gu_s, off_gu_m, off_dn_q, off_dn_s, off_dn_m;
     // gate/up
-    const float* x;               // [B][D] residual stream (normalised again here)
+    const float* x;               // [tokens][x_stride] residual stream (normalised again here)
     const uint16_t* norm_w;
     float eps;
     float* act;                   // [B*topk][I]
@@ -762,7 +766,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_gu(const ExpertArgs a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     grid_dep_launch();
     grid_dep_wait();              // which expert to read is the previous kernel's result
-    const int e = a.top_idx[pick];
+    const int e = a.top_idx[(size_t)b * a.idx_stride + pick % a.topk];
     const uint8_t* base = (e >= 0 && e < a.E) ? a.eptr[e] : nullptr;
     if (base == nullptr) {   // not resident here (another rank's expert) or a bad pick
         if (e < 0 || e >= a.E) { if (threadIdx.x == 0) atomicExch(a.err, 2); }
@@ -800,7 +804,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_gu(const ExpertArgs a) {
     float xr[MAXC][32];
     float xsum[MAXC];
     {
-        const float* xg = a.x + (size_t)b * a.D;
+        const float* xg = a.x + (size_t)b * a.x_stride;
         float ss = 0.f;
 #pragma unroll
         for (int jj = 0; jj < MAXC; jj++) {
@@ -872,7 +876,8 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) 
     grid_dep_launch();
     float* yp = a.ypart + ((size_t)b * (a.topk + 1) + r) * a.D;
     if (r == a.topk) {
-        // shared expert: int8 rows of SH values, one warp per row
+        // shared expert: int8 rows of SH values, one warp per row; only for this GPU's own tokens
+        if (b < a.local0 || b >= a.local0 + a.nlocal) return;
         const int shchunk = a.SH >> 4;
         int4 w = make_int4(0, 0, 0, 0);
         int o = row0 + warp;
@@ -882,7 +887,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) 
 #pragma unroll
         for (int q = 0; q < 4; q++) {
             float4 t = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (lane < shchunk) t = reinterpret_cast<const float4*>(a.sh_act + (size_t)b * a.SH + 16 * lane)[q];
+            if (lane < shchunk) t = reinterpret_cast<const float4*>(a.sh_act + (size_t)(b - a.local0) * a.SH + 16 * lane)[q];
             shx[4 * q] = t.x; shx[4 * q + 1] = t.y; shx[4 * q + 2] = t.z; shx[4 * q + 3] = t.w;
         }
         for (; o < row1; o += WARPS) {
@@ -894,7 +899,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) 
         }
     } else {
         grid_dep_wait();
-        const int e = a.top_idx[b * a.topk + r];
+        const int e = a.top_idx[(size_t)b * a.idx_stride + r];
         const uint8_t* base = (e >= 0 && e < a.E) ? a.eptr[e] : nullptr;
         const int nchunk = a.I >> 5;                  // 32-code slices per row (<= 16)
         const int ngroup = a.I >> 6;
@@ -935,9 +940,12 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) 
             }
         } else {
             if (e < 0 || e >= a.E) { if (threadIdx.x == 0) atomicExch(a.err, 2); }
-            for (int o = row0 + threadIdx.x; o < row1; o += THREADS) yp[o] = 0.f;   // another rank's expert
+            if (a.combine)
+                for (int o = row0 + threadIdx.x; o < row1; o += THREADS) yp[o] = 0.f;
+            // under expert parallelism another GPU computes this pick; nothing is written here
         }
     }
+    if (!a.combine) return;
     // last block of this (sequence, row block): weighted sum in rank order, into the residual stream
     __threadfence();
     __syncthreads();
@@ -951,7 +959,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) 
     for (int o = row0 + threadIdx.x; o < row1; o += THREADS) {
         const float* base = a.ypart + (size_t)b * (a.topk + 1) * a.D + o;
         float y = 0.f;
-        for (int k = 0; k < a.topk; k++) y = fmaf(a.top_w[b * a.topk + k], __ldcg(base + (size_t)k * a.D), y);
+        for (int k = 0; k < a.topk; k++) y = fmaf(a.top_w[(size_t)b * a.idx_stride + k], __ldcg(base + (size_t)k * a.D), y);
         if (a.shd_w) y = fmaf(a.sg[b], __ldcg(base + (size_t)a.topk * a.D), y);
         a.xout[(size_t)b * a.D + o] += y;
     }
@@ -1228,6 +1236,57 @@ __global__ void __launch_bounds__(THREADS) k_attn_merge(const AttnArgs a, int HD
         for (; s < a.nsplit; s++) if (sc[s] != 0.f) acc = fmaf(pb[s * sstride + d], sc[s], acc);
         const float gate = a.qraw[((size_t)b * a.H + head) * 2 * HD + HD + d];
         a.out[(size_t)b * a.H * HD + head * HD + d] = (acc * s_inv) * sigmoidf_(gate);
+    }
+}
+
+// ------------------------------------------------------------------------------------------
+// Expert parallelism. Sequences are split over the GPUs (mixers, router, shared expert local), the
+// experts of every layer too (expert e lives on GPU e / (E / world)). Per layer:
+//   k_ep_pack     record[b] = x[b] | picks | weights            (this GPU's B sequences)
+//   all-gather    records of all world * B sequences
+//   k_expert_gu / k_expert_down on every sequence's picks that hit a local expert -> ypart[token][r]
+//   all-to-all    block p of ypart (GPU p's sequences) goes to GPU p
+//   k_ep_combine  x[b] += sum_r w_r * ypart_from_owner(e_r)[b][r] + shared, picks in rank order: the
+//                 same sums in the same order as on one GPU, so the result is bit-identical.
+struct EpArgs {
+    const float* x;        // [B][D]
+    const int* top_idx;    // [B][topk]
+    const float* top_w;    // [B][topk]
+    float* rec;            // [B][D + 2 * topk]
+    const float* recv_y;   // [world][B][topk + 1][D]: block p came from GPU p
+    const float* sg;       // [B]
+    float* xout;           // [B][D]
+    int D, topk, B, E, world, rank, has_shared;
+};
+
+__global__ void k_ep_pack(const EpArgs a) {
+    const int b = blockIdx.x;
+    grid_dep_launch();
+    grid_dep_wait();
+    const int rw = a.D + 2 * a.topk;
+    float* r = a.rec + (size_t)b * rw;
+    for (int k = threadIdx.x; k < a.D; k += blockDim.x) r[k] = a.x[(size_t)b * a.D + k];
+    if (threadIdx.x < a.topk) {
+        r[a.D + threadIdx.x] = __int_as_float(a.top_idx[b * a.topk + threadIdx.x]);
+        r[a.D + a.topk + threadIdx.x] = a.top_w[b * a.topk + threadIdx.x];
+    }
+}
+
+__global__ void k_ep_combine(const EpArgs a) {
+    const int b = blockIdx.y;
+    grid_dep_launch();
+    grid_dep_wait();
+    const int per = a.E / a.world;
+    const size_t blk = (size_t)a.B * (a.topk + 1) * a.D;      // one GPU's block
+    for (int o = blockIdx.x * blockDim.x + threadIdx.x; o < a.D; o += gridDim.x * blockDim.x) {
+        float y = 0.f;
+        for (int r = 0; r < a.topk; r++) {
+            const int e = a.top_idx[b * a.topk + r];
+            const int owner = min(max(e, 0), a.E - 1) / per;
+            y = fmaf(a.top_w[b * a.topk + r], a.recv_y[owner * blk + ((size_t)b * (a.topk + 1) + r) * a.D + o], y);
+        }
+        if (a.has_shared) y = fmaf(a.sg[b], a.recv_y[a.rank * blk + ((size_t)b * (a.topk + 1) + a.topk) * a.D + o], y);
+        a.xout[(size_t)b * a.D + o] += y;
     }
 }
 

@@ -128,6 +128,7 @@ int b2_moe_forward(b2_moe* m, const float* h, int tokens, float* y, int32_t* idx
     launch_gemv(a, tokens, m->nsm, m->st);
     ExpertArgs x{};
     x.eptr = m->eptr; x.top_idx = m->top_idx; x.top_w = m->top_w; x.topk = c.TOPK; x.E = c.E; x.D = c.D; x.I = c.I;
+    x.idx_stride = c.TOPK; x.x_stride = c.D; x.combine = 1; x.local0 = 0; x.nlocal = tokens;
     x.off_gu_s = c.off_gu_s(); x.off_gu_m = c.off_gu_m(); x.off_dn_q = c.off_dn_q(); x.off_dn_s = c.off_dn_s(); x.off_dn_m = c.off_dn_m();
     x.x = m->h; x.norm_w = nullptr; x.act = m->act; x.sh_act = m->sh_act; x.sg = m->sgate;
     x.shd_w = m->sd_q; x.shd_s = m->sd_s; x.SH = c.SH; x.xout = m->y; x.err = m->err;

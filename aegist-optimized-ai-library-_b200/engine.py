@@ -40,6 +40,8 @@ SYMBOLS = {
     "b2_create": (_I, [C.c_char_p, _I, _I, _I, _I, _I, _I, C.POINTER(_P)]),
     "b2_put_tensor": (_I, [_P, C.c_char_p, C.c_char_p, C.POINTER(C.c_int64), _I, _P, C.c_size_t, _I]),
     "b2_finish": (_I, [_P]),
+    "b2_ep_unique_id": (_I, [_P, _P, C.c_size_t]),
+    "b2_ep_init": (_I, [_P, _P, C.c_size_t]),
     "b2_verify_file": (_I, [C.c_char_p, C.POINTER(_I), C.c_char_p, C.c_size_t]),
     "b2_close": (None, [_P]),
     "b2_feed": (_I, [_P, _P, _I, _P]),
@@ -153,6 +155,16 @@ class HybridEngine:
                 lib.b2_close(h)
             raise EngineError(msg)
         return HybridEngine(h, lib, batch)
+
+    # --- expert parallelism -----------------------------------------------------------------
+    def ep_unique_id(self) -> bytes:
+        buf = C.create_string_buffer(128)
+        self._check(self._lib.b2_ep_unique_id(self._h, buf, 128))
+        return buf.raw
+
+    def ep_init(self, unique_id: bytes):
+        buf = C.create_string_buffer(unique_id, 128)
+        self._check(self._lib.b2_ep_init(self._h, buf, 128))
 
     def _check(self, rc):
         if rc:

@@ -43,6 +43,16 @@ int b2_put_tensor(b2_engine* e, const char* name, const char* dtype, const int64
                   const void* data, size_t nbytes, int data_on_device);
 int b2_finish(b2_engine* e);
 
+/* Expert parallelism over `ep_world` GPUs of one node, one process per GPU, each with an engine made
+ * by b2_create(..., ep_rank, ep_world) for its own `batch` sequences: the experts of every layer are
+ * split over the GPUs and the picks travel by NCCL (an all-gather of the routed tokens and an
+ * all-to-all of the expert outputs per layer). Rank 0 calls b2_ep_unique_id and hands the 128 bytes
+ * to every rank by any means; then all ranks call b2_ep_init together, and from then on
+ * b2_feed_batch / b2_decode_greedy together, step for step. The reference engine is single-GPU
+ * (aegist_rs/src/hybrid.rs:511-514 only picks which one); this has no counterpart there. */
+int b2_ep_unique_id(b2_engine* e, void* id_out, size_t len);
+int b2_ep_init(b2_engine* e, const void* id_in, size_t len);
+
 /* NxFile::verify (aegist_rs/src/nx.rs:164-184): recompute the per-group SHA-256 of a brain file.
  * ok[0..2] = base, engine, cores (1 = matches the header). */
 int b2_verify_file(const char* nx_path, int ok[3], char* err, size_t err_len);

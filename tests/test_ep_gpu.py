@@ -1,0 +1,71 @@
+"""Expert-parallel decode on two GPUs through the C ABI + NCCL: identical to the single-GPU engine
+and within tolerance of the reference's stored batch rows. Skipped with fewer than two GPUs."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _tensors(micro_path):
+    import sys
+    sys.path.insert(0, ROOT)
+    from __graft_entry__ import load_package
+    load_package()
+    from b200moe.nxfile import NxFile
+    nx = NxFile(micro_path)
+    return nx, [(n, nx.info(n)["dtype"], np.array(nx.tensor(n))) for n in nx.header["tensors"]]
+
+
+def _worker(rank, world, port, micro_path, ids, steps, out_dir):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    nx, tensors = _tensors(micro_path)
+    from b200moe import engine as E
+    from b200moe import ep
+    B = ids.shape[0] // world
+    e = E.HybridEngine.from_tensors(nx.config, tensors, max_context=32, device=rank, batch=B, kv_dtype=E.KV_F32,
+                                    ep_rank=rank, ep_world=world)
+    ep.attach(e, rank, world)
+    mine = ids[rank * B:(rank + 1) * B]
+    rows = []
+    for t in range(mine.shape[1]):
+        nxt, lg = e.feed_batch(mine[:, t])
+        rows.append(lg)
+    for _ in range(steps):
+        nxt, lg = e.feed_batch(rows[-1].argmax(-1))
+        rows.append(lg)
+    np.save(os.path.join(out_dir, f"rows{rank}.npy"), np.stack(rows))
+    e.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpus_equal_one_gpu(pkg, micro_path, golden_dir, tmp_path):
+    import torch.multiprocessing as mp
+    from b200moe import engine as E
+    g = np.load(os.path.join(golden_dir, "micro_golden.npz"))
+    ids = g["batch_prompt"]
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mp.spawn(_worker, args=(2, port, micro_path, ids, 8, str(tmp_path)), nprocs=2, join=True)
+    two = np.concatenate([np.load(tmp_path / f"rows{r}.npy") for r in range(2)], 1)      # [T, 4, V]
+    e = E.HybridEngine.load(micro_path, max_context=32, batch=4)
+    rows = []
+    for t in range(ids.shape[1]):
+        rows.append(e.feed_batch(ids[:, t])[1])
+    for _ in range(8):
+        rows.append(e.feed_batch(rows[-1].argmax(-1))[1])
+    one = np.stack(rows)
+    e.close()
+    assert np.array_equal(two, one)                          # same sums in the same order
+    assert np.abs(two - g["batch_logits"]).max() < 3e-4       # and the reference's rows
