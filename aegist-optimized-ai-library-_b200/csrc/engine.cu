@@ -1160,4 +1160,5 @@ int b2_profile_step(b2_engine* e, int iters, float ms[8], double bytes[8], int l
 }  // extern "C"
 
 #include "ops.cuh"
+#include "noalloc.cuh"
 #include "sampler.hpp"

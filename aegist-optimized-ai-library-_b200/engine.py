@@ -33,6 +33,14 @@ class MoeWeights(C.Structure):
                 ("sh_down_q", C.c_void_p), ("sh_down_s", C.c_void_p), ("shared_gate_bf16", C.c_void_p)]
 
 
+class MoeDeviceWeights(C.Structure):
+    _fields_ = [("d_model", C.c_int), ("n_experts", C.c_int), ("top_k", C.c_int), ("expert_hidden", C.c_int),
+                ("shared_hidden", C.c_int),
+                ("router_bf16", C.c_void_p), ("expert_ptrs", C.c_void_p),
+                ("sh_gate_q", C.c_void_p), ("sh_gate_s", C.c_void_p), ("sh_up_q", C.c_void_p), ("sh_up_s", C.c_void_p),
+                ("sh_down_q", C.c_void_p), ("sh_down_s", C.c_void_p), ("shared_gate_bf16", C.c_void_p)]
+
+
 # every symbol include/b200moe.h declares: name -> (restype, argtypes)
 _P, _I, _F = C.c_void_p, C.c_int, C.c_float
 SYMBOLS = {
@@ -72,6 +80,7 @@ SYMBOLS = {
     "b2_moe_create": (_I, [_I, C.POINTER(MoeWeights), _I, C.POINTER(_P)]),
     "b2_moe_forward": (_I, [_P, _P, _I, _P, _P, _P, C.POINTER(_F)]),
     "b2_moe_destroy": (None, [_P]),
+    "b2_moe_forward_static": (_I, [C.POINTER(MoeDeviceWeights), _P, _I, _P, _P, _P, _P]),
     "b2_delta_create": (_I, [_I, _I, _I, _I, _I, _P, C.POINTER(_P)]),
     "b2_delta_step": (_I, [_P, _P, _P, _P, _P, _P, _P, C.POINTER(_F)]),
     "b2_delta_state": (_I, [_P, _P]),

@@ -158,6 +158,31 @@ int b2_moe_create(int device, const b2_moe_weights* w, int max_tokens, b2_moe** 
 int b2_moe_forward(b2_moe* m, const float* h, int tokens, float* y, int32_t* idx, float* wts, float* device_ms);
 void b2_moe_destroy(b2_moe* m);
 
+/* The same MoE layer operator for callers that must not allocate device memory (a process whose own
+ * arena already owns the GPU's free memory, a loop that cannot afford an allocation's device-wide
+ * synchronisation, a plug-in that is only ever handed pointers). It has no counterpart in the
+ * reference. It calls no cudaMalloc / cudaFree and no allocating library routine: every pointer below
+ * is DEVICE memory supplied by the caller (`expert_ptrs` is a device array of n_experts device
+ * addresses, one packed expert row each), and the kernels' work memory is a fixed array inside the
+ * library, 748 KB on every GPU that loads it. Limits: at most 8 tokens, d_model 2048, 256 experts,
+ * top-8, expert_hidden 512, shared_hidden 512; anything larger returns 2 with a message on stderr
+ * (3: bad argument, 1: CUDA error). All calls share that array, which keeps the last call's contents
+ * (the function clears what must start at zero, y included): calls that overlap on one GPU race, so
+ * run them one after the other. The first call on a device looks the array's address up; make it
+ * before any stream capture begins. Work is queued on `stream` (a cudaStream_t, NULL = default) and the
+ * function returns after it has completed. idx / wts are optional outputs. */
+typedef struct {
+    int d_model, n_experts, top_k, expert_hidden, shared_hidden;
+    const uint16_t* router_bf16;            /* [E][D] */
+    const uint8_t* const* expert_ptrs;      /* [E] device addresses of the packed experts */
+    const int8_t* sh_gate_q; const uint16_t* sh_gate_s;
+    const int8_t* sh_up_q;   const uint16_t* sh_up_s;
+    const int8_t* sh_down_q; const uint16_t* sh_down_s;
+    const uint16_t* shared_gate_bf16;       /* [D] */
+} b2_moe_device_weights;
+int b2_moe_forward_static(const b2_moe_device_weights* w, const float* h, int tokens, float* y, int32_t* idx,
+                          float* wts, void* stream);
+
 /* delta_rule_step (aegist/hybrid.py:318-324; delta_scan, kernels/hybrid.cu:240-300) with the state
  * kept on the device between calls. q, k [B][H][dk] (already normalised and scaled), v [B][H][dv],
  * g, beta [B][H]; out [B][H][dv]. */
