@@ -533,8 +533,7 @@ static void seal(GemvArgs& a) {
 
 static void launch_proj(const ProjArgs& a, int B, int nsm, cudaStream_t st) {
     // rows per block a multiple of 4 (four warp pairs per block), one wave of blocks
-    int rpb = 4;
-    while ((a.N + rpb - 1) / rpb > 2 * nsm) rpb += 4;
+    const int rpb = 4 * PROJ_RPW;     // the kernel covers exactly this many rows per block
     const int grid = (a.N + rpb - 1) / rpb;
     const size_t smem = (size_t)(2 * rpb) * 4;
     const int maxc = (a.K / 2 + 511) / 512;
@@ -553,7 +552,7 @@ static void launch_delta(const DeltaArgs& a, int DK, int B, cudaStream_t st) {
 static void launch_experts(const ExpertArgs& a, int B, int nsm, cudaStream_t st, b2_engine* prof = nullptr) {
     const int picks = B * a.topk;
     // whole rows per warp: I / 8 warps / blocks; 32 blocks give two rows per warp at I = 512
-    int gx = std::max(1, std::min((a.I + 2 * WARPS - 1) / (2 * WARPS), (2 * nsm + picks - 1) / picks));
+    const int gx = std::max(1, (a.I + GU_RPW * WARPS - 1) / (GU_RPW * WARPS));   // every warp gets its GU_RPW row pairs
     if (a.D <= 1024) launch_k(k_expert_gu<1>, dim3(gx, picks), THREADS, 0, st, a);
     else launch_k(k_expert_gu<2>, dim3(gx, picks), THREADS, 0, st, a);
     if (prof) prof->mark(5, st);

@@ -653,6 +653,8 @@ struct ProjArgs {
     int N, K;
 };
 
+constexpr int PROJ_RPW = 2;     // rows per warp pair: a block covers 4 * PROJ_RPW rows
+
 template <int MAXC>
 __global__ void __launch_bounds__(THREADS, 2) k_proj_out(const ProjArgs a) {
     extern __shared__ float smem[];
@@ -666,17 +668,18 @@ __global__ void __launch_bounds__(THREADS, 2) k_proj_out(const ProjArgs a) {
     const int row1 = min(a.N, row0 + rows_per_block);
     grid_dep_launch();
 
-    int4 wbuf[MAXC];
-    auto issue = [&](int row) {
+    // every row of this warp pair is requested before anything else: one round trip to HBM, not one per row
+    int4 wbuf[PROJ_RPW][MAXC];
+#pragma unroll
+    for (int u = 0; u < PROJ_RPW; u++) {
+        const int row = row0 + pair + 4 * u;
         const char* p = (const char*)a.w + (size_t)row * a.K + (size_t)half * (a.K >> 1);
 #pragma unroll
         for (int jj = 0; jj < MAXC; jj++) {
             const int c = lane + 32 * jj;
-            wbuf[jj] = c < nchunk_half ? ldw(p + (size_t)c * 16) : make_int4(0, 0, 0, 0);
+            wbuf[u][jj] = (row < row1 && c < nchunk_half) ? ldw(p + (size_t)c * 16) : make_int4(0, 0, 0, 0);
         }
-    };
-    int row = row0 + pair;
-    if (row < row1) issue(row);
+    }
     grid_dep_wait();
 
     const int koff = half * (a.K >> 1);
@@ -710,13 +713,21 @@ __global__ void __launch_bounds__(THREADS, 2) k_proj_out(const ProjArgs a) {
         }
     }
 
-    for (; row < row1; row += 4) {
-        float acc = 0.f;
+    float acc[PROJ_RPW];
 #pragma unroll
-        for (int jj = 0; jj < MAXC; jj++) acc += dot16_i8(wbuf[jj], &xr[jj][0]);
-        if (row + 4 < row1) issue(row + 4);
-        acc = warp_sum(acc);
-        if (lane == 0) part[half * rows_per_block + (row - row0)] = acc;
+    for (int u = 0; u < PROJ_RPW; u++) {
+        acc[u] = 0.f;
+#pragma unroll
+        for (int jj = 0; jj < MAXC; jj++) acc[u] += dot16_i8(wbuf[u][jj], &xr[jj][0]);
+    }
+#pragma unroll
+    for (int u = 0; u < PROJ_RPW; u++) acc[u] = warp_sum(acc[u]);
+    if (lane == 0) {
+#pragma unroll
+        for (int u = 0; u < PROJ_RPW; u++) {
+            const int row = row0 + pair + 4 * u;
+            if (row < row1) part[half * rows_per_block + (row - row0)] = acc[u];
+        }
     }
     __syncthreads();
     for (int r = threadIdx.x; r < row1 - row0; r += THREADS) {
@@ -760,6 +771,8 @@ struct ExpertArgs {
 
 // act[pick][i] = silu(gate_i . h) * (up_i . h), one warp per (gate, up) row pair.
 // grid (blocks per pick, B * topk).
+constexpr int GU_RPW = 2;       // (gate, up) row pairs per warp: the grid is sized so that this covers expert_hidden
+
 template <int MAXC>   // 32-code slices per lane: D <= MAXC * 1024
 __global__ void __launch_bounds__(THREADS, 2) k_expert_gu(const ExpertArgs a) {
     const int pick = blockIdx.y, b = pick / a.topk;
@@ -778,27 +791,28 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_gu(const ExpertArgs a) {
 
     const uint16_t* gs = (const uint16_t*)(base + a.off_gu_s);
     const uint16_t* gm = (const uint16_t*)(base + a.off_gu_m);
-    int4 wg[MAXC], wu[MAXC];
-    uint16_t sg_[MAXC], mg_[MAXC], su_[MAXC], mu_[MAXC];
-    auto issue = [&](int i) {
+    // both (gate, up) row pairs of this warp are requested up front: one round trip to HBM
+    int4 wg[GU_RPW][MAXC], wu[GU_RPW][MAXC];
+    uint16_t sg_[GU_RPW][MAXC], mg_[GU_RPW][MAXC], su_[GU_RPW][MAXC], mu_[GU_RPW][MAXC];
+#pragma unroll
+    for (int u = 0; u < GU_RPW; u++) {
+        const int i = gw + u * TW;
         const uint8_t* pg = base + (size_t)i * (a.D >> 1);
         const uint8_t* pu = base + (size_t)(a.I + i) * (a.D >> 1);
 #pragma unroll
         for (int jj = 0; jj < MAXC; jj++) {
             const int c = lane + 32 * jj;
-            if (c < nchunk) {
-                wg[jj] = ldw(pg + (size_t)c * 16); wu[jj] = ldw(pu + (size_t)c * 16);
+            if (i < a.I && c < nchunk) {
+                wg[u][jj] = ldw(pg + (size_t)c * 16); wu[u][jj] = ldw(pu + (size_t)c * 16);
                 const int g = c >> 1;
-                sg_[jj] = gs[(size_t)i * ngroup + g]; mg_[jj] = gm[(size_t)i * ngroup + g];
-                su_[jj] = gs[(size_t)(a.I + i) * ngroup + g]; mu_[jj] = gm[(size_t)(a.I + i) * ngroup + g];
+                sg_[u][jj] = gs[(size_t)i * ngroup + g]; mg_[u][jj] = gm[(size_t)i * ngroup + g];
+                su_[u][jj] = gs[(size_t)(a.I + i) * ngroup + g]; mu_[u][jj] = gm[(size_t)(a.I + i) * ngroup + g];
             } else {
-                wg[jj] = make_int4(0, 0, 0, 0); wu[jj] = make_int4(0, 0, 0, 0);
-                sg_[jj] = mg_[jj] = su_[jj] = mu_[jj] = 0;
+                wg[u][jj] = make_int4(0, 0, 0, 0); wu[u][jj] = make_int4(0, 0, 0, 0);
+                sg_[u][jj] = mg_[u][jj] = su_[u][jj] = mu_[u][jj] = 0;
             }
         }
-    };
-    int i = gw;
-    if (i < a.I) issue(i);
+    }
 
     // this lane's 32-value slices of norm2(x): slice jj is values [32 * (lane + 32 jj), +32)
     float xr[MAXC][32];
@@ -843,21 +857,27 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_gu(const ExpertArgs a) {
             for (int q = 0; q < 32; q++) xsum[jj] += xr[jj][q];
         }
     }
-    for (; i < a.I; i += TW) {
-        float ag = 0.f, au = 0.f;
+    float ag[GU_RPW], au[GU_RPW];
+#pragma unroll
+    for (int u = 0; u < GU_RPW; u++) {
+        ag[u] = 0.f; au[u] = 0.f;
 #pragma unroll
         for (int jj = 0; jj < MAXC; jj++) {
             // sum code * x = 16 * (sum f * x - sum x), f = 1 + code / 16
-            const float fg = dot32_q4f(wg[jj], &xr[jj][0]);
-            const float fu = dot32_q4f(wu[jj], &xr[jj][0]);
-            ag += h2f(sg_[jj]) * (16.0f * (fg - xsum[jj])) + h2f(mg_[jj]) * xsum[jj];
-            au += h2f(su_[jj]) * (16.0f * (fu - xsum[jj])) + h2f(mu_[jj]) * xsum[jj];
+            const float fg = dot32_q4f(wg[u][jj], &xr[jj][0]);
+            const float fu = dot32_q4f(wu[u][jj], &xr[jj][0]);
+            ag[u] += h2f(sg_[u][jj]) * (16.0f * (fg - xsum[jj])) + h2f(mg_[u][jj]) * xsum[jj];
+            au[u] += h2f(su_[u][jj]) * (16.0f * (fu - xsum[jj])) + h2f(mu_[u][jj]) * xsum[jj];
         }
-        const int done = i;
-        if (i + TW < a.I) issue(i + TW);
-        ag = warp_sum(ag);
-        au = warp_sum(au);
-        if (lane == 0) a.act[(size_t)pick * a.I + done] = siluf_(ag) * au;
+    }
+#pragma unroll
+    for (int u = 0; u < GU_RPW; u++) { ag[u] = warp_sum(ag[u]); au[u] = warp_sum(au[u]); }
+    if (lane == 0) {
+#pragma unroll
+        for (int u = 0; u < GU_RPW; u++) {
+            const int i = gw + u * TW;
+            if (i < a.I) a.act[(size_t)pick * a.I + i] = siluf_(ag[u]) * au[u];
+        }
     }
 }
 
@@ -879,9 +899,13 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) 
         // shared expert: int8 rows of SH values, one warp per row; only for this GPU's own tokens
         if (b < a.local0 || b >= a.local0 + a.nlocal) return;
         const int shchunk = a.SH >> 4;
-        int4 w = make_int4(0, 0, 0, 0);
-        int o = row0 + warp;
-        if (o < row1 && lane < shchunk) w = ldw(a.shd_w + (size_t)o * a.SH + (size_t)lane * 16);
+        constexpr int NIT = DOWN_ROWS / WARPS;        // rows per warp, all requested up front
+        int4 w[NIT];
+#pragma unroll
+        for (int u = 0; u < NIT; u++) {
+            const int o = row0 + warp + WARPS * u;
+            w[u] = (o < row1 && lane < shchunk) ? ldw(a.shd_w + (size_t)o * a.SH + (size_t)lane * 16) : make_int4(0, 0, 0, 0);
+        }
         grid_dep_wait();
         float shx[16];
 #pragma unroll
@@ -890,12 +914,17 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) 
             if (lane < shchunk) t = reinterpret_cast<const float4*>(a.sh_act + (size_t)(b - a.local0) * a.SH + 16 * lane)[q];
             shx[4 * q] = t.x; shx[4 * q + 1] = t.y; shx[4 * q + 2] = t.z; shx[4 * q + 3] = t.w;
         }
-        for (; o < row1; o += WARPS) {
-            float d = dot16_i8(w, shx);
-            const int done = o;
-            if (o + WARPS < row1 && lane < shchunk) w = ldw(a.shd_w + (size_t)(o + WARPS) * a.SH + (size_t)lane * 16);
-            d = warp_sum(d);
-            if (lane == 0) yp[done] = bf(a.shd_s[done]) * d;
+        float d[NIT];
+#pragma unroll
+        for (int u = 0; u < NIT; u++) d[u] = dot16_i8(w[u], shx);
+#pragma unroll
+        for (int u = 0; u < NIT; u++) d[u] = warp_sum(d[u]);
+        if (lane == 0) {
+#pragma unroll
+            for (int u = 0; u < NIT; u++) {
+                const int o = row0 + warp + WARPS * u;
+                if (o < row1) yp[o] = bf(a.shd_s[o]) * d[u];
+            }
         }
     } else {
         grid_dep_wait();
@@ -908,17 +937,18 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) 
             const uint8_t* q4 = base + a.off_dn_q;
             const uint16_t* ds = (const uint16_t*)(base + a.off_dn_s);
             const uint16_t* dm = (const uint16_t*)(base + a.off_dn_m);
-            int4 w = make_int4(0, 0, 0, 0);
-            uint16_t sc = 0, mn = 0;
-            auto issue = [&](int o) {
+            constexpr int NIT = DOWN_ROWS / (2 * WARPS);   // a warp covers two rows at a time; all of them requested up front
+            int4 w[NIT];
+            uint16_t sc[NIT], mn[NIT];
+#pragma unroll
+            for (int u = 0; u < NIT; u++) {
+                const int o = row0 + 2 * warp + hw + 2 * WARPS * u;
                 if (o < row1 && hl < nchunk) {
-                    w = ldw(q4 + (size_t)o * (a.I >> 1) + (size_t)hl * 16);
-                    sc = ds[(size_t)o * ngroup + (hl >> 1)];
-                    mn = dm[(size_t)o * ngroup + (hl >> 1)];
-                } else { w = make_int4(0, 0, 0, 0); sc = 0; mn = 0; }
-            };
-            int o = row0 + 2 * warp + hw;             // a warp covers two rows at a time
-            issue(o);
+                    w[u] = ldw(q4 + (size_t)o * (a.I >> 1) + (size_t)hl * 16);
+                    sc[u] = ds[(size_t)o * ngroup + (hl >> 1)];
+                    mn[u] = dm[(size_t)o * ngroup + (hl >> 1)];
+                } else { w[u] = make_int4(0, 0, 0, 0); sc[u] = 0; mn[u] = 0; }
+            }
             float xv[32];
             float xsum = 0.f;
             const float* ar = a.act + ((size_t)b * a.topk + r) * a.I + 32 * hl;
@@ -929,14 +959,23 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) 
                 xv[4 * q] = t.x; xv[4 * q + 1] = t.y; xv[4 * q + 2] = t.z; xv[4 * q + 3] = t.w;
                 xsum += t.x + t.y + t.z + t.w;
             }
-            for (; o - hw < row1; o += 2 * WARPS) {
-                const float f = dot32_q4f(w, xv);
-                float d = h2f(sc) * (16.0f * (f - xsum)) + h2f(mn) * xsum;
-                const int done = o;
-                issue(o + 2 * WARPS);
+            float d[NIT];
 #pragma unroll
-                for (int off = 8; off > 0; off >>= 1) d += __shfl_xor_sync(0xffffffffu, d, off);
-                if (hl == 0 && done < row1) yp[done] = d;
+            for (int u = 0; u < NIT; u++) {
+                const float f = dot32_q4f(w[u], xv);
+                d[u] = h2f(sc[u]) * (16.0f * (f - xsum)) + h2f(mn[u]) * xsum;
+            }
+#pragma unroll
+            for (int u = 0; u < NIT; u++) {
+#pragma unroll
+                for (int off = 8; off > 0; off >>= 1) d[u] += __shfl_xor_sync(0xffffffffu, d[u], off);
+            }
+            if (hl == 0) {
+#pragma unroll
+                for (int u = 0; u < NIT; u++) {
+                    const int o = row0 + 2 * warp + hw + 2 * WARPS * u;
+                    if (o < row1) yp[o] = d[u];
+                }
             }
         } else {
             if (e < 0 || e >= a.E) { if (threadIdx.x == 0) atomicExch(a.err, 2); }
