@@ -94,6 +94,8 @@ static size_t dtype_size(const std::string& d) {
 }
 
 // Blocks per SM of the streaming GEMV kernel (B2_GEMV_CTAS overrides; for experiments).
+// Row-per-lane GEMV kernel (k_rowgemv) instead of the row-per-warp one (B2_ROWGEMV=0 switches back).
+static bool g_rowgemv = [] { const char* v = getenv("B2_ROWGEMV"); return !(v && v[0] == '0'); }();
 static int g_gemv_ctas_per_sm = [] { const char* v = getenv("B2_GEMV_CTAS"); return v ? atoi(v) : 2; }();
 static int down_row_blocks(int D) { return (D + DOWN_ROWS - 1) / DOWN_ROWS; }
 
@@ -454,7 +456,7 @@ int b2_engine::finish() {
     const size_t Bg = (size_t)B * ep_world;   // sequences whose picks may land on this GPU's experts
     CU(dalloc(&act, Bg * c.TOPK * c.I)); CU(dalloc(&logits, (size_t)B * c.V));
     CU(dalloc(&top_idx, (size_t)c.L * B * c.TOPK)); CU(dalloc(&top_w, (size_t)c.L * B * c.TOPK));
-    head_grid = std::min((c.V + 7) / 8, g_gemv_ctas_per_sm * nsm);
+    head_grid = g_rowgemv ? std::min((c.V + 31) / 32, nsm) : std::min((c.V + 7) / 8, g_gemv_ctas_per_sm * nsm);
     CU(dalloc(&part_val, (size_t)B * head_grid)); CU(dalloc(&part_idx, (size_t)B * head_grid));
     // attention: enough slices to fill the GPU, but at least 64 positions each at full context
     nsplit = std::max(1, std::min({64, (2 * nsm) / std::max(1, c.KV * B), (cap + 63) / 64}));
@@ -507,13 +509,28 @@ static cudaError_t opt_in_smem(F* f, size_t bytes) {
     return cudaFuncSetAttribute((const void*)f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
 
-static cudaError_t launch_gemv(const GemvArgs& a, int B, int nsm, cudaStream_t st, int grid_override = 0) {
-    // one block per SM (the ring of one block is 96 KB, so the next kernel of the stream fits beside it)
+static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t st, int grid_override = 0) {
+    GemvArgs a = a0;
+    if (a.x_stride == 0) a.x_stride = a.K;
+    cudaError_t e;
+    if (g_rowgemv) {
+        // one block of 1024 threads per SM, NB sequences per pass
+        const int grid = grid_override ? grid_override : std::max(1, std::min(a.total_jobs, nsm));
+        if (B >= 2) {
+            const size_t smem = (size_t)2 * RL_STAGE_BYTES + (size_t)4 * a.K * 4 + (size_t)2 * 4 * RL_WARPS * 32 * 4;
+            e = opt_in_smem(k_rowgemv<4, 2>, smem);
+            if (e == cudaSuccess) e = launch_k(k_rowgemv<4, 2>, dim3(grid, (B + 3) / 4), RL_THREADS, smem, st, a, B);
+        } else {
+            const size_t smem = (size_t)3 * RL_STAGE_BYTES + (size_t)a.K * 4 + (size_t)2 * RL_WARPS * 32 * 4;
+            e = opt_in_smem(k_rowgemv<1, 3>, smem);
+            if (e == cudaSuccess) e = launch_k(k_rowgemv<1, 3>, dim3(grid, 1), RL_THREADS, smem, st, a, B);
+        }
+        return e;
+    }
     const int grid = grid_override ? grid_override : std::max(1, std::min(a.total_jobs, g_gemv_ctas_per_sm * nsm));
     const size_t smem = (size_t)RING_STAGES * RING_STAGE_BYTES;
     const int maxc = (a.K + 511) / 512;
     dim3 g(grid, B);
-    cudaError_t e;
     if (maxc <= 1) { e = opt_in_smem(k_gemv_norm<1>, smem); if (e == cudaSuccess) e = launch_k(k_gemv_norm<1>, g, GEMV_THREADS, smem, st, a); }
     else if (maxc == 2) { e = opt_in_smem(k_gemv_norm<2>, smem); if (e == cudaSuccess) e = launch_k(k_gemv_norm<2>, g, GEMV_THREADS, smem, st, a); }
     else { e = opt_in_smem(k_gemv_norm<4>, smem); if (e == cudaSuccess) e = launch_k(k_gemv_norm<4>, g, GEMV_THREADS, smem, st, a); }
@@ -523,15 +540,36 @@ static cudaError_t launch_gemv(const GemvArgs& a, int B, int nsm, cudaStream_t s
 static Seg make_seg(int kind, const void* w, const uint16_t* s, int rows, float* out, int out_stride) {
     Seg g{};
     g.w = w; g.s = s; g.rows = rows; g.kind = kind; g.out = out; g.out_stride = out_stride;
-    g.jobs = (kind == SEG_I8 || kind == SEG_I8_CONV || kind == SEG_I8_ARGMAX || kind == SEG_I8_SILU) ? (rows + 7) / 8 : (rows + 3) / 4;
+    g.jobs = 0;   // tiles: filled by seal(), which knows K
     return g;
 }
-static void seal(GemvArgs& a) {
+static void seal(GemvArgs& a, int K) {
+    a.K = K;
     a.total_jobs = 0;
-    for (int i = 0; i < a.nseg; i++) a.total_jobs += a.seg[i].jobs;
+    for (int i = 0; i < a.nseg; i++) {
+        Seg& g = a.seg[i];
+        const bool i8 = g.kind == SEG_I8 || g.kind == SEG_I8_CONV || g.kind == SEG_I8_ARGMAX || g.kind == SEG_I8_SILU || g.kind == SEG_I8_ACC;
+        if (g_rowgemv) g.jobs = (g.rows + rl_tile_rows(g.kind, K) - 1) / rl_tile_rows(g.kind, K);
+        else g.jobs = i8 ? (g.rows + 7) / 8 : (g.rows + 3) / 4;
+        a.total_jobs += g.jobs;
+    }
 }
 
+static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t st, int grid_override);
+static void seal(GemvArgs& a, int K);
+static Seg make_seg(int kind, const void* w, const uint16_t* s, int rows, float* out, int out_stride);
+
 static void launch_proj(const ProjArgs& a, int B, int nsm, cudaStream_t st) {
+    if (g_rowgemv) {
+        GemvArgs g{};
+        g.seg[0] = make_seg(SEG_I8_ACC, a.w, a.s, a.N, a.x, a.N);
+        g.nseg = 1;
+        seal(g, a.K);
+        g.x = a.in; g.x_stride = a.K; g.norm_w = nullptr; g.eps = a.eps;
+        if (a.mode == 0) { g.gn_w = a.gn_w; g.z = a.z; g.DV = a.DV; }
+        launch_gemv(g, B, nsm, st, 0);
+        return;
+    }
     // rows per block a multiple of 4 (four warp pairs per block), one wave of blocks
     const int rpb = 4 * PROJ_RPW;     // the kernel covers exactly this many rows per block
     const int grid = (a.N + rpb - 1) / rpb;
@@ -594,7 +632,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.seg[0] = make_seg(SEG_I8, l.q.w, l.q.s, l.q.n, big, 2 * c.H * c.HD);
             a.seg[1] = make_seg(SEG_I8, l.k.w, l.k.s, l.k.n, kraw, c.KV * c.HD);
             a.seg[2] = make_seg(SEG_I8, l.v.w, l.v.s, l.v.n, vraw, c.KV * c.HD);
-            a.nseg = 3; seal(a);
+            a.nseg = 3; seal(a, c.D);
             a.x = x; a.norm_w = l.norm1; a.eps = c.eps; a.K = c.D; a.err = d_err;
             launch_gemv(a, B, nsm, st);
             mark(1, st);
@@ -617,7 +655,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.seg[1] = make_seg(SEG_I8_SILU, l.in_z.w, l.in_z.s, l.in_z.n, zbuf, c.VD());
             a.seg[2] = make_seg(SEG_BF_SIGMOID, l.in_b, nullptr, c.HV, beta, c.HV);
             a.seg[3] = make_seg(SEG_BF_DECAY, l.in_a, nullptr, c.HV, gdec, c.HV);
-            a.nseg = 4; seal(a);
+            a.nseg = 4; seal(a, c.D);
             a.x = x; a.norm_w = l.norm1; a.eps = c.eps; a.K = c.D; a.err = d_err;
             a.conv_w = l.conv; a.conv_state = conv + (size_t)l.slot * B * c.C() * 3;
             a.a_log = l.a_log; a.dt_bias = l.dt_bias;
@@ -642,7 +680,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.seg[1] = make_seg(SEG_I8_GATEUP, l.sh_gate.w, l.sh_gate.s, c.SH, sh_act, c.SH);
             a.seg[1].w2 = l.sh_up.w; a.seg[1].s2 = l.sh_up.s;
             a.seg[2] = make_seg(SEG_BF_SIGMOID, l.sh_gw, nullptr, 1, sgate, 1);
-            a.nseg = 3; seal(a);
+            a.nseg = 3; seal(a, c.D);
             a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D; a.err = d_err;
             a.finisher = FIN_TOPK; a.counter = d_counter; a.E = c.E; a.topk = c.TOPK;
             a.top_idx = top_idx + (size_t)li * B * c.TOPK; a.top_w = top_w + (size_t)li * B * c.TOPK;
@@ -681,7 +719,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
     {
         GemvArgs a{};
         a.seg[0] = make_seg(SEG_I8_ARGMAX, lm_head.w, lm_head.s, c.V, logits, c.V);
-        a.nseg = 1; seal(a);
+        a.nseg = 1; seal(a, c.D);
         a.x = x; a.norm_w = norm; a.eps = c.eps; a.K = c.D; a.err = d_err;
         a.finisher = FIN_ARGMAX; a.counter = d_counter; a.part_val = part_val; a.part_idx = part_idx;
         a.next_tok = d_next; a.pos = d_pos;

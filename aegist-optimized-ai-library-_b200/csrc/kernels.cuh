@@ -202,7 +202,8 @@ enum SegKind : int {
     SEG_BF = 4,        // bf16 rows, out = dot (+ bias[row] if given)
     SEG_I8_GATEUP = 5, // two int8 matrices, out = silu(s1 * dot1) * (s2 * dot2)
     SEG_I8_ARGMAX = 6, // int8 rows, out = scale * dot, and the arg-max over all rows
-    SEG_I8_SILU = 7    // int8 rows, out = silu(scale * dot)
+    SEG_I8_SILU = 7,   // int8 rows, out = silu(scale * dot)
+    SEG_I8_ACC = 8     // int8 rows, out += scale * dot (a projection back into the residual stream)
 };
 enum Finisher : int { FIN_NONE = 0, FIN_TOPK = 1, FIN_ARGMAX = 2 };
 
@@ -223,10 +224,15 @@ struct GemvArgs {
     Seg seg[4];
     int nseg;
     int total_jobs;
-    const float* x;          // [B][K] residual stream
+    const float* x;          // [B][x_stride] residual stream
+    int x_stride;            // row stride of x (the host sets K when it is left 0)
     const uint16_t* norm_w;  // [K]
     float eps;
     int K;
+    // gated RMSNorm prologue instead of the ZNorm one (k_rowgemv only): x holds o, z holds silu(z)
+    const uint16_t* gn_w;    // [DV] or null
+    const float* z;          // [B][x_stride]
+    int DV;
     // SEG_I8_CONV
     const uint16_t* conv_w;  // [C][4]
     float* conv_state;       // [B][C][3], oldest first
@@ -543,6 +549,10 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv_norm(const GemvArgs a)
     }
     if (threadIdx.x == 0) a.counter[b] = 0;
 }
+
+}  // namespace b2
+#include "rowgemv.cuh"
+namespace b2 {
 
 // ------------------------------------------------------------------------------------------
 // k_delta_step: L2-normalise q and k, then one step of the gated delta rule on a [DK x 32] column
@@ -1139,19 +1149,24 @@ __global__ void __launch_bounds__(THREADS) k_attn(const AttnArgs a) {
         }
     }
 
+    // scores are kept in the base-2 domain: q carries 1/sqrt(HD) * log2(e), so p = 2^(s - m)
     float q[MAXG][DPL];
 #pragma unroll
     for (int g = 0; g < MAXG; g++)
 #pragma unroll
-        for (int i = 0; i < DPL; i++) q[g][i] = g < G ? qs[g][lane * DPL + i] * a.scale : 0.f;
-    float m[MAXG], l[MAXG], acc[MAXG][DPL];
+        for (int i = 0; i < DPL; i++) q[g][i] = g < G ? qs[g][lane * DPL + i] * (a.scale * 1.4426950408889634f) : 0.f;
+    // running max and sum of head (lane >> 2), the same in the four lanes of a head; acc[g][i] in every lane
+    float m_run = -INFINITY, l_run = 0.f;
+    float acc[MAXG][DPL];
 #pragma unroll
-    for (int g = 0; g < MAXG; g++) {
-        m[g] = -INFINITY; l[g] = 0.f;
+    for (int g = 0; g < MAXG; g++)
 #pragma unroll
         for (int i = 0; i < DPL; i++) acc[g][i] = 0.f;
-    }
-    // each lane owns DPL consecutive dims of a row: one 16-byte (bf16, HD 256) load per key
+    const int hg = lane >> 2, pu = lane & 3;
+    // each lane owns DPL consecutive dims of a row: one 16-byte (bf16, HD 256) load per key.
+    // Four positions at a time: 32 partial scores (8 heads x 4 positions) per lane are summed over the
+    // lanes by a halving exchange (31 shuffles) that leaves score j in lane j; the softmax bookkeeping
+    // is then one value per lane instead of 32 values in every lane.
     const int per_warp = chunk / WARPS;
     const int w0 = p0 + warp * per_warp, w1 = min(p1, w0 + per_warp);
     for (int pb = w0; pb < w1; pb += ATT_PPW) {
@@ -1172,24 +1187,50 @@ __global__ void __launch_bounds__(THREADS) k_attn(const AttnArgs a) {
                 }
             }
         }
+        float sp[32];
 #pragma unroll
-        for (int u = 0; u < ATT_PPW; u++) {
-            if (pb + u < w1) {
+        for (int g = 0; g < MAXG; g++)
 #pragma unroll
-                for (int g = 0; g < MAXG; g++) {
-                    if (g < G) {
-                        float s = 0.f;
+            for (int u = 0; u < ATT_PPW; u++) {
+                float s = 0.f;
 #pragma unroll
-                        for (int i = 0; i < DPL; i++) s = fmaf(q[g][i], kk[u][i], s);
-                        s = warp_sum(s);
-                        const float mn = fmaxf(m[g], s);
-                        const float corr = expf(m[g] - mn);
-                        const float pe = expf(s - mn);
-                        l[g] = l[g] * corr + pe;
+                for (int i = 0; i < DPL; i++) s = fmaf(q[g][i], kk[u][i], s);
+                sp[g * 4 + u] = s;
+            }
+        // halving exchange: after the step with offset o a lane keeps the half of the values whose index
+        // has the same bit o as its lane number
 #pragma unroll
-                        for (int i = 0; i < DPL; i++) acc[g][i] = fmaf(pe, vv[u][i], acc[g][i] * corr);
-                        m[g] = mn;
-                    }
+        for (int o = 16, n = 16; o > 0; o >>= 1, n >>= 1) {
+            const bool up = (lane & o) != 0;
+#pragma unroll
+            for (int i = 0; i < n; i++) {
+                const float send = up ? sp[i] : sp[i + n];
+                const float keep = up ? sp[i + n] : sp[i];
+                sp[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+            }
+        }
+        const bool valid = hg < G && pb + pu < w1;
+        const float s = valid ? sp[0] : -INFINITY;          // score of head hg, position pb + pu
+        float mx = fmaxf(s, __shfl_xor_sync(0xffffffffu, s, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(m_run, mx);
+        const float corr = m_new == -INFINITY ? 1.0f : exp2f(m_run - m_new);
+        const float pe = valid ? exp2f(s - m_new) : 0.f;
+        float ps = pe + __shfl_xor_sync(0xffffffffu, pe, 1);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        l_run = l_run * corr + ps;
+        m_run = m_new;
+#pragma unroll
+        for (int g = 0; g < MAXG; g++) {
+            if (g < G) {
+                const float cg = __shfl_sync(0xffffffffu, corr, 4 * g);
+#pragma unroll
+                for (int i = 0; i < DPL; i++) acc[g][i] *= cg;
+#pragma unroll
+                for (int u = 0; u < ATT_PPW; u++) {
+                    const float pg = __shfl_sync(0xffffffffu, pe, 4 * g + u);
+#pragma unroll
+                    for (int i = 0; i < DPL; i++) acc[g][i] = fmaf(pg, vv[u][i], acc[g][i]);
                 }
             }
         }
@@ -1198,7 +1239,9 @@ __global__ void __launch_bounds__(THREADS) k_attn(const AttnArgs a) {
 #pragma unroll
     for (int g = 0; g < MAXG; g++) {
         if (g < G) {
-            if (lane == 0) { m_s[warp][g] = m[g]; l_s[warp][g] = l[g]; }
+            const float mg = __shfl_sync(0xffffffffu, m_run, 4 * g);
+            const float lg = __shfl_sync(0xffffffffu, l_run, 4 * g);
+            if (lane == 0) { m_s[warp][g] = mg; l_s[warp][g] = lg; }
 #pragma unroll
             for (int i = 0; i < DPL; i++) accs[((size_t)warp * G + g) * HD + lane * DPL + i] = acc[g][i];
         }
@@ -1210,7 +1253,7 @@ __global__ void __launch_bounds__(THREADS) k_attn(const AttnArgs a) {
         for (int w = 0; w < WARPS; w++) mx = fmaxf(mx, m_s[w][g]);
         float cw[WARPS];
 #pragma unroll
-        for (int w = 0; w < WARPS; w++) cw[w] = m_s[w][g] == -INFINITY ? 0.f : expf(m_s[w][g] - mx);
+        for (int w = 0; w < WARPS; w++) cw[w] = m_s[w][g] == -INFINITY ? 0.f : exp2f(m_s[w][g] - mx);
         for (int d = threadIdx.x; d < HD; d += THREADS) {
             float s = 0.f;
 #pragma unroll
@@ -1227,7 +1270,8 @@ __global__ void __launch_bounds__(THREADS) k_attn(const AttnArgs a) {
     }
 }
 
-// out[b][head][d] = (sum_s acc_s[d] * e^(m_s - m)) / (sum_s l_s * e^(m_s - m)) * sigmoid(gate[d]).
+// out[b][head][d] = (sum_s acc_s[d] * 2^(m_s - m)) / (sum_s l_s * 2^(m_s - m)) * sigmoid(gate[d])
+// (the slices keep their maxima in the base-2 domain).
 // grid (H, B), one thread per dim (strided when HD > blockDim).
 __global__ void __launch_bounds__(THREADS) k_attn_merge(const AttnArgs a, int HD) {
     const int head = blockIdx.x, b = blockIdx.y;
@@ -1254,8 +1298,8 @@ __global__ void __launch_bounds__(THREADS) k_attn_merge(const AttnArgs a, int HD
         float lsum = 0.f;
 #pragma unroll
         for (int u = 0; u < 2; u++) {
-            const float c = ms[u] == -INFINITY ? 0.f : expf(ms[u] - mx);
-            if (lane + 32 * u < 64) sc[lane + 32 * u] = c;
+            const float c = ms[u] == -INFINITY ? 0.f : exp2f(ms[u] - mx);
+            sc[lane + 32 * u] = (lane + 32 * u < a.nsplit) ? c : 0.f;
             lsum += ls[u] * c;
         }
         lsum = warp_sum(lsum);
@@ -1263,16 +1307,13 @@ __global__ void __launch_bounds__(THREADS) k_attn_merge(const AttnArgs a, int HD
     }
     __syncthreads();
     for (int d = threadIdx.x; d < HD; d += THREADS) {
+        // all slices are requested at once (one round trip), then summed in slice order
+        float v[64];
+#pragma unroll
+        for (int s = 0; s < 64; s++) v[s] = (s < a.nsplit && sc[s] != 0.f) ? pb[s * sstride + d] : 0.f;
         float acc = 0.f;
-        int s = 0;
-        for (; s + 8 <= a.nsplit; s += 8) {
-            float v[8];
 #pragma unroll
-            for (int u = 0; u < 8; u++) v[u] = sc[s + u] != 0.f ? pb[(s + u) * sstride + d] : 0.f;
-#pragma unroll
-            for (int u = 0; u < 8; u++) acc = fmaf(v[u], sc[s + u], acc);
-        }
-        for (; s < a.nsplit; s++) if (sc[s] != 0.f) acc = fmaf(pb[s * sstride + d], sc[s], acc);
+        for (int s = 0; s < 64; s++) acc = fmaf(v[s], sc[s], acc);
         const float gate = a.qraw[((size_t)b * a.H + head) * 2 * HD + HD + d];
         a.out[(size_t)b * a.H * HD + head * HD + d] = (acc * s_inv) * sigmoidf_(gate);
     }

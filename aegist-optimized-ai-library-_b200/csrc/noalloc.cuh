@@ -101,7 +101,7 @@ extern "C" int b2_moe_forward_static(const b2_moe_device_weights* w, const float
     a.seg[1] = make_seg(SEG_I8_GATEUP, w->sh_gate_q, w->sh_gate_s, c.SH, s + NA_SHACT, c.SH);
     a.seg[1].w2 = w->sh_up_q; a.seg[1].s2 = w->sh_up_s;
     a.seg[2] = make_seg(SEG_BF_SIGMOID, w->shared_gate_bf16, nullptr, 1, s + NA_SGATE, 1);
-    a.nseg = 3; seal(a);
+    a.nseg = 3; seal(a, c.D);
     a.x = h; a.norm_w = nullptr; a.K = c.D; a.err = (int*)(s + NA_ERR);
     a.finisher = FIN_TOPK; a.counter = (unsigned int*)(s + NA_COUNTER); a.E = c.E; a.topk = c.TOPK; a.top_idx = top_idx; a.top_w = top_w;
     OPCU(launch_gemv(a, tokens, nsm, st));

@@ -61,8 +61,8 @@ int b2_op_linear_i8(int device, const int8_t* q, const uint16_t* scale, int n, i
     if (k <= 2048) {
         GemvArgs a{};
         a.seg[0] = make_seg(SEG_I8, dq, ds, n, dy, n);
-        a.nseg = 1; seal(a);
-        a.x = dx; a.norm_w = nullptr; a.K = k;
+        a.nseg = 1; seal(a, k);
+        a.x = dx; a.norm_w = nullptr;
         launch_gemv(a, tokens, prop.multiProcessorCount, 0);
     } else {
         ProjArgs p{};
@@ -122,7 +122,7 @@ int b2_moe_forward(b2_moe* m, const float* h, int tokens, float* y, int32_t* idx
     a.seg[1] = make_seg(SEG_I8_GATEUP, m->sg_q, m->sg_s, c.SH, m->sh_act, c.SH);
     a.seg[1].w2 = m->su_q; a.seg[1].s2 = m->su_s;
     a.seg[2] = make_seg(SEG_BF_SIGMOID, m->shared_gate, nullptr, 1, m->sgate, 1);
-    a.nseg = 3; seal(a);
+    a.nseg = 3; seal(a, c.D);
     a.x = m->h; a.norm_w = nullptr; a.K = c.D;
     a.finisher = FIN_TOPK; a.counter = m->counter; a.E = c.E; a.topk = c.TOPK; a.top_idx = m->top_idx; a.top_w = m->top_w;
     launch_gemv(a, tokens, m->nsm, m->st);
