@@ -145,6 +145,8 @@ struct b2_engine {
     float* part_val = nullptr;
     int* part_idx = nullptr;
     float* attn_part = nullptr;
+    __half* xh = nullptr;                    // [Tpad][2][4096] fp16 activations for the tensor-core path
+    int xh_tpad = 0;
     float* ypart = nullptr;                  // [B][TOPK + 1][D]
     unsigned int* d_dcounter = nullptr;      // [B][row blocks of the expert down projection]
     int nsplit = 1, head_grid = 1;
@@ -214,7 +216,7 @@ b2_engine::~b2_engine() {
     for (auto& l : layers) { cudaFree((void*)l.eptr); cudaFree(l.router_bias); }
     void* bufs[] = {conv, state, snap_conv[0], snap_conv[1], snap_state[0], snap_state[1], kpool, vpool, page_table, rope_cos,
                     rope_sin, d_tok, d_next, d_pos, d_err, d_counter, d_acounter, x, big, zbuf, kraw, vraw, beta, gdec, obuf, att,
-                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y};
+                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh};
     for (void* p : bufs) cudaFree(p);
     if (h_pin) cudaFreeHost(h_pin);
     if (ev0) cudaEventDestroy(ev0);
@@ -461,6 +463,10 @@ int b2_engine::finish() {
     // attention: enough slices to fill the GPU, but at least 64 positions each at full context
     nsplit = std::max(1, std::min({64, (2 * nsm) / std::max(1, c.KV * B), (cap + 63) / 64}));
     CU(dalloc(&attn_part, (size_t)B * c.KV * nsplit * (c.H / c.KV) * (c.HD + 2)));
+    if (B >= 8) {
+        xh_tpad = (B + MM_TOK - 1) / MM_TOK * MM_TOK;
+        CU(dalloc((uint16_t**)&xh, (size_t)xh_tpad * 2 * 4096));
+    }
     CU(dalloc(&ypart, Bg * (c.TOPK + 1) * c.D));
     CU(dalloc(&d_dcounter, Bg * down_row_blocks(c.D)));
     if (ep_world > 1) {
@@ -488,8 +494,11 @@ int b2_engine::finish() {
 // Programmatic dependent launch for every kernel of a step (B2_PDL=0 turns it off).
 static bool g_pdl = [] { const char* v = getenv("B2_PDL"); return !(v && v[0] == '0'); }();
 
+static int g_launch_count = 0;   // kernels launched so far (a step's count is the difference)
+
 template <typename... KArgs, typename... Args>
 static cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+    g_launch_count++;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -509,10 +518,52 @@ static cudaError_t opt_in_smem(F* f, size_t bytes) {
     return cudaFuncSetAttribute((const void*)f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
 
-static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t st, int grid_override = 0) {
+// Tensor-core path for 8 or more sequences (B2_MMA=0 switches it off): scratch for the fp16 activations.
+static bool g_mma = [] { const char* v = getenv("B2_MMA"); return !(v && v[0] == '0'); }();
+struct BatchCtx { __half* xh; int Tpad; };
+static void seal(GemvArgs& a, int K);
+
+static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t st, int grid_override = 0,
+                               const BatchCtx* bc = nullptr) {
     GemvArgs a = a0;
     if (a.x_stride == 0) a.x_stride = a.K;
     cudaError_t e;
+    if (g_rowgemv && g_mma && bc && bc->xh && B >= 8 && B <= bc->Tpad && a.K % MM_KC == 0) {
+        // int8 matrices (except the head with its arg-max) go to the tensor cores; bf16 rows stay on k_rowgemv
+        MmaArgs m{};
+        GemvArgs rest = a;
+        rest.nseg = 0;
+        for (int i = 0; i < a.nseg; i++) {
+            const Seg& g = a.seg[i];
+            const bool i8 = g.kind == SEG_I8 || g.kind == SEG_I8_CONV || g.kind == SEG_I8_SILU || g.kind == SEG_I8_ACC || g.kind == SEG_I8_GATEUP;
+            if (i8 && m.nseg < 3) {
+                MmaSeg& d = m.seg[m.nseg++];
+                d.w = (const int8_t*)g.w; d.s = g.s; d.w2 = (const int8_t*)g.w2; d.s2 = g.s2; d.out = g.out; d.rows = g.rows;
+                d.kind = g.kind; d.out_stride = g.out_stride;
+                const int rpb = g.kind == SEG_I8_GATEUP ? MM_ROWS / 2 : MM_ROWS;
+                d.blocks = (g.rows + rpb - 1) / rpb;
+                m.total_blocks += d.blocks;
+            } else {
+                rest.seg[rest.nseg++] = g;
+            }
+        }
+        if (m.nseg > 0) {
+            PrepArgs p{};
+            p.x = a.x; p.x_stride = a.x_stride; p.norm_w = a.norm_w; p.gn_w = a.gn_w; p.z = a.z; p.DV = a.DV; p.eps = a.eps;
+            p.K = a.K; p.T = B; p.out = bc->xh; p.Tpad = (B + MM_TOK - 1) / MM_TOK * MM_TOK;
+            e = launch_k(k_prep_x, dim3(p.Tpad), dim3(256), 0, st, p);
+            if (e != cudaSuccess) return e;
+            m.xh = bc->xh; m.K = a.K; m.T = B; m.conv_w = a.conv_w; m.conv_state = a.conv_state;
+            const size_t smem = (size_t)MM_STAGES * MM_STAGE_BYTES;
+            e = opt_in_smem(k_mma_i8, smem);
+            if (e == cudaSuccess) e = launch_k(k_mma_i8, dim3(m.total_blocks, p.Tpad / MM_TOK), dim3(MM_THREADS), smem, st, m);
+            if (e != cudaSuccess) return e;
+            if (rest.nseg == 0) return cudaSuccess;
+            seal(rest, a.K);
+            a = rest;
+            grid_override = 0;
+        }
+    }
     if (g_rowgemv) {
         // one block of 1024 threads per SM, NB sequences per pass
         const int grid = grid_override ? grid_override : std::max(1, std::min(a.total_jobs, nsm));
@@ -555,11 +606,10 @@ static void seal(GemvArgs& a, int K) {
     }
 }
 
-static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t st, int grid_override);
 static void seal(GemvArgs& a, int K);
 static Seg make_seg(int kind, const void* w, const uint16_t* s, int rows, float* out, int out_stride);
 
-static void launch_proj(const ProjArgs& a, int B, int nsm, cudaStream_t st) {
+static void launch_proj(const ProjArgs& a, int B, int nsm, cudaStream_t st, const BatchCtx* bc = nullptr) {
     if (g_rowgemv) {
         GemvArgs g{};
         g.seg[0] = make_seg(SEG_I8_ACC, a.w, a.s, a.N, a.x, a.N);
@@ -567,7 +617,7 @@ static void launch_proj(const ProjArgs& a, int B, int nsm, cudaStream_t st) {
         seal(g, a.K);
         g.x = a.in; g.x_stride = a.K; g.norm_w = nullptr; g.eps = a.eps;
         if (a.mode == 0) { g.gn_w = a.gn_w; g.z = a.z; g.DV = a.DV; }
-        launch_gemv(g, B, nsm, st, 0);
+        launch_gemv(g, B, nsm, st, 0, bc);
         return;
     }
     // rows per block a multiple of 4 (four warp pairs per block), one wave of blocks
@@ -619,6 +669,9 @@ static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaS
 // One decode step for all B sequences: token ids in d_tok, positions in d_pos.
 int b2_engine::enqueue_step(cudaStream_t st, bool count) {
     int n = 0;
+    const int launches0 = g_launch_count;
+    const BatchCtx bctx{xh, xh_tpad};
+    const BatchCtx* bc = xh ? &bctx : nullptr;
     cudaGetLastError();   // a stale error of an earlier, unrelated call must not be blamed on these launches
     mark(-1, st);
     launch_k(k_embed, dim3(B), dim3(256), 0, st, embed, (const int*)d_tok, x, c.D, c.V, d_err);
@@ -634,7 +687,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.seg[2] = make_seg(SEG_I8, l.v.w, l.v.s, l.v.n, vraw, c.KV * c.HD);
             a.nseg = 3; seal(a, c.D);
             a.x = x; a.norm_w = l.norm1; a.eps = c.eps; a.K = c.D; a.err = d_err;
-            launch_gemv(a, B, nsm, st);
+            launch_gemv(a, B, nsm, st, 0, bc);
             mark(1, st);
             AttnArgs t{};
             t.qraw = big; t.kraw = kraw; t.vraw = vraw; t.qn_w = l.q_norm; t.kn_w = l.k_norm;
@@ -648,7 +701,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             mark(3, st);
             ProjArgs p{};
             p.in = att; p.mode = 1; p.w = l.o.w; p.s = l.o.s; p.x = x; p.N = c.D; p.K = c.H * c.HD; p.eps = c.eps; p.DV = c.DV;
-            launch_proj(p, B, nsm, st);
+            launch_proj(p, B, nsm, st, bc);
         } else {
             GemvArgs a{};
             a.seg[0] = make_seg(SEG_I8_CONV, l.in_qkv.w, l.in_qkv.s, l.in_qkv.n, big, c.C());
@@ -659,7 +712,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.x = x; a.norm_w = l.norm1; a.eps = c.eps; a.K = c.D; a.err = d_err;
             a.conv_w = l.conv; a.conv_state = conv + (size_t)l.slot * B * c.C() * 3;
             a.a_log = l.a_log; a.dt_bias = l.dt_bias;
-            launch_gemv(a, B, nsm, st);
+            launch_gemv(a, B, nsm, st, 0, bc);
             mark(1, st);
             DeltaArgs d{};
             d.y = big; d.beta = beta; d.g = gdec; d.state = state + (size_t)l.slot * B * c.HV * c.DK * c.DV;
@@ -669,7 +722,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             ProjArgs p{};
             p.in = obuf; p.z = zbuf; p.gn_w = l.gnorm; p.eps = c.eps; p.DV = c.DV; p.mode = 0;
             p.w = l.out.w; p.s = l.out.s; p.x = x; p.N = c.D; p.K = c.VD();
-            launch_proj(p, B, nsm, st);
+            launch_proj(p, B, nsm, st, bc);
         }
         mark(4, st);
         n += l.attn ? 4 : 3;
@@ -684,7 +737,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D; a.err = d_err;
             a.finisher = FIN_TOPK; a.counter = d_counter; a.E = c.E; a.topk = c.TOPK;
             a.top_idx = top_idx + (size_t)li * B * c.TOPK; a.top_w = top_w + (size_t)li * B * c.TOPK;
-            launch_gemv(a, B, nsm, st);
+            launch_gemv(a, B, nsm, st, 0, bc);
             mark(1, st);
             ExpertArgs x2{};
             x2.eptr = l.eptr; x2.topk = c.TOPK; x2.E = c.E; x2.D = c.D; x2.I = c.I;
@@ -727,7 +780,8 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
         mark(7, st);
         n++;
     }
-    if (count) launches = n;
+    (void)n;
+    if (count) launches = g_launch_count - launches0;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail("kernel launch: %s", cudaGetErrorString(e));
     return 0;

@@ -1,0 +1,270 @@
+// Batched decode (8 or more sequences per GPU): the int8 linears as a tensor-core contraction.
+//
+// With B sequences the linears are [rows x K] x [K x B] products: real dense contractions, and on
+// CUDA cores they are bound by the FMA rate, not by HBM (64 sequences x 1.7 G weights = 110 GFMA per
+// step). Here each warp multiplies a 16-row slab of int8 weights, widened exactly to fp16 in
+// registers (byte permute into 1024 + q + 128, minus 1152), with the activations split into two fp16
+// halves, x = hi + lo (about 22 bits of x), by mma.sync.m16n8k16 with fp32 accumulation. Products of
+// an fp16 integer and an fp16 value are exact in fp32, so the result differs from the fp32 GEMV only
+// by the 2^-22 relative truncation of x and the order of the additions.
+//
+//   k_prep_x   activations -> normalised fp16 (hi | lo) rows [T][2][K] (ZNorm, gated RMSNorm or none)
+//   k_mma_i8   out[t][row] = epilogue(scale[row] * sum_k W[row][k] x[t][k]) for up to 3 matrices
+//
+// A block is 4 warps = 64 weight rows; the K dimension is streamed in 256-wide chunks through a
+// 3-stage cp.async ring holding the 64 x 256 int8 weight tile (row pitch 320 B) and the fp16
+// activation tile of 32 sequences (64 columns x 256, column pitch 528 B); both pitches make the
+// fragment loads bank-conflict free. The k index inside a 16-wide mma step is permuted identically on
+// both operands (a thread takes 4 consecutive bytes / halves per step), which lets a thread fetch
+// its A bytes for four steps with one 16-byte load.
+#pragma once
+#include <cuda_fp16.h>
+
+namespace b2 {
+
+constexpr int MM_ROWS = 64;          // weight rows per block (16 per warp)
+constexpr int MM_KC = 256;           // K chunk
+constexpr int MM_TOK = 32;           // sequences per pass (64 columns: hi and lo)
+constexpr int MM_PA = 320;           // bytes between weight rows in shared memory
+constexpr int MM_PB = 528;           // bytes between activation columns in shared memory
+constexpr int MM_STAGES = 3;
+constexpr int MM_STAGE_BYTES = MM_ROWS * MM_PA + 2 * MM_TOK * MM_PB;   // 20480 + 33792
+constexpr int MM_THREADS = 128;
+
+struct PrepArgs {
+    const float* x;          // [T][x_stride]
+    int x_stride;
+    const uint16_t* norm_w;  // ZNorm weight [K] or null
+    const uint16_t* gn_w;    // gated RMSNorm weight [DV] or null (then z is silu(z))
+    const float* z;
+    int DV;
+    float eps;
+    int K, T;
+    __half* out;             // [Tpad][2][K]; rows T..Tpad-1 are zero
+    int Tpad;
+};
+
+// one block per sequence
+__global__ void __launch_bounds__(256) k_prep_x(const PrepArgs a) {
+    __shared__ float red[8];
+    const int t = blockIdx.x;
+    grid_dep_launch();
+    grid_dep_wait();
+    __half* hi = a.out + (size_t)t * 2 * a.K;
+    __half* lo = hi + a.K;
+    if (t >= a.T) {
+        for (int k = threadIdx.x; k < a.K; k += 256) { hi[k] = __float2half(0.f); lo[k] = __float2half(0.f); }
+        return;
+    }
+    const float* x = a.x + (size_t)t * a.x_stride;
+    if (a.gn_w) {
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        const float* z = a.z + (size_t)t * a.x_stride;
+        for (int h = warp; h < a.K / a.DV; h += 8) {
+            float ss = 0.f;
+            for (int i = lane; i < a.DV; i += 32) { const float v = x[h * a.DV + i]; ss = fmaf(v, v, ss); }
+            ss = warp_sum(ss);
+            const float r = 1.0f / sqrtf(ss / (float)a.DV + a.eps);
+            for (int i = lane; i < a.DV; i += 32) {
+                const int k = h * a.DV + i;
+                const float v = (bf(a.gn_w[i]) * (x[k] * r)) * z[k];
+                const __half h1 = __float2half(v);
+                hi[k] = h1;
+                lo[k] = __float2half(v - __half2float(h1));
+            }
+        }
+        return;
+    }
+    float r = 1.0f;
+    if (a.norm_w) {
+        float ss = 0.f;
+        for (int k = threadIdx.x; k < a.K; k += 256) { const float v = x[k]; ss = fmaf(v, v, ss); }
+        ss = block_sum(ss, red);
+        r = 1.0f / sqrtf(ss / (float)a.K + a.eps);
+    }
+    for (int k = threadIdx.x; k < a.K; k += 256) {
+        float v = x[k];
+        if (a.norm_w) v = v * r * (1.0f + bf(a.norm_w[k]));
+        const __half h1 = __float2half(v);
+        hi[k] = h1;
+        lo[k] = __float2half(v - __half2float(h1));
+    }
+}
+
+struct MmaSeg {
+    const int8_t* w;         // [rows][K]
+    const uint16_t* s;       // bf16 scale per row
+    const int8_t* w2;        // SEG_I8_GATEUP: the up matrix
+    const uint16_t* s2;
+    float* out;              // [T][out_stride]
+    int rows, kind, out_stride;
+    int blocks;              // ceil(rows / MM_ROWS), filled by the host
+};
+
+struct MmaArgs {
+    MmaSeg seg[3];
+    int nseg, total_blocks;
+    const __half* xh;        // [Tpad][2][K]
+    int K, T;
+    // SEG_I8_CONV
+    const uint16_t* conv_w;
+    float* conv_state;       // [T][C][3]
+};
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// four int8 -> two half2 (exact): bytes (0,1) and (2,3) of w
+__device__ __forceinline__ void i8x4_to_h2x2(uint32_t w, uint32_t& h01, uint32_t& h23) {
+    const uint32_t u = w ^ 0x80808080u;
+    const uint32_t bias = 0x64806480u;                       // (1152, 1152)
+    uint32_t a = __byte_perm(u, 0x64646464u, 0x4140);        // 1024 + (q0 + 128), 1024 + (q1 + 128)
+    uint32_t b = __byte_perm(u, 0x64646464u, 0x4342);
+    __half2 ha = __hsub2(*reinterpret_cast<__half2*>(&a), *reinterpret_cast<const __half2*>(&bias));
+    __half2 hb = __hsub2(*reinterpret_cast<__half2*>(&b), *reinterpret_cast<const __half2*>(&bias));
+    h01 = *reinterpret_cast<uint32_t*>(&ha);
+    h23 = *reinterpret_cast<uint32_t*>(&hb);
+}
+
+// grid (total_blocks, passes of MM_TOK sequences). NMAT = 2 for gate/up pairs handled by one warp.
+__global__ void __launch_bounds__(MM_THREADS) k_mma_i8(const MmaArgs a) {
+    extern __shared__ __align__(128) unsigned char mm_smem[];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int gid = lane >> 2, tid = lane & 3;
+    const int t0 = blockIdx.y * MM_TOK;
+    grid_dep_launch();
+    // which matrix and which 64 rows
+    int s = 0, blk = blockIdx.x;
+    while (s + 1 < a.nseg && blk >= a.seg[s].blocks) { blk -= a.seg[s].blocks; s++; }
+    const MmaSeg sg = a.seg[s];
+    const bool pair = sg.kind == SEG_I8_GATEUP;
+    // a pair block covers 32 gate rows and the same 32 up rows: warps 0,1 gate, warps 2,3 up
+    const int rows_per_block = pair ? MM_ROWS / 2 : MM_ROWS;
+    const int row0 = blk * rows_per_block;
+    const int nk = a.K / MM_KC;
+
+    auto load_stage = [&](int kc, int st) {
+        unsigned char* sa = mm_smem + (size_t)st * MM_STAGE_BYTES;
+        unsigned char* sb = sa + MM_ROWS * MM_PA;
+        // weights: 64 rows x 256 B = 1024 16-byte pieces
+        for (int p = threadIdx.x; p < MM_ROWS * (MM_KC / 16); p += MM_THREADS) {
+            const int r = p / (MM_KC / 16), c = p % (MM_KC / 16);
+            int grow;
+            const int8_t* base;
+            if (pair) { base = r < 32 ? sg.w : sg.w2; grow = row0 + (r & 31); }
+            else { base = sg.w; grow = row0 + r; }
+            grow = min(grow, sg.rows - 1);                    // rows past the end repeat the last row (never stored)
+            cp_async16(sa + r * MM_PA + c * 16, base + (size_t)grow * a.K + (size_t)kc * MM_KC + c * 16);
+        }
+        // activations: 64 columns (32 sequences x hi, lo) x 256 halves = 2048 pieces
+        for (int p = threadIdx.x; p < 2 * MM_TOK * (MM_KC / 8); p += MM_THREADS) {
+            const int col = p / (MM_KC / 8), c = p % (MM_KC / 8);
+            const int tok = t0 + (col & (MM_TOK - 1)), part = col >> 5;        // columns 0..31 hi, 32..63 lo
+            cp_async16(sb + col * MM_PB + c * 16, a.xh + ((size_t)tok * 2 + part) * a.K + (size_t)kc * MM_KC + c * 8);
+        }
+        cp_async_commit();
+    };
+
+    grid_dep_wait();          // the activations are the previous kernel's output
+    for (int i = 0; i < MM_STAGES - 1; i++) {
+        if (i < nk) load_stage(i, i); else cp_async_commit();
+    }
+    float acc[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; j++)
+#pragma unroll
+        for (int q = 0; q < 4; q++) acc[j][q] = 0.f;
+
+    for (int kc = 0; kc < nk; kc++) {
+        cp_async_wait<MM_STAGES - 2>();
+        __syncthreads();
+        if (kc + MM_STAGES - 1 < nk) load_stage(kc + MM_STAGES - 1, (kc + MM_STAGES - 1) % MM_STAGES); else cp_async_commit();
+        const unsigned char* sa = mm_smem + (size_t)(kc % MM_STAGES) * MM_STAGE_BYTES;
+        const unsigned char* sb = sa + MM_ROWS * MM_PA;
+        const unsigned char* ar0 = sa + (warp * 16 + gid) * MM_PA;
+        const unsigned char* ar1 = ar0 + 8 * MM_PA;
+#pragma unroll
+        for (int sbk = 0; sbk < MM_KC / 64; sbk++) {
+            // this thread's 16 bytes of rows gid and gid + 8 cover four k16 steps
+            const uint4 w0 = *reinterpret_cast<const uint4*>(ar0 + sbk * 64 + tid * 16);
+            const uint4 w1 = *reinterpret_cast<const uint4*>(ar1 + sbk * 64 + tid * 16);
+            const uint32_t wa[4] = {w0.x, w0.y, w0.z, w0.w}, wb[4] = {w1.x, w1.y, w1.z, w1.w};
+            uint32_t af[4][4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                i8x4_to_h2x2(wa[j], af[j][0], af[j][2]);
+                i8x4_to_h2x2(wb[j], af[j][1], af[j][3]);
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; nt++) {
+                // column 8 nt + gid: 16 halves = this thread's k range of the super-block
+                const unsigned char* bp = sb + (nt * 8 + gid) * MM_PB + sbk * 128 + tid * 32;
+                const uint4 x0 = *reinterpret_cast<const uint4*>(bp);
+                const uint4 x1 = *reinterpret_cast<const uint4*>(bp + 16);
+                mma16816(acc[nt], af[0], x0.x, x0.y);
+                mma16816(acc[nt], af[1], x0.z, x0.w);
+                mma16816(acc[nt], af[2], x1.x, x1.y);
+                mma16816(acc[nt], af[3], x1.z, x1.w);
+            }
+        }
+    }
+    cp_async_wait<0>();
+
+    // epilogue. Thread holds rows (gid, gid + 8) of its warp's slab and, in n-tile nt, columns 2 tid, 2 tid + 1:
+    // sequences 8 nt + 2 tid (+1) for nt < 4 (hi) and the same sequences' lo parts in nt + 4.
+    __shared__ float gate_s[2][16][MM_TOK + 1];     // pairs: the gate warps hand their sums to the up warps
+    if (pair && warp < 2) {
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++)
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+                const int r = gid + (q >> 1) * 8, col = nt * 8 + 2 * tid + (q & 1);
+                gate_s[warp][r][col] = acc[nt][q] + acc[nt + 4][q];
+            }
+    }
+    if (pair) __syncthreads();
+    if (pair && warp < 2) return;
+#pragma unroll
+    for (int nt = 0; nt < 4; nt++) {
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+            const int rl = gid + (q >> 1) * 8;                               // row inside the warp's slab
+            const int col = nt * 8 + 2 * tid + (q & 1);
+            const int tok = t0 + col;
+            const int row = pair ? row0 + (warp - 2) * 16 + rl : row0 + warp * 16 + rl;
+            if (tok >= a.T || row >= sg.rows) continue;
+            const float dot = acc[nt][q] + acc[nt + 4][q];
+            float* out = sg.out + (size_t)tok * sg.out_stride;
+            switch (sg.kind) {
+            case SEG_I8: out[row] = bf(sg.s[row]) * dot; break;
+            case SEG_I8_SILU: out[row] = siluf_(bf(sg.s[row]) * dot); break;
+            case SEG_I8_ACC: out[row] += bf(sg.s[row]) * dot; break;
+            case SEG_I8_GATEUP: out[row] = siluf_(bf(sg.s[row]) * gate_s[warp - 2][rl][col]) * (bf(sg.s2[row]) * dot); break;
+            case SEG_I8_CONV: {
+                const float raw = bf(sg.s[row]) * dot;
+                float* stt = a.conv_state + ((size_t)tok * sg.rows + row) * 3;
+                const uint2 cw = *reinterpret_cast<const uint2*>(a.conv_w + (size_t)row * 4);
+                const float s0 = stt[0], s1 = stt[1], s2 = stt[2];
+                float y = bflo(cw.x) * s0;
+                y = fmaf(bfhi(cw.x), s1, y);
+                y = fmaf(bflo(cw.y), s2, y);
+                y = fmaf(bfhi(cw.y), raw, y);
+                stt[0] = s1; stt[1] = s2; stt[2] = raw;
+                out[row] = siluf_(y);
+            } break;
+            default: break;
+            }
+        }
+    }
+}
+
+}  // namespace b2

@@ -28,3 +28,12 @@ def golden_dir():
 @pytest.fixture(scope="session")
 def micro_path():
     return os.path.join(GOLDEN, "micro.nx")
+
+
+@pytest.fixture(scope="session")
+def tiny_path(pkg, tmp_path_factory):
+    """The 4-layer hidden-512 vocab-32768 brain of the benchmark spec, rebuilt from seed 0."""
+    from b200moe import brain
+    path = str(tmp_path_factory.mktemp("tiny") / "tiny.nx")
+    brain.write_brain(path, pkg.HybridConfig.tiny(), seed=0)
+    return path
