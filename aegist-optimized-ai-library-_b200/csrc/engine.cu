@@ -147,6 +147,11 @@ struct b2_engine {
     float* attn_part = nullptr;
     __half* xh = nullptr;                    // [Tpad][2][4096] fp16 activations for the tensor-core path
     int xh_tpad = 0;
+    // grouped expert GEMM: picks sorted by expert, chunk table, fp16 expert activations, group sums
+    int *g_list = nullptr, *g_chunk = nullptr;
+    __half* acth = nullptr;
+    float *xsum_tok = nullptr, *xsum_act = nullptr;
+    int max_chunks = 0;
     float* ypart = nullptr;                  // [B][TOPK + 1][D]
     unsigned int* d_dcounter = nullptr;      // [B][row blocks of the expert down projection]
     int nsplit = 1, head_grid = 1;
@@ -216,7 +221,7 @@ b2_engine::~b2_engine() {
     for (auto& l : layers) { cudaFree((void*)l.eptr); cudaFree(l.router_bias); }
     void* bufs[] = {conv, state, snap_conv[0], snap_conv[1], snap_state[0], snap_state[1], kpool, vpool, page_table, rope_cos,
                     rope_sin, d_tok, d_next, d_pos, d_err, d_counter, d_acounter, x, big, zbuf, kraw, vraw, beta, gdec, obuf, att,
-                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh};
+                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh, g_list, g_chunk, acth, xsum_tok, xsum_act};
     for (void* p : bufs) cudaFree(p);
     if (h_pin) cudaFreeHost(h_pin);
     if (ev0) cudaEventDestroy(ev0);
@@ -464,8 +469,15 @@ int b2_engine::finish() {
     nsplit = std::max(1, std::min({64, (2 * nsm) / std::max(1, c.KV * B), (cap + 63) / 64}));
     CU(dalloc(&attn_part, (size_t)B * c.KV * nsplit * (c.H / c.KV) * (c.HD + 2)));
     if (B >= 8) {
-        xh_tpad = (B + MM_TOK - 1) / MM_TOK * MM_TOK;
+        xh_tpad = ((int)Bg + MM_TOK - 1) / MM_TOK * MM_TOK;
         CU(dalloc((uint16_t**)&xh, (size_t)xh_tpad * 2 * 4096));
+        const size_t P = Bg * c.TOPK;
+        max_chunks = (int)std::min<size_t>(P, c.E / ep_world) + (int)(P / GQ_CH) + 1;
+        CU(dalloc(&g_list, P));
+        CU(dalloc(&g_chunk, (size_t)3 * max_chunks + 1));
+        CU(dalloc((uint16_t**)&acth, P * 2 * c.I));
+        CU(dalloc(&xsum_tok, Bg * (c.D / 64)));
+        CU(dalloc(&xsum_act, P * std::max(1, c.I / 64)));
     }
     CU(dalloc(&ypart, Bg * (c.TOPK + 1) * c.D));
     CU(dalloc(&d_dcounter, Bg * down_row_blocks(c.D)));
@@ -648,6 +660,54 @@ static void launch_experts(const ExpertArgs& a, int B, int nsm, cudaStream_t st,
     if (prof) prof->mark(6, st);
 }
 
+// The experts of one layer for T tokens as a grouped tensor-core GEMM: group the picks, gate/up, down into
+// ypart, the shared expert's down projection into ypart's last slot. The caller combines.
+struct ExpertMmaCtx {
+    int* list; int* chunk; int max_chunks;
+    __half* xh; __half* acth; float* xsum_tok; float* xsum_act;
+};
+static cudaError_t launch_experts_mma(const ExpertArgs& a, int T, const ExpertMmaCtx& m, cudaStream_t st, b2_engine* prof) {
+    cudaError_t e;
+    const int P = T * a.topk;
+    GroupArgs g{};
+    g.top_idx = a.top_idx; g.idx_stride = a.idx_stride; g.T = T; g.topk = a.topk; g.E = a.E; g.eptr = a.eptr;
+    g.list = m.list; g.chunk_expert = m.chunk; g.chunk_start = m.chunk + m.max_chunks; g.chunk_n = m.chunk + 2 * m.max_chunks;
+    g.nchunks = m.chunk + 3 * m.max_chunks; g.max_chunks = m.max_chunks;
+    if ((e = launch_k(k_group_picks, dim3(1), dim3(1024), 0, st, g)) != cudaSuccess) return e;
+    PrepArgs p{};
+    p.x = a.x; p.x_stride = a.x_stride; p.norm_w = a.norm_w; p.eps = a.eps; p.K = a.D; p.T = T; p.Tpad = T; p.out = m.xh; p.xsum = m.xsum_tok;
+    if ((e = launch_k(k_prep_x, dim3(T), dim3(256), 0, st, p)) != cudaSuccess) return e;
+    Q4Args q{};
+    q.eptr = a.eptr; q.list = g.list; q.chunk_expert = g.chunk_expert; q.chunk_start = g.chunk_start; q.chunk_n = g.chunk_n;
+    q.nchunks = g.nchunks; q.topk = a.topk;
+    const size_t smem = (size_t)Q4_STAGES * Q4_STAGE_BYTES;
+    if ((e = opt_in_smem(k_mma_q4, smem)) != cudaSuccess) return e;
+    q.pair = 1; q.rows = a.I; q.K = a.D; q.off_q = 0; q.off_s = a.off_gu_s; q.off_m = a.off_gu_m; q.up_row0 = a.I;
+    q.xh = m.xh; q.xsum = m.xsum_tok; q.by_pick = 0; q.out = a.act;
+    if ((e = launch_k(k_mma_q4, dim3((a.I + 31) / 32, m.max_chunks), dim3(MM_THREADS), smem, st, q)) != cudaSuccess) return e;
+    if (prof) prof->mark(5, st);
+    PrepArgs p2{};
+    p2.x = a.act; p2.x_stride = a.I; p2.K = a.I; p2.T = P; p2.Tpad = P; p2.out = m.acth; p2.xsum = m.xsum_act;
+    if ((e = launch_k(k_prep_x, dim3(P), dim3(256), 0, st, p2)) != cudaSuccess) return e;
+    q.pair = 0; q.rows = a.D; q.K = a.I; q.off_q = a.off_dn_q; q.off_s = a.off_dn_s; q.off_m = a.off_dn_m; q.up_row0 = 0;
+    q.xh = m.acth; q.xsum = m.xsum_act; q.by_pick = 1; q.out = a.ypart;
+    if ((e = launch_k(k_mma_q4, dim3((a.D + Q4_ROWS - 1) / Q4_ROWS, m.max_chunks), dim3(MM_THREADS), smem, st, q)) != cudaSuccess) return e;
+    // shared expert down for this GPU's own tokens: int8 [D][SH] on the dense tensor-core kernel
+    PrepArgs p3{};
+    p3.x = a.sh_act; p3.x_stride = a.SH; p3.K = a.SH; p3.T = a.nlocal; p3.Tpad = (a.nlocal + MM_TOK - 1) / MM_TOK * MM_TOK; p3.out = m.xh;
+    if ((e = launch_k(k_prep_x, dim3(p3.Tpad), dim3(256), 0, st, p3)) != cudaSuccess) return e;
+    MmaArgs d{};
+    d.seg[0].w = a.shd_w; d.seg[0].s = a.shd_s; d.seg[0].rows = a.D; d.seg[0].kind = SEG_I8;
+    d.seg[0].out = a.ypart + ((size_t)a.local0 * (a.topk + 1) + a.topk) * a.D; d.seg[0].out_stride = (a.topk + 1) * a.D;
+    d.seg[0].blocks = (a.D + MM_ROWS - 1) / MM_ROWS;
+    d.nseg = 1; d.total_blocks = d.seg[0].blocks; d.xh = m.xh; d.K = a.SH; d.T = a.nlocal;
+    const size_t smem2 = (size_t)MM_STAGES * MM_STAGE_BYTES;
+    if ((e = opt_in_smem(k_mma_i8, smem2)) != cudaSuccess) return e;
+    if ((e = launch_k(k_mma_i8, dim3(d.total_blocks, p3.Tpad / MM_TOK), dim3(MM_THREADS), smem2, st, d)) != cudaSuccess) return e;
+    if (prof) prof->mark(6, st);
+    return cudaSuccess;
+}
+
 static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaStream_t st, b2_engine* prof = nullptr) {
     const int G = a.H / a.KV;
     const size_t smem = (size_t)WARPS * G * HD * 4;
@@ -745,10 +805,23 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             x2.norm_w = l.norm2; x2.eps = c.eps; x2.act = act; x2.sh_act = sh_act; x2.sg = sgate;
             x2.shd_w = l.sh_down.w; x2.shd_s = l.sh_down.s; x2.SH = c.SH; x2.xout = x; x2.err = d_err;
             x2.ypart = ypart; x2.counter = d_dcounter;
+            const int Tg = B * ep_world;
+            const bool grouped = g_mma && xh && Tg >= 16 && Tg * c.TOPK <= GQ_MAXP && c.D % MM_KC == 0 && c.I % MM_KC == 0 &&
+                                 c.SH % MM_KC == 0 && c.D <= 2048 && c.I <= 2048 && c.E <= 256;
+            const ExpertMmaCtx mctx{g_list, g_chunk, max_chunks, xh, acth, xsum_tok, xsum_act};
             if (ep_world == 1) {
                 x2.x = x; x2.x_stride = c.D; x2.top_idx = a.top_idx; x2.top_w = a.top_w; x2.idx_stride = c.TOPK;
                 x2.combine = 1; x2.local0 = 0; x2.nlocal = B;
-                launch_experts(x2, B, nsm, st, this);
+                if (grouped) {
+                    cudaError_t ce = launch_experts_mma(x2, B, mctx, st, this);
+                    if (ce != cudaSuccess) return fail("grouped expert GEMM: %s", cudaGetErrorString(ce));
+                    EpArgs ep{};
+                    ep.x = x; ep.top_idx = a.top_idx; ep.top_w = a.top_w; ep.recv_y = ypart; ep.sg = sgate; ep.xout = x;
+                    ep.D = c.D; ep.topk = c.TOPK; ep.B = B; ep.E = c.E; ep.world = 1; ep.rank = 0; ep.has_shared = 1;
+                    launch_k(k_ep_combine, dim3(std::max(1, (c.D + 255) / 256), B), dim3(256), 0, st, ep);
+                } else {
+                    launch_experts(x2, B, nsm, st, this);
+                }
             } else {
                 const int rw = c.D + 2 * c.TOPK;
                 EpArgs ep{};
@@ -758,7 +831,12 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
                 if (ep_exchange_records(st)) return 1;
                 x2.x = rec_all; x2.x_stride = rw; x2.top_idx = (const int*)(rec_all + c.D); x2.top_w = rec_all + c.D + c.TOPK; x2.idx_stride = rw;
                 x2.combine = 0; x2.local0 = ep_rank * B; x2.nlocal = B;
-                launch_experts(x2, B * ep_world, nsm, st, this);
+                if (grouped) {
+                    cudaError_t ce = launch_experts_mma(x2, Tg, mctx, st, this);
+                    if (ce != cudaSuccess) return fail("grouped expert GEMM: %s", cudaGetErrorString(ce));
+                } else {
+                    launch_experts(x2, Tg, nsm, st, this);
+                }
                 if (ep_exchange_outputs(st)) return 1;
                 launch_k(k_ep_combine, dim3(std::max(1, (c.D + 255) / 256), B), dim3(256), 0, st, ep);
                 n += 2;

@@ -553,6 +553,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv_norm(const GemvArgs a)
 }  // namespace b2
 #include "rowgemv.cuh"
 #include "mmagemm.cuh"
+#include "mmaexperts.cuh"
 namespace b2 {
 
 // ------------------------------------------------------------------------------------------

@@ -42,11 +42,13 @@ struct PrepArgs {
     int K, T;
     __half* out;             // [Tpad][2][K]; rows T..Tpad-1 are zero
     int Tpad;
+    float* xsum;             // optional [T][K / 64]: the sum of each 64-value group (for the 4-bit min term)
 };
 
 // one block per sequence
 __global__ void __launch_bounds__(256) k_prep_x(const PrepArgs a) {
     __shared__ float red[8];
+    __shared__ float vs[4096];
     const int t = blockIdx.x;
     grid_dep_launch();
     grid_dep_wait();
@@ -68,9 +70,18 @@ __global__ void __launch_bounds__(256) k_prep_x(const PrepArgs a) {
             for (int i = lane; i < a.DV; i += 32) {
                 const int k = h * a.DV + i;
                 const float v = (bf(a.gn_w[i]) * (x[k] * r)) * z[k];
+                vs[k] = v;
                 const __half h1 = __float2half(v);
                 hi[k] = h1;
                 lo[k] = __float2half(v - __half2float(h1));
+            }
+        }
+        if (a.xsum) {
+            __syncthreads();
+            for (int g = threadIdx.x; g < a.K / 64; g += 256) {
+                float s = 0.f;
+                for (int i = 0; i < 64; i++) s += vs[64 * g + i];
+                a.xsum[(size_t)t * (a.K / 64) + g] = s;
             }
         }
         return;
@@ -85,9 +96,18 @@ __global__ void __launch_bounds__(256) k_prep_x(const PrepArgs a) {
     for (int k = threadIdx.x; k < a.K; k += 256) {
         float v = x[k];
         if (a.norm_w) v = v * r * (1.0f + bf(a.norm_w[k]));
+        vs[k] = v;
         const __half h1 = __float2half(v);
         hi[k] = h1;
         lo[k] = __float2half(v - __half2float(h1));
+    }
+    if (a.xsum) {
+        __syncthreads();
+        for (int g = threadIdx.x; g < a.K / 64; g += 256) {
+            float s = 0.f;
+            for (int i = 0; i < 64; i++) s += vs[64 * g + i];
+            a.xsum[(size_t)t * (a.K / 64) + g] = s;
+        }
     }
 }
 
