@@ -151,7 +151,7 @@ struct b2_engine {
     int *g_list = nullptr, *g_chunk = nullptr;
     __half* acth = nullptr;
     float *xsum_tok = nullptr, *xsum_act = nullptr;
-    int max_chunks = 0;
+    int cap_small = 0, cap_big = 0;
     float* ypart = nullptr;                  // [B][TOPK + 1][D]
     unsigned int* d_dcounter = nullptr;      // [B][row blocks of the expert down projection]
     int nsplit = 1, head_grid = 1;
@@ -472,9 +472,10 @@ int b2_engine::finish() {
         xh_tpad = ((int)Bg + MM_TOK - 1) / MM_TOK * MM_TOK;
         CU(dalloc((uint16_t**)&xh, (size_t)xh_tpad * 2 * 4096));
         const size_t P = Bg * c.TOPK;
-        max_chunks = (int)std::min<size_t>(P, c.E / ep_world) + (int)(P / GQ_CH) + 1;
+        cap_small = (int)std::min<size_t>(P, c.E / ep_world);
+        cap_big = (int)(P / (GQ_SMALL + 1)) + 1;
         CU(dalloc(&g_list, P));
-        CU(dalloc(&g_chunk, (size_t)3 * max_chunks + 1));
+        CU(dalloc(&g_chunk, (size_t)3 * (cap_small + cap_big) + 2));
         CU(dalloc((uint16_t**)&acth, P * 2 * c.I));
         CU(dalloc(&xsum_tok, Bg * (c.D / 64)));
         CU(dalloc(&xsum_act, P * std::max(1, c.I / 64)));
@@ -663,35 +664,52 @@ static void launch_experts(const ExpertArgs& a, int B, int nsm, cudaStream_t st,
 // The experts of one layer for T tokens as a grouped tensor-core GEMM: group the picks, gate/up, down into
 // ypart, the shared expert's down projection into ypart's last slot. The caller combines.
 struct ExpertMmaCtx {
-    int* list; int* chunk; int max_chunks;
+    int* list; int* chunk; int cap_small, cap_big;
     __half* xh; __half* acth; float* xsum_tok; float* xsum_act;
 };
+static void chunk_tables(const ExpertMmaCtx& m, ChunkTable& small, ChunkTable& big) {
+    int* p = m.chunk;
+    small.expert = p; small.start = p + m.cap_small; small.n = p + 2 * m.cap_small; small.cap = m.cap_small;
+    p += 3 * m.cap_small;
+    big.expert = p; big.start = p + m.cap_big; big.n = p + 2 * m.cap_big; big.cap = m.cap_big;
+    p += 3 * m.cap_big;
+    small.count = p; big.count = p + 1;
+}
+static cudaError_t launch_q4(Q4Args q, const ChunkTable& small, const ChunkTable& big, int row_blocks, cudaStream_t st) {
+    cudaError_t e;
+    const size_t sm1 = (size_t)Q4_STAGES * q4_stage_bytes(1), sm4 = (size_t)Q4_STAGES * q4_stage_bytes(4);
+    if ((e = opt_in_smem(k_mma_q4<1>, sm1)) != cudaSuccess) return e;
+    if ((e = opt_in_smem(k_mma_q4<4>, sm4)) != cudaSuccess) return e;
+    q.chunks = small;
+    if ((e = launch_k(k_mma_q4<1>, dim3(row_blocks, small.cap), dim3(MM_THREADS), sm1, st, q)) != cudaSuccess) return e;
+    q.chunks = big;
+    return launch_k(k_mma_q4<4>, dim3(row_blocks, big.cap), dim3(MM_THREADS), sm4, st, q);
+}
 static cudaError_t launch_experts_mma(const ExpertArgs& a, int T, const ExpertMmaCtx& m, cudaStream_t st, b2_engine* prof) {
     cudaError_t e;
     const int P = T * a.topk;
     GroupArgs g{};
     g.top_idx = a.top_idx; g.idx_stride = a.idx_stride; g.T = T; g.topk = a.topk; g.E = a.E; g.eptr = a.eptr;
-    g.list = m.list; g.chunk_expert = m.chunk; g.chunk_start = m.chunk + m.max_chunks; g.chunk_n = m.chunk + 2 * m.max_chunks;
-    g.nchunks = m.chunk + 3 * m.max_chunks; g.max_chunks = m.max_chunks;
+    g.list = m.list;
+    chunk_tables(m, g.small, g.big);
     if ((e = launch_k(k_group_picks, dim3(1), dim3(1024), 0, st, g)) != cudaSuccess) return e;
     PrepArgs p{};
-    p.x = a.x; p.x_stride = a.x_stride; p.norm_w = a.norm_w; p.eps = a.eps; p.K = a.D; p.T = T; p.Tpad = T; p.out = m.xh; p.xsum = m.xsum_tok;
+    p.x = a.x; p.x_stride = a.x_stride; p.norm_w = a.norm_w; p.eps = a.eps; p.K = a.D; p.T = T; p.Tpad = T; p.out = m.xh;
+    p.xsum = m.xsum_tok; p.perm8 = 1;
     if ((e = launch_k(k_prep_x, dim3(T), dim3(256), 0, st, p)) != cudaSuccess) return e;
     Q4Args q{};
-    q.eptr = a.eptr; q.list = g.list; q.chunk_expert = g.chunk_expert; q.chunk_start = g.chunk_start; q.chunk_n = g.chunk_n;
-    q.nchunks = g.nchunks; q.topk = a.topk;
-    const size_t smem = (size_t)Q4_STAGES * Q4_STAGE_BYTES;
-    if ((e = opt_in_smem(k_mma_q4, smem)) != cudaSuccess) return e;
+    q.eptr = a.eptr; q.list = g.list; q.topk = a.topk;
     q.pair = 1; q.rows = a.I; q.K = a.D; q.off_q = 0; q.off_s = a.off_gu_s; q.off_m = a.off_gu_m; q.up_row0 = a.I;
-    q.xh = m.xh; q.xsum = m.xsum_tok; q.by_pick = 0; q.out = a.act;
-    if ((e = launch_k(k_mma_q4, dim3((a.I + 31) / 32, m.max_chunks), dim3(MM_THREADS), smem, st, q)) != cudaSuccess) return e;
+    q.xh = m.xh; q.xsum = m.xsum_tok; q.by_pick = 0; q.out = a.act; q.row_tiles = 1;
+    if ((e = launch_q4(q, g.small, g.big, (a.I + 31) / 32, st)) != cudaSuccess) return e;
     if (prof) prof->mark(5, st);
     PrepArgs p2{};
-    p2.x = a.act; p2.x_stride = a.I; p2.K = a.I; p2.T = P; p2.Tpad = P; p2.out = m.acth; p2.xsum = m.xsum_act;
+    p2.x = a.act; p2.x_stride = a.I; p2.K = a.I; p2.T = P; p2.Tpad = P; p2.out = m.acth; p2.xsum = m.xsum_act; p2.perm8 = 1;
     if ((e = launch_k(k_prep_x, dim3(P), dim3(256), 0, st, p2)) != cudaSuccess) return e;
     q.pair = 0; q.rows = a.D; q.K = a.I; q.off_q = a.off_dn_q; q.off_s = a.off_dn_s; q.off_m = a.off_dn_m; q.up_row0 = 0;
     q.xh = m.acth; q.xsum = m.xsum_act; q.by_pick = 1; q.out = a.ypart;
-    if ((e = launch_k(k_mma_q4, dim3((a.D + Q4_ROWS - 1) / Q4_ROWS, m.max_chunks), dim3(MM_THREADS), smem, st, q)) != cudaSuccess) return e;
+    q.row_tiles = std::max(1, std::min(4, 2048 / a.I));      // keep about 8 ring steps per block
+    if ((e = launch_q4(q, g.small, g.big, (a.D + Q4_ROWS * q.row_tiles - 1) / (Q4_ROWS * q.row_tiles), st)) != cudaSuccess) return e;
     // shared expert down for this GPU's own tokens: int8 [D][SH] on the dense tensor-core kernel
     PrepArgs p3{};
     p3.x = a.sh_act; p3.x_stride = a.SH; p3.K = a.SH; p3.T = a.nlocal; p3.Tpad = (a.nlocal + MM_TOK - 1) / MM_TOK * MM_TOK; p3.out = m.xh;
@@ -808,7 +826,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             const int Tg = B * ep_world;
             const bool grouped = g_mma && xh && Tg >= 16 && Tg * c.TOPK <= GQ_MAXP && c.D % MM_KC == 0 && c.I % MM_KC == 0 &&
                                  c.SH % MM_KC == 0 && c.D <= 2048 && c.I <= 2048 && c.E <= 256;
-            const ExpertMmaCtx mctx{g_list, g_chunk, max_chunks, xh, acth, xsum_tok, xsum_act};
+            const ExpertMmaCtx mctx{g_list, g_chunk, cap_small, cap_big, xh, acth, xsum_tok, xsum_act};
             if (ep_world == 1) {
                 x2.x = x; x2.x_stride = c.D; x2.top_idx = a.top_idx; x2.top_w = a.top_w; x2.idx_stride = c.TOPK;
                 x2.combine = 1; x2.local0 = 0; x2.nlocal = B;

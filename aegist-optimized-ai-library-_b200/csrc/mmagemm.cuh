@@ -43,6 +43,7 @@ struct PrepArgs {
     __half* out;             // [Tpad][2][K]; rows T..Tpad-1 are zero
     int Tpad;
     float* xsum;             // optional [T][K / 64]: the sum of each 64-value group (for the 4-bit min term)
+    int perm8;               // store every 8 values in the order 0 4 1 5 2 6 3 7 (what the 4-bit unpacking yields)
 };
 
 // one block per sequence
@@ -98,8 +99,9 @@ __global__ void __launch_bounds__(256) k_prep_x(const PrepArgs a) {
         if (a.norm_w) v = v * r * (1.0f + bf(a.norm_w[k]));
         vs[k] = v;
         const __half h1 = __float2half(v);
-        hi[k] = h1;
-        lo[k] = __float2half(v - __half2float(h1));
+        const int ks = a.perm8 ? ((k & ~7) | ((k & 3) << 1) | ((k >> 2) & 1)) : k;
+        hi[ks] = h1;
+        lo[ks] = __float2half(v - __half2float(h1));
     }
     if (a.xsum) {
         __syncthreads();
