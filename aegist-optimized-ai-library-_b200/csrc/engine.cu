@@ -96,6 +96,10 @@ static size_t dtype_size(const std::string& d) {
 // Blocks per SM of the streaming GEMV kernel (B2_GEMV_CTAS overrides; for experiments).
 // Row-per-lane GEMV kernel (k_rowgemv) instead of the row-per-warp one (B2_ROWGEMV=0 switches back).
 static bool g_rowgemv = [] { const char* v = getenv("B2_ROWGEMV"); return !(v && v[0] == '0'); }();
+// Tensor-core GEMV (k_tcgemv) for the int8 matrices of small batches (B2_TCGEMV=0 switches back to k_rowgemv);
+// B2_TC_WARPS = 8 or 16 warps per block.
+static bool g_tcgemv = [] { const char* v = getenv("B2_TCGEMV"); return !(v && v[0] == '0'); }();
+static int g_tc_warps = [] { const char* v = getenv("B2_TC_WARPS"); return (v && atoi(v) == 8) ? 8 : 16; }();
 static int g_gemv_ctas_per_sm = [] { const char* v = getenv("B2_GEMV_CTAS"); return v ? atoi(v) : 2; }();
 static int down_row_blocks(int D) { return (D + DOWN_ROWS - 1) / DOWN_ROWS; }
 
@@ -152,6 +156,7 @@ struct b2_engine {
     __half* acth = nullptr;
     float *xsum_tok = nullptr, *xsum_act = nullptr;
     int cap_small = 0, cap_big = 0;
+    unsigned long long* d_trace = nullptr;   // step timeline slots, allocated by the first b2_debug_trace_step
     float* ypart = nullptr;                  // [B][TOPK + 1][D]
     unsigned int* d_dcounter = nullptr;      // [B][row blocks of the expert down projection]
     int nsplit = 1, head_grid = 1;
@@ -221,7 +226,7 @@ b2_engine::~b2_engine() {
     for (auto& l : layers) { cudaFree((void*)l.eptr); cudaFree(l.router_bias); }
     void* bufs[] = {conv, state, snap_conv[0], snap_conv[1], snap_state[0], snap_state[1], kpool, vpool, page_table, rope_cos,
                     rope_sin, d_tok, d_next, d_pos, d_err, d_counter, d_acounter, x, big, zbuf, kraw, vraw, beta, gdec, obuf, att,
-                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh, g_list, g_chunk, acth, xsum_tok, xsum_act};
+                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh, g_list, g_chunk, acth, xsum_tok, xsum_act, d_trace};
     for (void* p : bufs) cudaFree(p);
     if (h_pin) cudaFreeHost(h_pin);
     if (ev0) cudaEventDestroy(ev0);
@@ -509,6 +514,21 @@ static bool g_pdl = [] { const char* v = getenv("B2_PDL"); return !(v && v[0] ==
 
 static int g_launch_count = 0;   // kernels launched so far (a step's count is the difference)
 
+// Step timeline (b2_debug_trace_step): while g_trace_base is set, the launch with index i since g_trace_first
+// gets the slot g_trace_base + 8 i in its argument struct (structs with a `trace` member; null otherwise).
+static unsigned long long* g_trace_base = nullptr;
+static int g_trace_first = 0;
+constexpr int TRACE_MAX_LAUNCHES = 4096;
+template <typename T>
+static auto with_trace(const T& a, int) -> decltype((void)a.trace, T()) {
+    T c = a;
+    const int i = g_launch_count - 1 - g_trace_first;
+    c.trace = (g_trace_base && i >= 0 && i < TRACE_MAX_LAUNCHES) ? g_trace_base + (size_t)8 * i : nullptr;
+    return c;
+}
+template <typename T>
+static const T& with_trace(const T& a, long) { return a; }
+
 template <typename... KArgs, typename... Args>
 static cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
     g_launch_count++;
@@ -522,7 +542,7 @@ static cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = g_pdl ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+    return cudaLaunchKernelEx(&cfg, kernel, with_trace(args, 0)...);
 }
 
 template <typename F>
@@ -576,6 +596,41 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
             a = rest;
             grid_override = 0;
         }
+    }
+    if (g_rowgemv && g_tcgemv && tc_shape_ok(a.K, g_tc_warps)) {
+        // int8 products on the tensor cores; one block per SM, NB sequences per pass. Rows per tile (r for
+        // 2048-byte slots, r / 2 for wide rows and pairs) such that the longest block has the least to stream.
+        int best_r = 32;
+        long best_cost = -1;
+        for (int r = 32; r >= 16; r -= 2) {
+            int T = 0;
+            for (int i = 0; i < a.nseg; i++) {
+                const int tr = rl_tile_rows(a.seg[i].kind, a.K) == 32 ? r : r / 2;
+                T += (a.seg[i].rows + tr - 1) / tr;
+            }
+            const int G = grid_override ? grid_override : std::max(1, std::min(T, nsm));
+            const long cost = (long)((T + G - 1) / G) * r;
+            if (best_cost < 0 || cost < best_cost) { best_cost = cost; best_r = r; }
+        }
+        a.total_jobs = 0;
+        for (int i = 0; i < a.nseg; i++) {
+            Seg& g = a.seg[i];
+            g.tr = rl_tile_rows(g.kind, a.K) == 32 ? best_r : best_r / 2;
+            g.jobs = (g.rows + g.tr - 1) / g.tr;
+            a.total_jobs += g.jobs;
+        }
+        const int grid = grid_override ? grid_override : std::max(1, std::min(a.total_jobs, nsm));
+#define TCG(NBv, NSTv, Wv)                                                                                      \
+    {                                                                                                           \
+        const size_t smem = tc_smem_bytes(a, NBv, NSTv, Wv);                                                    \
+        e = opt_in_smem(k_tcgemv<NBv, NSTv, Wv>, smem);                                                         \
+        if (e == cudaSuccess)                                                                                   \
+            e = launch_k(k_tcgemv<NBv, NSTv, Wv>, dim3(grid, (B + NBv - 1) / NBv), dim3((Wv + TC_EPI) * 32), smem, st, a, B); \
+    }
+        if (B >= 2) { if (g_tc_warps == 8) TCG(4, 2, 8) else TCG(4, 2, 16) }
+        else { if (g_tc_warps == 8) TCG(1, 3, 8) else TCG(1, 3, 16) }
+#undef TCG
+        return e;
     }
     if (g_rowgemv) {
         // one block of 1024 threads per SM, NB sequences per pass
@@ -1318,6 +1373,38 @@ double b2_step_bytes(const b2_engine* e) {
     double s = 0;
     for (double v : cls) s += v;
     return s;
+}
+
+int b2_debug_trace_step(b2_engine* e, unsigned long long* out, int cap_launches, int* n_launches) {
+    if (feed_checks(e, 1)) return 1;
+    if (!e->d_trace && cudaMalloc(&e->d_trace, (size_t)TRACE_MAX_LAUNCHES * 64) != cudaSuccess) return e->fail("trace buffer: out of memory");
+    std::vector<unsigned long long> init((size_t)TRACE_MAX_LAUNCHES * 8, 0ull);
+    for (int i = 0; i < TRACE_MAX_LAUNCHES; i++) init[(size_t)8 * i] = ~0ull;
+    cudaMemcpyAsync(e->d_trace, init.data(), init.size() * 8, cudaMemcpyHostToDevice, e->stream);
+    cudaStreamSynchronize(e->stream);
+    // the same step as the decode graph, captured once more with the time stamp slots handed out
+    cudaGraph_t g;
+    cudaGraphExec_t ge = nullptr;
+    g_trace_base = e->d_trace;
+    g_trace_first = g_launch_count;
+    cudaError_t ce = cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal);
+    int rc = ce == cudaSuccess ? e->enqueue_step(e->stream, false) : 1;
+    const int n = g_launch_count - g_trace_first;
+    g_trace_base = nullptr;
+    cudaError_t ce2 = cudaStreamEndCapture(e->stream, &g);
+    if (rc || ce != cudaSuccess || ce2 != cudaSuccess) return e->fail("trace step: capture failed");
+    ce = cudaGraphInstantiate(&ge, g, 0);
+    cudaGraphDestroy(g);
+    if (ce != cudaSuccess) return e->fail("trace step: %s", cudaGetErrorString(ce));
+    ce = cudaGraphLaunch(ge, e->stream);
+    if (ce == cudaSuccess) ce = cudaStreamSynchronize(e->stream);
+    cudaGraphExecDestroy(ge);
+    if (ce != cudaSuccess) return e->fail("trace step: %s", cudaGetErrorString(ce));
+    e->length += 1;
+    const int m = std::min(std::min(n, cap_launches), TRACE_MAX_LAUNCHES);
+    cudaMemcpy(out, e->d_trace, (size_t)m * 64, cudaMemcpyDeviceToHost);
+    *n_launches = m;
+    return 0;
 }
 
 int b2_profile_step(b2_engine* e, int iters, float ms[8], double bytes[8], int launches[8]) {

@@ -57,6 +57,28 @@ __device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Time stamps of a launch for the step timeline (debugging aid; trace is null in normal runs). Per launch
+// 8 words: [0] first block in, [1] block 0 past the dependency wait, [2] block 0 past its prologue,
+// [3] block 0 past its main loop, [4] last block out, [5] kernel code, [6] a shape hint.
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool trace_block0() { return (blockIdx.x | blockIdx.y | blockIdx.z) == 0; }
+__device__ __forceinline__ void trace_in(unsigned long long* p, int code, int hint) {
+    if (p && threadIdx.x == 0) {
+        atomicMin(p, gtime());
+        if (trace_block0()) { p[5] = (unsigned long long)code; p[6] = (unsigned long long)hint; }
+    }
+}
+__device__ __forceinline__ void trace_pt(unsigned long long* p, int i) {
+    if (p && threadIdx.x == 0 && trace_block0()) p[i] = gtime();
+}
+__device__ __forceinline__ void trace_out(unsigned long long* p) {
+    if (p && threadIdx.x == 0) atomicMax(p + 4, gtime());
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
@@ -218,9 +240,11 @@ struct Seg {
     int kind;
     int out_stride;
     int jobs;          // filled by the host: tiles of 8 rows (int8 kinds) or 4 rows (bf16 rows, gate/up pairs)
+    int tr;            // k_tcgemv: rows per tile chosen by the host (0 = as many as a stage holds)
 };
 
 struct GemvArgs {
+    unsigned long long* trace;   // step timeline slot of this launch, or null
     Seg seg[4];
     int nseg;
     int total_jobs;
@@ -554,6 +578,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv_norm(const GemvArgs a)
 #include "rowgemv.cuh"
 #include "mmagemm.cuh"
 #include "mmaexperts.cuh"
+#include "tcgemv.cuh"
 namespace b2 {
 
 // ------------------------------------------------------------------------------------------
@@ -563,6 +588,7 @@ namespace b2 {
 // Columns of S never interact, so a head is split over DV/32 blocks. State is [B][HV][DK][DV] fp32
 // and crosses HBM once in each direction.
 struct DeltaArgs {
+    unsigned long long* trace;   // step timeline slot of this launch, or null
     const float* y;      // [B][C] conv+SiLU output: q | k | v
     const float* beta;   // [B][HV]
     const float* g;      // [B][HV]
@@ -584,7 +610,9 @@ __global__ void __launch_bounds__(THREADS) k_delta_step(const DeltaArgs a) {
     const int key_dim = a.HK * DK;
     const int col = slab * 32 + lane;
     grid_dep_launch();
+    trace_in(a.trace, 3, gridDim.x);
     grid_dep_wait();        // the state itself is written by this kernel's previous launch
+    trace_pt(a.trace, 1);
 
     float* S = a.state + (((size_t)b * a.HV + h) * DK) * a.DV + col;
     float st[RPT];
@@ -642,6 +670,7 @@ __global__ void __launch_bounds__(THREADS) k_delta_step(const DeltaArgs a) {
         for (int w = 0; w < WARPS; w++) o += red[w][lane];
         a.o[(size_t)b * a.HV * a.DV + h * a.DV + col] = o;
     }
+    trace_out(a.trace);
 }
 
 // ------------------------------------------------------------------------------------------
@@ -754,6 +783,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_proj_out(const ProjArgs a) {
 // w = code * scale + min, so a row's dot is  sum_g ( s_g * sum(code * x) + m_g * sum(x) )  over its
 // 64-value groups (the factorisation of hybrid.cu:405-406).
 struct ExpertArgs {
+    unsigned long long* trace;   // step timeline slot of this launch, or null
     const uint8_t* const* eptr;   // [E] device address of each resident expert (null: not on this GPU)
     const int* top_idx;           // [tokens][idx_stride] the router's picks
     const float* top_w;           // [tokens][idx_stride]
@@ -790,7 +820,9 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_gu(const ExpertArgs a) {
     const int pick = blockIdx.y, b = pick / a.topk;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     grid_dep_launch();
+    trace_in(a.trace, 5, gridDim.x);
     grid_dep_wait();              // which expert to read is the previous kernel's result
+    trace_pt(a.trace, 1);
     const int e = a.top_idx[(size_t)b * a.idx_stride + pick % a.topk];
     const uint8_t* base = (e >= 0 && e < a.E) ? a.eptr[e] : nullptr;
     if (base == nullptr) {   // not resident here (another rank's expert) or a bad pick
@@ -891,6 +923,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_gu(const ExpertArgs a) {
             if (i < a.I) a.act[(size_t)pick * a.I + i] = siluf_(ag[u]) * au[u];
         }
     }
+    trace_out(a.trace);
 }
 
 // The down projections. grid (row blocks, topk + 1, B): blockIdx.y < topk computes one pick's
@@ -906,6 +939,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) 
     const int row0 = rb * DOWN_ROWS, row1 = min(a.D, row0 + DOWN_ROWS);
     __shared__ int s_last;
     grid_dep_launch();
+    trace_in(a.trace, 6, gridDim.x);
     float* yp = a.ypart + ((size_t)b * (a.topk + 1) + r) * a.D;
     if (r == a.topk) {
         // shared expert: int8 rows of SH values, one warp per row; only for this GPU's own tokens
@@ -996,7 +1030,8 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) 
             // under expert parallelism another GPU computes this pick; nothing is written here
         }
     }
-    if (!a.combine) return;
+    trace_pt(a.trace, 3);
+    if (!a.combine) { trace_out(a.trace); return; }
     // last block of this (sequence, row block): weighted sum in rank order, into the residual stream
     __threadfence();
     __syncthreads();
@@ -1005,7 +1040,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) 
         s_last = (n == (unsigned int)a.topk);
     }
     __syncthreads();
-    if (!s_last) return;
+    if (!s_last) { trace_out(a.trace); return; }
     __threadfence();
     for (int o = row0 + threadIdx.x; o < row1; o += THREADS) {
         const float* base = a.ypart + (size_t)b * (a.topk + 1) * a.D + o;
@@ -1015,6 +1050,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_down(const ExpertArgs a) 
         a.xout[(size_t)b * a.D + o] += y;
     }
     if (threadIdx.x == 0) a.counter[(size_t)b * gridDim.x + rb] = 0;
+    trace_out(a.trace);
 }
 
 // N consecutive cache values (bf16 or fp32) starting at a 4*N- or 2*N-byte aligned address -> fp32.
@@ -1058,6 +1094,7 @@ __device__ __forceinline__ void load_kv(const void* base, size_t elem, float (&o
 // all eight row loads in flight. A block leaves (acc, max, sum) per query head in scratch memory;
 // k_attn_merge combines the slices and applies sigmoid(gate).
 struct AttnArgs {
+    unsigned long long* trace;   // step timeline slot of this launch, or null
     const float* qraw;        // [B][H][2*HD]  (query | gate) per head
     const float* kraw;        // [B][KV][HD]
     const float* vraw;        // [B][KV][HD]
@@ -1087,7 +1124,9 @@ __global__ void __launch_bounds__(THREADS) k_attn(const AttnArgs a) {
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     grid_dep_launch();
+    trace_in(a.trace, 7, gridDim.x);
     grid_dep_wait();
+    trace_pt(a.trace, 1);
     const int pos = a.pos[b];
     const int L = pos + 1;
     int chunk = (L + a.nsplit - 1) / a.nsplit;
@@ -1270,6 +1309,7 @@ __global__ void __launch_bounds__(THREADS) k_attn(const AttnArgs a) {
             part[g * pstride + HD + 1] = lsum;
         }
     }
+    trace_out(a.trace);
 }
 
 // out[b][head][d] = (sum_s acc_s[d] * 2^(m_s - m)) / (sum_s l_s * 2^(m_s - m)) * sigmoid(gate[d])
@@ -1281,7 +1321,9 @@ __global__ void __launch_bounds__(THREADS) k_attn_merge(const AttnArgs a, int HD
     __shared__ float sc[64];
     __shared__ float s_inv;
     grid_dep_launch();
+    trace_in(a.trace, 8, gridDim.x);
     grid_dep_wait();
+    trace_pt(a.trace, 1);
     const size_t pstride = HD + 2;
     const float* pb = a.part + (((size_t)b * a.KV + kvh) * a.nsplit) * G * pstride + (size_t)g * pstride;
     const size_t sstride = (size_t)G * pstride;
@@ -1319,6 +1361,7 @@ __global__ void __launch_bounds__(THREADS) k_attn_merge(const AttnArgs a, int HD
         const float gate = a.qraw[((size_t)b * a.H + head) * 2 * HD + HD + d];
         a.out[(size_t)b * a.H * HD + head * HD + d] = (acc * s_inv) * sigmoidf_(gate);
     }
+    trace_out(a.trace);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -1,0 +1,463 @@
+// k_tcgemv: the decode GEMV (norm prologue + several weight matrices against the same activation
+// rows) with the multiply-adds of the int8 matrices on the tensor cores.
+//
+// A GEMV streams every weight once, so what limits it besides HBM is the instruction stream that turns
+// bytes into products: about 3.3 instructions per int8 weight when each product is an FMA. Here a warp
+// widens 16 bytes of two rows to fp16 (exact, 1.25 instructions per weight) and hands them to
+// mma.sync.m16n8k16 as the A operand; the B operand holds the activations as fp16 hi + lo halves
+// (x = hi + lo to about 22 bits) in columns b (hi) and 4 + b (lo) for up to 4 sequences, so one
+// instruction multiplies 16 rows x 16 values for all of them with fp32 accumulation.
+//
+// The tile, its bulk copies and the segment bookkeeping are those of k_rowgemv: 32 row slots of up to
+// 2048 bytes (16 slots for rows of up to 4096 bytes: bf16 rows, int8 rows of 4096 values), one bulk
+// copy per slot, slots padded by 64 bytes so that the fragment loads of rows r and r + 1 fall into
+// different halves of the banks. The W compute warps of a block split a tile into (16-row block, K
+// slice) parts and leave their partial sums in shared memory. Two more warps take the tiles in turn:
+// they fetch the epilogue operands (scales, convolution taps and state) while the tile is being
+// multiplied, wait on a named barrier for its partial sums, re-arm the freed stage with the next bulk
+// copies, add the partial sums in slice order and run the epilogue with one lane per row slot, so the
+// global-memory round trips of the epilogue are off the compute warps' path. bf16 rows (router,
+// DeltaNet a/b projections) keep fp32 FMAs on fp32 activations with the same thread-to-byte mapping.
+// The rows of a tile (at most 32, or 16 wide ones) are chosen per launch so that the tiles divide
+// evenly among the blocks.
+#pragma once
+
+namespace b2 {
+
+constexpr int TC_PAD = 64;
+constexpr int TC_SLOT_STRIDE = RL_SLOT_MAX + TC_PAD;              // 2112
+constexpr int TC_SLOT_STRIDE_WIDE = 2 * RL_SLOT_MAX + TC_PAD;     // 4160
+constexpr int TC_STAGE_BYTES = 32 * TC_SLOT_STRIDE;               // 67,584 (>= 16 * 4160)
+
+__host__ __device__ __forceinline__ bool tc_has_bf(const GemvArgs& a) {
+    for (int i = 0; i < a.nseg; i++)
+        if (rl_is_bf(a.seg[i].kind)) return true;
+    return false;
+}
+constexpr int TC_EPI = 2;          // epilogue warps
+__device__ __forceinline__ void bar_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+__device__ __forceinline__ void bar_arrive(int id, int n) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(n) : "memory"); }
+// rows of a tile of this segment: what the host chose, else the most a stage holds
+__host__ __device__ __forceinline__ int tc_tile_rows(const Seg& g, int K) { return g.tr > 0 ? g.tr : rl_tile_rows(g.kind, K); }
+// bytes of dynamic shared memory: stages | fp16 activations [2 NB][K] | fp32 activations [NB][K] (only with
+// bf16 rows) | partial sums [2][NB][W][32]
+__host__ __device__ __forceinline__ size_t tc_smem_bytes(const GemvArgs& a, int NB, int NST, int W) {
+    return (size_t)NST * TC_STAGE_BYTES + (size_t)2 * NB * a.K * 2 + (tc_has_bf(a) ? (size_t)NB * a.K * 4 : 0) +
+           (size_t)2 * NB * W * 32 * 4;
+}
+// the shapes the tensor-core path takes: K slices of whole 64-byte steps
+__host__ __device__ __forceinline__ bool tc_shape_ok(int K, int W) { return K % (32 * W) == 0 && K <= 2 * RL_SLOT_MAX; }
+
+
+
+// NJ 64-byte steps of a warp's K slice for rows (gid, gid + 8): every load first, then NJ independent
+// accumulation chains, so that the latencies of the loads, the widening and the mma overlap.
+template <int NJ>
+__device__ __forceinline__ void tc_i8_steps(const unsigned char* pa, const unsigned char* pb, const __half* px, bool colact,
+                                            float (&c)[4]) {
+    uint4 wa[NJ], wb[NJ], x0[NJ], x1[NJ];
+#pragma unroll
+    for (int j = 0; j < NJ; j++) {
+        wa[j] = *reinterpret_cast<const uint4*>(pa + 64 * j);
+        wb[j] = *reinterpret_cast<const uint4*>(pb + 64 * j);
+        x0[j] = make_uint4(0u, 0u, 0u, 0u); x1[j] = x0[j];
+        if (colact) {
+            x0[j] = *reinterpret_cast<const uint4*>(px + 64 * j);
+            x1[j] = *reinterpret_cast<const uint4*>(px + 64 * j + 8);
+        }
+    }
+    float cc[NJ][4];
+#pragma unroll
+    for (int j = 0; j < NJ; j++)
+#pragma unroll
+        for (int q = 0; q < 4; q++) cc[j][q] = 0.f;
+#pragma unroll
+    for (int m = 0; m < 4; m++) {
+#pragma unroll
+        for (int j = 0; j < NJ; j++) {
+            const uint32_t a = m == 0 ? wa[j].x : m == 1 ? wa[j].y : m == 2 ? wa[j].z : wa[j].w;
+            const uint32_t b = m == 0 ? wb[j].x : m == 1 ? wb[j].y : m == 2 ? wb[j].z : wb[j].w;
+            const uint32_t xa = m == 0 ? x0[j].x : m == 1 ? x0[j].z : m == 2 ? x1[j].x : x1[j].z;
+            const uint32_t xb = m == 0 ? x0[j].y : m == 1 ? x0[j].w : m == 2 ? x1[j].y : x1[j].w;
+            uint32_t af[4];
+            i8x4_to_h2x2(a, af[0], af[2]);
+            i8x4_to_h2x2(b, af[1], af[3]);
+            mma16816(cc[j], af, xa, xb);
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NJ; j++)
+#pragma unroll
+        for (int q = 0; q < 4; q++) c[q] += cc[j][q];
+}
+
+template <int NB, int NST, int W>
+__global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs a, int nseq) {
+    constexpr int WT = W + TC_EPI;                 // all warps
+    constexpr int NT = WT * 32;
+    constexpr int XPT = (2 * RL_SLOT_MAX + NT - 1) / NT;   // activation values per thread in the prologue
+    constexpr int BAR_N = W * 32 + 32;             // the compute warps and the one epilogue warp of a tile
+    extern __shared__ __align__(128) unsigned char tc_smem[];
+    const bool has_bf = tc_has_bf(a);
+    unsigned char* stages = tc_smem;                                                     // [NST][TC_STAGE_BYTES]
+    __half* xh = reinterpret_cast<__half*>(tc_smem + (size_t)NST * TC_STAGE_BYTES);      // [2 NB][K]: hi rows, then lo rows
+    float* xs = reinterpret_cast<float*>(xh + (size_t)2 * NB * a.K);                     // [NB][K] when has_bf
+    float* part = xs + (has_bf ? (size_t)NB * a.K : 0);                                  // [2][NB][W][32]
+    __shared__ __align__(8) uint64_t full_bar[NST];
+    __shared__ float red[WT][NB];
+    __shared__ int s_last;
+    __shared__ float s_bv[TC_EPI][NB];
+    __shared__ int s_bi[TC_EPI][NB];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int gid = lane >> 2, tid = lane & 3;
+    const int b0 = blockIdx.y * NB;                    // first sequence of this pass
+    const int t0 = (int)((long long)blockIdx.x * a.total_jobs / gridDim.x);
+    const int t1 = (int)((long long)(blockIdx.x + 1) * a.total_jobs / gridDim.x);
+    grid_dep_launch();
+    trace_in(a.trace, 1, a.seg[0].rows);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NST; s++) mbar_init(&full_bar[s], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    auto locate = [&](int t, int& s, int& tin) {
+        s = 0; tin = t;
+        while (s + 1 < a.nseg && tin >= a.seg[s].jobs) { tin -= a.seg[s].jobs; s++; }
+    };
+    // one warp asks for tile t into stage st, one bulk copy per slot
+    auto request = [&](int t, int st) {
+        int s, tin;
+        locate(t, s, tin);
+        const Seg& sg = a.seg[s];
+        const int tr = tc_tile_rows(sg, a.K);
+        const int row0 = tin * tr;
+        const int n = min(tr, sg.rows - row0);
+        const bool pair = sg.kind == SEG_I8_GATEUP;
+        const uint32_t rb = rl_is_bf(sg.kind) ? 2u * a.K : (uint32_t)a.K;          // bytes per slot
+        const int nslots = pair ? 2 * n : n;
+        if (lane == 0) mbar_expect_tx(&full_bar[st], rb * nslots);
+        __syncwarp();
+        const int sstride = rl_two_lanes(sg.kind, a.K) ? TC_SLOT_STRIDE_WIDE : TC_SLOT_STRIDE;
+        const bool active = pair ? (lane < n || (lane >= 16 && lane < 16 + n)) : lane < n;
+        if (active) {
+            const char* src = pair ? (lane < 16 ? (const char*)sg.w + (size_t)(row0 + lane) * a.K
+                                                : (const char*)sg.w2 + (size_t)(row0 + lane - 16) * a.K)
+                                   : (const char*)sg.w + (size_t)(row0 + lane) * rb;
+            bulk_load(stages + (size_t)st * TC_STAGE_BYTES + (size_t)lane * sstride, src, rb, &full_bar[st]);
+        }
+    };
+    if (warp == W)
+        for (int i = 0; i < NST && t0 + i < t1; i++) request(t0 + i, i);
+    grid_dep_wait();
+    trace_pt(a.trace, 1);
+
+    // prologue: the normalised activations as fp16 hi | lo (and fp32 when bf16 rows follow); every value
+    // crosses from global memory once, all loads of a thread in flight together
+    auto put_x = [&](int b, int k, float v) {
+        const __half h = __float2half(v);
+        xh[(size_t)b * a.K + k] = h;
+        xh[(size_t)(NB + b) * a.K + k] = __float2half(v - __half2float(h));
+        if (has_bf) xs[(size_t)b * a.K + k] = v;
+    };
+    if (a.gn_w) {
+        // DeltaNet output projection: w * rmsnorm_DV(o) * silu(z) per value head (aegist/hybrid.py:133-147);
+        // a warp takes heads warp, warp + WT, ...; a lane DV / 32 values of each
+        constexpr int HPW = 4, DVL = 8;              // up to 4 heads per warp, DV <= 256
+        const int nh = a.K / a.DV, dvl = a.DV >> 5;
+#pragma unroll 1
+        for (int b = 0; b < NB; b++) {
+            const bool live = b0 + b < nseq;
+            const float* in = a.x + (size_t)(b0 + b) * a.x_stride;
+            const float* z = a.z + (size_t)(b0 + b) * a.x_stride;
+            for (int hb = 0; hb < nh; hb += HPW * WT) {
+                float vi[HPW][DVL], vz[HPW][DVL], vw[DVL];
+#pragma unroll
+                for (int i = 0; i < DVL; i++) vw[i] = i < dvl ? bf(a.gn_w[lane + 32 * i]) : 0.f;
+#pragma unroll
+                for (int hh = 0; hh < HPW; hh++) {
+                    const int h = hb + warp + hh * WT;
+#pragma unroll
+                    for (int i = 0; i < DVL; i++) {
+                        const bool ok = live && h < nh && i < dvl;
+                        vi[hh][i] = ok ? in[h * a.DV + lane + 32 * i] : 0.f;
+                        vz[hh][i] = ok ? z[h * a.DV + lane + 32 * i] : 0.f;
+                    }
+                }
+#pragma unroll
+                for (int hh = 0; hh < HPW; hh++) {
+                    const int h = hb + warp + hh * WT;
+                    float ss = 0.f;
+#pragma unroll
+                    for (int i = 0; i < DVL; i++) ss = fmaf(vi[hh][i], vi[hh][i], ss);
+                    ss = warp_sum(ss);
+                    const float r = 1.0f / sqrtf(ss / (float)a.DV + a.eps);
+                    if (h < nh)
+#pragma unroll
+                        for (int i = 0; i < DVL; i++)
+                            if (i < dvl) put_x(b, h * a.DV + lane + 32 * i, (vw[i] * (vi[hh][i] * r)) * vz[hh][i]);
+                }
+            }
+        }
+    } else {
+        float xv[NB][XPT], nw[XPT];
+#pragma unroll
+        for (int j = 0; j < XPT; j++) {
+            const int k = threadIdx.x + j * NT;
+            nw[j] = (a.norm_w && k < a.K) ? 1.0f + bf(a.norm_w[k]) : 1.0f;
+#pragma unroll
+            for (int b = 0; b < NB; b++) xv[b][j] = (k < a.K && b0 + b < nseq) ? a.x[(size_t)(b0 + b) * a.x_stride + k] : 0.f;
+        }
+        float rn[NB];
+#pragma unroll
+        for (int b = 0; b < NB; b++) rn[b] = 1.0f;
+        if (a.norm_w) {
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                float ss = 0.f;
+#pragma unroll
+                for (int j = 0; j < XPT; j++) ss = fmaf(xv[b][j], xv[b][j], ss);
+                ss = warp_sum(ss);
+                if (lane == 0) red[warp][b] = ss;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                float t = 0.f;
+#pragma unroll
+                for (int w = 0; w < WT; w++) t += red[w][b];
+                rn[b] = 1.0f / sqrtf(t / (float)a.K + a.eps);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < XPT; j++) {
+            const int k = threadIdx.x + j * NT;
+            if (k < a.K)
+#pragma unroll
+                for (int b = 0; b < NB; b++) put_x(b, k, a.norm_w ? xv[b][j] * rn[b] * nw[j] : xv[b][j]);
+        }
+    }
+    __syncthreads();
+    trace_pt(a.trace, 2);
+
+    float best_v[NB];
+    int best_i[NB];
+#pragma unroll
+    for (int b = 0; b < NB; b++) { best_v[b] = -INFINITY; best_i[b] = 0x7fffffff; }
+
+    if (warp < W) {
+        // ---- compute warps: partial sums of every tile into part[tile & 1] ----
+        // this lane's activation column in the B operand: hi of sequence (gid & 3) or lo of it
+        const bool colact = (gid & 3) < NB;
+        const __half* xcol = xh + (size_t)((gid >> 2) * NB + (gid & 3)) * a.K;
+        for (int t = t0, i = 0; t < t1; t++, i++) {
+            const int st = i % NST, buf = i & 1;
+            int s, tin;
+            locate(t, s, tin);
+            const int kind = a.seg[s].kind;
+            const bool isbf = rl_is_bf(kind);
+            const bool two = rl_two_lanes(kind, a.K);
+            float* pt = part + (size_t)buf * NB * W * 32;
+            const unsigned char* stage = stages + (size_t)st * TC_STAGE_BYTES;
+            if (i >= 2) bar_sync(3 + buf, BAR_N);          // the epilogue of tile i - 2 has read this buffer
+            mbar_wait(&full_bar[st], (i / NST) & 1, a.err);
+            if (!isbf) {
+                const int nrb = two ? 1 : 2;               // 16-slot blocks in the tile
+                const int nks = W / nrb;
+                const int rbk = warp % nrb, ks = warp / nrb;
+                const int slice = a.K / nks;               // bytes = values; a multiple of 64
+                const int sstride = two ? TC_SLOT_STRIDE_WIDE : TC_SLOT_STRIDE;
+                const unsigned char* pa = stage + (size_t)(rbk * 16 + gid) * sstride + ks * slice + tid * 16;
+                const unsigned char* pb = pa + (size_t)8 * sstride;
+                const __half* px = xcol + ks * slice + tid * 16;
+                float c0[4] = {0.f, 0.f, 0.f, 0.f};
+                int j = 0;
+                for (; j + 256 <= slice; j += 256) tc_i8_steps<4>(pa + j, pb + j, px + j, colact, c0);
+                if (j + 128 <= slice) { tc_i8_steps<2>(pa + j, pb + j, px + j, colact, c0); j += 128; }
+                if (j + 64 <= slice) tc_i8_steps<1>(pa + j, pb + j, px + j, colact, c0);
+                // c[q]: row gid (+8 for q >= 2), column 2 tid + (q & 1); hi + lo of a sequence are 4 columns apart
+#pragma unroll
+                for (int q = 0; q < 4; q++) {
+                    float v = c0[q];
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    const int b = 2 * tid + (q & 1);
+                    if (tid < 2 && b < NB) pt[((size_t)b * W + ks) * 32 + rbk * 16 + gid + (q >> 1) * 8] = v;
+                }
+            } else {
+                // bf16 rows: 16 slots of 2 K bytes; warp -> (8-row half, K slice), lane -> (row, 16-byte unit of a 64-byte step)
+                const int nks = W / 2;
+                const int rh = warp & 1, ks = warp >> 1;
+                const int slice = 2 * a.K / nks;           // bytes
+                const unsigned char* pa = stage + (size_t)(rh * 8 + gid) * TC_SLOT_STRIDE_WIDE + ks * slice + tid * 16;
+                float acc[NB];
+#pragma unroll
+                for (int b = 0; b < NB; b++) acc[b] = 0.f;
+#pragma unroll 4
+                for (int j = 0; j < slice; j += 64) {
+                    const uint4 wv = *reinterpret_cast<const uint4*>(pa + j);
+                    const int k0 = (ks * slice + j + tid * 16) >> 1;
+#pragma unroll
+                    for (int b = 0; b < NB; b++) {
+                        const float4* pxs = reinterpret_cast<const float4*>(xs + (size_t)b * a.K + k0);
+                        const float4 x0 = pxs[0], x1 = pxs[1];
+                        float p = x0.x * bflo(wv.x);
+                        p = fmaf(x0.y, bfhi(wv.x), p); p = fmaf(x0.z, bflo(wv.y), p); p = fmaf(x0.w, bfhi(wv.y), p);
+                        p = fmaf(x1.x, bflo(wv.z), p); p = fmaf(x1.y, bfhi(wv.z), p); p = fmaf(x1.z, bflo(wv.w), p);
+                        p = fmaf(x1.w, bfhi(wv.w), p);
+                        acc[b] += p;
+                    }
+                }
+#pragma unroll
+                for (int b = 0; b < NB; b++) {
+                    float v = acc[b];
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    v += __shfl_xor_sync(0xffffffffu, v, 2);
+                    if (tid == 0) pt[((size_t)b * W + ks) * 32 + rh * 8 + gid] = v;
+                }
+            }
+            bar_arrive(1 + buf, BAR_N);            // partial sums written, the stage read
+        }
+    } else {
+        // ---- epilogue warps: warp W + p takes tiles p, p + 2, ... of this block ----
+        const int p = warp - W;
+        for (int t = t0 + p, i = p; t < t1; t += TC_EPI, i += TC_EPI) {
+            const int st = i % NST;
+            int s, tin;
+            locate(t, s, tin);
+            const Seg& sg = a.seg[s];
+            const bool isbf = rl_is_bf(sg.kind);
+            const bool two = rl_two_lanes(sg.kind, a.K);
+            const bool pair = sg.kind == SEG_I8_GATEUP;
+            const int tr = tc_tile_rows(sg, a.K);
+            const int np = isbf ? W / 2 : (two ? W : W / 2);       // partial sums per row slot
+            const int row = tin * tr + lane;                        // lane j owns output row0 + j
+            const bool mine = lane < tr && row < sg.rows;
+            const float* pt = part + (size_t)p * NB * W * 32;
+            // everything the epilogue needs from global memory is requested before the tile is waited for
+            float e0 = 0.f, e1 = 0.f;
+            uint2 ecw = make_uint2(0u, 0u);
+            float cst[NB][3];
+            if (mine) {
+                switch (sg.kind) {
+                case SEG_I8: case SEG_I8_ARGMAX: case SEG_I8_SILU: case SEG_I8_CONV: case SEG_I8_ACC: e0 = bf(sg.s[row]); break;
+                case SEG_I8_GATEUP: e0 = bf(sg.s[row]); e1 = bf(sg.s2[row]); break;
+                case SEG_BF_DECAY: e0 = bf(a.a_log[row]); e1 = bf(a.dt_bias[row]); break;
+                case SEG_BF: e0 = sg.bias ? sg.bias[row] : 0.f; break;
+                default: break;
+                }
+                if (sg.kind == SEG_I8_CONV) {
+                    ecw = *reinterpret_cast<const uint2*>(a.conv_w + (size_t)row * 4);
+#pragma unroll
+                    for (int b = 0; b < NB; b++) {
+                        if (b0 + b >= nseq) continue;
+                        const float* stt = a.conv_state + ((size_t)(b0 + b) * sg.rows + row) * 3;
+                        cst[b][0] = stt[0]; cst[b][1] = stt[1]; cst[b][2] = stt[2];
+                    }
+                }
+            }
+            bar_sync(1 + p, BAR_N);                // partial sums of tile i complete; its stage is free
+            if (t + NST < t1) request(t + NST, st);
+#pragma unroll
+            for (int b = 0; b < NB; b++) {
+                if (!mine || b0 + b >= nseq) continue;
+                const float* pb = pt + (size_t)b * W * 32;
+                float sA = 0.f, sB = 0.f;
+                for (int w = 0; w < np; w++) { sA += pb[w * 32 + lane]; if (pair) sB += pb[w * 32 + lane + 16]; }
+                float* out = sg.out + (size_t)(b0 + b) * sg.out_stride;
+                switch (sg.kind) {
+                case SEG_I8: out[row] = e0 * sA; break;
+                case SEG_I8_ACC: out[row] += e0 * sA; break;
+                case SEG_I8_SILU: out[row] = siluf_(e0 * sA); break;
+                case SEG_I8_ARGMAX: {
+                    const float v0 = e0 * sA;
+                    out[row] = v0;
+                    if (v0 > best_v[b] || (v0 == best_v[b] && row < best_i[b])) { best_v[b] = v0; best_i[b] = row; }
+                } break;
+                case SEG_I8_CONV: {
+                    // hybrid.py:393-398: y = silu(sum_j w[c][j] * taps[j]), taps = 3 previous inputs + the new one
+                    const float raw = e0 * sA;
+                    float* stt = a.conv_state + ((size_t)(b0 + b) * sg.rows + row) * 3;
+                    float y = bflo(ecw.x) * cst[b][0];
+                    y = fmaf(bfhi(ecw.x), cst[b][1], y);
+                    y = fmaf(bflo(ecw.y), cst[b][2], y);
+                    y = fmaf(bfhi(ecw.y), raw, y);
+                    stt[0] = cst[b][1]; stt[1] = cst[b][2]; stt[2] = raw;
+                    out[row] = siluf_(y);
+                } break;
+                case SEG_BF_SIGMOID: out[row] = sigmoidf_(sA); break;
+                case SEG_BF_DECAY: out[row] = -expf(e0) * softplusf_(sA + e1); break;
+                case SEG_BF: out[row] = sA + e0; break;
+                case SEG_I8_GATEUP: out[row] = siluf_(e0 * sA) * (e1 * sB); break;
+                }
+            }
+            if (t + TC_EPI < t1) bar_arrive(3 + p, BAR_N);     // the buffer may be written again
+        }
+    }
+    trace_pt(a.trace, 3);
+    if (a.finisher == FIN_NONE) { trace_out(a.trace); return; }
+    // finishers, one pass of NB sequences at a time
+    if (a.finisher == FIN_ARGMAX) {
+        if (warp >= W) {
+#pragma unroll
+            for (int b = 0; b < NB; b++) {          // best over the lanes of an epilogue warp
+                float v = best_v[b];
+                int ix = best_i[b];
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) {
+                    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+                    const int oi = __shfl_xor_sync(0xffffffffu, ix, o);
+                    if (ov > v || (ov == v && oi < ix)) { v = ov; ix = oi; }
+                }
+                if (lane == 0) { s_bv[warp - W][b] = v; s_bi[warp - W][b] = ix; }
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x < NB && b0 + threadIdx.x < nseq) {
+            const int b = threadIdx.x;
+            float v = s_bv[0][b];
+            int ix = s_bi[0][b];
+            for (int w = 1; w < TC_EPI; w++)
+                if (s_bv[w][b] > v || (s_bv[w][b] == v && s_bi[w][b] < ix)) { v = s_bv[w][b]; ix = s_bi[w][b]; }
+            a.part_val[(size_t)(b0 + b) * gridDim.x + blockIdx.x] = v;
+            a.part_idx[(size_t)(b0 + b) * gridDim.x + blockIdx.x] = ix;
+        }
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned int n = atomicAdd(a.counter + blockIdx.y, 1u);
+        s_last = (n == gridDim.x - 1);
+    }
+    __syncthreads();
+    if (!s_last) { trace_out(a.trace); return; }
+    __threadfence();
+    if (warp < NB && b0 + warp < nseq) {
+        const int b = b0 + warp;
+        if (a.finisher == FIN_TOPK) {
+            router_topk_warp(a.seg[0].out + (size_t)b * a.seg[0].out_stride, a.E, a.topk, a.top_idx + (size_t)b * a.topk,
+                             a.top_w + (size_t)b * a.topk, lane);
+        } else {
+            float v = -INFINITY;
+            int ix = 0x7fffffff;
+            for (int g = lane; g < (int)gridDim.x; g += 32) {
+                const float pv = __ldcg(a.part_val + (size_t)b * gridDim.x + g);
+                const int pi = __ldcg(a.part_idx + (size_t)b * gridDim.x + g);
+                if (pv > v || (pv == v && pi < ix)) { v = pv; ix = pi; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, ix, o);
+                if (ov > v || (ov == v && oi < ix)) { v = ov; ix = oi; }
+            }
+            if (lane == 0) {
+                a.next_tok[b] = ix;
+                if (a.pos) a.pos[b] += 1;
+            }
+        }
+    }
+    if (threadIdx.x == 0) a.counter[blockIdx.y] = 0;
+    trace_out(a.trace);
+}
+
+}  // namespace b2

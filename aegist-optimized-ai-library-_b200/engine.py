@@ -76,6 +76,7 @@ SYMBOLS = {
     "b2_launches_per_step": (_I, [_P]),
     "b2_step_bytes": (C.c_double, [_P]),
     "b2_profile_step": (_I, [_P, _I, C.POINTER(_F), C.POINTER(C.c_double), C.POINTER(_I)]),
+    "b2_debug_trace_step": (_I, [_P, C.POINTER(C.c_uint64), _I, C.POINTER(_I)]),
     "b2_op_linear_i8": (_I, [_I, _P, _P, _I, _I, _P, _I, _P]),
     "b2_moe_create": (_I, [_I, C.POINTER(MoeWeights), _I, C.POINTER(_P)]),
     "b2_moe_forward": (_I, [_P, _P, _I, _P, _P, _P, C.POINTER(_F)]),
@@ -295,6 +296,13 @@ class HybridEngine:
         ms, by, ln = (C.c_float * 8)(), (C.c_double * 8)(), (C.c_int * 8)()
         self._check(self._lib.b2_profile_step(self._h, iters, ms, by, ln))
         return {n: {"ms": ms[i], "bytes": by[i], "launches": ln[i]} for i, n in enumerate(self.KERNEL_CLASSES)}
+
+    def trace_step(self, cap: int = 4096):
+        """Timeline of one graph-run decode step: an int64 array [launches][8] (see b2_debug_trace_step)."""
+        buf = (C.c_uint64 * (8 * cap))()
+        n = C.c_int(0)
+        self._check(self._lib.b2_debug_trace_step(self._h, buf, cap, C.byref(n)))
+        return np.frombuffer(buf, dtype=np.uint64)[: 8 * n.value].reshape(n.value, 8).copy()
 
 
 # --- sampler (aegist_rs/src/chat.rs:221-272) ----------------------------------------------------
