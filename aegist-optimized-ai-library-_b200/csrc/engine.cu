@@ -98,6 +98,8 @@ static size_t dtype_size(const std::string& d) {
 static bool g_rowgemv = [] { const char* v = getenv("B2_ROWGEMV"); return !(v && v[0] == '0'); }();
 // Tensor-core GEMV (k_tcgemv) for the int8 matrices of small batches (B2_TCGEMV=0 switches back to k_rowgemv);
 // B2_TC_WARPS = 8 or 16 warps per block.
+// Expert kernels for fewer than 8 tokens (k_moe_gu1 / k_moe_down1; B2_MOE1=0 switches back to the per-pick kernels).
+static bool g_moe1 = [] { const char* v = getenv("B2_MOE1"); return !(v && v[0] == '0'); }();
 static bool g_tcgemv = [] { const char* v = getenv("B2_TCGEMV"); return !(v && v[0] == '0'); }();
 static int g_tc_warps = [] { const char* v = getenv("B2_TC_WARPS"); return (v && atoi(v) == 8) ? 8 : 16; }();
 static int g_gemv_ctas_per_sm = [] { const char* v = getenv("B2_GEMV_CTAS"); return v ? atoi(v) : 2; }();
@@ -156,6 +158,9 @@ struct b2_engine {
     __half* acth = nullptr;
     float *xsum_tok = nullptr, *xsum_act = nullptr;
     int cap_small = 0, cap_big = 0;
+    const uint8_t** top_ptr = nullptr;       // [B][TOPK] expert blobs of the current layer's picks (k_moe_gu1 -> k_moe_down1)
+    int8_t* actq = nullptr;                  // [B * TOPK][4][I] digit planes of act
+    float *asc = nullptr, *asum = nullptr;   // [B * TOPK][I / 32] scale and sum of each 32-value group of act
     unsigned long long* d_trace = nullptr;   // step timeline slots, allocated by the first b2_debug_trace_step
     float* ypart = nullptr;                  // [B][TOPK + 1][D]
     unsigned int* d_dcounter = nullptr;      // [B][row blocks of the expert down projection]
@@ -226,7 +231,7 @@ b2_engine::~b2_engine() {
     for (auto& l : layers) { cudaFree((void*)l.eptr); cudaFree(l.router_bias); }
     void* bufs[] = {conv, state, snap_conv[0], snap_conv[1], snap_state[0], snap_state[1], kpool, vpool, page_table, rope_cos,
                     rope_sin, d_tok, d_next, d_pos, d_err, d_counter, d_acounter, x, big, zbuf, kraw, vraw, beta, gdec, obuf, att,
-                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh, g_list, g_chunk, acth, xsum_tok, xsum_act, d_trace};
+                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh, g_list, g_chunk, acth, xsum_tok, xsum_act, d_trace, (void*)top_ptr, actq, asc, asum};
     for (void* p : bufs) cudaFree(p);
     if (h_pin) cudaFreeHost(h_pin);
     if (ev0) cudaEventDestroy(ev0);
@@ -468,6 +473,9 @@ int b2_engine::finish() {
     const size_t Bg = (size_t)B * ep_world;   // sequences whose picks may land on this GPU's experts
     CU(dalloc(&act, Bg * c.TOPK * c.I)); CU(dalloc(&logits, (size_t)B * c.V));
     CU(dalloc(&top_idx, (size_t)c.L * B * c.TOPK)); CU(dalloc(&top_w, (size_t)c.L * B * c.TOPK));
+    CU(dalloc(&top_ptr, (size_t)B * c.TOPK));
+    CU(dalloc(&actq, (size_t)B * c.TOPK * M1_PLANES * c.I));
+    CU(dalloc(&asc, (size_t)B * c.TOPK * std::max(1, c.I / 32))); CU(dalloc(&asum, (size_t)B * c.TOPK * std::max(1, c.I / 32)));
     head_grid = g_rowgemv ? std::min((c.V + 31) / 32, nsm) : std::min((c.V + 7) / 8, g_gemv_ctas_per_sm * nsm);
     CU(dalloc(&part_val, (size_t)B * head_grid)); CU(dalloc(&part_idx, (size_t)B * head_grid));
     // attention: enough slices to fill the GPU, but at least 64 positions each at full context
@@ -515,7 +523,7 @@ static bool g_pdl = [] { const char* v = getenv("B2_PDL"); return !(v && v[0] ==
 static int g_launch_count = 0;   // kernels launched so far (a step's count is the difference)
 
 // Step timeline (b2_debug_trace_step): while g_trace_base is set, the launch with index i since g_trace_first
-// gets the slot g_trace_base + 8 i in its argument struct (structs with a `trace` member; null otherwise).
+// gets the slot g_trace_base + 16 i in its argument struct (structs with a `trace` member; null otherwise).
 static unsigned long long* g_trace_base = nullptr;
 static int g_trace_first = 0;
 constexpr int TRACE_MAX_LAUNCHES = 4096;
@@ -523,7 +531,7 @@ template <typename T>
 static auto with_trace(const T& a, int) -> decltype((void)a.trace, T()) {
     T c = a;
     const int i = g_launch_count - 1 - g_trace_first;
-    c.trace = (g_trace_base && i >= 0 && i < TRACE_MAX_LAUNCHES) ? g_trace_base + (size_t)8 * i : nullptr;
+    c.trace = (g_trace_base && i >= 0 && i < TRACE_MAX_LAUNCHES) ? g_trace_base + (size_t)16 * i : nullptr;
     return c;
 }
 template <typename T>
@@ -868,10 +876,35 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.seg[2] = make_seg(SEG_BF_SIGMOID, l.sh_gw, nullptr, 1, sgate, 1);
             a.nseg = 3; seal(a, c.D);
             a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D; a.err = d_err;
-            a.finisher = FIN_TOPK; a.counter = d_counter; a.E = c.E; a.topk = c.TOPK;
+            // fewer than 8 tokens on one GPU: the top-8 moves into the expert kernel and the experts are spread over all SMs
+            const bool moe1 = g_moe1 && ep_world == 1 && B < 8 && c.D % 512 == 0 && c.D <= 4096 && c.I % 128 == 0 && c.I <= 2048 &&
+                              c.SH % 128 == 0 && c.TOPK <= 8 && c.E <= 256;
+            a.finisher = moe1 ? FIN_NONE : FIN_TOPK; a.counter = d_counter; a.E = c.E; a.topk = c.TOPK;
             a.top_idx = top_idx + (size_t)li * B * c.TOPK; a.top_w = top_w + (size_t)li * B * c.TOPK;
             launch_gemv(a, B, nsm, st, 0, bc);
             mark(1, st);
+            if (moe1) {
+                Gu1Args g{};
+                g.logits = rlogits; g.x = x; g.norm_w = l.norm2; g.eps = c.eps; g.eptr = l.eptr;
+                g.off_gu_s = c.off_gu_s(); g.off_gu_m = c.off_gu_m(); g.D = c.D; g.I = c.I; g.E = c.E; g.topk = c.TOPK;
+                g.top_idx = a.top_idx; g.top_w = a.top_w; g.top_ptr = top_ptr; g.actq = actq; g.asc = asc; g.asum = asum; g.err = d_err;
+                const int gx = c.TOPK * c.I / M1_GU_PAIRS;
+                cudaError_t ce = opt_in_smem(k_moe_gu1, m1_gu_smem(c.D));
+                if (ce == cudaSuccess) ce = launch_k(k_moe_gu1, dim3(gx, B), dim3(M1_GU_THREADS), m1_gu_smem(c.D), st, g);
+                mark(5, st);
+                Down1Args d{};
+                d.top_ptr = top_ptr; d.top_w = a.top_w; d.actq = actq; d.asc = asc; d.asum = asum; d.sh_act = sh_act; d.sg = sgate;
+                d.shd_w = (const int8_t*)l.sh_down.w; d.shd_s = l.sh_down.s;
+                d.off_dn_q = c.off_dn_q(); d.off_dn_s = c.off_dn_s(); d.off_dn_m = c.off_dn_m();
+                d.D = c.D; d.I = c.I; d.SH = c.SH; d.topk = c.TOPK; d.xout = x;
+                const size_t dsm = m1_down_smem(c.I, c.SH, c.TOPK);
+                if (ce == cudaSuccess) ce = opt_in_smem(k_moe_down1, dsm);
+                if (ce == cudaSuccess)
+                    ce = launch_k(k_moe_down1, dim3((c.D + M1_DOWN_ROWS - 1) / M1_DOWN_ROWS, B), dim3(2 * (c.TOPK + 1) * 32), dsm, st, d);
+                if (ce != cudaSuccess) return fail("expert kernels: %s", cudaGetErrorString(ce));
+                mark(6, st);
+                n += 3;
+            } else {
             ExpertArgs x2{};
             x2.eptr = l.eptr; x2.topk = c.TOPK; x2.E = c.E; x2.D = c.D; x2.I = c.I;
             x2.off_gu_s = c.off_gu_s(); x2.off_gu_m = c.off_gu_m(); x2.off_dn_q = c.off_dn_q(); x2.off_dn_s = c.off_dn_s(); x2.off_dn_m = c.off_dn_m();
@@ -915,6 +948,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
                 n += 2;
             }
             n += 3;
+            }
         }
         for (size_t j = 0; j < tap_layers.size(); j++)
             if (tap_layers[j] == li)
@@ -1377,9 +1411,9 @@ double b2_step_bytes(const b2_engine* e) {
 
 int b2_debug_trace_step(b2_engine* e, unsigned long long* out, int cap_launches, int* n_launches) {
     if (feed_checks(e, 1)) return 1;
-    if (!e->d_trace && cudaMalloc(&e->d_trace, (size_t)TRACE_MAX_LAUNCHES * 64) != cudaSuccess) return e->fail("trace buffer: out of memory");
-    std::vector<unsigned long long> init((size_t)TRACE_MAX_LAUNCHES * 8, 0ull);
-    for (int i = 0; i < TRACE_MAX_LAUNCHES; i++) init[(size_t)8 * i] = ~0ull;
+    if (!e->d_trace && cudaMalloc(&e->d_trace, (size_t)TRACE_MAX_LAUNCHES * 128) != cudaSuccess) return e->fail("trace buffer: out of memory");
+    std::vector<unsigned long long> init((size_t)TRACE_MAX_LAUNCHES * 16, 0ull);
+    for (int i = 0; i < TRACE_MAX_LAUNCHES; i++) init[(size_t)16 * i] = ~0ull;
     cudaMemcpyAsync(e->d_trace, init.data(), init.size() * 8, cudaMemcpyHostToDevice, e->stream);
     cudaStreamSynchronize(e->stream);
     // the same step as the decode graph, captured once more with the time stamp slots handed out
@@ -1402,7 +1436,7 @@ int b2_debug_trace_step(b2_engine* e, unsigned long long* out, int cap_launches,
     if (ce != cudaSuccess) return e->fail("trace step: %s", cudaGetErrorString(ce));
     e->length += 1;
     const int m = std::min(std::min(n, cap_launches), TRACE_MAX_LAUNCHES);
-    cudaMemcpy(out, e->d_trace, (size_t)m * 64, cudaMemcpyDeviceToHost);
+    cudaMemcpy(out, e->d_trace, (size_t)m * 128, cudaMemcpyDeviceToHost);
     *n_launches = m;
     return 0;
 }

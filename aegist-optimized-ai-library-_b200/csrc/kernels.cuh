@@ -58,8 +58,10 @@ __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
 // Time stamps of a launch for the step timeline (debugging aid; trace is null in normal runs). Per launch
-// 8 words: [0] first block in, [1] block 0 past the dependency wait, [2] block 0 past its prologue,
-// [3] block 0 past its main loop, [4] last block out, [5] kernel code, [6] a shape hint.
+// 16 words: [0] first block in and [4] last block out (ns of the global timer, which is slow to read, so it is
+// read only there), [5] kernel code, [6] a shape hint, [8] block 0's SM cycle counter when it came in,
+// [9] .. [15] the same counter at points 1 .. 7 of block 0 (1 past the dependency wait, 2 past the prologue,
+// 3 past the main loop; the others as the kernel defines them).
 __device__ __forceinline__ unsigned long long gtime() {
     unsigned long long t;
     asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -69,11 +71,11 @@ __device__ __forceinline__ bool trace_block0() { return (blockIdx.x | blockIdx.y
 __device__ __forceinline__ void trace_in(unsigned long long* p, int code, int hint) {
     if (p && threadIdx.x == 0) {
         atomicMin(p, gtime());
-        if (trace_block0()) { p[5] = (unsigned long long)code; p[6] = (unsigned long long)hint; }
+        if (trace_block0()) { p[5] = (unsigned long long)code; p[6] = (unsigned long long)hint; p[8] = (unsigned long long)clock64(); }
     }
 }
 __device__ __forceinline__ void trace_pt(unsigned long long* p, int i) {
-    if (p && threadIdx.x == 0 && trace_block0()) p[i] = gtime();
+    if (p && threadIdx.x == 0 && trace_block0()) p[8 + i] = (unsigned long long)clock64();
 }
 __device__ __forceinline__ void trace_out(unsigned long long* p) {
     if (p && threadIdx.x == 0) atomicMax(p + 4, gtime());
@@ -579,6 +581,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv_norm(const GemvArgs a)
 #include "mmagemm.cuh"
 #include "mmaexperts.cuh"
 #include "tcgemv.cuh"
+#include "moe1.cuh"
 namespace b2 {
 
 // ------------------------------------------------------------------------------------------

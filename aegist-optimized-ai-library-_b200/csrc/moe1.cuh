@@ -1,0 +1,611 @@
+// The routed experts of one layer for a handful of tokens (fewer than 8), as two kernels whose work
+// is spread evenly over the GPU instead of one block per pick:
+//
+//   k_moe_gu1    every block: router softmax + top-8 from the logits (redundantly, which replaces a
+//                last-block finisher and its fence + atomic + reload), norm2(x) as int8 digit planes, then
+//                32 of the token's topk * I (gate, up) row pairs, fetched in one go with 16-byte
+//                asynchronous copies and multiplied on the tensor cores; act = silu(gate) * up leaves the
+//                block as digit planes of its own (one scale per 32 values) for the down projection
+//   k_moe_down1  one block per 16 output rows: two warps per pick multiply those rows of the pick's down
+//                matrix with its act planes, two more the shared expert's rows, and the block adds the 9
+//                parts in rank order into the residual stream (no cross-block combine)
+//
+// Arithmetic: the 4-bit codes (0..15) and the int8 weights go to mma.sync.m16n8k32.s8 unchanged; the
+// activations are split into four int8 digit planes, x = scale * (d0 + d1/128 + d2/128^2 + d3/128^3)
+// with scale = max|x| / 127, which holds every fp32 activation to 2^-22 of the largest one; the planes
+// are four of the eight B columns. The integer sums are exact; per 64-value group they are scaled by
+// the group's fp16 scale, and the group minimum times the group's activation sum is added
+// (w = code * s + m, aegist/hybrid.py ExpertBank).
+#pragma once
+
+namespace b2 {
+
+constexpr int M1_PLANES = 4;
+constexpr int M1_GU_WARPS = 32;           // 4 blocks of 8 pairs x 8 eighths of K
+constexpr int M1_GU_THREADS = M1_GU_WARPS * 32;
+constexpr int M1_GU_PAIRS = 32;           // pairs per block of k_moe_gu1: one 32-value group of act
+constexpr int M1_DOWN_ROWS = 16;
+constexpr int M1_DOWN_WARPS = 18;         // (8 picks + shared) x 2 halves of K
+
+__device__ __forceinline__ void imma16832(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// an integer of magnitude below 2^22 as fp32, without the conversion unit
+__device__ __forceinline__ float small_int_to_float(int t) { return __int_as_float(t + 0x4B400000) - 12582912.0f; }
+
+// four digits of q = v * inv (|q| <= 127): q = d0 + d1/128 + d2/128^2 + d3/128^3 up to 2^-22; every step is exact
+__device__ __forceinline__ void to_digits(float v, float inv, int (&d)[M1_PLANES]) {
+    float q = v * inv;
+#pragma unroll
+    for (int p = 0; p < M1_PLANES; p++) {
+        const float r = rintf(q);
+        d[p] = (int)r;
+        q = (q - r) * 128.0f;
+    }
+}
+// eight consecutive values -> per plane the 8 digits as two words; `evenodd`: even positions first (the
+// order in which the low / high nibbles of a word of eight codes come out), else natural order
+__device__ __forceinline__ void digits8(const float (&v)[8], float inv, bool evenodd, uint2 (&w)[M1_PLANES]) {
+    int d[8][M1_PLANES];
+#pragma unroll
+    for (int i = 0; i < 8; i++) to_digits(v[i], inv, d[i]);
+#pragma unroll
+    for (int p = 0; p < M1_PLANES; p++) {
+        const uint32_t b0 = d[0][p] & 255, b1 = d[1][p] & 255, b2 = d[2][p] & 255, b3 = d[3][p] & 255;
+        const uint32_t b4 = d[4][p] & 255, b5 = d[5][p] & 255, b6 = d[6][p] & 255, b7 = d[7][p] & 255;
+        w[p].x = evenodd ? (b0 | (b2 << 8) | (b4 << 16) | (b6 << 24)) : (b0 | (b1 << 8) | (b2 << 16) | (b3 << 24));
+        w[p].y = evenodd ? (b1 | (b3 << 8) | (b5 << 16) | (b7 << 24)) : (b4 | (b5 << 8) | (b6 << 16) | (b7 << 24));
+    }
+}
+// n fp16 values global -> shared: asynchronous 16-byte pieces when n is a multiple of 8, plain loads otherwise;
+// piece `c` of the (n * 2 + 15) / 16 pieces of the row
+__device__ __forceinline__ void copy_f16_piece(uint16_t* dst, const uint8_t* src, int n, int c) {
+    if ((n & 7) == 0) {
+        cp_async16(reinterpret_cast<unsigned char*>(dst) + c * 16, src + (size_t)c * 16);
+    } else {
+        const uint16_t* s = reinterpret_cast<const uint16_t*>(src);
+        for (int i = 8 * c; i < min(n, 8 * c + 8); i++) dst[i] = s[i];
+    }
+}
+// Scale rows in shared memory: per row [scales | mins] of ngroup fp16 each, in 16-byte pieces; piece q of row
+// `slot` sits at position q ^ (slot & mask), so that the same piece of 8 neighbouring rows covers all banks.
+// mask = pieces per row - 1 (at most 7) when the pieces per row are a power of two, else 0.
+__device__ __forceinline__ int sc_mask(int ngroup) {
+    const int npq = 2 * ((ngroup * 2 + 15) >> 4);
+    return ((ngroup & 7) == 0 && (npq & (npq - 1)) == 0) ? min(npq, 8) - 1 : 0;
+}
+// address (in fp16 units, relative to the row) of value g of part `which` (0 scales, 1 mins)
+__device__ __forceinline__ int sc_pos(int ngroup, int mask, int slot, int which, int g) {
+    if (mask == 0) return which * ngroup + g;
+    const int q = which * (ngroup >> 3) + (g >> 3);
+    return ((q ^ (slot & mask)) << 3) + (g & 7);
+}
+// weight of the planes a lane holds after an mma (columns 2 tid and 2 tid + 1 = planes 0,1 | 2,3 | none)
+__device__ __forceinline__ void plane_weights(int tid, float scale, float& w0, float& w1) {
+    w0 = tid == 0 ? scale : (tid == 1 ? scale * (1.0f / 16384.0f) : 0.f);
+    w1 = w0 * (1.0f / 128.0f);
+}
+
+// Softmax over E <= 256 router logits and the topk <= 8 largest in descending order, ties to the lower
+// index, weights renormalised over the picks (aegist/hybrid.py:641-645); one warp, the same values as
+// router_topk_warp. A probability is positive, so its bits order like an unsigned integer: a round is two
+// warp-wide integer reductions (largest key, then lowest expert holding it) instead of shuffle ladders.
+// Pick r ends up in lane r.
+__device__ __forceinline__ void router_topk_lanes(const float* __restrict__ logits, int E, int topk, int lane, int& my_e, float& my_w) {
+    float p[8];
+    float mx = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int e = lane + 32 * i;
+        p[i] = e < E ? __ldcg(logits + e) : -INFINITY;
+        mx = fmaxf(mx, p[i]);
+    }
+    mx = warp_max(mx);
+    float sum = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int e = lane + 32 * i;
+        p[i] = e < E ? expf(p[i] - mx) : 0.f;
+        sum += p[i];
+    }
+    sum = warp_sum(sum);
+    uint32_t key[8];                     // bits of the probability + 1; 0 = not available
+#pragma unroll
+    for (int i = 0; i < 8; i++) key[i] = (lane + 32 * i) < E ? __float_as_uint(p[i] / sum) + 1u : 0u;
+    float tsum = 0.f, myv = 0.f;
+    my_e = -1;
+#pragma unroll 1
+    for (int r = 0; r < topk; r++) {
+        uint32_t bk = 0u;
+        int bi = 0;
+#pragma unroll
+        for (int i = 0; i < 8; i++)       // ascending expert id within the lane: '>' keeps the lower id
+            if (key[i] > bk) { bk = key[i]; bi = i; }
+        const uint32_t m = __reduce_max_sync(0xffffffffu, bk);
+        const uint32_t cand = (bk == m && m != 0u) ? (uint32_t)(lane + 32 * bi) : 0x7fffffffu;
+        const int e = (int)__reduce_min_sync(0xffffffffu, cand);
+        if ((e & 31) == lane) {
+#pragma unroll
+            for (int i = 0; i < 8; i++) if (i == (e >> 5)) key[i] = 0u;
+        }
+        const float v = m ? __uint_as_float(m - 1u) : 0.f;
+        if (lane == r) { myv = v; my_e = e; }
+        tsum += v;
+    }
+    my_w = myv / tsum;
+}
+
+struct Gu1Args {
+    unsigned long long* trace;
+    const float* logits;          // [B][E] router logits (bias included)
+    const float* x;               // [B][D] residual stream
+    const uint16_t* norm_w;       // [D]
+    float eps;
+    const uint8_t* const* eptr;   // [E] resident experts
+    size_t off_gu_s, off_gu_m;
+    int D, I, E, topk;
+    int* top_idx;                 // [B][topk] out (block 0 of every token)
+    float* top_w;                 // [B][topk] out
+    const uint8_t** top_ptr;      // [B][topk] out: the picks' expert blobs, for k_moe_down1
+    int8_t* actq;                 // [B * topk][PLANES][I] out: digit planes of act, even/odd order within 8
+    float* asc;                   // [B * topk][I / 32] out: scale of each 32-value group of act
+    float* asum;                  // [B * topk][I / 32] out: sum of each 32-value group of act
+    int* err;
+};
+
+// dynamic shared memory: rows | scales | digit planes of x | group sums of x
+__host__ __device__ __forceinline__ size_t m1_gu_smem(int D) {
+    return (size_t)2 * M1_GU_PAIRS * ((D >> 1) + 32) + (size_t)2 * M1_GU_PAIRS * 2 * (D >> 6) * 2 + (size_t)M1_PLANES * (D + 64) + (size_t)(D >> 6) * 4;
+}
+
+// grid (topk * I / 32, B); 32 warps. Prologue: warps 0-7 rank the experts (one thread per expert counts
+// the experts ahead of it, which is short and parallel where a select-the-largest loop is a long
+// chain), warps 8-15 normalise x and split it into digit planes, 8 consecutive values per thread.
+__global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
+    extern __shared__ __align__(128) unsigned char m1_smem[];
+    const int D = a.D, half = D >> 1;                   // bytes of codes per row
+    const int pitch = half + 32;                        // rows r .. r+3 fall into different quarters of the banks
+    const int ngroup = D >> 6;
+    unsigned char* s_rows = m1_smem;                                            // [2 * M1_GU_PAIRS][pitch]
+    uint16_t* s_sc = reinterpret_cast<uint16_t*>(s_rows + (size_t)2 * M1_GU_PAIRS * pitch);   // [2 * PAIRS][2][ngroup]: scales | mins
+    const int XS = D + 64;                              // plane stride: planes p, p+1 in different halves of the banks
+    int8_t* s_xq = reinterpret_cast<int8_t*>(s_sc + (size_t)2 * M1_GU_PAIRS * 2 * ngroup);    // [PLANES][XS], even/odd order
+    float* s_xsum = reinterpret_cast<float*>(s_xq + (size_t)M1_PLANES * XS);                  // [ngroup]
+    __shared__ __align__(16) uint32_t s_key[256];
+    __shared__ int s_top[8];
+    __shared__ float s_topv[8];
+    __shared__ float s_red[2][8];
+    __shared__ float s_part[8][4][16][2];               // [K eighth][row block][row][gate | up]
+    __shared__ float s_scale;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int gid = lane >> 2, tid = lane & 3;
+    const int b = blockIdx.y;
+    grid_dep_launch();
+    trace_in(a.trace, 5, gridDim.x);
+    grid_dep_wait();
+    trace_pt(a.trace, 1);
+
+    if (warp < 8) {
+        // aegist/hybrid.py:641-645: softmax, the topk largest in descending order (ties to the lower index)
+        const int e = threadIdx.x;
+        const float v = e < a.E ? __ldcg(a.logits + (size_t)b * a.E + e) : -INFINITY;
+        float mx = warp_max(v);
+        if (lane == 0) s_red[0][warp] = mx;
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        mx = s_red[0][0];
+#pragma unroll
+        for (int w = 1; w < 8; w++) mx = fmaxf(mx, s_red[0][w]);
+        const float p = e < a.E ? expf(v - mx) : 0.f;
+        float sum = warp_sum(p);
+        if (lane == 0) s_red[1][warp] = sum;
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) sum += s_red[1][w];
+        const float prob = p / sum;
+        const uint32_t key = e < a.E ? __float_as_uint(prob) + 1u : 0u;      // positive floats order like their bits
+        s_key[e] = key;
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        // experts ahead of this one: a larger probability, or an equal one and a lower index. Below this thread's
+        // own group of four "not smaller" is counted (key - 1), from it on "larger"; its own group is corrected after.
+        int ahead = 0;
+        const int eg = e & ~3;
+#pragma unroll 8
+        for (int j = 0; j < 256; j += 4) {
+            const uint4 k4 = *reinterpret_cast<const uint4*>(s_key + j);
+            const uint32_t kk = j < eg ? key - 1u : key;
+            ahead += (k4.x > kk) + (k4.y > kk) + (k4.z > kk) + (k4.w > kk);
+        }
+        for (int j = eg; j < e; j++) ahead += (s_key[j] == key);
+        if (ahead < a.topk && key != 0u) { s_top[ahead] = e; s_topv[ahead] = prob; }
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        if (blockIdx.x == 0 && threadIdx.x < a.topk) {
+            float tsum = 0.f;
+            for (int r = 0; r < a.topk; r++) tsum += s_topv[r];
+            const int ex = s_top[threadIdx.x];
+            a.top_idx[(size_t)b * a.topk + threadIdx.x] = ex;
+            a.top_w[(size_t)b * a.topk + threadIdx.x] = s_topv[threadIdx.x] / tsum;
+            a.top_ptr[(size_t)b * a.topk + threadIdx.x] = (ex >= 0 && ex < a.E) ? a.eptr[ex] : nullptr;
+        }
+        trace_pt(a.trace, 2);
+    } else if (warp < 16) {
+        // norm2(x) -> digit planes and group sums; D / 8 chunks over 256 threads
+        const int xt = threadIdx.x - 256;
+        constexpr int XC = 2;                           // turns: D <= 256 * 8 * 2
+        float xv[XC][8], nw[XC][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int j = 0; j < XC; j++) {
+            const int k = (xt + j * 256) * 8;
+            if (k < D) {
+                const float4 v0 = *reinterpret_cast<const float4*>(a.x + (size_t)b * D + k);
+                const float4 v1 = *reinterpret_cast<const float4*>(a.x + (size_t)b * D + k + 4);
+                xv[j][0] = v0.x; xv[j][1] = v0.y; xv[j][2] = v0.z; xv[j][3] = v0.w;
+                xv[j][4] = v1.x; xv[j][5] = v1.y; xv[j][6] = v1.z; xv[j][7] = v1.w;
+                uint4 wv = make_uint4(0u, 0u, 0u, 0u);
+                if (a.norm_w) wv = *reinterpret_cast<const uint4*>(a.norm_w + k);
+                nw[j][0] = 1.0f + bflo(wv.x); nw[j][1] = 1.0f + bfhi(wv.x); nw[j][2] = 1.0f + bflo(wv.y); nw[j][3] = 1.0f + bfhi(wv.y);
+                nw[j][4] = 1.0f + bflo(wv.z); nw[j][5] = 1.0f + bfhi(wv.z); nw[j][6] = 1.0f + bflo(wv.w); nw[j][7] = 1.0f + bfhi(wv.w);
+            } else {
+#pragma unroll
+                for (int i = 0; i < 8; i++) { xv[j][i] = 0.f; nw[j][i] = 1.0f; }
+            }
+#pragma unroll
+            for (int i = 0; i < 8; i++) ss = fmaf(xv[j][i], xv[j][i], ss);
+        }
+        float r = 1.0f;
+        float* red = &s_part[0][0][0][0];               // scratch until the main part starts
+        if (a.norm_w) {
+            ss = warp_sum(ss);
+            if (lane == 0) red[warp] = ss;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            float t = 0.f;
+#pragma unroll
+            for (int w = 8; w < 16; w++) t += red[w];
+            r = 1.0f / sqrtf(t / (float)D + a.eps);
+        }
+        float mx = 0.f;
+#pragma unroll
+        for (int j = 0; j < XC; j++)
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                if (a.norm_w) xv[j][i] = xv[j][i] * r * nw[j][i];
+                mx = fmaxf(mx, fabsf(xv[j][i]));
+            }
+        mx = warp_max(mx);
+        if (lane == 0) red[16 + warp] = mx;
+        asm volatile("bar.sync 1, 256;" ::: "memory");
+        mx = 0.f;
+#pragma unroll
+        for (int w = 8; w < 16; w++) mx = fmaxf(mx, red[16 + w]);
+        const float inv = mx > 0.f ? 127.0f / mx : 0.f;
+        if (xt == 0) s_scale = mx / 127.0f;
+#pragma unroll
+        for (int j = 0; j < XC; j++) {
+            const int k = (xt + j * 256) * 8;
+            // the sum of a 64-value group: 8 neighbouring lanes, values in index order within a lane
+            float s8 = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) s8 += xv[j][i];
+            s8 += __shfl_xor_sync(0xffffffffu, s8, 1);
+            s8 += __shfl_xor_sync(0xffffffffu, s8, 2);
+            s8 += __shfl_xor_sync(0xffffffffu, s8, 4);
+            if (k < D) {
+                uint2 w[M1_PLANES];
+                digits8(xv[j], inv, true, w);
+#pragma unroll
+                for (int p = 0; p < M1_PLANES; p++) *reinterpret_cast<uint2*>(s_xq + (size_t)p * XS + k) = w[p];
+                if ((lane & 7) == 0) s_xsum[k >> 6] = s8;
+            }
+        }
+    }
+    __syncthreads();
+    trace_pt(a.trace, 3);
+
+    // this block's 32 pairs: rows i0 .. i0 + 31 of pick rnk
+    const int p0 = blockIdx.x * M1_GU_PAIRS;
+    const int rnk = p0 / a.I, i0 = p0 - rnk * a.I;
+    const int e = s_top[rnk];
+    const uint8_t* base = (e >= 0 && e < a.E) ? a.eptr[e] : nullptr;
+    if (base == nullptr) {                               // a bad pick: say so, nothing to compute
+        if (threadIdx.x == 0) atomicExch(a.err, 2);
+        trace_out(a.trace);
+        return;
+    }
+    // slot of pair s: block s / 8, gate in row s % 8 of the block's 16 rows, up in row 8 + s % 8; a warp
+    // fetches two whole rows, a lane 16-byte pieces of them
+    const int chunks = half >> 4;
+    const int sch = (ngroup * 2 + 15) >> 4;              // 16-byte pieces of a row's scales (ngroup fp16)
+    const int scm = sc_mask(ngroup);
+#pragma unroll
+    for (int it = 0; it < 2 * M1_GU_PAIRS / M1_GU_WARPS; it++) {
+        const int rowi = warp + it * M1_GU_WARPS;
+        const int s = rowi >> 1, up = rowi & 1;
+        const int slot = (s >> 3) * 16 + up * 8 + (s & 7);
+        const size_t grow = (size_t)(up * a.I + i0 + s);
+        const uint8_t* src = base + grow * half;
+        unsigned char* dst = s_rows + (size_t)slot * pitch;
+        for (int ch = lane; ch < chunks; ch += 32) cp_async16(dst + ch * 16, src + (size_t)ch * 16);
+        if (lane < 2 * sch) {
+            const int which = lane / sch, ch = lane - which * sch;
+            const uint8_t* ssrc = base + (which ? a.off_gu_m : a.off_gu_s) + grow * ngroup * 2;
+            uint16_t* srow = s_sc + (size_t)slot * 2 * ngroup;
+            if (scm) cp_async16(reinterpret_cast<unsigned char*>(srow + (((which * sch + ch) ^ (slot & scm)) << 3)), ssrc + (size_t)ch * 16);
+            else copy_f16_piece(srow + which * ngroup, ssrc, ngroup, ch);
+        }
+    }
+    cp_async_commit();
+    trace_pt(a.trace, 4);
+    cp_async_wait<0>();
+    __syncthreads();
+    trace_pt(a.trace, 5);
+
+    // warp -> (block of 8 pairs, eighth of K); lane (gid, tid) -> rows gid (gate) and gid + 8 (up) of the block,
+    // 16 codes of every 64-code group. Two groups are in flight together: loads, then the mma, then the scaling.
+    const int rb = warp & 3, ke = warp >> 2;
+    const int ge = ngroup >> 3;
+    constexpr int GQ = 2;
+    float accg[2] = {0.f, 0.f}, accu[2] = {0.f, 0.f};   // planes 2 tid and 2 tid + 1
+    float mng = 0.f, mnu = 0.f;
+    {
+        const unsigned char* pg = s_rows + (size_t)(rb * 16 + gid) * pitch + tid * 8;
+        const unsigned char* pu = pg + (size_t)8 * pitch;
+        const int slg = rb * 16 + gid, slu = slg + 8;
+        const uint16_t* sg = s_sc + (size_t)slg * 2 * ngroup;
+        const uint16_t* su = s_sc + (size_t)slu * 2 * ngroup;
+        const int8_t* px = s_xq + (size_t)(gid & 3) * XS + tid * 16;
+        const bool colact = gid < M1_PLANES;
+        for (int g0 = ke * ge; g0 < (ke + 1) * ge; g0 += GQ) {
+            const int gend = (ke + 1) * ge;
+            uint2 wg[GQ], wu[GQ];
+            uint4 xb[GQ];
+            float sgv[GQ], suv[GQ], mgv[GQ], muv[GQ], xs[GQ];
+#pragma unroll
+            for (int q = 0; q < GQ; q++) {
+                const int g = min(g0 + q, gend - 1);
+                wg[q] = *reinterpret_cast<const uint2*>(pg + g * 32);
+                wu[q] = *reinterpret_cast<const uint2*>(pu + g * 32);
+                xb[q] = make_uint4(0u, 0u, 0u, 0u);
+                if (colact) xb[q] = *reinterpret_cast<const uint4*>(px + g * 64);
+                const bool live = g0 + q < gend;
+                sgv[q] = live ? h2f(sg[sc_pos(ngroup, scm, slg, 0, g)]) : 0.f; suv[q] = live ? h2f(su[sc_pos(ngroup, scm, slu, 0, g)]) : 0.f;
+                mgv[q] = live ? h2f(sg[sc_pos(ngroup, scm, slg, 1, g)]) : 0.f; muv[q] = live ? h2f(su[sc_pos(ngroup, scm, slu, 1, g)]) : 0.f;
+                xs[q] = s_xsum[g];
+            }
+            int t[GQ][4];
+#pragma unroll
+            for (int q = 0; q < GQ; q++) {
+                t[q][0] = t[q][1] = t[q][2] = t[q][3] = 0;
+                imma16832(t[q], wg[q].x & 0x0F0F0F0Fu, wu[q].x & 0x0F0F0F0Fu, (wg[q].x >> 4) & 0x0F0F0F0Fu, (wu[q].x >> 4) & 0x0F0F0F0Fu, xb[q].x, xb[q].y);
+            }
+#pragma unroll
+            for (int q = 0; q < GQ; q++)
+                imma16832(t[q], wg[q].y & 0x0F0F0F0Fu, wu[q].y & 0x0F0F0F0Fu, (wg[q].y >> 4) & 0x0F0F0F0Fu, (wu[q].y >> 4) & 0x0F0F0F0Fu, xb[q].z, xb[q].w);
+#pragma unroll
+            for (int q = 0; q < GQ; q++) {
+                accg[0] = fmaf(sgv[q], small_int_to_float(t[q][0]), accg[0]); accg[1] = fmaf(sgv[q], small_int_to_float(t[q][1]), accg[1]);
+                accu[0] = fmaf(suv[q], small_int_to_float(t[q][2]), accu[0]); accu[1] = fmaf(suv[q], small_int_to_float(t[q][3]), accu[1]);
+                mng = fmaf(mgv[q], xs[q], mng);
+                mnu = fmaf(muv[q], xs[q], mnu);
+            }
+        }
+    }
+    {
+        float w0, w1;
+        plane_weights(tid, s_scale, w0, w1);
+        float vg = accg[0] * w0 + accg[1] * w1, vu = accu[0] * w0 + accu[1] * w1;
+        vg += __shfl_xor_sync(0xffffffffu, vg, 1); vu += __shfl_xor_sync(0xffffffffu, vu, 1);
+        if (tid == 0) { s_part[ke][rb][gid][0] = vg + mng; s_part[ke][rb][gid][1] = vu + mnu; }
+    }
+    __syncthreads();
+    trace_pt(a.trace, 6);
+    if (warp == 0) {
+        // act of pair `lane`, then this 32-value group of act as digit planes with its own scale
+        const int s = lane;
+        float g = 0.f, u = 0.f;
+#pragma unroll
+        for (int q = 0; q < 8; q++) { g += s_part[q][s >> 3][s & 7][0]; u += s_part[q][s >> 3][s & 7][1]; }
+        const float v = siluf_(g) * u;
+        const float mx = warp_max(fabsf(v));
+        const float inv = mx > 0.f ? 127.0f / mx : 0.f;
+        int d[M1_PLANES];
+        to_digits(v, inv, d);
+        const size_t pick = (size_t)b * a.topk + rnk;
+        const int pos = i0 + ((s & ~7) | ((s & 1) << 2) | ((s & 7) >> 1));      // even ones first within 8
+#pragma unroll
+        for (int p = 0; p < M1_PLANES; p++) a.actq[(pick * M1_PLANES + p) * a.I + pos] = (int8_t)d[p];
+        const float sm = warp_sum(v);
+        if (lane == 0) {
+            a.asc[pick * (a.I >> 5) + (i0 >> 5)] = mx / 127.0f;
+            a.asum[pick * (a.I >> 5) + (i0 >> 5)] = sm;
+        }
+    }
+    trace_pt(a.trace, 7);
+    trace_out(a.trace);
+}
+
+struct Down1Args {
+    unsigned long long* trace;
+    const uint8_t* const* top_ptr;   // [B][topk] the picks' expert blobs (null: not resident)
+    const float* top_w;              // [B][topk]
+    const int8_t* actq;              // [B * topk][PLANES][I] digit planes of act (k_moe_gu1)
+    const float* asc;                // [B * topk][I / 32]
+    const float* asum;               // [B * topk][I / 32]
+    const float* sh_act;             // [B][SH]
+    const float* sg;                 // [B] sigmoid(shared gate)
+    const int8_t* shd_w;             // [D][SH] shared down, or null
+    const uint16_t* shd_s;           // [D]
+    size_t off_dn_q, off_dn_s, off_dn_m;
+    int D, I, SH, topk;
+    float* xout;                     // [B][D] residual stream, += result
+};
+
+// per pick warp (a half of K): 16 rows x (I / 4 + 16) codes | scales [16][2][I / 64] | planes [4][I / 2] | 2 x [I / 64] group scales
+// and sums; per shared warp: 16 rows x (SH / 2 + 64) | planes [4][SH / 2]
+__host__ __device__ __forceinline__ size_t m1_down_pick_bytes(int I) {
+    return (size_t)M1_DOWN_ROWS * ((I >> 2) + 16) + (size_t)M1_DOWN_ROWS * 2 * (I >> 6) * 2 + (size_t)M1_PLANES * (I >> 1) + (size_t)2 * (I >> 5) * 4;
+}
+__host__ __device__ __forceinline__ size_t m1_down_shared_bytes(int SH) { return (size_t)M1_DOWN_ROWS * ((SH >> 1) + 64) + (size_t)M1_PLANES * (SH >> 1); }
+__host__ __device__ __forceinline__ size_t m1_down_smem(int I, int SH, int topk) {
+    return (size_t)2 * topk * m1_down_pick_bytes(I) + 2 * m1_down_shared_bytes(SH);
+}
+
+// grid (D / 16, B); 2 * (topk + 1) warps: warp 2 r + h = half h of K of pick r, the last two the shared expert
+__global__ void __launch_bounds__(M1_DOWN_WARPS * 32) k_moe_down1(const Down1Args a) {
+    extern __shared__ __align__(128) unsigned char m1d_smem[];
+    __shared__ float s_y[M1_DOWN_WARPS][M1_DOWN_ROWS];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int gid = lane >> 2, tid = lane & 3;
+    const int b = blockIdx.y;
+    const int row0 = blockIdx.x * M1_DOWN_ROWS;
+    const int I = a.I, SH = a.SH;
+    const int r = warp >> 1, kh = warp & 1;
+    grid_dep_launch();
+    trace_in(a.trace, 6, gridDim.x);
+    float y0 = 0.f, y1 = 0.f;             // rows gid and gid + 8 (valid in lanes with tid == 0)
+    if (r < a.topk) {
+        const int halfk = I >> 2;                        // bytes of codes of this warp's half of a row
+        const int pitch = halfk + 16;                    // 8 rows x 16 bytes cover all banks
+        const int ngroup = I >> 6, gh = ngroup >> 1;     // groups per half
+        unsigned char* s_rows = m1d_smem + (size_t)warp * m1_down_pick_bytes(I);
+        uint16_t* s_sc = reinterpret_cast<uint16_t*>(s_rows + (size_t)M1_DOWN_ROWS * pitch);     // [16][2][ngroup]
+        int8_t* s_xq = reinterpret_cast<int8_t*>(s_sc + (size_t)M1_DOWN_ROWS * 2 * ngroup);      // [PLANES][I / 2]
+        float* s_as = reinterpret_cast<float*>(s_xq + (size_t)M1_PLANES * (I >> 1));             // [2 gh] scales | [2 gh] sums
+        grid_dep_wait();
+        trace_pt(a.trace, 1);
+        const size_t pick = (size_t)b * a.topk + r;
+        const uint8_t* base = a.top_ptr[pick];
+        if (base != nullptr) {
+            const int chunks = halfk >> 4;
+            for (int c = lane; c < M1_DOWN_ROWS * chunks; c += 32) {
+                const int rr = c / chunks, ch = c - rr * chunks;
+                if (row0 + rr < a.D)
+                    cp_async16(s_rows + (size_t)rr * pitch + ch * 16, base + a.off_dn_q + (size_t)(row0 + rr) * (I >> 1) + (size_t)kh * halfk + (size_t)ch * 16);
+            }
+            const int sch = (ngroup * 2 + 15) >> 4;
+            for (int c = lane; c < M1_DOWN_ROWS * 2 * sch; c += 32) {
+                const int q = c / sch, ch = c - q * sch;
+                const int rr = q >> 1, which = q & 1;
+                if (row0 + rr < a.D)
+                    copy_f16_piece(s_sc + ((size_t)rr * 2 + which) * ngroup, base + (which ? a.off_dn_m : a.off_dn_s) + ((size_t)(row0 + rr) * ngroup) * 2, ngroup, ch);
+            }
+            const int pch = (I >> 1) >> 4;               // 16-byte pieces of a plane's half
+            for (int c = lane; c < M1_PLANES * pch; c += 32) {
+                const int p = c / pch, ch = c - p * pch;
+                cp_async16(s_xq + (size_t)p * (I >> 1) + ch * 16, a.actq + (pick * M1_PLANES + p) * I + (size_t)kh * (I >> 1) + (size_t)ch * 16);
+            }
+            cp_async_commit();
+            for (int c = lane; c < 2 * gh; c += 32) {
+                s_as[c] = a.asc[pick * (I >> 5) + kh * 2 * gh + c];
+                s_as[2 * gh + c] = a.asum[pick * (I >> 5) + kh * 2 * gh + c];
+            }
+            cp_async_wait<0>();
+            __syncwarp();
+            const unsigned char* p0 = s_rows + (size_t)gid * pitch + tid * 4;
+            const unsigned char* p1 = p0 + (size_t)8 * pitch;
+            const uint16_t* s0 = s_sc + (size_t)gid * 2 * ngroup + kh * gh;
+            const uint16_t* s1 = s0 + (size_t)8 * 2 * ngroup;
+            const int8_t* px = s_xq + (size_t)(gid & 3) * (I >> 1) + tid * 8;
+            const bool colact = gid < M1_PLANES;
+            float pw0, pw1;
+            plane_weights(tid, 1.0f, pw0, pw1);
+            float m0 = 0.f, m1 = 0.f;
+            for (int g = 0; g < gh; g++) {
+                const uint32_t a00 = *reinterpret_cast<const uint32_t*>(p0 + g * 32), a01 = *reinterpret_cast<const uint32_t*>(p0 + g * 32 + 16);
+                const uint32_t a10 = *reinterpret_cast<const uint32_t*>(p1 + g * 32), a11 = *reinterpret_cast<const uint32_t*>(p1 + g * 32 + 16);
+                uint2 xb0 = make_uint2(0u, 0u), xb1 = xb0;
+                if (colact) {
+                    xb0 = *reinterpret_cast<const uint2*>(px + g * 64);
+                    xb1 = *reinterpret_cast<const uint2*>(px + g * 64 + 32);
+                }
+                int t0[4] = {0, 0, 0, 0}, t1[4] = {0, 0, 0, 0};
+                imma16832(t0, a00 & 0x0F0F0F0Fu, a10 & 0x0F0F0F0Fu, (a00 >> 4) & 0x0F0F0F0Fu, (a10 >> 4) & 0x0F0F0F0Fu, xb0.x, xb0.y);
+                imma16832(t1, a01 & 0x0F0F0F0Fu, a11 & 0x0F0F0F0Fu, (a01 >> 4) & 0x0F0F0F0Fu, (a11 >> 4) & 0x0F0F0F0Fu, xb1.x, xb1.y);
+                const float c0 = s_as[2 * g], c1 = s_as[2 * g + 1];           // scales of the two 32-value groups
+                const float xs = s_as[2 * gh + 2 * g] + s_as[2 * gh + 2 * g + 1];
+                const float v0 = c0 * (small_int_to_float(t0[0]) * pw0 + small_int_to_float(t0[1]) * pw1) +
+                                 c1 * (small_int_to_float(t1[0]) * pw0 + small_int_to_float(t1[1]) * pw1);
+                const float v1 = c0 * (small_int_to_float(t0[2]) * pw0 + small_int_to_float(t0[3]) * pw1) +
+                                 c1 * (small_int_to_float(t1[2]) * pw0 + small_int_to_float(t1[3]) * pw1);
+                y0 = fmaf(h2f(s0[g]), v0, y0);
+                y1 = fmaf(h2f(s1[g]), v1, y1);
+                m0 = fmaf(h2f(s0[ngroup + g]), xs, m0);
+                m1 = fmaf(h2f(s1[ngroup + g]), xs, m1);
+            }
+            y0 += __shfl_xor_sync(0xffffffffu, y0, 1); y1 += __shfl_xor_sync(0xffffffffu, y1, 1);
+            y0 += m0; y1 += m1;
+        }
+    } else {
+        // shared expert: int8 rows of SH values against sh_act, this warp's half of SH
+        const int hk = SH >> 1, pitch = hk + 64;
+        unsigned char* s_rows = m1d_smem + (size_t)2 * a.topk * m1_down_pick_bytes(I) + (size_t)kh * m1_down_shared_bytes(SH);
+        int8_t* s_xq = reinterpret_cast<int8_t*>(s_rows + (size_t)M1_DOWN_ROWS * pitch);
+        if (a.shd_w) {
+            const int chunks = hk >> 4;
+            for (int c = lane; c < M1_DOWN_ROWS * chunks; c += 32) {          // weights do not depend on the previous kernel
+                const int rr = c / chunks, ch = c - rr * chunks;
+                if (row0 + rr < a.D)
+                    cp_async16(s_rows + (size_t)rr * pitch + ch * 16, (const unsigned char*)a.shd_w + (size_t)(row0 + rr) * SH + (size_t)kh * hk + (size_t)ch * 16);
+            }
+            cp_async_commit();
+        }
+        grid_dep_wait();
+        if (a.shd_w) {
+            // this half of sh_act as digit planes with its own scale: 8 consecutive values per lane and turn
+            const float* src = a.sh_act + (size_t)b * SH + kh * hk;
+            float mx = 0.f;
+            for (int k = lane * 8; k < hk; k += 256)
+#pragma unroll
+                for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(src[k + i]));
+            mx = warp_max(mx);
+            const float inv = mx > 0.f ? 127.0f / mx : 0.f;
+            for (int k = lane * 8; k < hk; k += 256) {
+                float v[8];
+#pragma unroll
+                for (int i = 0; i < 8; i++) v[i] = src[k + i];
+                uint2 w[M1_PLANES];
+                digits8(v, inv, false, w);
+#pragma unroll
+                for (int p = 0; p < M1_PLANES; p++) *reinterpret_cast<uint2*>(s_xq + (size_t)p * hk + k) = w[p];
+            }
+            cp_async_wait<0>();
+            __syncwarp();
+            const unsigned char* p0 = s_rows + (size_t)gid * pitch + tid * 16;
+            const unsigned char* p1 = p0 + (size_t)8 * pitch;
+            const int8_t* px = s_xq + (size_t)(gid & 3) * hk + tid * 16;
+            const bool colact = gid < M1_PLANES;
+            int t[4] = {0, 0, 0, 0};
+            for (int k = 0; k < hk; k += 64) {
+                const uint4 w0 = *reinterpret_cast<const uint4*>(p0 + k);
+                const uint4 w1 = *reinterpret_cast<const uint4*>(p1 + k);
+                uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+                if (colact) xb = *reinterpret_cast<const uint4*>(px + k);
+                imma16832(t, w0.x, w1.x, w0.y, w1.y, xb.x, xb.y);
+                imma16832(t, w0.z, w1.z, w0.w, w1.w, xb.z, xb.w);
+            }
+            float w0f, w1f;
+            plane_weights(tid, mx / 127.0f, w0f, w1f);
+            y0 = (float)t[0] * w0f + (float)t[1] * w1f;
+            y1 = (float)t[2] * w0f + (float)t[3] * w1f;
+            y0 += __shfl_xor_sync(0xffffffffu, y0, 1); y1 += __shfl_xor_sync(0xffffffffu, y1, 1);
+            if (row0 + gid < a.D) y0 *= bf(a.shd_s[row0 + gid]);
+            if (row0 + gid + 8 < a.D) y1 *= bf(a.shd_s[row0 + gid + 8]);
+        }
+    }
+    if (tid == 0) { s_y[warp][gid] = y0; s_y[warp][gid + 8] = y1; }
+    __syncthreads();
+    trace_pt(a.trace, 3);
+    // x[o] += sum_r w_r * y_r[o] + sigmoid(shared gate) * y_shared[o], picks in rank order
+    if (threadIdx.x < M1_DOWN_ROWS && row0 + threadIdx.x < a.D) {
+        const int o = threadIdx.x;
+        float y = 0.f;
+        for (int k = 0; k < a.topk; k++) y = fmaf(a.top_w[(size_t)b * a.topk + k], s_y[2 * k][o] + s_y[2 * k + 1][o], y);
+        if (a.shd_w) y = fmaf(a.sg[b], s_y[2 * a.topk][o] + s_y[2 * a.topk + 1][o], y);
+        a.xout[(size_t)b * a.D + row0 + o] += y;
+    }
+    trace_out(a.trace);
+}
+
+}  // namespace b2

@@ -298,11 +298,11 @@ class HybridEngine:
         return {n: {"ms": ms[i], "bytes": by[i], "launches": ln[i]} for i, n in enumerate(self.KERNEL_CLASSES)}
 
     def trace_step(self, cap: int = 4096):
-        """Timeline of one graph-run decode step: an int64 array [launches][8] (see b2_debug_trace_step)."""
-        buf = (C.c_uint64 * (8 * cap))()
+        """Timeline of one graph-run decode step: a uint64 array [launches][16] (see b2_debug_trace_step)."""
+        buf = (C.c_uint64 * (16 * cap))()
         n = C.c_int(0)
         self._check(self._lib.b2_debug_trace_step(self._h, buf, cap, C.byref(n)))
-        return np.frombuffer(buf, dtype=np.uint64)[: 8 * n.value].reshape(n.value, 8).copy()
+        return np.frombuffer(buf, dtype=np.uint64)[: 16 * n.value].reshape(n.value, 16).copy()
 
 
 # --- sampler (aegist_rs/src/chat.rs:221-272) ----------------------------------------------------

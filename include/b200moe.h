@@ -136,11 +136,12 @@ double b2_step_bytes(const b2_engine* e);
  * shared down, 7 head. */
 int b2_profile_step(b2_engine* e, int iters, float ms[8], double bytes[8], int launches[8]);
 /* Timeline of one decode step as the CUDA graph runs it (debugging aid, no reference counterpart; the step
- * feeds the current tokens and advances the length by one). Per launch 8 words, times in ns of the GPU's
- * global timer: [0] first block entered, [1] block 0 past the wait for the previous kernel, [2] block 0
- * past its prologue, [3] block 0 past its main loop, [4] last block left, [5] kernel code (1 GEMV, 3 DeltaNet
- * step, 5 expert gate/up, 6 expert down, 7 attention, 8 attention merge; 0 = a kernel that records nothing),
- * [6] a shape hint (rows of the first matrix, or the grid). `out` holds 8 * cap_launches words. */
+ * feeds the current tokens and advances the length by one). Per launch 16 words: [0] first block entered and
+ * [4] last block left, in ns of the GPU's global timer; [5] kernel code (1 GEMV, 3 DeltaNet step, 5 expert
+ * gate/up, 6 expert down, 7 attention, 8 attention merge; 0 = a kernel that records nothing); [6] a shape hint
+ * (rows of the first matrix, or the grid); [8] the SM cycle counter of block 0 when it entered and [9]..[15]
+ * the same counter at its points 1..7 (1 past the wait for the previous kernel, 2 past the prologue, 3 past the
+ * main loop, others kernel-specific). `out` holds 16 * cap_launches words. */
 int b2_debug_trace_step(b2_engine* e, unsigned long long* out, int cap_launches, int* n_launches);
 
 /* -- single operators, host buffers in and out (the reference's per-op semantics) ----------- */
