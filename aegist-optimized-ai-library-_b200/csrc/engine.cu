@@ -96,12 +96,11 @@ static size_t dtype_size(const std::string& d) {
 // Blocks per SM of the streaming GEMV kernel (B2_GEMV_CTAS overrides; for experiments).
 // Row-per-lane GEMV kernel (k_rowgemv) instead of the row-per-warp one (B2_ROWGEMV=0 switches back).
 static bool g_rowgemv = [] { const char* v = getenv("B2_ROWGEMV"); return !(v && v[0] == '0'); }();
-// Tensor-core GEMV (k_tcgemv) for the int8 matrices of small batches (B2_TCGEMV=0 switches back to k_rowgemv);
-// B2_TC_WARPS = 8 or 16 warps per block.
+// Tensor-core GEMV (k_tcgemv) for the int8 matrices of small batches (B2_TCGEMV=0 switches back to k_rowgemv).
 // Expert kernels for fewer than 8 tokens (k_moe_gu1 / k_moe_down1; B2_MOE1=0 switches back to the per-pick kernels).
 static bool g_moe1 = [] { const char* v = getenv("B2_MOE1"); return !(v && v[0] == '0'); }();
 static bool g_tcgemv = [] { const char* v = getenv("B2_TCGEMV"); return !(v && v[0] == '0'); }();
-static int g_tc_warps = [] { const char* v = getenv("B2_TC_WARPS"); return (v && atoi(v) == 8) ? 8 : 16; }();
+constexpr int g_tc_warps = 16;   // compute warps per block
 static int g_gemv_ctas_per_sm = [] { const char* v = getenv("B2_GEMV_CTAS"); return v ? atoi(v) : 2; }();
 static int down_row_blocks(int D) { return (D + DOWN_ROWS - 1) / DOWN_ROWS; }
 
@@ -628,15 +627,16 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
             a.total_jobs += g.jobs;
         }
         const int grid = grid_override ? grid_override : std::max(1, std::min(a.total_jobs, nsm));
-#define TCG(NBv, NSTv, Wv)                                                                                      \
+        const int per_block = (a.total_jobs + grid - 1) / grid;
+        const int nst = std::max(1, std::min(per_block, TC_MAX_STAGES));   // stages: what the longest block needs
+#define TCG(NBv, Wv)                                                                                            \
     {                                                                                                           \
-        const size_t smem = tc_smem_bytes(a, NBv, NSTv, Wv);                                                    \
-        e = opt_in_smem(k_tcgemv<NBv, NSTv, Wv>, smem);                                                         \
+        const size_t smem = tc_smem_bytes(a, NBv, nst, Wv);                                                     \
+        e = opt_in_smem(k_tcgemv<NBv, Wv>, smem);                                                               \
         if (e == cudaSuccess)                                                                                   \
-            e = launch_k(k_tcgemv<NBv, NSTv, Wv>, dim3(grid, (B + NBv - 1) / NBv), dim3((Wv + TC_EPI) * 32), smem, st, a, B); \
+            e = launch_k(k_tcgemv<NBv, Wv>, dim3(grid, (B + NBv - 1) / NBv), dim3((Wv + TC_EPI) * 32), smem, st, a, B, nst, tc_stage_bytes(a)); \
     }
-        if (B >= 2) { if (g_tc_warps == 8) TCG(4, 2, 8) else TCG(4, 2, 16) }
-        else { if (g_tc_warps == 8) TCG(1, 3, 8) else TCG(1, 3, 16) }
+        if (B >= 2) TCG(2, 16) else TCG(1, 16)
 #undef TCG
         return e;
     }

@@ -59,7 +59,7 @@ __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.w
 
 // Time stamps of a launch for the step timeline (debugging aid; trace is null in normal runs). Per launch
 // 16 words: [0] first block in and [4] last block out (ns of the global timer, which is slow to read, so it is
-// read only there), [5] kernel code, [6] a shape hint, [8] block 0's SM cycle counter when it came in,
+// read only there), [5] kernel code, [6] a shape hint, [7] last block in, [8] block 0's SM cycle counter when it came in,
 // [9] .. [15] the same counter at points 1 .. 7 of block 0 (1 past the dependency wait, 2 past the prologue,
 // 3 past the main loop; the others as the kernel defines them).
 __device__ __forceinline__ unsigned long long gtime() {
@@ -70,7 +70,9 @@ __device__ __forceinline__ unsigned long long gtime() {
 __device__ __forceinline__ bool trace_block0() { return (blockIdx.x | blockIdx.y | blockIdx.z) == 0; }
 __device__ __forceinline__ void trace_in(unsigned long long* p, int code, int hint) {
     if (p && threadIdx.x == 0) {
-        atomicMin(p, gtime());
+        const unsigned long long t = gtime();
+        atomicMin(p, t);
+        atomicMax(p + 7, t);        // when the last block came in
         if (trace_block0()) { p[5] = (unsigned long long)code; p[6] = (unsigned long long)hint; p[8] = (unsigned long long)clock64(); }
     }
 }
@@ -580,6 +582,7 @@ __global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv_norm(const GemvArgs a)
 #include "rowgemv.cuh"
 #include "mmagemm.cuh"
 #include "mmaexperts.cuh"
+#include "digits.cuh"
 #include "tcgemv.cuh"
 #include "moe1.cuh"
 namespace b2 {

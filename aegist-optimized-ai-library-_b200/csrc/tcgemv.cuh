@@ -2,11 +2,11 @@
 // rows) with the multiply-adds of the int8 matrices on the tensor cores.
 //
 // A GEMV streams every weight once, so what limits it besides HBM is the instruction stream that turns
-// bytes into products: about 3.3 instructions per int8 weight when each product is an FMA. Here a warp
-// widens 16 bytes of two rows to fp16 (exact, 1.25 instructions per weight) and hands them to
-// mma.sync.m16n8k16 as the A operand; the B operand holds the activations as fp16 hi + lo halves
-// (x = hi + lo to about 22 bits) in columns b (hi) and 4 + b (lo) for up to 4 sequences, so one
-// instruction multiplies 16 rows x 16 values for all of them with fp32 accumulation.
+// bytes into products: about 3.3 instructions per int8 weight when each product is an FMA. Here the
+// int8 weights go to mma.sync.m16n8k32.s8 exactly as they lie in memory (a warp reads 16 bytes of two
+// rows and issues two instructions for 1024 products per sequence), and the activations are split once
+// per launch into four int8 digit planes (digits.cuh) that occupy four of the eight B columns per
+// sequence, so up to two sequences share a pass. The integer sums are exact.
 //
 // The tile, its bulk copies and the segment bookkeeping are those of k_rowgemv: 32 row slots of up to
 // 2048 bytes (16 slots for rows of up to 4096 bytes: bf16 rows, int8 rows of 4096 values), one bulk
@@ -34,77 +34,78 @@ __host__ __device__ __forceinline__ bool tc_has_bf(const GemvArgs& a) {
         if (rl_is_bf(a.seg[i].kind)) return true;
     return false;
 }
-constexpr int TC_EPI = 2;          // epilogue warps
+constexpr int TC_EPI = 4;          // epilogue warps = partial-sum buffers: a tile's epilogue may take four tile times
 __device__ __forceinline__ void bar_sync(int id, int n) { asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 __device__ __forceinline__ void bar_arrive(int id, int n) { asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(n) : "memory"); }
 // rows of a tile of this segment: what the host chose, else the most a stage holds
 __host__ __device__ __forceinline__ int tc_tile_rows(const Seg& g, int K) { return g.tr > 0 ? g.tr : rl_tile_rows(g.kind, K); }
-// bytes of dynamic shared memory: stages | fp16 activations [2 NB][K] | fp32 activations [NB][K] (only with
-// bf16 rows) | partial sums [2][NB][W][32]
+// bytes of dynamic shared memory: stages | digit planes [NB][4][K + 64] | fp32 activations [NB][K] (only with
+// bf16 rows) | partial sums [TC_EPI][NB][W][32]
+// bytes of a stage: the slots the largest tile of the launch occupies (the up rows of a pair tile start at slot 16)
+__host__ __device__ __forceinline__ int tc_stage_bytes(const GemvArgs& a) {
+    int m = 0;
+    for (int i = 0; i < a.nseg; i++) {
+        const Seg& g = a.seg[i];
+        const int tr = tc_tile_rows(g, a.K);
+        const int slots = g.kind == SEG_I8_GATEUP ? 16 + tr : tr;
+        const int bytes = slots * (rl_two_lanes(g.kind, a.K) ? TC_SLOT_STRIDE_WIDE : TC_SLOT_STRIDE);
+        m = bytes > m ? bytes : m;
+    }
+    return m;
+}
 __host__ __device__ __forceinline__ size_t tc_smem_bytes(const GemvArgs& a, int NB, int NST, int W) {
-    return (size_t)NST * TC_STAGE_BYTES + (size_t)2 * NB * a.K * 2 + (tc_has_bf(a) ? (size_t)NB * a.K * 4 : 0) +
-           (size_t)2 * NB * W * 32 * 4;
+    return (size_t)NST * tc_stage_bytes(a) + (size_t)NB * M1_PLANES * (a.K + 64) + (tc_has_bf(a) ? (size_t)NB * a.K * 4 : 0) +
+           (size_t)TC_EPI * NB * W * 32 * 4;
 }
 // the shapes the tensor-core path takes: K slices of whole 64-byte steps
-__host__ __device__ __forceinline__ bool tc_shape_ok(int K, int W) { return K % (32 * W) == 0 && K <= 2 * RL_SLOT_MAX; }
+__host__ __device__ __forceinline__ bool tc_shape_ok(int K, int W) { return K % (32 * W) == 0 && K <= 2 * RL_SLOT_MAX && K % 8 == 0; }
 
 
 
-// NJ 64-byte steps of a warp's K slice for rows (gid, gid + 8): every load first, then NJ independent
-// accumulation chains, so that the latencies of the loads, the widening and the mma overlap.
+// NJ 64-byte steps of a warp's K slice for rows (gid, gid + 8): every load first, then the mma's on NJ
+// independent accumulators.
 template <int NJ>
-__device__ __forceinline__ void tc_i8_steps(const unsigned char* pa, const unsigned char* pb, const __half* px, bool colact,
-                                            float (&c)[4]) {
-    uint4 wa[NJ], wb[NJ], x0[NJ], x1[NJ];
+__device__ __forceinline__ void tc_i8_steps(const unsigned char* pa, const unsigned char* pb, const int8_t* px, bool colact, int (&c)[4]) {
+    uint4 wa[NJ], wb[NJ], xb[NJ];
 #pragma unroll
     for (int j = 0; j < NJ; j++) {
         wa[j] = *reinterpret_cast<const uint4*>(pa + 64 * j);
         wb[j] = *reinterpret_cast<const uint4*>(pb + 64 * j);
-        x0[j] = make_uint4(0u, 0u, 0u, 0u); x1[j] = x0[j];
-        if (colact) {
-            x0[j] = *reinterpret_cast<const uint4*>(px + 64 * j);
-            x1[j] = *reinterpret_cast<const uint4*>(px + 64 * j + 8);
-        }
+        xb[j] = make_uint4(0u, 0u, 0u, 0u);
+        if (colact) xb[j] = *reinterpret_cast<const uint4*>(px + 64 * j);
     }
-    float cc[NJ][4];
+    int cc[NJ][4];
 #pragma unroll
-    for (int j = 0; j < NJ; j++)
-#pragma unroll
-        for (int q = 0; q < 4; q++) cc[j][q] = 0.f;
-#pragma unroll
-    for (int m = 0; m < 4; m++) {
-#pragma unroll
-        for (int j = 0; j < NJ; j++) {
-            const uint32_t a = m == 0 ? wa[j].x : m == 1 ? wa[j].y : m == 2 ? wa[j].z : wa[j].w;
-            const uint32_t b = m == 0 ? wb[j].x : m == 1 ? wb[j].y : m == 2 ? wb[j].z : wb[j].w;
-            const uint32_t xa = m == 0 ? x0[j].x : m == 1 ? x0[j].z : m == 2 ? x1[j].x : x1[j].z;
-            const uint32_t xb = m == 0 ? x0[j].y : m == 1 ? x0[j].w : m == 2 ? x1[j].y : x1[j].w;
-            uint32_t af[4];
-            i8x4_to_h2x2(a, af[0], af[2]);
-            i8x4_to_h2x2(b, af[1], af[3]);
-            mma16816(cc[j], af, xa, xb);
-        }
+    for (int j = 0; j < NJ; j++) {
+        cc[j][0] = cc[j][1] = cc[j][2] = cc[j][3] = 0;
+        imma16832(cc[j], wa[j].x, wb[j].x, wa[j].y, wb[j].y, xb[j].x, xb[j].y);
     }
+#pragma unroll
+    for (int j = 0; j < NJ; j++) imma16832(cc[j], wa[j].z, wb[j].z, wa[j].w, wb[j].w, xb[j].z, xb[j].w);
 #pragma unroll
     for (int j = 0; j < NJ; j++)
 #pragma unroll
         for (int q = 0; q < 4; q++) c[q] += cc[j][q];
 }
 
-template <int NB, int NST, int W>
-__global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs a, int nseq) {
+// NST stages of shared memory (1 .. TC_MAX_STAGES): as many as the longest block has tiles. (Keeping two of these
+// blocks, or one and an expert block, on an SM so that the next kernel's first tiles arrive under the previous
+// kernel was measured and lost: it costs a stage and 40 registers per thread.)
+constexpr int TC_MAX_STAGES = 3;
+template <int NB, int W>
+__global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs a, int nseq, int NST, int stage_bytes) {
     constexpr int WT = W + TC_EPI;                 // all warps
-    constexpr int NT = WT * 32;
-    constexpr int XPT = (2 * RL_SLOT_MAX + NT - 1) / NT;   // activation values per thread in the prologue
     constexpr int BAR_N = W * 32 + 32;             // the compute warps and the one epilogue warp of a tile
     extern __shared__ __align__(128) unsigned char tc_smem[];
     const bool has_bf = tc_has_bf(a);
-    unsigned char* stages = tc_smem;                                                     // [NST][TC_STAGE_BYTES]
-    __half* xh = reinterpret_cast<__half*>(tc_smem + (size_t)NST * TC_STAGE_BYTES);      // [2 NB][K]: hi rows, then lo rows
-    float* xs = reinterpret_cast<float*>(xh + (size_t)2 * NB * a.K);                     // [NB][K] when has_bf
-    float* part = xs + (has_bf ? (size_t)NB * a.K : 0);                                  // [2][NB][W][32]
-    __shared__ __align__(8) uint64_t full_bar[NST];
-    __shared__ float red[WT][NB];
+    unsigned char* stages = tc_smem;                                                     // [NST][stage_bytes]
+    const int XS = a.K + 64;                                                             // plane stride: neighbouring planes in different halves of the banks
+    int8_t* xq = reinterpret_cast<int8_t*>(tc_smem + (size_t)NST * stage_bytes);         // [NB][4][XS] digit planes
+    float* xs = reinterpret_cast<float*>(xq + (size_t)NB * M1_PLANES * XS);              // [NB][K] when has_bf
+    float* part = xs + (has_bf ? (size_t)NB * a.K : 0);                                  // [TC_EPI][NB][W][32]
+    __shared__ __align__(8) uint64_t full_bar[TC_MAX_STAGES];
+    __shared__ float red[2][WT][NB];
+    __shared__ float s_xscale[NB];
     __shared__ int s_last;
     __shared__ float s_bv[TC_EPI][NB];
     __shared__ int s_bi[TC_EPI][NB];
@@ -144,7 +145,7 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
             const char* src = pair ? (lane < 16 ? (const char*)sg.w + (size_t)(row0 + lane) * a.K
                                                 : (const char*)sg.w2 + (size_t)(row0 + lane - 16) * a.K)
                                    : (const char*)sg.w + (size_t)(row0 + lane) * rb;
-            bulk_load(stages + (size_t)st * TC_STAGE_BYTES + (size_t)lane * sstride, src, rb, &full_bar[st]);
+            bulk_load(stages + (size_t)st * stage_bytes + (size_t)lane * sstride, src, rb, &full_bar[st]);
         }
     };
     if (warp == W)
@@ -152,89 +153,94 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
     grid_dep_wait();
     trace_pt(a.trace, 1);
 
-    // prologue: the normalised activations as fp16 hi | lo (and fp32 when bf16 rows follow); every value
-    // crosses from global memory once, all loads of a thread in flight together
-    auto put_x = [&](int b, int k, float v) {
-        const __half h = __float2half(v);
-        xh[(size_t)b * a.K + k] = h;
-        xh[(size_t)(NB + b) * a.K + k] = __float2half(v - __half2float(h));
-        if (has_bf) xs[(size_t)b * a.K + k] = v;
-    };
-    if (a.gn_w) {
-        // DeltaNet output projection: w * rmsnorm_DV(o) * silu(z) per value head (aegist/hybrid.py:133-147);
-        // a warp takes heads warp, warp + WT, ...; a lane DV / 32 values of each
-        constexpr int HPW = 4, DVL = 8;              // up to 4 heads per warp, DV <= 256
-        const int nh = a.K / a.DV, dvl = a.DV >> 5;
-#pragma unroll 1
+    // prologue: the normalised activations as int8 digit planes (and fp32 when bf16 rows follow). Thread c takes
+    // the 8 consecutive values of chunk c, so every value crosses from global memory once, as two 16-byte loads.
+    {
+        const int kc = threadIdx.x * 8;
+        const bool has = kc < a.K;
+        float xv[NB][8];
+#pragma unroll
         for (int b = 0; b < NB; b++) {
-            const bool live = b0 + b < nseq;
-            const float* in = a.x + (size_t)(b0 + b) * a.x_stride;
-            const float* z = a.z + (size_t)(b0 + b) * a.x_stride;
-            for (int hb = 0; hb < nh; hb += HPW * WT) {
-                float vi[HPW][DVL], vz[HPW][DVL], vw[DVL];
-#pragma unroll
-                for (int i = 0; i < DVL; i++) vw[i] = i < dvl ? bf(a.gn_w[lane + 32 * i]) : 0.f;
-#pragma unroll
-                for (int hh = 0; hh < HPW; hh++) {
-                    const int h = hb + warp + hh * WT;
-#pragma unroll
-                    for (int i = 0; i < DVL; i++) {
-                        const bool ok = live && h < nh && i < dvl;
-                        vi[hh][i] = ok ? in[h * a.DV + lane + 32 * i] : 0.f;
-                        vz[hh][i] = ok ? z[h * a.DV + lane + 32 * i] : 0.f;
-                    }
-                }
-#pragma unroll
-                for (int hh = 0; hh < HPW; hh++) {
-                    const int h = hb + warp + hh * WT;
-                    float ss = 0.f;
-#pragma unroll
-                    for (int i = 0; i < DVL; i++) ss = fmaf(vi[hh][i], vi[hh][i], ss);
-                    ss = warp_sum(ss);
-                    const float r = 1.0f / sqrtf(ss / (float)a.DV + a.eps);
-                    if (h < nh)
-#pragma unroll
-                        for (int i = 0; i < DVL; i++)
-                            if (i < dvl) put_x(b, h * a.DV + lane + 32 * i, (vw[i] * (vi[hh][i] * r)) * vz[hh][i]);
-                }
+            float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0;
+            if (has && b0 + b < nseq) {
+                v0 = *reinterpret_cast<const float4*>(a.x + (size_t)(b0 + b) * a.x_stride + kc);
+                v1 = *reinterpret_cast<const float4*>(a.x + (size_t)(b0 + b) * a.x_stride + kc + 4);
             }
+            xv[b][0] = v0.x; xv[b][1] = v0.y; xv[b][2] = v0.z; xv[b][3] = v0.w;
+            xv[b][4] = v1.x; xv[b][5] = v1.y; xv[b][6] = v1.z; xv[b][7] = v1.w;
         }
-    } else {
-        float xv[NB][XPT], nw[XPT];
+        if (a.gn_w) {
+            // DeltaNet output projection: w * rmsnorm_DV(o) * silu(z) per value head (aegist/hybrid.py:133-147);
+            // a head is DV / 8 neighbouring lanes
+            uint4 wv = make_uint4(0u, 0u, 0u, 0u);
+            if (has) wv = *reinterpret_cast<const uint4*>(a.gn_w + (kc % a.DV));
+            const float gw[8] = {bflo(wv.x), bfhi(wv.x), bflo(wv.y), bfhi(wv.y), bflo(wv.z), bfhi(wv.z), bflo(wv.w), bfhi(wv.w)};
 #pragma unroll
-        for (int j = 0; j < XPT; j++) {
-            const int k = threadIdx.x + j * NT;
-            nw[j] = (a.norm_w && k < a.K) ? 1.0f + bf(a.norm_w[k]) : 1.0f;
+            for (int b = 0; b < NB; b++) {
+                float4 z0 = make_float4(0.f, 0.f, 0.f, 0.f), z1 = z0;
+                if (has && b0 + b < nseq) {
+                    z0 = *reinterpret_cast<const float4*>(a.z + (size_t)(b0 + b) * a.x_stride + kc);
+                    z1 = *reinterpret_cast<const float4*>(a.z + (size_t)(b0 + b) * a.x_stride + kc + 4);
+                }
+                const float zz[8] = {z0.x, z0.y, z0.z, z0.w, z1.x, z1.y, z1.z, z1.w};
+                float ss = 0.f;
 #pragma unroll
-            for (int b = 0; b < NB; b++) xv[b][j] = (k < a.K && b0 + b < nseq) ? a.x[(size_t)(b0 + b) * a.x_stride + k] : 0.f;
-        }
-        float rn[NB];
+                for (int i = 0; i < 8; i++) ss = fmaf(xv[b][i], xv[b][i], ss);
+                for (int o = a.DV >> 4; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                const float r = 1.0f / sqrtf(ss / (float)a.DV + a.eps);
 #pragma unroll
-        for (int b = 0; b < NB; b++) rn[b] = 1.0f;
-        if (a.norm_w) {
+                for (int i = 0; i < 8; i++) xv[b][i] = (gw[i] * (xv[b][i] * r)) * zz[i];
+            }
+        } else if (a.norm_w) {
+            uint4 wv = make_uint4(0u, 0u, 0u, 0u);
+            if (has) wv = *reinterpret_cast<const uint4*>(a.norm_w + kc);
+            const float nw[8] = {1.0f + bflo(wv.x), 1.0f + bfhi(wv.x), 1.0f + bflo(wv.y), 1.0f + bfhi(wv.y),
+                                 1.0f + bflo(wv.z), 1.0f + bfhi(wv.z), 1.0f + bflo(wv.w), 1.0f + bfhi(wv.w)};
 #pragma unroll
             for (int b = 0; b < NB; b++) {
                 float ss = 0.f;
 #pragma unroll
-                for (int j = 0; j < XPT; j++) ss = fmaf(xv[b][j], xv[b][j], ss);
+                for (int i = 0; i < 8; i++) ss = fmaf(xv[b][i], xv[b][i], ss);
                 ss = warp_sum(ss);
-                if (lane == 0) red[warp][b] = ss;
+                if (lane == 0) red[0][warp][b] = ss;
             }
             __syncthreads();
 #pragma unroll
             for (int b = 0; b < NB; b++) {
                 float t = 0.f;
 #pragma unroll
-                for (int w = 0; w < WT; w++) t += red[w][b];
-                rn[b] = 1.0f / sqrtf(t / (float)a.K + a.eps);
+                for (int w = 0; w < WT; w++) t += red[0][w][b];
+                const float rn = 1.0f / sqrtf(t / (float)a.K + a.eps);
+#pragma unroll
+                for (int i = 0; i < 8; i++) xv[b][i] = xv[b][i] * rn * nw[i];
             }
         }
 #pragma unroll
-        for (int j = 0; j < XPT; j++) {
-            const int k = threadIdx.x + j * NT;
-            if (k < a.K)
+        for (int b = 0; b < NB; b++) {
+            float mx = 0.f;
 #pragma unroll
-                for (int b = 0; b < NB; b++) put_x(b, k, a.norm_w ? xv[b][j] * rn[b] * nw[j] : xv[b][j]);
+            for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(xv[b][i]));
+            mx = warp_max(mx);
+            if (lane == 0) red[1][warp][b] = mx;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int b = 0; b < NB; b++) {
+            float mx = 0.f;
+#pragma unroll
+            for (int w = 0; w < WT; w++) mx = fmaxf(mx, red[1][w][b]);
+            const float inv = mx > 0.f ? 127.0f / mx : 0.f;
+            if (threadIdx.x == 0) s_xscale[b] = mx / 127.0f;
+            if (has) {
+                uint2 w[M1_PLANES];
+                digits8(xv[b], inv, false, w);
+#pragma unroll
+                for (int p = 0; p < M1_PLANES; p++) *reinterpret_cast<uint2*>(xq + (size_t)(b * M1_PLANES + p) * XS + kc) = w[p];
+                if (has_bf) {
+                    *reinterpret_cast<float4*>(xs + (size_t)b * a.K + kc) = make_float4(xv[b][0], xv[b][1], xv[b][2], xv[b][3]);
+                    *reinterpret_cast<float4*>(xs + (size_t)b * a.K + kc + 4) = make_float4(xv[b][4], xv[b][5], xv[b][6], xv[b][7]);
+                }
+            }
         }
     }
     __syncthreads();
@@ -247,19 +253,23 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
 
     if (warp < W) {
         // ---- compute warps: partial sums of every tile into part[tile & 1] ----
-        // this lane's activation column in the B operand: hi of sequence (gid & 3) or lo of it
-        const bool colact = (gid & 3) < NB;
-        const __half* xcol = xh + (size_t)((gid >> 2) * NB + (gid & 3)) * a.K;
+        // this lane's activation column in the B operand: plane (gid & 3) of sequence (gid >> 2)
+        const bool colact = (gid >> 2) < NB;
+        const int8_t* xcol = xq + (size_t)gid * XS;
+        // what this lane's two result columns (2 tid, 2 tid + 1) weigh: planes 2 (tid & 1), 2 (tid & 1) + 1 of sequence tid >> 1
+        const float pw0 = ((tid >> 1) < NB ? s_xscale[(tid >> 1) < NB ? (tid >> 1) : 0] : 0.f) * ((tid & 1) ? (1.0f / 16384.0f) : 1.0f);
+        const float pw1 = pw0 * (1.0f / 128.0f);
         for (int t = t0, i = 0; t < t1; t++, i++) {
-            const int st = i % NST, buf = i & 1;
+            const int st = i % NST, buf = i % TC_EPI;
             int s, tin;
             locate(t, s, tin);
             const int kind = a.seg[s].kind;
             const bool isbf = rl_is_bf(kind);
             const bool two = rl_two_lanes(kind, a.K);
+            const int tr = tc_tile_rows(a.seg[s], a.K);    // slots beyond the tile's rows are not part of the stage: clamp
             float* pt = part + (size_t)buf * NB * W * 32;
-            const unsigned char* stage = stages + (size_t)st * TC_STAGE_BYTES;
-            if (i >= 2) bar_sync(3 + buf, BAR_N);          // the epilogue of tile i - 2 has read this buffer
+            const unsigned char* stage = stages + (size_t)st * stage_bytes;
+            if (i >= TC_EPI) bar_sync(1 + TC_EPI + buf, BAR_N);   // the epilogue of tile i - TC_EPI has read this buffer
             mbar_wait(&full_bar[st], (i / NST) & 1, a.err);
             if (!isbf) {
                 const int nrb = two ? 1 : 2;               // 16-slot blocks in the tile
@@ -267,28 +277,29 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
                 const int rbk = warp % nrb, ks = warp / nrb;
                 const int slice = a.K / nks;               // bytes = values; a multiple of 64
                 const int sstride = two ? TC_SLOT_STRIDE_WIDE : TC_SLOT_STRIDE;
-                const unsigned char* pa = stage + (size_t)(rbk * 16 + gid) * sstride + ks * slice + tid * 16;
-                const unsigned char* pb = pa + (size_t)8 * sstride;
-                const __half* px = xcol + ks * slice + tid * 16;
-                float c0[4] = {0.f, 0.f, 0.f, 0.f};
+                const int slot_hi = (kind == SEG_I8_GATEUP ? rbk * 16 : 0) + tr - 1;       // last slot this row block may read
+                const unsigned char* pa = stage + (size_t)min(rbk * 16 + gid, slot_hi) * sstride + ks * slice + tid * 16;
+                const unsigned char* pb = stage + (size_t)min(rbk * 16 + gid + 8, slot_hi) * sstride + ks * slice + tid * 16;
+                const int8_t* px = xcol + ks * slice + tid * 16;
+                int c0[4] = {0, 0, 0, 0};
                 int j = 0;
                 for (; j + 256 <= slice; j += 256) tc_i8_steps<4>(pa + j, pb + j, px + j, colact, c0);
                 if (j + 128 <= slice) { tc_i8_steps<2>(pa + j, pb + j, px + j, colact, c0); j += 128; }
                 if (j + 64 <= slice) tc_i8_steps<1>(pa + j, pb + j, px + j, colact, c0);
-                // c[q]: row gid (+8 for q >= 2), column 2 tid + (q & 1); hi + lo of a sequence are 4 columns apart
+                // c0[q]: row gid (+8 for q >= 2), column 2 tid + (q & 1); the four planes of a sequence are lanes tid, tid ^ 1
 #pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    float v = c0[q];
-                    v += __shfl_xor_sync(0xffffffffu, v, 2);
-                    const int b = 2 * tid + (q & 1);
-                    if (tid < 2 && b < NB) pt[((size_t)b * W + ks) * 32 + rbk * 16 + gid + (q >> 1) * 8] = v;
+                for (int h = 0; h < 2; h++) {
+                    float v = (float)c0[2 * h] * pw0 + (float)c0[2 * h + 1] * pw1;
+                    v += __shfl_xor_sync(0xffffffffu, v, 1);
+                    const int b = tid >> 1;
+                    if ((tid & 1) == 0 && b < NB) pt[((size_t)b * W + ks) * 32 + rbk * 16 + gid + h * 8] = v;
                 }
             } else {
                 // bf16 rows: 16 slots of 2 K bytes; warp -> (8-row half, K slice), lane -> (row, 16-byte unit of a 64-byte step)
                 const int nks = W / 2;
                 const int rh = warp & 1, ks = warp >> 1;
                 const int slice = 2 * a.K / nks;           // bytes
-                const unsigned char* pa = stage + (size_t)(rh * 8 + gid) * TC_SLOT_STRIDE_WIDE + ks * slice + tid * 16;
+                const unsigned char* pa = stage + (size_t)min(rh * 8 + gid, tr - 1) * TC_SLOT_STRIDE_WIDE + ks * slice + tid * 16;
                 float acc[NB];
 #pragma unroll
                 for (int b = 0; b < NB; b++) acc[b] = 0.f;
@@ -390,7 +401,7 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
                 case SEG_I8_GATEUP: out[row] = siluf_(e0 * sA) * (e1 * sB); break;
                 }
             }
-            if (t + TC_EPI < t1) bar_arrive(3 + p, BAR_N);     // the buffer may be written again
+            if (t + TC_EPI < t1) bar_arrive(1 + TC_EPI + p, BAR_N);     // the buffer may be written again
         }
     }
     trace_pt(a.trace, 3);
