@@ -134,7 +134,8 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
     const int XS = D + 64;                              // plane stride: planes p, p+1 in different halves of the banks
     int8_t* s_xq = reinterpret_cast<int8_t*>(s_sc + (size_t)2 * M1_GU_PAIRS * 2 * ngroup);    // [PLANES][XS], even/odd order
     float* s_xsum = reinterpret_cast<float*>(s_xq + (size_t)M1_PLANES * XS);                  // [ngroup]
-    __shared__ __align__(16) uint32_t s_key[256];
+    __shared__ uint32_t s_key[64];                      // the 8 best keys of each of the 8 ranking warps
+    __shared__ int s_cand[64];                          // and their experts
     __shared__ int s_top[8];
     __shared__ float s_topv[8];
     __shared__ float s_red[2][8];
@@ -167,20 +168,37 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
         for (int w = 0; w < 8; w++) sum += s_red[1][w];
         const float prob = p / sum;
         const uint32_t key = e < a.E ? __float_as_uint(prob) + 1u : 0u;      // positive floats order like their bits
-        s_key[e] = key;
-        asm volatile("bar.sync 2, 256;" ::: "memory");
-        // experts ahead of this one: a larger probability, or an equal one and a lower index. Below this thread's
-        // own group of four "not smaller" is counted (key - 1), from it on "larger"; its own group is corrected after.
-        int ahead = 0;
-        const int eg = e & ~3;
-#pragma unroll 8
-        for (int j = 0; j < 256; j += 4) {
-            const uint4 k4 = *reinterpret_cast<const uint4*>(s_key + j);
-            const uint32_t kk = j < eg ? key - 1u : key;
-            ahead += (k4.x > kk) + (k4.y > kk) + (k4.z > kk) + (k4.w > kk);
+        // every warp picks the 8 best of its 32 experts (8 rounds of two warp-wide integer reductions: largest
+        // key, then the lowest expert holding it), then warp 0 picks the 8 best of the 64 candidates the same way
+        {
+            uint32_t k = key;
+            for (int r = 0; r < 8; r++) {
+                const uint32_t m = __reduce_max_sync(0xffffffffu, k);
+                const uint32_t who = __reduce_min_sync(0xffffffffu, (k == m && m != 0u) ? (uint32_t)lane : 0xffu);
+                if (lane == r) { s_key[warp * 8 + r] = m; s_cand[warp * 8 + r] = who < 32u ? warp * 32 + (int)who : 0x7fffffff; }
+                if ((uint32_t)lane == who) k = 0u;
+            }
         }
-        for (int j = eg; j < e; j++) ahead += (s_key[j] == key);
-        if (ahead < a.topk && key != 0u) { s_top[ahead] = e; s_topv[ahead] = prob; }
+        asm volatile("bar.sync 2, 256;" ::: "memory");
+        if (warp == 0) {
+            // candidates are in ascending expert order for equal keys only within a warp's list, so the tie rule is
+            // applied on the expert number itself
+            uint32_t k0 = s_key[lane], k1 = s_key[32 + lane];
+            const int e0 = s_cand[lane], e1 = s_cand[32 + lane];
+            for (int r = 0; r < a.topk; r++) {
+                const uint32_t bk = k0 > k1 ? k0 : k1;
+                const uint32_t m = __reduce_max_sync(0xffffffffu, bk);
+                uint32_t c = 0x7fffffffu;
+                if (m != 0u) {
+                    if (k0 == m) c = (uint32_t)e0;
+                    if (k1 == m && (uint32_t)e1 < c) c = (uint32_t)e1;
+                }
+                const uint32_t ex = __reduce_min_sync(0xffffffffu, c);
+                if (k0 == m && (uint32_t)e0 == ex) k0 = 0u;
+                if (k1 == m && (uint32_t)e1 == ex) k1 = 0u;
+                if (lane == r) { s_top[r] = ex < 0x7fffffffu ? (int)ex : -1; s_topv[r] = m ? __uint_as_float(m - 1u) : 0.f; }
+            }
+        }
         asm volatile("bar.sync 2, 256;" ::: "memory");
         if (blockIdx.x == 0 && threadIdx.x < a.topk) {
             float tsum = 0.f;
@@ -318,6 +336,11 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
         const uint16_t* su = s_sc + (size_t)slu * 2 * ngroup;
         const int8_t* px = s_xq + (size_t)(gid & 3) * XS + tid * 16;
         const bool colact = gid < M1_PLANES;
+        // a warp's groups lie inside one 8-value piece of a scale row when ge divides 8: positions are base + offset
+        const int gf = ke * ge;
+        const bool lin = ge <= 8 && (8 % ge) == 0;
+        const int bgs = sc_pos(ngroup, scm, slg, 0, gf), bgm = sc_pos(ngroup, scm, slg, 1, gf);
+        const int bus = sc_pos(ngroup, scm, slu, 0, gf), bum = sc_pos(ngroup, scm, slu, 1, gf);
         for (int g0 = ke * ge; g0 < (ke + 1) * ge; g0 += GQ) {
             const int gend = (ke + 1) * ge;
             uint2 wg[GQ], wu[GQ];
@@ -331,8 +354,11 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
                 xb[q] = make_uint4(0u, 0u, 0u, 0u);
                 if (colact) xb[q] = *reinterpret_cast<const uint4*>(px + g * 64);
                 const bool live = g0 + q < gend;
-                sgv[q] = live ? h2f(sg[sc_pos(ngroup, scm, slg, 0, g)]) : 0.f; suv[q] = live ? h2f(su[sc_pos(ngroup, scm, slu, 0, g)]) : 0.f;
-                mgv[q] = live ? h2f(sg[sc_pos(ngroup, scm, slg, 1, g)]) : 0.f; muv[q] = live ? h2f(su[sc_pos(ngroup, scm, slu, 1, g)]) : 0.f;
+                const int o = g - gf;
+                sgv[q] = live ? h2f(sg[lin ? bgs + o : sc_pos(ngroup, scm, slg, 0, g)]) : 0.f;
+                suv[q] = live ? h2f(su[lin ? bus + o : sc_pos(ngroup, scm, slu, 0, g)]) : 0.f;
+                mgv[q] = live ? h2f(sg[lin ? bgm + o : sc_pos(ngroup, scm, slg, 1, g)]) : 0.f;
+                muv[q] = live ? h2f(su[lin ? bum + o : sc_pos(ngroup, scm, slu, 1, g)]) : 0.f;
                 xs[q] = s_xsum[g];
             }
             int t[GQ][4];

@@ -288,8 +288,14 @@ class HybridEngine:
     def step_bytes(self) -> float:
         return self._lib.b2_step_bytes(self._h)
 
-    KERNEL_CLASSES = ("k_embed", "k_gemv_norm", "k_delta_step", "k_attn", "k_proj_out", "k_expert_gu",
-                      "k_expert_down", "k_gemv_norm[head]")
+    # roles of the launches of a decode step; which kernel fills a role depends on the batch:
+    #   1-7 sequences: k_tcgemv (in_proj, out_proj, head), k_moe_gu1, k_moe_down1
+    #   8+ sequences:  k_prep_x + k_mma_i8 (+ k_tcgemv for bf16 rows and the head), k_expert_gu / k_expert_down,
+    #                  or k_group_picks + k_mma_q4 from 16 tokens on
+    KERNEL_CLASSES = ("embed", "in_proj", "delta_step", "attention", "out_proj", "expert_gate_up", "expert_down", "head")
+    KERNELS_SMALL_BATCH = {"embed": "k_embed", "in_proj": "k_tcgemv", "delta_step": "k_delta_step",
+                           "attention": "k_attn + k_attn_merge", "out_proj": "k_tcgemv", "expert_gate_up": "k_moe_gu1",
+                           "expert_down": "k_moe_down1", "head": "k_tcgemv"}
 
     def profile_step(self, iters: int = 8) -> dict:
         """Per kernel class: mean ms per step, algorithmic bytes per step, launches per step."""

@@ -175,6 +175,22 @@ def run_profile_case(args):
     toks, ms = eng.decode_greedy([toks[-1, 0]], args.steps)
     print(json.dumps({"profile_case": True, "layers": args.profile_case, "steps": args.steps, "ms_per_step": ms / args.steps,
                       "launches_per_step": eng.launches_per_step(), "note": "not a bench value"}), flush=True)
+    if args.timeline:
+        # the step as the CUDA graph runs it: per launch, microseconds on the device global timer relative to the
+        # first launch, and block 0's own progress (SM cycle counter at the sampled clock) at its points 1..7
+        names = {1: "k_tcgemv", 3: "k_delta_step", 5: "k_moe_gu1", 6: "k_moe_down1", 7: "k_attn", 8: "k_attn_merge"}
+        eng.trace_step()
+        t = eng.trace_step().astype(np.int64)
+        ghz = args.timeline_ghz
+        live = t[t[:, 5] > 0]
+        t0 = live[:, 0].min()
+        prev = None
+        print("kernel hint | first block in, last block in, last block out | since previous kernel's end | block 0: us after it came in, at points 1..7")
+        for r in live:
+            s, li, e = (r[0] - t0) / 1e3, (r[7] - t0) / 1e3, (r[4] - t0) / 1e3
+            pts = " ".join(f"{(r[8 + j] - r[8]) / ghz / 1e3:6.2f}" if r[8 + j] > 0 else "     -" for j in range(1, 8))
+            print(f"{names.get(int(r[5]), '?'):13s} {int(r[6]):6d} | {s:7.2f} {li:7.2f} {e:7.2f} | {e - (prev if prev is not None else s):6.2f} | {pts}")
+            prev = e
 
 
 def run_b64(args):
@@ -284,6 +300,34 @@ def run_b64(args):
         dist.destroy_process_group()
 
 
+# DRAM bytes (read + write) per launch from the ncu launch list of the 4-layer full-width case, averaged over the
+# launches of a role in the 40-layer model (30 DeltaNet + 10 attention layers): in_proj = (30 x 26.01 + 10 x 19.77 +
+# 40 x 3.29) / 80 MB, and so on; the per-launch figures are in the file named below.
+NCU_DRAM_SOURCE = "profiles/decode_step_launch_list_4layer_case.md"
+NCU_DRAM_BYTES_PER_LAUNCH = {"in_proj": 13.87e6, "out_proj": 8.76e6, "expert_gate_up": 10.2e6, "expert_down": 6.0e6,
+                             "head": 325.4e6, "delta_step": 2.14e6, "attention": 4.42e6}
+
+
+def graph_timeline(eng, prof):
+    """Per role: microseconds per step inside the CUDA graph (from the end of the previous launch to the end of this
+    one, device global timer) and the GB/s that gives for the role's algorithmic bytes."""
+    role_of = {3: "delta_step", 5: "expert_gate_up", 6: "expert_down", 7: "attention", 8: "attention"}
+    eng.trace_step()
+    t = eng.trace_step().astype(np.int64)
+    acc, prev_end = {}, None
+    for r in t:
+        if r[5] == 0:
+            continue
+        if r[5] == 1:
+            role = "head" if r[6] > 100000 else ("out_proj" if r[6] == eng.d_model else "in_proj")
+        else:
+            role = role_of.get(int(r[5]), "other")
+        acc[role] = acc.get(role, 0.0) + (r[4] - (prev_end if prev_end is not None else r[0])) / 1000.0
+        prev_end = r[4]
+    return {n: {"us_per_step": round(us, 1), "GBps": round(prof[n]["bytes"] / us / 1e3, 1) if n in prof and us > 0 else None}
+            for n, us in acc.items()}
+
+
 def run_ours(args):
     import torch
     import torch.distributed as dist
@@ -354,20 +398,25 @@ def run_ours(args):
         e2e_s = float(t.item())
     e2e = world * K / e2e_s
 
-    # per-kernel times (events around every launch of un-graphed steps) for the roofline object
+    # per-role times for the roofline object: CUDA events around every launch of un-graphed steps (which include the
+    # host's launch gaps), and the device-side timeline of a graph-run step (what the timed loop above executes)
     prof = eng.profile_step(8)
     peak, peak_kind = peaks()
     name = max((n for n in prof if prof[n]["launches"]), key=lambda n: prof[n]["ms"])
     dom = prof[name]
     achieved = dom["bytes"] / (dom["ms"] * 1e-3) / 1e9
     step_gbs = bytes_step / (ms / K * 1e-3) / 1e9
-    roof = {"bound": "hbm", "kernel": name, "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-            "peak_kind": peak_kind, "traffic": None,
+    in_graph = graph_timeline(eng, prof)
+    roof = {"bound": "hbm", "kernel": f"{name} ({E.HybridEngine.KERNELS_SMALL_BATCH[name]})", "achieved": achieved, "peak": peak,
+            "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
+            "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(name), "traffic_source": NCU_DRAM_SOURCE,
             "launches_per_step": dom["launches"], "bytes_per_launch": dom["bytes"] / max(dom["launches"], 1),
             "ms_per_launch": dom["ms"] / max(dom["launches"], 1),
+            "timing": "CUDA events around each launch of 8 un-graphed steps; in_graph = device global timer inside the CUDA graph",
             "whole_step": {"bytes": bytes_step, "achieved": step_gbs, "frac": step_gbs / peak},
             "per_kernel": {n: {"ms_per_step": round(v["ms"], 4), "GBps": round(v["bytes"] / max(v["ms"], 1e-9) / 1e6, 1),
-                               "launches": v["launches"]} for n, v in prof.items()}}
+                               "launches": v["launches"], "kernel": E.HybridEngine.KERNELS_SMALL_BATCH[n]} for n, v in prof.items()},
+            "in_graph": in_graph}
     cb = None
     n_launch = eng.launches_per_step()
     if rank == 0 and world == 1 and not args.no_cpu:
@@ -400,6 +449,9 @@ if __name__ == "__main__":
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--workload", default="auto", choices=["auto", "b1", "b64"],
                     help="b1: batch-1 decode (the default on one GPU); b64: 64 sequences, expert-parallel (the default on several)")
+    ap.add_argument("--timeline", action="store_true",
+                    help="with --profile-case: also print the device-side timeline of one graph-run step (b2_debug_trace_step)")
+    ap.add_argument("--timeline-ghz", type=float, default=1.965, help="SM clock for converting block 0's cycle counts")
     ap.add_argument("--profile-case", type=int, default=0, metavar="LAYERS",
                     help="a short run for profiler captures: the first LAYERS layers at full width, the context "
                          "length set to 4096 without a prompt, no end-to-end or CPU leg; its line is not a bench value")
