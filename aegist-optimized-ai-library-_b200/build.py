@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200moe.so")
 SOURCES = ["engine.cu"]
-HEADERS = ["kernels.cuh", "rowgemv.cuh", "mmagemm.cuh", "mmaexperts.cuh", "digits.cuh", "tcgemv.cuh", "moe1.cuh", "ops.cuh", "noalloc.cuh", "sampler.hpp", "nxfile.hpp", "json.hpp", "sha256.hpp", "../../include/b200moe.h"]
+HEADERS = ["kernels.cuh", "rowgemv.cuh", "mmagemm.cuh", "mmaexperts.cuh", "digits.cuh", "attnmma.cuh", "tcgemv.cuh", "moe1.cuh", "ops.cuh", "noalloc.cuh", "sampler.hpp", "nxfile.hpp", "json.hpp", "sha256.hpp", "../../include/b200moe.h"]
 
 
 def nvcc() -> str:

@@ -99,6 +99,8 @@ static bool g_rowgemv = [] { const char* v = getenv("B2_ROWGEMV"); return !(v &&
 // Tensor-core GEMV (k_tcgemv) for the int8 matrices of small batches (B2_TCGEMV=0 switches back to k_rowgemv).
 // Expert kernels for fewer than 8 tokens (k_moe_gu1 / k_moe_down1; B2_MOE1=0 switches back to the per-pick kernels).
 static bool g_moe1 = [] { const char* v = getenv("B2_MOE1"); return !(v && v[0] == '0'); }();
+// Tensor-core decode attention for a bf16 cache (k_attn_mma; B2_ATTN_MMA=0 switches back to k_attn).
+static bool g_attn_mma = [] { const char* v = getenv("B2_ATTN_MMA"); return !(v && v[0] == '0'); }();
 static bool g_tcgemv = [] { const char* v = getenv("B2_TCGEMV"); return !(v && v[0] == '0'); }();
 constexpr int g_tc_warps = 16;   // compute warps per block
 static int g_gemv_ctas_per_sm = [] { const char* v = getenv("B2_GEMV_CTAS"); return v ? atoi(v) : 2; }();
@@ -164,6 +166,7 @@ struct b2_engine {
     float* ypart = nullptr;                  // [B][TOPK + 1][D]
     unsigned int* d_dcounter = nullptr;      // [B][row blocks of the expert down projection]
     int nsplit = 1, head_grid = 1;
+    int attn_tiles = 1;                      // 64-position tiles a slice of the longest context spans
     uint32_t* h_pin = nullptr;               // pinned staging [B]
     std::vector<int> tap_layers;
     float* tap_buf = nullptr;
@@ -479,6 +482,8 @@ int b2_engine::finish() {
     CU(dalloc(&part_val, (size_t)B * head_grid)); CU(dalloc(&part_idx, (size_t)B * head_grid));
     // attention: enough slices to fill the GPU, but at least 64 positions each at full context
     nsplit = std::max(1, std::min({64, (2 * nsm) / std::max(1, c.KV * B), (cap + 63) / 64}));
+    if (const char* v = getenv("B2_ATTN_SPLITS")) nsplit = std::max(1, std::min(64, atoi(v)));   // for tests: long slices at short contexts
+    attn_tiles = ((cap + nsplit - 1) / nsplit + AM_TILE - 1) / AM_TILE;
     CU(dalloc(&attn_part, (size_t)B * c.KV * nsplit * (c.H / c.KV) * (c.HD + 2)));
     if (B >= 8) {
         xh_tpad = ((int)Bg + MM_TOK - 1) / MM_TOK * MM_TOK;
@@ -789,7 +794,7 @@ static cudaError_t launch_experts_mma(const ExpertArgs& a, int T, const ExpertMm
     return cudaSuccess;
 }
 
-static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaStream_t st, b2_engine* prof = nullptr) {
+static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaStream_t st, int tiles_per_slice, b2_engine* prof = nullptr) {
     const int G = a.H / a.KV;
     const size_t smem = (size_t)WARPS * G * HD * 4;
     dim3 g(a.nsplit, a.KV, B);
@@ -798,6 +803,23 @@ static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaS
         cudaError_t e = opt_in_smem(k_attn<hd, f>, smem);                              \
         if (e != cudaSuccess) return e;                                                \
         launch_k(k_attn<hd, f>, g, THREADS, smem, st, a);                              \
+    }
+    const int hr = a.RD / 2;
+    const bool rope_ok = hr % 32 == 0 || (hr > 0 && hr < 32 && (hr & (hr - 1)) == 0);   // pairs in one lane, or a power of two lanes apart
+    if (!f32 && g_attn_mma && G <= 8 && rope_ok && (HD == 256 || HD == 128 || HD == 64)) {
+        // bf16 cache: both contractions on the tensor cores; two tile buffers when a slice can span several tiles
+        const int nbuf = tiles_per_slice > 1 ? 2 : 1;
+        cudaError_t e;
+#define ATM(hd)                                                                                     \
+    {                                                                                               \
+        e = opt_in_smem(k_attn_mma<hd>, am_smem<hd>(nbuf));                                         \
+        if (e == cudaSuccess) e = launch_k(k_attn_mma<hd>, g, THREADS, am_smem<hd>(nbuf), st, a, nbuf); \
+    }
+        if (HD == 256) ATM(256) else if (HD == 128) ATM(128) else ATM(64)
+#undef ATM
+        if (e != cudaSuccess) return e;
+        launch_k(k_attn_merge, dim3(a.H, B), THREADS, 0, st, a, HD);
+        return cudaSuccess;
     }
     if (HD == 64) { if (f32) ATT(64, true) else ATT(64, false) }
     else if (HD == 128) { if (f32) ATT(128, true) else ATT(128, false) }
@@ -837,7 +859,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             t.page_table = page_table; t.pages_per_seq = pages_per_seq;
             t.H = c.H; t.KV = c.KV; t.RD = c.RD; t.eps = c.eps; t.scale = 1.0f / std::sqrt((float)c.HD);
             t.part = attn_part; t.out = att; t.nsplit = nsplit;
-            cudaError_t e = launch_attn(t, c.HD, kv_f32, B, st);
+            cudaError_t e = launch_attn(t, c.HD, kv_f32, B, st, attn_tiles);
             if (e != cudaSuccess) return fail("attention launch: %s", cudaGetErrorString(e));
             mark(3, st);
             ProjArgs p{};

@@ -1370,6 +1370,10 @@ __global__ void __launch_bounds__(THREADS) k_attn_merge(const AttnArgs a, int HD
     trace_out(a.trace);
 }
 
+}  // namespace b2
+#include "attnmma.cuh"
+namespace b2 {
+
 // ------------------------------------------------------------------------------------------
 // Expert parallelism. Sequences are split over the GPUs (mixers, router, shared expert local), the
 // experts of every layer too (expert e lives on GPU e / (E / world)). Per layer:

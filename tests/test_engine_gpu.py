@@ -314,3 +314,25 @@ def test_batched_decode_grouped_expert_gemm(E, wide_path, batch):
         cur = got.argmax(-1)
         assert (cur == want.argmax(-1)).all() and (nxt == cur).all()
     e.close()
+
+
+@pytest.mark.parametrize("splits", [2, 5])
+def test_bf16_cache_attention_over_several_tiles(E, tiny_path, splits, monkeypatch):
+    """bf16 cache on the tensor-core attention kernel with few, long slices (B2_ATTN_SPLITS): slices of several
+    64-position tiles, the double-buffered path, partial last tiles, two sequences; against the oracle with the
+    same cache rounding for 200 tokens."""
+    monkeypatch.setenv("B2_ATTN_SPLITS", str(splits))
+    rng = np.random.default_rng(40 + splits)
+    ids = rng.integers(0, 32768, (2, 200))
+    e = E.HybridEngine.load(tiny_path, max_context=256, batch=2, kv_dtype=E.KV_BF16)
+    model = O.HybridOracle(O.Brain(tiny_path))
+    cache = model.new_cache(2, 256, kv_dtype="bf16")
+    worst = 0.0
+    for t in range(200):
+        want = model.forward(ids[:, t][:, None], cache)
+        nxt, got = e.feed_batch(ids[:, t])
+        if t % 16 == 0 or t > 190:
+            worst = max(worst, float(np.abs(got - want).max()))
+            assert (got.argmax(-1) == want.argmax(-1)).all()
+    assert worst < TOL, worst
+    e.close()
