@@ -125,12 +125,12 @@ __global__ void __launch_bounds__(THREADS) k_attn_mma(const AttnArgs a, int nbuf
 #pragma unroll
         for (int i = 0; i < DPL; i++) {
             const int d = lane + 32 * i;
-            float other;
+            float other = __shfl_xor_sync(0xffffffffu, v[i], hr & 31);   // hr < 32: only register 0 holds rotated dims
             if (hr >= 32) {
-                const int sh = hr >> 5;                 // the partner is sh registers away, same lane
-                other = d < hr ? (i + sh < DPL ? v[(i + sh) % DPL] : 0.f) : (i - sh >= 0 ? v[(i - sh + DPL) % DPL] : 0.f);
-            } else {
-                other = __shfl_xor_sync(0xffffffffu, v[i], hr);   // only register 0 holds rotated dims
+                const int pi = d < hr ? i + (hr >> 5) : i - (hr >> 5);    // the partner is hr / 32 registers away, same lane
+                other = 0.f;
+#pragma unroll
+                for (int k = 0; k < DPL; k++) other = k == pi ? v[k] : other;
             }
             y[i] = d < hr ? v[i] * c[i] - other * s[i] : (d < a.RD ? v[i] * c[i] + other * s[i] : v[i]);
         }

@@ -578,13 +578,18 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
         MmaArgs m{};
         GemvArgs rest = a;
         rest.nseg = 0;
+        const float* argmax_logits = nullptr;
+        int argmax_rows = 0, argmax_stride = 0;
         for (int i = 0; i < a.nseg; i++) {
             const Seg& g = a.seg[i];
-            const bool i8 = g.kind == SEG_I8 || g.kind == SEG_I8_CONV || g.kind == SEG_I8_SILU || g.kind == SEG_I8_ACC || g.kind == SEG_I8_GATEUP;
+            // the head's rows are multiplied like any int8 matrix; its arg-max runs as a kernel of its own over the logits
+            const bool i8 = g.kind == SEG_I8 || g.kind == SEG_I8_CONV || g.kind == SEG_I8_SILU || g.kind == SEG_I8_ACC || g.kind == SEG_I8_GATEUP ||
+                            (g.kind == SEG_I8_ARGMAX && a.finisher == FIN_ARGMAX);
             if (i8 && m.nseg < 3) {
                 MmaSeg& d = m.seg[m.nseg++];
                 d.w = (const int8_t*)g.w; d.s = g.s; d.w2 = (const int8_t*)g.w2; d.s2 = g.s2; d.out = g.out; d.rows = g.rows;
-                d.kind = g.kind; d.out_stride = g.out_stride;
+                d.kind = g.kind == SEG_I8_ARGMAX ? (int)SEG_I8 : g.kind; d.out_stride = g.out_stride;
+                if (g.kind == SEG_I8_ARGMAX) { argmax_logits = g.out; argmax_rows = g.rows; argmax_stride = g.out_stride; }
                 const int rpb = g.kind == SEG_I8_GATEUP ? MM_ROWS / 2 : MM_ROWS;
                 d.blocks = (g.rows + rpb - 1) / rpb;
                 m.total_blocks += d.blocks;
@@ -603,6 +608,10 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
             e = opt_in_smem(k_mma_i8, smem);
             if (e == cudaSuccess) e = launch_k(k_mma_i8, dim3(m.total_blocks, p.Tpad / MM_TOK), dim3(MM_THREADS), smem, st, m);
             if (e != cudaSuccess) return e;
+            if (argmax_logits) {
+                e = launch_k(k_argmax_rows, dim3(B), dim3(1024), 0, st, argmax_logits, argmax_rows, argmax_stride, a.next_tok, a.pos);
+                if (e != cudaSuccess) return e;
+            }
             if (rest.nseg == 0) return cudaSuccess;
             seal(rest, a.K);
             a = rest;
@@ -983,7 +992,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
         a.x = x; a.norm_w = norm; a.eps = c.eps; a.K = c.D; a.err = d_err;
         a.finisher = FIN_ARGMAX; a.counter = d_counter; a.part_val = part_val; a.part_idx = part_idx;
         a.next_tok = d_next; a.pos = d_pos;
-        launch_gemv(a, B, nsm, st, head_grid);
+        launch_gemv(a, B, nsm, st, head_grid, bc);
         mark(7, st);
         n++;
     }

@@ -1333,6 +1333,13 @@ __global__ void __launch_bounds__(THREADS) k_attn_merge(const AttnArgs a, int HD
     const size_t pstride = HD + 2;
     const float* pb = a.part + (((size_t)b * a.KV + kvh) * a.nsplit) * G * pstride + (size_t)g * pstride;
     const size_t sstride = (size_t)G * pstride;
+    // everything is requested at once (one round trip): this thread's dim of every slice, the gate, and in warp 0
+    // the slices' maxima and sums. A slice that was empty left its old (finite) sums in place; its weight is zero.
+    const int d0 = threadIdx.x;
+    float v[64];
+#pragma unroll
+    for (int s = 0; s < 64; s++) v[s] = (s < a.nsplit && d0 < HD) ? __ldcg(pb + s * sstride + d0) : 0.f;
+    const float gate0 = d0 < HD ? a.qraw[((size_t)b * a.H + head) * 2 * HD + HD + d0] : 0.f;
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x;
         float ms[2], ls[2];
@@ -1340,8 +1347,8 @@ __global__ void __launch_bounds__(THREADS) k_attn_merge(const AttnArgs a, int HD
 #pragma unroll
         for (int u = 0; u < 2; u++) {
             const int s = lane + 32 * u;
-            ms[u] = s < a.nsplit ? pb[s * sstride + HD] : -INFINITY;
-            ls[u] = s < a.nsplit ? pb[s * sstride + HD + 1] : 0.f;
+            ms[u] = s < a.nsplit ? __ldcg(pb + s * sstride + HD) : -INFINITY;
+            ls[u] = s < a.nsplit ? __ldcg(pb + s * sstride + HD + 1) : 0.f;
             mx = fmaxf(mx, ms[u]);
         }
         mx = warp_max(mx);
@@ -1356,14 +1363,16 @@ __global__ void __launch_bounds__(THREADS) k_attn_merge(const AttnArgs a, int HD
         if (lane == 0) s_inv = 1.0f / lsum;
     }
     __syncthreads();
-    for (int d = threadIdx.x; d < HD; d += THREADS) {
-        // all slices are requested at once (one round trip), then summed in slice order
-        float v[64];
+    if (d0 < HD) {
+        float acc = 0.f;                         // slices in order
 #pragma unroll
-        for (int s = 0; s < 64; s++) v[s] = (s < a.nsplit && sc[s] != 0.f) ? pb[s * sstride + d] : 0.f;
+        for (int s = 0; s < 64; s++) acc = fmaf(sc[s] != 0.f ? v[s] : 0.f, sc[s], acc);
+        a.out[(size_t)b * a.H * HD + head * HD + d0] = (acc * s_inv) * sigmoidf_(gate0);
+    }
+    for (int d = d0 + THREADS; d < HD; d += THREADS) {      // HD > 256 only
         float acc = 0.f;
-#pragma unroll
-        for (int s = 0; s < 64; s++) acc = fmaf(v[s], sc[s], acc);
+        for (int s = 0; s < a.nsplit; s++)
+            if (sc[s] != 0.f) acc = fmaf(__ldcg(pb + s * sstride + d), sc[s], acc);
         const float gate = a.qraw[((size_t)b * a.H + head) * 2 * HD + HD + d];
         a.out[(size_t)b * a.H * HD + head * HD + d] = (acc * s_inv) * sigmoidf_(gate);
     }
@@ -1427,6 +1436,45 @@ __global__ void k_ep_combine(const EpArgs a) {
 
 // ------------------------------------------------------------------------------------------
 // Small helpers for the host: fill and copy.
+// next_tok[b] = arg-max of logits[b][0..rows) (the first of equal maxima), pos[b] += 1: the greedy step of a batch
+// whose head ran as a plain matrix product. One block per sequence.
+__global__ void __launch_bounds__(1024) k_argmax_rows(const float* __restrict__ logits, int rows, int stride, int* __restrict__ next_tok,
+                                                      int* __restrict__ pos) {
+    __shared__ float s_v[32];
+    __shared__ int s_i[32];
+    const int b = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    grid_dep_launch();
+    grid_dep_wait();
+    const float* row = logits + (size_t)b * stride;
+    float v = -INFINITY;
+    int ix = 0x7fffffff;
+    for (int i = threadIdx.x; i < rows; i += 1024) {         // ascending i: '>' keeps the first
+        const float t = row[i];
+        if (t > v) { v = t; ix = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, ix, o);
+        if (ov > v || (ov == v && oi < ix)) { v = ov; ix = oi; }
+    }
+    if (lane == 0) { s_v[warp] = v; s_i[warp] = ix; }
+    __syncthreads();
+    if (warp == 0) {
+        v = s_v[lane]; ix = s_i[lane];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, ix, o);
+            if (ov > v || (ov == v && oi < ix)) { v = ov; ix = oi; }
+        }
+        if (lane == 0) {
+            next_tok[b] = ix;
+            if (pos) pos[b] += 1;
+        }
+    }
+}
+
 __global__ void k_fill_i32(int* p, int v, int n) {
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i < n) p[i] = v;

@@ -27,7 +27,7 @@ constexpr int MM_KC = 256;           // K chunk
 constexpr int MM_TOK = 32;           // sequences per pass (64 columns: hi and lo)
 constexpr int MM_PA = 320;           // bytes between weight rows in shared memory
 constexpr int MM_PB = 528;           // bytes between activation columns in shared memory
-constexpr int MM_STAGES = 3;
+constexpr int MM_STAGES = 2;          // two blocks of 4 warps fit an SM (2 x 106 KB); with 3 stages only one did, and it ran slower
 constexpr int MM_STAGE_BYTES = MM_ROWS * MM_PA + 2 * MM_TOK * MM_PB;   // 20480 + 33792
 constexpr int MM_THREADS = 128;
 

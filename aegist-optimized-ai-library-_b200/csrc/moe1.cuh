@@ -298,6 +298,7 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
     const int chunks = half >> 4;
     const int sch = (ngroup * 2 + 15) >> 4;              // 16-byte pieces of a row's scales (ngroup fp16)
     const int scm = sc_mask(ngroup);
+    const int which = lane / sch, ch = lane - which * sch;      // this lane's piece of a row's scales | mins
 #pragma unroll
     for (int it = 0; it < 2 * M1_GU_PAIRS / M1_GU_WARPS; it++) {
         const int rowi = warp + it * M1_GU_WARPS;
@@ -306,9 +307,8 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
         const size_t grow = (size_t)(up * a.I + i0 + s);
         const uint8_t* src = base + grow * half;
         unsigned char* dst = s_rows + (size_t)slot * pitch;
-        for (int ch = lane; ch < chunks; ch += 32) cp_async16(dst + ch * 16, src + (size_t)ch * 16);
+        for (int c = lane; c < chunks; c += 32) cp_async16(dst + c * 16, src + (size_t)c * 16);
         if (lane < 2 * sch) {
-            const int which = lane / sch, ch = lane - which * sch;
             const uint8_t* ssrc = base + (which ? a.off_gu_m : a.off_gu_s) + grow * ngroup * 2;
             uint16_t* srow = s_sc + (size_t)slot * 2 * ngroup;
             if (scm) cp_async16(reinterpret_cast<unsigned char*>(srow + (((which * sch + ch) ^ (slot & scm)) << 3)), ssrc + (size_t)ch * 16);
@@ -452,6 +452,11 @@ __global__ void __launch_bounds__(M1_DOWN_WARPS * 32) k_moe_down1(const Down1Arg
     grid_dep_launch();
     trace_in(a.trace, 6, gridDim.x);
     float y0 = 0.f, y1 = 0.f;             // rows gid and gid + 8 (valid in lanes with tid == 0)
+    // what the final sum needs from global memory is requested by its threads right after the wait, not at the end
+    float cw[8], csg = 0.f, cx = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; k++) cw[k] = 0.f;
+    const bool comb = threadIdx.x < M1_DOWN_ROWS && row0 + threadIdx.x < a.D;
     if (r < a.topk) {
         const int halfk = I >> 2;                        // bytes of codes of this warp's half of a row
         const int pitch = halfk + 16;                    // 8 rows x 16 bytes cover all banks
@@ -462,6 +467,12 @@ __global__ void __launch_bounds__(M1_DOWN_WARPS * 32) k_moe_down1(const Down1Arg
         float* s_as = reinterpret_cast<float*>(s_xq + (size_t)M1_PLANES * (I >> 1));             // [2 gh] scales | [2 gh] sums
         grid_dep_wait();
         trace_pt(a.trace, 1);
+        if (comb) {
+#pragma unroll
+            for (int k = 0; k < 8; k++) cw[k] = k < a.topk ? a.top_w[(size_t)b * a.topk + k] : 0.f;
+            csg = a.shd_w ? a.sg[b] : 0.f;
+            cx = a.xout[(size_t)b * a.D + row0 + threadIdx.x];
+        }
         const size_t pick = (size_t)b * a.topk + r;
         const uint8_t* base = a.top_ptr[pick];
         if (base != nullptr) {
@@ -585,12 +596,14 @@ __global__ void __launch_bounds__(M1_DOWN_WARPS * 32) k_moe_down1(const Down1Arg
     __syncthreads();
     trace_pt(a.trace, 3);
     // x[o] += sum_r w_r * y_r[o] + sigmoid(shared gate) * y_shared[o], picks in rank order
-    if (threadIdx.x < M1_DOWN_ROWS && row0 + threadIdx.x < a.D) {
+    if (comb) {
         const int o = threadIdx.x;
         float y = 0.f;
-        for (int k = 0; k < a.topk; k++) y = fmaf(a.top_w[(size_t)b * a.topk + k], s_y[2 * k][o] + s_y[2 * k + 1][o], y);
-        if (a.shd_w) y = fmaf(a.sg[b], s_y[2 * a.topk][o] + s_y[2 * a.topk + 1][o], y);
-        a.xout[(size_t)b * a.D + row0 + o] += y;
+#pragma unroll
+        for (int k = 0; k < 8; k++)
+            if (k < a.topk) y = fmaf(cw[k], s_y[2 * k][o] + s_y[2 * k + 1][o], y);
+        if (a.shd_w) y = fmaf(csg, s_y[2 * a.topk][o] + s_y[2 * a.topk + 1][o], y);
+        a.xout[(size_t)b * a.D + row0 + o] = cx + y;
     }
     trace_out(a.trace);
 }
