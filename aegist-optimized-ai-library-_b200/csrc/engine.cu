@@ -580,14 +580,19 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
         rest.nseg = 0;
         const float* argmax_logits = nullptr;
         int argmax_rows = 0, argmax_stride = 0;
+        bool topk_moved = false;
         for (int i = 0; i < a.nseg; i++) {
             const Seg& g = a.seg[i];
             // the head's rows are multiplied like any int8 matrix; its arg-max runs as a kernel of its own over the logits
             const bool i8 = g.kind == SEG_I8 || g.kind == SEG_I8_CONV || g.kind == SEG_I8_SILU || g.kind == SEG_I8_ACC || g.kind == SEG_I8_GATEUP ||
-                            (g.kind == SEG_I8_ARGMAX && a.finisher == FIN_ARGMAX);
-            if (i8 && m.nseg < 3) {
+                            (g.kind == SEG_I8_ARGMAX && a.finisher == FIN_ARGMAX) ||
+                            // bf16 rows (router, DeltaNet a/b, shared gate) are widened to fp16 in registers; the router's
+                            // top-8 then runs as a launch of its own
+                            ((g.kind == SEG_BF_SIGMOID || g.kind == SEG_BF_DECAY || g.kind == SEG_BF) && a.K % (MM_KC / 2) == 0);
+            if (i8 && m.nseg < 4) {
+                if (g.kind == SEG_BF && a.finisher == FIN_TOPK && i == 0) topk_moved = true;
                 MmaSeg& d = m.seg[m.nseg++];
-                d.w = (const int8_t*)g.w; d.s = g.s; d.w2 = (const int8_t*)g.w2; d.s2 = g.s2; d.out = g.out; d.rows = g.rows;
+                d.w = (const int8_t*)g.w; d.s = g.s; d.w2 = (const int8_t*)g.w2; d.s2 = g.s2; d.out = g.out; d.rows = g.rows; d.bias = g.bias;
                 d.kind = g.kind == SEG_I8_ARGMAX ? (int)SEG_I8 : g.kind; d.out_stride = g.out_stride;
                 if (g.kind == SEG_I8_ARGMAX) { argmax_logits = g.out; argmax_rows = g.rows; argmax_stride = g.out_stride; }
                 const int rpb = g.kind == SEG_I8_GATEUP ? MM_ROWS / 2 : MM_ROWS;
@@ -603,7 +608,7 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
             p.K = a.K; p.T = B; p.out = bc->xh; p.Tpad = (B + MM_TOK - 1) / MM_TOK * MM_TOK;
             e = launch_k(k_prep_x, dim3(p.Tpad), dim3(256), 0, st, p);
             if (e != cudaSuccess) return e;
-            m.xh = bc->xh; m.K = a.K; m.T = B; m.conv_w = a.conv_w; m.conv_state = a.conv_state;
+            m.xh = bc->xh; m.K = a.K; m.T = B; m.conv_w = a.conv_w; m.conv_state = a.conv_state; m.a_log = a.a_log; m.dt_bias = a.dt_bias;
             const size_t smem = (size_t)MM_STAGES * MM_STAGE_BYTES;
             e = opt_in_smem(k_mma_i8, smem);
             if (e == cudaSuccess) e = launch_k(k_mma_i8, dim3(m.total_blocks, p.Tpad / MM_TOK), dim3(MM_THREADS), smem, st, m);
@@ -611,6 +616,12 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
             if (argmax_logits) {
                 e = launch_k(k_argmax_rows, dim3(B), dim3(1024), 0, st, argmax_logits, argmax_rows, argmax_stride, a.next_tok, a.pos);
                 if (e != cudaSuccess) return e;
+            }
+            if (topk_moved) {
+                e = launch_k(k_router_topk, dim3((B + 7) / 8), dim3(256), 0, st, (const float*)a.seg[0].out, a.seg[0].out_stride, a.E, a.topk,
+                             a.top_idx, a.top_w, B);
+                if (e != cudaSuccess) return e;
+                rest.finisher = FIN_NONE;
             }
             if (rest.nseg == 0) return cudaSuccess;
             seal(rest, a.K);

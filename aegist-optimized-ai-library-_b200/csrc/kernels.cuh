@@ -1393,6 +1393,7 @@ namespace b2 {
 //   k_ep_combine  x[b] += sum_r w_r * ypart_from_owner(e_r)[b][r] + shared, picks in rank order: the
 //                 same sums in the same order as on one GPU, so the result is bit-identical.
 struct EpArgs {
+    unsigned long long* trace;   // step timeline slot of this launch, or null
     const float* x;        // [B][D]
     const int* top_idx;    // [B][topk]
     const float* top_w;    // [B][topk]
@@ -1419,6 +1420,7 @@ __global__ void k_ep_pack(const EpArgs a) {
 __global__ void k_ep_combine(const EpArgs a) {
     const int b = blockIdx.y;
     grid_dep_launch();
+    trace_in(a.trace, 13, gridDim.x);
     grid_dep_wait();
     const int per = a.E / a.world;
     const size_t blk = (size_t)a.B * (a.topk + 1) * a.D;      // one GPU's block
@@ -1432,6 +1434,7 @@ __global__ void k_ep_combine(const EpArgs a) {
         if (a.has_shared) y = fmaf(a.sg[b], a.recv_y[a.rank * blk + ((size_t)b * (a.topk + 1) + a.topk) * a.D + o], y);
         a.xout[(size_t)b * a.D + o] += y;
     }
+    trace_out(a.trace);
 }
 
 // ------------------------------------------------------------------------------------------

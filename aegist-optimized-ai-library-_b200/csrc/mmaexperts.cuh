@@ -34,6 +34,7 @@ struct ChunkTable {
 };
 
 struct GroupArgs {
+    unsigned long long* trace;   // step timeline slot of this launch, or null
     const int* top_idx;           // [T][idx_stride]
     int idx_stride, T, topk, E;
     const uint8_t* const* eptr;   // only experts resident here are grouped
@@ -46,6 +47,7 @@ __global__ void __launch_bounds__(1024) k_group_picks(const GroupArgs a) {
     __shared__ int s_e[GQ_MAXP];
     __shared__ int s_cnt[256], s_off[256];
     grid_dep_launch();
+    trace_in(a.trace, 11, gridDim.x);
     grid_dep_wait();
     const int P = a.T * a.topk;
     for (int e = threadIdx.x; e < 256; e += blockDim.x) s_cnt[e] = 0;
@@ -85,6 +87,7 @@ __global__ void __launch_bounds__(1024) k_group_picks(const GroupArgs a) {
         for (int q = 0; q < p; q++) pos += (s_e[q] == e);
         a.list[s_off[e] + pos] = p;
     }
+    trace_out(a.trace);
 }
 
 constexpr int Q4_ROWS = 64;                 // weight rows per tile (16 per warp); a pair tile = 32 gate + 32 up
@@ -95,6 +98,7 @@ constexpr int Q4_STAGES = 3;
 __host__ __device__ constexpr int q4_stage_bytes(int NT) { return Q4_STAGE_A + Q4_STAGE_S + 16 * NT * MM_PB; }   // 19712 (NT 1), 45056 (NT 4)
 
 struct Q4Args {
+    unsigned long long* trace;   // step timeline slot of this launch, or null
     const uint8_t* const* eptr;
     const int* list;
     ChunkTable chunks;
@@ -144,9 +148,10 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_q4(const Q4Args a) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int gid = lane >> 2, tid = lane & 3;
     grid_dep_launch();
+    trace_in(a.trace, 12, gridDim.x * 1000 + NT);
     grid_dep_wait();
     const int chunk = blockIdx.y;
-    if (chunk >= *a.chunks.count) return;
+    if (chunk >= *a.chunks.count) { trace_out(a.trace); return; }
     const int e = a.chunks.expert[chunk];
     const int n = min(a.chunks.n[chunk], NCOL);
     const uint8_t* base = a.eptr[e];
@@ -289,6 +294,7 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_q4(const Q4Args a) {
         rt++;
     }
     cp_async_wait<0>();
+    trace_out(a.trace);
 }
 
 }  // namespace b2

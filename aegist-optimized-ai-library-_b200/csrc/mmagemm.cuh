@@ -32,6 +32,7 @@ constexpr int MM_STAGE_BYTES = MM_ROWS * MM_PA + 2 * MM_TOK * MM_PB;   // 20480 
 constexpr int MM_THREADS = 128;
 
 struct PrepArgs {
+    unsigned long long* trace;   // step timeline slot of this launch, or null
     const float* x;          // [T][x_stride]
     int x_stride;
     const uint16_t* norm_w;  // ZNorm weight [K] or null
@@ -52,11 +53,13 @@ __global__ void __launch_bounds__(256) k_prep_x(const PrepArgs a) {
     __shared__ float vs[4096];
     const int t = blockIdx.x;
     grid_dep_launch();
+    trace_in(a.trace, 9, gridDim.x);
     grid_dep_wait();
     __half* hi = a.out + (size_t)t * 2 * a.K;
     __half* lo = hi + a.K;
     if (t >= a.T) {
         for (int k = threadIdx.x; k < a.K; k += 256) { hi[k] = __float2half(0.f); lo[k] = __float2half(0.f); }
+        trace_out(a.trace);
         return;
     }
     const float* x = a.x + (size_t)t * a.x_stride;
@@ -85,6 +88,7 @@ __global__ void __launch_bounds__(256) k_prep_x(const PrepArgs a) {
                 a.xsum[(size_t)t * (a.K / 64) + g] = s;
             }
         }
+        trace_out(a.trace);
         return;
     }
     float r = 1.0f;
@@ -111,27 +115,44 @@ __global__ void __launch_bounds__(256) k_prep_x(const PrepArgs a) {
             a.xsum[(size_t)t * (a.K / 64) + g] = s;
         }
     }
+    trace_out(a.trace);
 }
 
 struct MmaSeg {
-    const int8_t* w;         // [rows][K]
+    const int8_t* w;         // [rows][K] int8, or [rows][K] bf16 for the SEG_BF* kinds
     const uint16_t* s;       // bf16 scale per row
     const int8_t* w2;        // SEG_I8_GATEUP: the up matrix
     const uint16_t* s2;
+    const float* bias;       // SEG_BF only, may be null
     float* out;              // [T][out_stride]
     int rows, kind, out_stride;
     int blocks;              // ceil(rows / MM_ROWS), filled by the host
 };
 
 struct MmaArgs {
-    MmaSeg seg[3];
+    unsigned long long* trace;   // step timeline slot of this launch, or null
+    MmaSeg seg[4];
     int nseg, total_blocks;
     const __half* xh;        // [Tpad][2][K]
     int K, T;
     // SEG_I8_CONV
     const uint16_t* conv_w;
     float* conv_state;       // [T][C][3]
+    // SEG_BF_DECAY
+    const uint16_t* a_log;
+    const uint16_t* dt_bias;
 };
+
+// eight bf16 (a 16-byte piece of a row) -> four half2. Exact for magnitudes from 2^-14 up; smaller ones round to
+// the fp16 subnormal grid (absolute error below 2^-25).
+__device__ __forceinline__ void bf16x8_to_h2x4(const uint4& w, uint32_t (&h)[4]) {
+    const uint32_t v[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const __half2 t = __floats2half2_rn(__uint_as_float(v[i] << 16), __uint_as_float(v[i] & 0xFFFF0000u));
+        h[i] = *reinterpret_cast<const uint32_t*>(&t);
+    }
+}
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
@@ -164,15 +185,18 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_i8(const MmaArgs a) {
     const int gid = lane >> 2, tid = lane & 3;
     const int t0 = blockIdx.y * MM_TOK;
     grid_dep_launch();
+    trace_in(a.trace, 10, gridDim.x);
     // which matrix and which 64 rows
     int s = 0, blk = blockIdx.x;
     while (s + 1 < a.nseg && blk >= a.seg[s].blocks) { blk -= a.seg[s].blocks; s++; }
     const MmaSeg sg = a.seg[s];
     const bool pair = sg.kind == SEG_I8_GATEUP;
+    const bool isbf = sg.kind == SEG_BF || sg.kind == SEG_BF_SIGMOID || sg.kind == SEG_BF_DECAY;
+    const int kcw = isbf ? MM_KC / 2 : MM_KC;         // weights per K chunk: a chunk is 256 bytes of a row either way
     // a pair block covers 32 gate rows and the same 32 up rows: warps 0,1 gate, warps 2,3 up
     const int rows_per_block = pair ? MM_ROWS / 2 : MM_ROWS;
     const int row0 = blk * rows_per_block;
-    const int nk = a.K / MM_KC;
+    const int nk = a.K / kcw;
 
     auto load_stage = [&](int kc, int st) {
         unsigned char* sa = mm_smem + (size_t)st * MM_STAGE_BYTES;
@@ -185,13 +209,14 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_i8(const MmaArgs a) {
             if (pair) { base = r < 32 ? sg.w : sg.w2; grow = row0 + (r & 31); }
             else { base = sg.w; grow = row0 + r; }
             grow = min(grow, sg.rows - 1);                    // rows past the end repeat the last row (never stored)
-            cp_async16(sa + r * MM_PA + c * 16, base + (size_t)grow * a.K + (size_t)kc * MM_KC + c * 16);
+            cp_async16(sa + r * MM_PA + c * 16, base + ((size_t)grow * a.K + (size_t)kc * kcw) * (isbf ? 2 : 1) + c * 16);
         }
         // activations: 64 columns (32 sequences x hi, lo) x 256 halves = 2048 pieces
-        for (int p = threadIdx.x; p < 2 * MM_TOK * (MM_KC / 8); p += MM_THREADS) {
-            const int col = p / (MM_KC / 8), c = p % (MM_KC / 8);
+        const int pcs = kcw / 8;                                               // 16-byte pieces per column
+        for (int p = threadIdx.x; p < 2 * MM_TOK * pcs; p += MM_THREADS) {
+            const int col = p / pcs, c = p - col * pcs;
             const int tok = t0 + (col & (MM_TOK - 1)), part = col >> 5;        // columns 0..31 hi, 32..63 lo
-            cp_async16(sb + col * MM_PB + c * 16, a.xh + ((size_t)tok * 2 + part) * a.K + (size_t)kc * MM_KC + c * 8);
+            cp_async16(sb + col * MM_PB + c * 16, a.xh + ((size_t)tok * 2 + part) * a.K + (size_t)kc * kcw + c * 8);
         }
         cp_async_commit();
     };
@@ -214,6 +239,25 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_i8(const MmaArgs a) {
         const unsigned char* sb = sa + MM_ROWS * MM_PA;
         const unsigned char* ar0 = sa + (warp * 16 + gid) * MM_PA;
         const unsigned char* ar1 = ar0 + 8 * MM_PA;
+        if (isbf) {
+            // bf16 rows: 64 bytes of a row are 32 weights = two k16 steps; a lane takes 8 consecutive weights
+#pragma unroll
+            for (int sbk = 0; sbk < MM_KC / 64; sbk++) {
+                const uint4 w0 = *reinterpret_cast<const uint4*>(ar0 + sbk * 64 + tid * 16);
+                const uint4 w1 = *reinterpret_cast<const uint4*>(ar1 + sbk * 64 + tid * 16);
+                uint32_t h0[4], h1[4];
+                bf16x8_to_h2x4(w0, h0);
+                bf16x8_to_h2x4(w1, h1);
+                const uint32_t afa[4] = {h0[0], h1[0], h0[1], h1[1]}, afb[4] = {h0[2], h1[2], h0[3], h1[3]};
+#pragma unroll
+                for (int nt = 0; nt < 8; nt++) {
+                    const uint4 x0 = *reinterpret_cast<const uint4*>(sb + (nt * 8 + gid) * MM_PB + sbk * 64 + tid * 16);
+                    mma16816(acc[nt], afa, x0.x, x0.y);
+                    mma16816(acc[nt], afb, x0.z, x0.w);
+                }
+            }
+            continue;
+        }
 #pragma unroll
         for (int sbk = 0; sbk < MM_KC / 64; sbk++) {
             // this thread's 16 bytes of rows gid and gid + 8 cover four k16 steps
@@ -254,7 +298,7 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_i8(const MmaArgs a) {
             }
     }
     if (pair) __syncthreads();
-    if (pair && warp < 2) return;
+    if (pair && warp < 2) { trace_out(a.trace); return; }
 #pragma unroll
     for (int nt = 0; nt < 4; nt++) {
 #pragma unroll
@@ -283,10 +327,14 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_i8(const MmaArgs a) {
                 stt[0] = s1; stt[1] = s2; stt[2] = raw;
                 out[row] = siluf_(y);
             } break;
+            case SEG_BF: out[row] = dot + (sg.bias ? sg.bias[row] : 0.f); break;
+            case SEG_BF_SIGMOID: out[row] = sigmoidf_(dot); break;
+            case SEG_BF_DECAY: out[row] = -expf(bf(a.a_log[row])) * softplusf_(dot + bf(a.dt_bias[row])); break;
             default: break;
             }
         }
     }
+    trace_out(a.trace);
 }
 
 }  // namespace b2

@@ -98,6 +98,20 @@ __device__ __forceinline__ void router_topk_lanes(const float* __restrict__ logi
     my_w = myv / tsum;
 }
 
+// top-k of every sequence's router logits, one warp per sequence (batched decode, after the logits came from a
+// matrix product). grid (ceil(B / 8)), 256 threads.
+__global__ void __launch_bounds__(256) k_router_topk(const float* __restrict__ logits, int stride, int E, int topk, int* __restrict__ top_idx,
+                                                     float* __restrict__ top_w, int B) {
+    const int lane = threadIdx.x & 31, b = blockIdx.x * 8 + (threadIdx.x >> 5);
+    grid_dep_launch();
+    grid_dep_wait();
+    if (b >= B) return;
+    int e;
+    float w;
+    router_topk_lanes(logits + (size_t)b * stride, E, topk, lane, e, w);
+    if (lane < topk) { top_idx[(size_t)b * topk + lane] = e; top_w[(size_t)b * topk + lane] = w; }
+}
+
 struct Gu1Args {
     unsigned long long* trace;
     const float* logits;          // [B][E] router logits (bias included)
