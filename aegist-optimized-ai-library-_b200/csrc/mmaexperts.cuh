@@ -42,50 +42,62 @@ struct GroupArgs {
     ChunkTable small, big;
 };
 
-// one block of 1024 threads
+// one block of 1024 threads. The order of the picks inside an expert's list is whatever the shared-memory atomics
+// give: every pick's result goes to its own place in ypart, so the order changes nothing downstream.
 __global__ void __launch_bounds__(1024) k_group_picks(const GroupArgs a) {
     __shared__ int s_e[GQ_MAXP];
-    __shared__ int s_cnt[256], s_off[256];
+    __shared__ int s_cnt[256], s_off[256], s_fill[256];
+    __shared__ int s_w[3][8];
     grid_dep_launch();
     trace_in(a.trace, 11, gridDim.x);
     grid_dep_wait();
     const int P = a.T * a.topk;
-    for (int e = threadIdx.x; e < 256; e += blockDim.x) s_cnt[e] = 0;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (threadIdx.x < 256) { s_cnt[threadIdx.x] = 0; s_fill[threadIdx.x] = 0; }
+    __syncthreads();
     for (int p = threadIdx.x; p < P; p += blockDim.x) {
         const int e = a.top_idx[(size_t)(p / a.topk) * a.idx_stride + p % a.topk];
-        s_e[p] = (e >= 0 && e < a.E && a.eptr[e] != nullptr) ? e : -1;
+        const int ok = (e >= 0 && e < a.E && a.eptr[e] != nullptr) ? e : -1;
+        s_e[p] = ok;
+        if (ok >= 0) atomicAdd(&s_cnt[ok], 1);
     }
     __syncthreads();
-    for (int p = threadIdx.x; p < P; p += blockDim.x)
-        if (s_e[p] >= 0) atomicAdd(&s_cnt[s_e[p]], 1);
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        int off = 0, cs = 0, cb = 0;
-        for (int e = 0; e < a.E; e++) {
-            s_off[e] = off;
-            int s0 = 0, left = s_cnt[e];
-            while (left > GQ_SMALL && cb < a.big.cap) {
-                const int n = min(GQ_BIG, left);
-                a.big.expert[cb] = e; a.big.start[cb] = off + s0; a.big.n[cb] = n;
-                cb++; s0 += n; left -= n;
-            }
-            if (left > 0 && left <= GQ_SMALL && cs < a.small.cap) {
-                a.small.expert[cs] = e; a.small.start[cs] = off + s0; a.small.n[cs] = left;
-                cs++;
-            }
-            off += s_cnt[e];
+    // per expert: big chunks of up to 32 picks while more than 8 are left, then one small chunk of the rest;
+    // exclusive prefix sums over the experts of the pick counts and of the two chunk counts (256 threads)
+    int cnt = 0, nb = 0, ns = 0, x0 = 0, x1 = 0, x2 = 0;
+    if (threadIdx.x < 256) {
+        const int e = threadIdx.x;
+        cnt = e < a.E ? s_cnt[e] : 0;
+        nb = cnt > GQ_SMALL ? (cnt - GQ_SMALL + GQ_BIG - 1) / GQ_BIG : 0;
+        ns = (cnt - nb * GQ_BIG) > 0 ? 1 : 0;
+        x0 = cnt; x1 = nb; x2 = ns;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int y0 = __shfl_up_sync(0xffffffffu, x0, o), y1 = __shfl_up_sync(0xffffffffu, x1, o), y2 = __shfl_up_sync(0xffffffffu, x2, o);
+            if (lane >= o) { x0 += y0; x1 += y1; x2 += y2; }
         }
-        *a.small.count = cs;
-        *a.big.count = cb;
+        if (lane == 31) { s_w[0][warp] = x0; s_w[1][warp] = x1; s_w[2][warp] = x2; }
     }
     __syncthreads();
-    // position of a pick inside its expert's list = number of earlier picks of the same expert
+    if (threadIdx.x < 256) {
+        const int e = threadIdx.x;
+        int b0 = 0, b1 = 0, b2 = 0;
+        for (int w = 0; w < warp; w++) { b0 += s_w[0][w]; b1 += s_w[1][w]; b2 += s_w[2][w]; }
+        const int off = b0 + x0 - cnt, cb0 = b1 + x1 - nb, cs0 = b2 + x2 - ns;
+        s_off[e] = off;
+        int s0 = 0, left = cnt;
+        for (int k = 0; k < nb; k++) {
+            const int n = min(GQ_BIG, left);
+            if (cb0 + k < a.big.cap) { a.big.expert[cb0 + k] = e; a.big.start[cb0 + k] = off + s0; a.big.n[cb0 + k] = n; }
+            s0 += n; left -= n;
+        }
+        if (ns && cs0 < a.small.cap) { a.small.expert[cs0] = e; a.small.start[cs0] = off + s0; a.small.n[cs0] = left; }
+        if (e == 255) { *a.big.count = min(cb0 + nb, a.big.cap); *a.small.count = min(cs0 + ns, a.small.cap); }
+    }
+    __syncthreads();
     for (int p = threadIdx.x; p < P; p += blockDim.x) {
         const int e = s_e[p];
-        if (e < 0) continue;
-        int pos = 0;
-        for (int q = 0; q < p; q++) pos += (s_e[q] == e);
-        a.list[s_off[e] + pos] = p;
+        if (e >= 0) a.list[s_off[e] + atomicAdd(&s_fill[e], 1)] = p;
     }
     trace_out(a.trace);
 }
@@ -94,7 +106,7 @@ constexpr int Q4_ROWS = 64;                 // weight rows per tile (16 per warp
 constexpr int Q4_PA = 160;                  // bytes between code rows in shared memory (128 used)
 constexpr int Q4_STAGE_A = Q4_ROWS * Q4_PA; // 10240
 constexpr int Q4_STAGE_S = Q4_ROWS * 16;    // per row: 4 groups x (scale, min) f16
-constexpr int Q4_STAGES = 3;
+constexpr int Q4_STAGES = 2;                // two blocks of the 32-pick variant fit an SM
 __host__ __device__ constexpr int q4_stage_bytes(int NT) { return Q4_STAGE_A + Q4_STAGE_S + 16 * NT * MM_PB; }   // 19712 (NT 1), 45056 (NT 4)
 
 struct Q4Args {
