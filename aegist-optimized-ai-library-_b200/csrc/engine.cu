@@ -763,17 +763,20 @@ static void chunk_tables(const ExpertMmaCtx& m, ChunkTable& small, ChunkTable& b
     p += 3 * m.cap_big;
     small.count = p; big.count = p + 1;
 }
-static cudaError_t launch_q4(Q4Args q, const ChunkTable& small, const ChunkTable& big, int row_blocks, cudaStream_t st) {
+static cudaError_t launch_q4(Q4Args q, const ChunkTable& small, const ChunkTable& big, int row_blocks, int nsm, cudaStream_t st) {
     cudaError_t e;
     const size_t sm1 = (size_t)Q4_STAGES * q4_stage_bytes(1), sm4 = (size_t)Q4_STAGES * q4_stage_bytes(4);
     if ((e = opt_in_smem(k_mma_q4<1>, sm1)) != cudaSuccess) return e;
     if ((e = opt_in_smem(k_mma_q4<4>, sm4)) != cudaSuccess) return e;
+    // blocks per row block: what fills the SMs at the occupancy each variant reaches (5 and 2 blocks per SM)
+    const int gs = std::max(1, std::min(small.cap, (5 * nsm + row_blocks - 1) / row_blocks));
+    const int gb = std::max(1, std::min(big.cap, (2 * nsm + row_blocks - 1) / row_blocks));
     q.chunks = small;
-    if ((e = launch_k(k_mma_q4<1>, dim3(row_blocks, small.cap), dim3(MM_THREADS), sm1, st, q)) != cudaSuccess) return e;
+    if ((e = launch_k(k_mma_q4<1>, dim3(row_blocks, gs), dim3(MM_THREADS), sm1, st, q)) != cudaSuccess) return e;
     q.chunks = big;
-    return launch_k(k_mma_q4<4>, dim3(row_blocks, big.cap), dim3(MM_THREADS), sm4, st, q);
+    return launch_k(k_mma_q4<4>, dim3(row_blocks, gb), dim3(MM_THREADS), sm4, st, q);
 }
-static cudaError_t launch_experts_mma(const ExpertArgs& a, int T, const ExpertMmaCtx& m, cudaStream_t st, b2_engine* prof) {
+static cudaError_t launch_experts_mma(const ExpertArgs& a, int T, const ExpertMmaCtx& m, int nsm, cudaStream_t st, b2_engine* prof) {
     cudaError_t e;
     const int P = T * a.topk;
     GroupArgs g{};
@@ -789,7 +792,7 @@ static cudaError_t launch_experts_mma(const ExpertArgs& a, int T, const ExpertMm
     q.eptr = a.eptr; q.list = g.list; q.topk = a.topk;
     q.pair = 1; q.rows = a.I; q.K = a.D; q.off_q = 0; q.off_s = a.off_gu_s; q.off_m = a.off_gu_m; q.up_row0 = a.I;
     q.xh = m.xh; q.xsum = m.xsum_tok; q.by_pick = 0; q.out = a.act; q.row_tiles = 1;
-    if ((e = launch_q4(q, g.small, g.big, (a.I + 31) / 32, st)) != cudaSuccess) return e;
+    if ((e = launch_q4(q, g.small, g.big, (a.I + 31) / 32, nsm, st)) != cudaSuccess) return e;
     if (prof) prof->mark(5, st);
     PrepArgs p2{};
     p2.x = a.act; p2.x_stride = a.I; p2.K = a.I; p2.T = P; p2.Tpad = P; p2.out = m.acth; p2.xsum = m.xsum_act; p2.perm8 = 1;
@@ -797,7 +800,7 @@ static cudaError_t launch_experts_mma(const ExpertArgs& a, int T, const ExpertMm
     q.pair = 0; q.rows = a.D; q.K = a.I; q.off_q = a.off_dn_q; q.off_s = a.off_dn_s; q.off_m = a.off_dn_m; q.up_row0 = 0;
     q.xh = m.acth; q.xsum = m.xsum_act; q.by_pick = 1; q.out = a.ypart;
     q.row_tiles = std::max(1, std::min(4, 2048 / a.I));      // keep about 8 ring steps per block
-    if ((e = launch_q4(q, g.small, g.big, (a.D + Q4_ROWS * q.row_tiles - 1) / (Q4_ROWS * q.row_tiles), st)) != cudaSuccess) return e;
+    if ((e = launch_q4(q, g.small, g.big, (a.D + Q4_ROWS * q.row_tiles - 1) / (Q4_ROWS * q.row_tiles), nsm, st)) != cudaSuccess) return e;
     // shared expert down for this GPU's own tokens: int8 [D][SH] on the dense tensor-core kernel
     PrepArgs p3{};
     p3.x = a.sh_act; p3.x_stride = a.SH; p3.K = a.SH; p3.T = a.nlocal; p3.Tpad = (a.nlocal + MM_TOK - 1) / MM_TOK * MM_TOK; p3.out = m.xh;
@@ -961,7 +964,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
                 x2.x = x; x2.x_stride = c.D; x2.top_idx = a.top_idx; x2.top_w = a.top_w; x2.idx_stride = c.TOPK;
                 x2.combine = 1; x2.local0 = 0; x2.nlocal = B;
                 if (grouped) {
-                    cudaError_t ce = launch_experts_mma(x2, B, mctx, st, this);
+                    cudaError_t ce = launch_experts_mma(x2, B, mctx, nsm, st, this);
                     if (ce != cudaSuccess) return fail("grouped expert GEMM: %s", cudaGetErrorString(ce));
                     EpArgs ep{};
                     ep.x = x; ep.top_idx = a.top_idx; ep.top_w = a.top_w; ep.recv_y = ypart; ep.sg = sgate; ep.xout = x;
@@ -980,7 +983,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
                 x2.x = rec_all; x2.x_stride = rw; x2.top_idx = (const int*)(rec_all + c.D); x2.top_w = rec_all + c.D + c.TOPK; x2.idx_stride = rw;
                 x2.combine = 0; x2.local0 = ep_rank * B; x2.nlocal = B;
                 if (grouped) {
-                    cudaError_t ce = launch_experts_mma(x2, Tg, mctx, st, this);
+                    cudaError_t ce = launch_experts_mma(x2, Tg, mctx, nsm, st, this);
                     if (ce != cudaSuccess) return fail("grouped expert GEMM: %s", cudaGetErrorString(ce));
                 } else {
                     launch_experts(x2, Tg, nsm, st, this);

@@ -148,7 +148,7 @@ __device__ __forceinline__ void q4x8_to_h2x4(uint32_t w, uint32_t& p0, uint32_t&
     p3 = *reinterpret_cast<uint32_t*>(&hd);
 }
 
-// grid (row blocks, chunk capacity); NT = 8-pick tiles per chunk (1: small table, 4: big table)
+// grid (row blocks, blocks per row block); NT = 8-pick tiles per chunk (1: small table, 4: big table)
 template <int NT>
 __global__ void __launch_bounds__(MM_THREADS) k_mma_q4(const Q4Args a) {
     constexpr int STAGE = q4_stage_bytes(NT);
@@ -162,8 +162,10 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_q4(const Q4Args a) {
     grid_dep_launch();
     trace_in(a.trace, 12, gridDim.x * 1000 + NT);
     grid_dep_wait();
-    const int chunk = blockIdx.y;
-    if (chunk >= *a.chunks.count) { trace_out(a.trace); return; }
+    // a block walks the chunks blockIdx.y, blockIdx.y + gridDim.y, ...: the grid is sized for the SMs, not for the
+    // largest possible number of chunks
+    const int nchunk = *a.chunks.count;
+    for (int chunk = blockIdx.y; chunk < nchunk; chunk += gridDim.y) {
     const int e = a.chunks.expert[chunk];
     const int n = min(a.chunks.n[chunk], NCOL);
     const uint8_t* base = a.eptr[e];
@@ -306,6 +308,8 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_q4(const Q4Args a) {
         rt++;
     }
     cp_async_wait<0>();
+    __syncthreads();                   // the chunk's tables and stages are reused by the next one
+    }
     trace_out(a.trace);
 }
 
