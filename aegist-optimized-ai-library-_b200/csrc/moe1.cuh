@@ -336,61 +336,39 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
     trace_pt(a.trace, 5);
 
     // warp -> (block of 8 pairs, eighth of K); lane (gid, tid) -> rows gid (gate) and gid + 8 (up) of the block,
-    // 16 codes of every 64-code group. Two groups are in flight together: loads, then the mma, then the scaling.
+    // 16 codes of every 64-code group. A warp's ge = ngroup / 8 groups (1, 2, 4 or 8) lie inside one 16-byte piece of
+    // a scale row, so their scales and mins are at consecutive positions from a base computed once.
     const int rb = warp & 3, ke = warp >> 2;
     const int ge = ngroup >> 3;
-    constexpr int GQ = 2;
     float accg[2] = {0.f, 0.f}, accu[2] = {0.f, 0.f};   // planes 2 tid and 2 tid + 1
     float mng = 0.f, mnu = 0.f;
     {
-        const unsigned char* pg = s_rows + (size_t)(rb * 16 + gid) * pitch + tid * 8;
-        const unsigned char* pu = pg + (size_t)8 * pitch;
-        const int slg = rb * 16 + gid, slu = slg + 8;
-        const uint16_t* sg = s_sc + (size_t)slg * 2 * ngroup;
-        const uint16_t* su = s_sc + (size_t)slu * 2 * ngroup;
-        const int8_t* px = s_xq + (size_t)(gid & 3) * XS + tid * 16;
-        const bool colact = gid < M1_PLANES;
-        // a warp's groups lie inside one 8-value piece of a scale row when ge divides 8: positions are base + offset
         const int gf = ke * ge;
-        const bool lin = ge <= 8 && (8 % ge) == 0;
-        const int bgs = sc_pos(ngroup, scm, slg, 0, gf), bgm = sc_pos(ngroup, scm, slg, 1, gf);
-        const int bus = sc_pos(ngroup, scm, slu, 0, gf), bum = sc_pos(ngroup, scm, slu, 1, gf);
-        for (int g0 = ke * ge; g0 < (ke + 1) * ge; g0 += GQ) {
-            const int gend = (ke + 1) * ge;
-            uint2 wg[GQ], wu[GQ];
-            uint4 xb[GQ];
-            float sgv[GQ], suv[GQ], mgv[GQ], muv[GQ], xs[GQ];
-#pragma unroll
-            for (int q = 0; q < GQ; q++) {
-                const int g = min(g0 + q, gend - 1);
-                wg[q] = *reinterpret_cast<const uint2*>(pg + g * 32);
-                wu[q] = *reinterpret_cast<const uint2*>(pu + g * 32);
-                xb[q] = make_uint4(0u, 0u, 0u, 0u);
-                if (colact) xb[q] = *reinterpret_cast<const uint4*>(px + g * 64);
-                const bool live = g0 + q < gend;
-                const int o = g - gf;
-                sgv[q] = live ? h2f(sg[lin ? bgs + o : sc_pos(ngroup, scm, slg, 0, g)]) : 0.f;
-                suv[q] = live ? h2f(su[lin ? bus + o : sc_pos(ngroup, scm, slu, 0, g)]) : 0.f;
-                mgv[q] = live ? h2f(sg[lin ? bgm + o : sc_pos(ngroup, scm, slg, 1, g)]) : 0.f;
-                muv[q] = live ? h2f(su[lin ? bum + o : sc_pos(ngroup, scm, slu, 1, g)]) : 0.f;
-                xs[q] = s_xsum[g];
-            }
-            int t[GQ][4];
-#pragma unroll
-            for (int q = 0; q < GQ; q++) {
-                t[q][0] = t[q][1] = t[q][2] = t[q][3] = 0;
-                imma16832(t[q], wg[q].x & 0x0F0F0F0Fu, wu[q].x & 0x0F0F0F0Fu, (wg[q].x >> 4) & 0x0F0F0F0Fu, (wu[q].x >> 4) & 0x0F0F0F0Fu, xb[q].x, xb[q].y);
-            }
-#pragma unroll
-            for (int q = 0; q < GQ; q++)
-                imma16832(t[q], wg[q].y & 0x0F0F0F0Fu, wu[q].y & 0x0F0F0F0Fu, (wg[q].y >> 4) & 0x0F0F0F0Fu, (wu[q].y >> 4) & 0x0F0F0F0Fu, xb[q].z, xb[q].w);
-#pragma unroll
-            for (int q = 0; q < GQ; q++) {
-                accg[0] = fmaf(sgv[q], small_int_to_float(t[q][0]), accg[0]); accg[1] = fmaf(sgv[q], small_int_to_float(t[q][1]), accg[1]);
-                accu[0] = fmaf(suv[q], small_int_to_float(t[q][2]), accu[0]); accu[1] = fmaf(suv[q], small_int_to_float(t[q][3]), accu[1]);
-                mng = fmaf(mgv[q], xs[q], mng);
-                mnu = fmaf(muv[q], xs[q], mnu);
-            }
+        const int slg = rb * 16 + gid, slu = slg + 8;
+        const unsigned char* pg = s_rows + (size_t)slg * pitch + tid * 8 + gf * 32;
+        const unsigned char* pu = pg + (size_t)8 * pitch;
+        const uint16_t* sgs = s_sc + (size_t)slg * 2 * ngroup + sc_pos(ngroup, scm, slg, 0, gf);
+        const uint16_t* sgm = s_sc + (size_t)slg * 2 * ngroup + sc_pos(ngroup, scm, slg, 1, gf);
+        const uint16_t* sus = s_sc + (size_t)slu * 2 * ngroup + sc_pos(ngroup, scm, slu, 0, gf);
+        const uint16_t* sum_ = s_sc + (size_t)slu * 2 * ngroup + sc_pos(ngroup, scm, slu, 1, gf);
+        const int8_t* px = s_xq + (size_t)(gid & 3) * XS + tid * 16 + gf * 64;
+        const float* pxs = s_xsum + gf;
+        const bool colact = gid < M1_PLANES;
+#pragma unroll 2
+        for (int g = 0; g < ge; g++) {
+            const uint2 wg = *reinterpret_cast<const uint2*>(pg + g * 32);
+            const uint2 wu = *reinterpret_cast<const uint2*>(pu + g * 32);
+            uint4 xb = make_uint4(0u, 0u, 0u, 0u);
+            if (colact) xb = *reinterpret_cast<const uint4*>(px + g * 64);
+            const float sgv = h2f(sgs[g]), suv = h2f(sus[g]), mgv = h2f(sgm[g]), muv = h2f(sum_[g]);
+            const float xs = pxs[g];
+            int t[4] = {0, 0, 0, 0};
+            imma16832(t, wg.x & 0x0F0F0F0Fu, wu.x & 0x0F0F0F0Fu, (wg.x >> 4) & 0x0F0F0F0Fu, (wu.x >> 4) & 0x0F0F0F0Fu, xb.x, xb.y);
+            imma16832(t, wg.y & 0x0F0F0F0Fu, wu.y & 0x0F0F0F0Fu, (wg.y >> 4) & 0x0F0F0F0Fu, (wu.y >> 4) & 0x0F0F0F0Fu, xb.z, xb.w);
+            accg[0] = fmaf(sgv, small_int_to_float(t[0]), accg[0]); accg[1] = fmaf(sgv, small_int_to_float(t[1]), accg[1]);
+            accu[0] = fmaf(suv, small_int_to_float(t[2]), accu[0]); accu[1] = fmaf(suv, small_int_to_float(t[3]), accu[1]);
+            mng = fmaf(mgv, xs, mng);
+            mnu = fmaf(muv, xs, mnu);
         }
     }
     {

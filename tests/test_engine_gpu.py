@@ -336,3 +336,20 @@ def test_bf16_cache_attention_over_several_tiles(E, tiny_path, splits, monkeypat
             assert (got.argmax(-1) == want.argmax(-1)).all()
     assert worst < TOL, worst
     e.close()
+
+
+def test_step_timeline(E, tiny_path):
+    """b2_debug_trace_step: one row per launch of a graph-run step; the kernels that record stamp a first-in time,
+    a last-out time after it, and launches follow one another in time; the step still advances the state."""
+    e = E.HybridEngine.load(tiny_path, max_context=32)
+    e.feed([1, 2, 3])
+    n0 = e.length()
+    t = e.trace_step().astype(np.int64)
+    assert e.length() == n0 + 1
+    assert t.shape == (e.launches_per_step(), 16)
+    live = t[t[:, 5] > 0]
+    assert len(live) >= 4 * 5                       # every per-layer kernel of the 4 layers records
+    assert (live[:, 4] > live[:, 0]).all()          # last block out after first block in
+    assert (np.diff(live[:, 4]) > 0).all()          # kernels end in launch order
+    assert set(live[:, 5]) >= {1, 3, 5, 6, 7, 8}    # GEMV, delta step, expert gate/up, expert down, attention, merge
+    e.close()
