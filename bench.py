@@ -178,7 +178,7 @@ def run_profile_case(args):
     if args.timeline:
         # the step as the CUDA graph runs it: per launch, microseconds on the device global timer relative to the
         # first launch, and block 0's own progress (SM cycle counter at the sampled clock) at its points 1..7
-        names = {1: "k_tcgemv", 3: "k_delta_step", 5: "k_moe_gu1", 6: "k_moe_down1", 7: "k_attn", 8: "k_attn_merge"}
+        names = {1: "k_tcgemv", 3: "k_delta_step", 5: "k_moe_gu1", 6: "k_moe_down1", 7: "k_attn(_mma)", 8: "k_attn_merge"}
         eng.trace_step()
         t = eng.trace_step().astype(np.int64)
         ghz = args.timeline_ghz
@@ -301,11 +301,11 @@ def run_b64(args):
 
 
 # DRAM bytes (read + write) per launch from the ncu launch list of the 4-layer full-width case, averaged over the
-# launches of a role in the 40-layer model (30 DeltaNet + 10 attention layers): in_proj = (30 x 26.01 + 10 x 19.77 +
-# 40 x 3.29) / 80 MB, and so on; the per-launch figures are in the file named below.
+# launches of a role in the 40-layer model (30 DeltaNet + 10 attention layers): in_proj = (30 x 26.59 + 10 x 19.58 +
+# 40 x 3.33) / 80 MB, and so on; the per-launch figures are in the file named below.
 NCU_DRAM_SOURCE = "profiles/decode_step_launch_list_4layer_case.md"
-NCU_DRAM_BYTES_PER_LAUNCH = {"in_proj": 13.87e6, "out_proj": 8.76e6, "expert_gate_up": 10.2e6, "expert_down": 6.0e6,
-                             "head": 325.4e6, "delta_step": 2.14e6, "attention": 4.42e6}
+NCU_DRAM_BYTES_PER_LAUNCH = {"in_proj": 14.08e6, "out_proj": 8.77e6, "expert_gate_up": 10.07e6, "expert_down": 6.05e6,
+                             "head": 322.0e6, "delta_step": 2.13e6, "attention": 4.72e6}
 
 
 def graph_timeline(eng, prof):
