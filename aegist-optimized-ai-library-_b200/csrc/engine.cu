@@ -922,7 +922,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.nseg = 3; seal(a, c.D);
             a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D; a.err = d_err;
             // fewer than 8 tokens on one GPU: the top-8 moves into the expert kernel and the experts are spread over all SMs
-            const bool moe1 = g_moe1 && ep_world == 1 && B < 8 && (c.D == 512 || c.D == 1024 || c.D == 2048 || c.D == 4096) && c.I % 128 == 0 && c.I <= 2048 &&
+            const bool moe1 = g_moe1 && ep_world == 1 && B < 8 && (c.D == 512 || c.D == 1024 || c.D == 2048 || c.D == 4096) && c.I >= 128 && c.I <= 2048 && (c.I & (c.I - 1)) == 0 &&
                               c.SH % 128 == 0 && c.TOPK <= 8 && c.E <= 256;
             a.finisher = moe1 ? FIN_NONE : FIN_TOPK; a.counter = d_counter; a.E = c.E; a.topk = c.TOPK;
             a.top_idx = top_idx + (size_t)li * B * c.TOPK; a.top_w = top_w + (size_t)li * B * c.TOPK;

@@ -468,22 +468,23 @@ __global__ void __launch_bounds__(M1_DOWN_WARPS * 32) k_moe_down1(const Down1Arg
         const size_t pick = (size_t)b * a.topk + r;
         const uint8_t* base = a.top_ptr[pick];
         if (base != nullptr) {
-            const int chunks = halfk >> 4;
+            // I is a power of two: pieces per row are too, so rows and pieces come from shifts
+            const int chunks = halfk >> 4, csh = __ffs(chunks) - 1;
             for (int c = lane; c < M1_DOWN_ROWS * chunks; c += 32) {
-                const int rr = c / chunks, ch = c - rr * chunks;
+                const int rr = c >> csh, ch = c & (chunks - 1);
                 if (row0 + rr < a.D)
                     cp_async16(s_rows + (size_t)rr * pitch + ch * 16, base + a.off_dn_q + (size_t)(row0 + rr) * (I >> 1) + (size_t)kh * halfk + (size_t)ch * 16);
             }
-            const int sch = (ngroup * 2 + 15) >> 4;
+            const int sch = (ngroup * 2 + 15) >> 4, ssh = __ffs(sch) - 1;
             for (int c = lane; c < M1_DOWN_ROWS * 2 * sch; c += 32) {
-                const int q = c / sch, ch = c - q * sch;
+                const int q = c >> ssh, ch = c & (sch - 1);
                 const int rr = q >> 1, which = q & 1;
                 if (row0 + rr < a.D)
                     copy_f16_piece(s_sc + ((size_t)rr * 2 + which) * ngroup, base + (which ? a.off_dn_m : a.off_dn_s) + ((size_t)(row0 + rr) * ngroup) * 2, ngroup, ch);
             }
-            const int pch = (I >> 1) >> 4;               // 16-byte pieces of a plane's half
+            const int pch = (I >> 1) >> 4, psh = __ffs(pch) - 1;   // 16-byte pieces of a plane's half
             for (int c = lane; c < M1_PLANES * pch; c += 32) {
-                const int p = c / pch, ch = c - p * pch;
+                const int p = c >> psh, ch = c & (pch - 1);
                 cp_async16(s_xq + (size_t)p * (I >> 1) + ch * 16, a.actq + (pick * M1_PLANES + p) * I + (size_t)kh * (I >> 1) + (size_t)ch * 16);
             }
             cp_async_commit();
@@ -535,7 +536,7 @@ __global__ void __launch_bounds__(M1_DOWN_WARPS * 32) k_moe_down1(const Down1Arg
         if (a.shd_w) {
             const int chunks = hk >> 4;
             for (int c = lane; c < M1_DOWN_ROWS * chunks; c += 32) {          // weights do not depend on the previous kernel
-                const int rr = c / chunks, ch = c - rr * chunks;
+                const int rr = c / chunks, ch = c - rr * chunks;               // (before the wait: not on the critical path)
                 if (row0 + rr < a.D)
                     cp_async16(s_rows + (size_t)rr * pitch + ch * 16, (const unsigned char*)a.shd_w + (size_t)(row0 + rr) * SH + (size_t)kh * hk + (size_t)ch * 16);
             }
