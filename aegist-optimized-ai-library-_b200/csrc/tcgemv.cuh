@@ -259,8 +259,9 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
         // what this lane's two result columns (2 tid, 2 tid + 1) weigh: planes 2 (tid & 1), 2 (tid & 1) + 1 of sequence tid >> 1
         const float pw0 = ((tid >> 1) < NB ? s_xscale[(tid >> 1) < NB ? (tid >> 1) : 0] : 0.f) * ((tid & 1) ? (1.0f / 16384.0f) : 1.0f);
         const float pw1 = pw0 * (1.0f / 128.0f);
+        int st = 0, ph = 0;                               // stage of tile i and the parity of its use: no divisions per tile
         for (int t = t0, i = 0; t < t1; t++, i++) {
-            const int st = i % NST, buf = i % TC_EPI;
+            const int buf = i & (TC_EPI - 1);
             int s, tin;
             locate(t, s, tin);
             const int kind = a.seg[s].kind;
@@ -270,12 +271,11 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
             float* pt = part + (size_t)buf * NB * W * 32;
             const unsigned char* stage = stages + (size_t)st * stage_bytes;
             if (i >= TC_EPI) bar_sync(1 + TC_EPI + buf, BAR_N);   // the epilogue of tile i - TC_EPI has read this buffer
-            mbar_wait(&full_bar[st], (i / NST) & 1, a.err);
+            mbar_wait(&full_bar[st], ph, a.err);
             if (!isbf) {
                 const int nrb = two ? 1 : 2;               // 16-slot blocks in the tile
-                const int nks = W / nrb;
-                const int rbk = warp % nrb, ks = warp / nrb;
-                const int slice = a.K / nks;               // bytes = values; a multiple of 64
+                const int rbk = warp & (nrb - 1), ks = warp >> (nrb - 1);
+                const int slice = two ? a.K / W : a.K / (W / 2);      // bytes = values; a multiple of 64 (constant divisors)
                 const int sstride = two ? TC_SLOT_STRIDE_WIDE : TC_SLOT_STRIDE;
                 const int slot_hi = (kind == SEG_I8_GATEUP ? rbk * 16 : 0) + tr - 1;       // last slot this row block may read
                 const unsigned char* pa = stage + (size_t)min(rbk * 16 + gid, slot_hi) * sstride + ks * slice + tid * 16;
@@ -296,9 +296,8 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
                 }
             } else {
                 // bf16 rows: 16 slots of 2 K bytes; warp -> (8-row half, K slice), lane -> (row, 16-byte unit of a 64-byte step)
-                const int nks = W / 2;
                 const int rh = warp & 1, ks = warp >> 1;
-                const int slice = 2 * a.K / nks;           // bytes
+                const int slice = 2 * a.K / (W / 2);       // bytes
                 const unsigned char* pa = stage + (size_t)min(rh * 8 + gid, tr - 1) * TC_SLOT_STRIDE_WIDE + ks * slice + tid * 16;
                 float acc[NB];
 #pragma unroll
@@ -327,12 +326,14 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
                 }
             }
             bar_arrive(1 + buf, BAR_N);            // partial sums written, the stage read
+            if (++st == NST) { st = 0; ph ^= 1; }
         }
     } else {
         // ---- epilogue warps: warp W + p takes tiles p, p + 2, ... of this block ----
         const int p = warp - W;
+        int st = p % NST;                                  // stage of this warp's next tile
+        const int dst = TC_EPI % NST;
         for (int t = t0 + p, i = p; t < t1; t += TC_EPI, i += TC_EPI) {
-            const int st = i % NST;
             int s, tin;
             locate(t, s, tin);
             const Seg& sg = a.seg[s];
@@ -402,6 +403,8 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
                 }
             }
             if (t + TC_EPI < t1) bar_arrive(1 + TC_EPI + p, BAR_N);     // the buffer may be written again
+            st += dst;
+            if (st >= NST) st -= NST;
         }
     }
     trace_pt(a.trace, 3);
