@@ -16,15 +16,18 @@ __device__ __forceinline__ void imma16832(int (&c)[4], uint32_t a0, uint32_t a1,
 // an integer of magnitude below 2^22 as fp32, without the conversion unit
 __device__ __forceinline__ float small_int_to_float(int t) { return __int_as_float(t + 0x4B400000) - 12582912.0f; }
 
-// four digits of q = v * inv (|q| <= 127): q = d0 + d1/128 + d2/128^2 + d3/128^3 up to 2^-22; every step is exact
+// four digits of q = v * inv (|q| <= 127): q = d0 + d1/128 + d2/128^2 + d3/128^3 up to 2^-22. q is rounded once to
+// a multiple of 2^-21 (one conversion), then split with integer arithmetic into balanced base-128 digits: d1..d3 in
+// [-64, 63], d0 = what remains (|d0| <= 127).
 __device__ __forceinline__ void to_digits(float v, float inv, int (&d)[M1_PLANES]) {
-    float q = v * inv;
+    int q = __float2int_rn(v * inv * 2097152.0f);
 #pragma unroll
-    for (int p = 0; p < M1_PLANES; p++) {
-        const float r = rintf(q);
-        d[p] = (int)r;
-        q = (q - r) * 128.0f;
+    for (int p = M1_PLANES - 1; p > 0; p--) {
+        const int r = ((q + 64) & 127) - 64;
+        d[p] = r;
+        q = (q - r) >> 7;
     }
+    d[0] = q;
 }
 // eight consecutive values -> per plane the 8 digits as two words; `evenodd`: even positions first (the
 // order in which the low / high nibbles of a word of eight codes come out), else natural order

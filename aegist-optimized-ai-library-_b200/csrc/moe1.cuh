@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
         mx = 0.f;
 #pragma unroll
         for (int w = 8; w < 16; w++) mx = fmaxf(mx, red[16 + w]);
-        const float inv = mx > 0.f ? 127.0f / mx : 0.f;
+        const float inv = mx > 1e-30f ? 127.0f / mx : 0.f;
         if (xt == 0) s_scale = mx / 127.0f;
 #pragma unroll
         for (int j = 0; j < XC; j++) {
@@ -388,7 +388,7 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
         for (int q = 0; q < 8; q++) { g += s_part[q][s >> 3][s & 7][0]; u += s_part[q][s >> 3][s & 7][1]; }
         const float v = siluf_(g) * u;
         const float mx = warp_max(fabsf(v));
-        const float inv = mx > 0.f ? 127.0f / mx : 0.f;
+        const float inv = mx > 1e-30f ? 127.0f / mx : 0.f;
         int d[M1_PLANES];
         to_digits(v, inv, d);
         const size_t pick = (size_t)b * a.topk + rnk;
@@ -551,7 +551,7 @@ __global__ void __launch_bounds__(M1_DOWN_WARPS * 32) k_moe_down1(const Down1Arg
 #pragma unroll
                 for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(src[k + i]));
             mx = warp_max(mx);
-            const float inv = mx > 0.f ? 127.0f / mx : 0.f;
+            const float inv = mx > 1e-30f ? 127.0f / mx : 0.f;
             for (int k = lane * 8; k < hk; k += 256) {
                 float v[8];
 #pragma unroll

@@ -229,7 +229,7 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
             float mx = 0.f;
 #pragma unroll
             for (int w = 0; w < WT; w++) mx = fmaxf(mx, red[1][w][b]);
-            const float inv = mx > 0.f ? 127.0f / mx : 0.f;
+            const float inv = mx > 1e-30f ? 127.0f / mx : 0.f;
             if (threadIdx.x == 0) s_xscale[b] = mx / 127.0f;
             if (has) {
                 uint2 w[M1_PLANES];
