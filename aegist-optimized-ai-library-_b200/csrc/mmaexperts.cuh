@@ -155,6 +155,7 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_q4(const Q4Args a) {
     constexpr int NCOL = 8 * NT;                  // picks per chunk
     extern __shared__ __align__(128) unsigned char q4_smem[];
     __shared__ int s_pick[NCOL];
+    __shared__ int s_src[NCOL], s_dst[NCOL];     // per pick: row of its activations, row of its output (no divisions later)
     __shared__ float s_xsum[NCOL][33];           // [pick of the chunk][group]
     __shared__ float gate_s[2][16][NCOL + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -169,15 +170,20 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_q4(const Q4Args a) {
     const int e = a.chunks.expert[chunk];
     const int n = min(a.chunks.n[chunk], NCOL);
     const uint8_t* base = a.eptr[e];
-    if (threadIdx.x < NCOL) s_pick[threadIdx.x] = threadIdx.x < n ? a.list[a.chunks.start[chunk] + threadIdx.x] : -1;
+    if (threadIdx.x < NCOL) {
+        const int pk = threadIdx.x < n ? a.list[a.chunks.start[chunk] + threadIdx.x] : -1;
+        const int tk = pk < 0 ? 0 : pk / a.topk;
+        s_pick[threadIdx.x] = pk;
+        s_src[threadIdx.x] = pk < 0 ? 0 : (a.by_pick ? pk : tk);
+        s_dst[threadIdx.x] = pk < 0 ? 0 : (a.pair ? pk : tk * (a.topk + 1) + (pk - tk * a.topk));
+    }
     __syncthreads();
     const int rows_per_tile = a.pair ? Q4_ROWS / 2 : Q4_ROWS;
     const int row0 = blockIdx.x * rows_per_tile * a.row_tiles;
     const int ngroup = a.K >> 6;                 // <= 32
     for (int p = threadIdx.x; p < n * ngroup; p += MM_THREADS) {
         const int c = p / ngroup, g = p % ngroup;
-        const int pk = s_pick[c];
-        s_xsum[c][g] = a.xsum[(size_t)(a.by_pick ? pk : pk / a.topk) * ngroup + g];
+        s_xsum[c][g] = a.xsum[(size_t)s_src[c] * ngroup + g];
     }
     const int rowbytes = a.K >> 1;
     const int nk = a.K / MM_KC;
@@ -208,8 +214,7 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_q4(const Q4Args a) {
         for (int p = threadIdx.x; p < 2 * n * (MM_KC / 8); p += MM_THREADS) {
             const int j = p / (MM_KC / 8), c = p % (MM_KC / 8);
             const int part = j >= n, tc = part ? j - n : j;
-            const int pk = s_pick[tc];
-            const int src_row = a.by_pick ? pk : pk / a.topk;
+            const int src_row = s_src[tc];
             cp_async16(sb + (part * NCOL + tc) * MM_PB + c * 16, a.xh + ((size_t)src_row * 2 + part) * a.K + (size_t)kc * MM_KC + c * 8);
         }
         cp_async_commit();
@@ -298,7 +303,7 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_q4(const Q4Args a) {
                     if (pk < 0 || row >= a.rows) continue;
                     const float dot = acc[nt][q] + acc[NT + nt][q];
                     if (a.pair) a.out[(size_t)pk * a.rows + row] = siluf_(gate_s[warp - 2][rl][col]) * dot;
-                    else a.out[((size_t)(pk / a.topk) * (a.topk + 1) + pk % a.topk) * a.rows + row] = dot;
+                    else a.out[(size_t)s_dst[col] * a.rows + row] = dot;
                 }
         }
 #pragma unroll

@@ -212,9 +212,9 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_i8(const MmaArgs a) {
             cp_async16(sa + r * MM_PA + c * 16, base + ((size_t)grow * a.K + (size_t)kc * kcw) * (isbf ? 2 : 1) + c * 16);
         }
         // activations: 64 columns (32 sequences x hi, lo) x 256 halves = 2048 pieces
-        const int pcs = kcw / 8;                                               // 16-byte pieces per column
+        const int pcs = kcw / 8, psh = isbf ? 4 : 5;                           // 16-byte pieces per column: 16 or 32
         for (int p = threadIdx.x; p < 2 * MM_TOK * pcs; p += MM_THREADS) {
-            const int col = p / pcs, c = p - col * pcs;
+            const int col = p >> psh, c = p & (pcs - 1);
             const int tok = t0 + (col & (MM_TOK - 1)), part = col >> 5;        // columns 0..31 hi, 32..63 lo
             cp_async16(sb + col * MM_PB + c * 16, a.xh + ((size_t)tok * 2 + part) * a.K + (size_t)kc * kcw + c * 8);
         }
