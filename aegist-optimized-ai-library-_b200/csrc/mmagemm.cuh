@@ -64,28 +64,43 @@ __global__ void __launch_bounds__(256) k_prep_x(const PrepArgs a) {
     }
     const float* x = a.x + (size_t)t * a.x_stride;
     if (a.gn_w) {
-        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        // DeltaNet output projection input: w * rmsnorm_DV(o) * silu(z) per value head. A thread takes 8 consecutive
+        // values per turn, all of its loads in flight together; a head is DV / 8 neighbouring lanes.
         const float* z = a.z + (size_t)t * a.x_stride;
-        for (int h = warp; h < a.K / a.DV; h += 8) {
-            float ss = 0.f;
-            for (int i = lane; i < a.DV; i += 32) { const float v = x[h * a.DV + i]; ss = fmaf(v, v, ss); }
-            ss = warp_sum(ss);
-            const float r = 1.0f / sqrtf(ss / (float)a.DV + a.eps);
-            for (int i = lane; i < a.DV; i += 32) {
-                const int k = h * a.DV + i;
-                const float v = (bf(a.gn_w[i]) * (x[k] * r)) * z[k];
-                vs[k] = v;
-                const __half h1 = __float2half(v);
-                hi[k] = h1;
-                lo[k] = __float2half(v - __half2float(h1));
+        constexpr int TURNS = 2;                        // K <= 256 threads * 8 * 2
+        float xv[TURNS][8], zv[TURNS][8], gw[TURNS][8];
+#pragma unroll
+        for (int j = 0; j < TURNS; j++) {
+            const int k = (threadIdx.x + j * 256) * 8;
+            const bool has = k < a.K;
+            float4 v0 = make_float4(0.f, 0.f, 0.f, 0.f), v1 = v0, z0 = v0, z1 = v0;
+            uint4 wv = make_uint4(0u, 0u, 0u, 0u);
+            if (has) {
+                v0 = *reinterpret_cast<const float4*>(x + k); v1 = *reinterpret_cast<const float4*>(x + k + 4);
+                z0 = *reinterpret_cast<const float4*>(z + k); z1 = *reinterpret_cast<const float4*>(z + k + 4);
+                wv = *reinterpret_cast<const uint4*>(a.gn_w + (k % a.DV));
             }
+            xv[j][0] = v0.x; xv[j][1] = v0.y; xv[j][2] = v0.z; xv[j][3] = v0.w; xv[j][4] = v1.x; xv[j][5] = v1.y; xv[j][6] = v1.z; xv[j][7] = v1.w;
+            zv[j][0] = z0.x; zv[j][1] = z0.y; zv[j][2] = z0.z; zv[j][3] = z0.w; zv[j][4] = z1.x; zv[j][5] = z1.y; zv[j][6] = z1.z; zv[j][7] = z1.w;
+            gw[j][0] = bflo(wv.x); gw[j][1] = bfhi(wv.x); gw[j][2] = bflo(wv.y); gw[j][3] = bfhi(wv.y);
+            gw[j][4] = bflo(wv.z); gw[j][5] = bfhi(wv.z); gw[j][6] = bflo(wv.w); gw[j][7] = bfhi(wv.w);
         }
-        if (a.xsum) {
-            __syncthreads();
-            for (int g = threadIdx.x; g < a.K / 64; g += 256) {
-                float s = 0.f;
-                for (int i = 0; i < 64; i++) s += vs[64 * g + i];
-                a.xsum[(size_t)t * (a.K / 64) + g] = s;
+#pragma unroll
+        for (int j = 0; j < TURNS; j++) {
+            const int k = (threadIdx.x + j * 256) * 8;
+            float ss = 0.f;
+#pragma unroll
+            for (int i = 0; i < 8; i++) ss = fmaf(xv[j][i], xv[j][i], ss);
+            for (int o = a.DV >> 4; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            const float r = 1.0f / sqrtf(ss / (float)a.DV + a.eps);
+            if (k < a.K) {
+#pragma unroll
+                for (int i = 0; i < 8; i++) {
+                    const float v = (gw[j][i] * (xv[j][i] * r)) * zv[j][i];
+                    const __half h1 = __float2half(v);
+                    hi[k + i] = h1;
+                    lo[k + i] = __float2half(v - __half2float(h1));
+                }
             }
         }
         trace_out(a.trace);
