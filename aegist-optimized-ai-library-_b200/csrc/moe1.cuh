@@ -135,9 +135,9 @@ __host__ __device__ __forceinline__ size_t m1_gu_smem(int D) {
     return (size_t)2 * M1_GU_PAIRS * ((D >> 1) + 32) + (size_t)2 * M1_GU_PAIRS * 2 * (D >> 6) * 2 + (size_t)M1_PLANES * (D + 64) + (size_t)(D >> 6) * 4;
 }
 
-// grid (topk * I / 32, B); 32 warps. Prologue: warps 0-7 rank the experts (one thread per expert counts
-// the experts ahead of it, which is short and parallel where a select-the-largest loop is a long
-// chain), warps 8-15 normalise x and split it into digit planes, 8 consecutive values per thread.
+// grid (topk * I / 32, B); 32 warps. Prologue: warps 0-7 rank the experts (one thread per expert: every warp
+// selects the 8 best of its 32 with warp-wide integer reductions, warp 0 the 8 best of those 64), warps 8-15
+// normalise x and split it into digit planes, 8 consecutive values per thread.
 __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
     extern __shared__ __align__(128) unsigned char m1_smem[];
     const int D = a.D, half = D >> 1;                   // bytes of codes per row
