@@ -652,6 +652,7 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
             a.total_jobs += g.jobs;
         }
         const int grid = grid_override ? grid_override : std::max(1, std::min(a.total_jobs, nsm));
+        a.jq = a.total_jobs / grid; a.jr = a.total_jobs % grid;
         const int per_block = (a.total_jobs + grid - 1) / grid;
         const int nst = std::max(1, std::min(per_block, TC_MAX_STAGES));   // stages: what the longest block needs
 #define TCG(NBv, Wv)                                                                                            \

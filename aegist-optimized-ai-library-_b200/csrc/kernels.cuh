@@ -252,6 +252,7 @@ struct GemvArgs {
     Seg seg[4];
     int nseg;
     int total_jobs;
+    int jq, jr;              // k_tcgemv: total_jobs = jq * grid + jr; block b starts at b * jq + min(b, jr)
     const float* x;          // [B][x_stride] residual stream
     int x_stride;            // row stride of x (the host sets K when it is left 0)
     const uint16_t* norm_w;  // [K]

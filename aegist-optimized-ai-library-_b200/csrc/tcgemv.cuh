@@ -112,8 +112,8 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int gid = lane >> 2, tid = lane & 3;
     const int b0 = blockIdx.y * NB;                    // first sequence of this pass
-    const int t0 = (int)((long long)blockIdx.x * a.total_jobs / gridDim.x);
-    const int t1 = (int)((long long)(blockIdx.x + 1) * a.total_jobs / gridDim.x);
+    const int t0 = (int)blockIdx.x * a.jq + min((int)blockIdx.x, a.jr);          // the first jr blocks take one tile more
+    const int t1 = t0 + a.jq + ((int)blockIdx.x < a.jr ? 1 : 0);
     grid_dep_launch();
     trace_in(a.trace, 1, a.seg[0].rows);
     if (threadIdx.x == 0) {
