@@ -136,8 +136,8 @@ __host__ __device__ __forceinline__ size_t m1_gu_smem(int D) {
 }
 
 // grid (topk * I / 32, B); 32 warps. Prologue: warps 0-7 rank the experts (one thread per expert: every warp
-// selects the 8 best of its 32 with warp-wide integer reductions, warp 0 the 8 best of those 64), warps 8-15
-// normalise x and split it into digit planes, 8 consecutive values per thread.
+// lists the 8 best of its 32 by counting, for each, the ones that beat it; the 64 listed are ranked the same
+// way), warps 8-15 normalise x and split it into digit planes, 8 consecutive values per thread.
 __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
     extern __shared__ __align__(128) unsigned char m1_smem[];
     const int D = a.D, half = D >> 1;                   // bytes of codes per row
@@ -148,8 +148,9 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
     const int XS = D + 64;                              // plane stride: planes p, p+1 in different halves of the banks
     int8_t* s_xq = reinterpret_cast<int8_t*>(s_sc + (size_t)2 * M1_GU_PAIRS * 2 * ngroup);    // [PLANES][XS], even/odd order
     float* s_xsum = reinterpret_cast<float*>(s_xq + (size_t)M1_PLANES * XS);                  // [ngroup]
-    __shared__ uint32_t s_key[64];                      // the 8 best keys of each of the 8 ranking warps
-    __shared__ int s_cand[64];                          // and their experts
+    __shared__ __align__(16) uint32_t s_key[64];        // the 8 best keys of each of the 8 ranking warps
+    __shared__ __align__(16) int s_cand[64];            // and their experts
+    __shared__ const uint8_t* s_eptr[256];              // the layer's expert table (E <= 256)
     __shared__ int s_top[8];
     __shared__ float s_topv[8];
     __shared__ float s_red[2][8];
@@ -160,6 +161,9 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
     const int b = blockIdx.y;
     grid_dep_launch();
     trace_in(a.trace, 5, gridDim.x);
+    // the expert table is written at load time only: read it while the previous kernel still runs
+    if (threadIdx.x < a.E && threadIdx.x < 256) s_eptr[threadIdx.x] = a.eptr[threadIdx.x];
+    if (threadIdx.x < 8) { s_top[threadIdx.x] = -1; s_topv[threadIdx.x] = 0.f; }
     grid_dep_wait();
     trace_pt(a.trace, 1);
 
@@ -182,35 +186,39 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
         for (int w = 0; w < 8; w++) sum += s_red[1][w];
         const float prob = p / sum;
         const uint32_t key = e < a.E ? __float_as_uint(prob) + 1u : 0u;      // positive floats order like their bits
-        // every warp picks the 8 best of its 32 experts (8 rounds of two warp-wide integer reductions: largest
-        // key, then the lowest expert holding it), then warp 0 picks the 8 best of the 64 candidates the same way
+        // two rounds of rank counting (independent compares instead of a chain of reductions): every warp ranks its
+        // 32 experts among themselves over 31 rotations and lists its 8 best, then the 64 listed are ranked, four
+        // threads per candidate. Order: larger key first, equal keys by the lower expert number.
         {
-            uint32_t k = key;
-            for (int r = 0; r < 8; r++) {
-                const uint32_t m = __reduce_max_sync(0xffffffffu, k);
-                const uint32_t who = __reduce_min_sync(0xffffffffu, (k == m && m != 0u) ? (uint32_t)lane : 0xffu);
-                if (lane == r) { s_key[warp * 8 + r] = m; s_cand[warp * 8 + r] = who < 32u ? warp * 32 + (int)who : 0x7fffffff; }
-                if ((uint32_t)lane == who) k = 0u;
+            int rank = 0;
+#pragma unroll
+            for (int s = 1; s < 32; s++) {
+                const uint32_t o = __shfl_sync(0xffffffffu, key, (lane + s) & 31);
+                const bool lower = lane + s >= 32;                  // the other lane holds a lower expert number
+                rank += (o > key || (o == key && lower)) ? 1 : 0;
             }
+            if (rank < 8) { s_key[warp * 8 + rank] = key; s_cand[warp * 8 + rank] = key ? e : 0x7fffffff; }
         }
         asm volatile("bar.sync 2, 256;" ::: "memory");
-        if (warp == 0) {
-            // candidates are in ascending expert order for equal keys only within a warp's list, so the tie rule is
-            // applied on the expert number itself
-            uint32_t k0 = s_key[lane], k1 = s_key[32 + lane];
-            const int e0 = s_cand[lane], e1 = s_cand[32 + lane];
-            for (int r = 0; r < a.topk; r++) {
-                const uint32_t bk = k0 > k1 ? k0 : k1;
-                const uint32_t m = __reduce_max_sync(0xffffffffu, bk);
-                uint32_t c = 0x7fffffffu;
-                if (m != 0u) {
-                    if (k0 == m) c = (uint32_t)e0;
-                    if (k1 == m && (uint32_t)e1 < c) c = (uint32_t)e1;
-                }
-                const uint32_t ex = __reduce_min_sync(0xffffffffu, c);
-                if (k0 == m && (uint32_t)e0 == ex) k0 = 0u;
-                if (k1 == m && (uint32_t)e1 == ex) k1 = 0u;
-                if (lane == r) { s_top[r] = ex < 0x7fffffffu ? (int)ex : -1; s_topv[r] = m ? __uint_as_float(m - 1u) : 0.f; }
+        {
+            const int c = threadIdx.x >> 2, q = threadIdx.x & 3;
+            const uint32_t kc = s_key[c];
+            const int ec = s_cand[c];
+            int cnt = 0;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const uint4 kk = *reinterpret_cast<const uint4*>(s_key + q * 16 + j * 4);
+                const int4 ee = *reinterpret_cast<const int4*>(s_cand + q * 16 + j * 4);
+                cnt += (kk.x > kc || (kk.x == kc && ee.x < ec)) ? 1 : 0;
+                cnt += (kk.y > kc || (kk.y == kc && ee.y < ec)) ? 1 : 0;
+                cnt += (kk.z > kc || (kk.z == kc && ee.z < ec)) ? 1 : 0;
+                cnt += (kk.w > kc || (kk.w == kc && ee.w < ec)) ? 1 : 0;
+            }
+            cnt += __shfl_xor_sync(0xffffffffu, cnt, 1);
+            cnt += __shfl_xor_sync(0xffffffffu, cnt, 2);
+            if (q == 0 && cnt < a.topk) {
+                s_top[cnt] = ec < 0x7fffffff ? ec : -1;
+                s_topv[cnt] = kc ? __uint_as_float(kc - 1u) : 0.f;
             }
         }
         asm volatile("bar.sync 2, 256;" ::: "memory");
@@ -220,7 +228,7 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
             const int ex = s_top[threadIdx.x];
             a.top_idx[(size_t)b * a.topk + threadIdx.x] = ex;
             a.top_w[(size_t)b * a.topk + threadIdx.x] = s_topv[threadIdx.x] / tsum;
-            a.top_ptr[(size_t)b * a.topk + threadIdx.x] = (ex >= 0 && ex < a.E) ? a.eptr[ex] : nullptr;
+            a.top_ptr[(size_t)b * a.topk + threadIdx.x] = (ex >= 0 && ex < a.E) ? s_eptr[ex] : nullptr;
         }
         trace_pt(a.trace, 2);
     } else if (warp < 16) {
@@ -301,7 +309,7 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
     const int p0 = blockIdx.x * M1_GU_PAIRS;
     const int rnk = p0 / a.I, i0 = p0 - rnk * a.I;
     const int e = s_top[rnk];
-    const uint8_t* base = (e >= 0 && e < a.E) ? a.eptr[e] : nullptr;
+    const uint8_t* base = (e >= 0 && e < a.E) ? s_eptr[e] : nullptr;
     if (base == nullptr) {                               // a bad pick: say so, nothing to compute
         if (threadIdx.x == 0) atomicExch(a.err, 2);
         trace_out(a.trace);
