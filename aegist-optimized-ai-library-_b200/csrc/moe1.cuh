@@ -254,33 +254,32 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
                 for (int i = 0; i < 8; i++) { xv[j][i] = 0.f; nw[j][i] = 1.0f; }
             }
 #pragma unroll
-            for (int i = 0; i < 8; i++) ss = fmaf(xv[j][i], xv[j][i], ss);
+            for (int i = 0; i < 8; i++) { ss = fmaf(xv[j][i], xv[j][i], ss); xv[j][i] *= nw[j][i]; }
         }
-        float r = 1.0f;
+        // the rms is one factor for the whole vector: the sum of squares and the largest |(1 + w) x| are reduced
+        // together, behind one barrier
         float* red = &s_part[0][0][0][0];               // scratch until the main part starts
-        if (a.norm_w) {
-            ss = warp_sum(ss);
-            if (lane == 0) red[warp] = ss;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            float t = 0.f;
-#pragma unroll
-            for (int w = 8; w < 16; w++) t += red[w];
-            r = 1.0f / sqrtf(t / (float)D + a.eps);
-        }
         float mx = 0.f;
 #pragma unroll
         for (int j = 0; j < XC; j++)
 #pragma unroll
-            for (int i = 0; i < 8; i++) {
-                if (a.norm_w) xv[j][i] = xv[j][i] * r * nw[j][i];
-                mx = fmaxf(mx, fabsf(xv[j][i]));
-            }
+            for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(xv[j][i]));
+        ss = warp_sum(ss);
         mx = warp_max(mx);
-        if (lane == 0) red[16 + warp] = mx;
+        if (lane == 0) { red[warp] = ss; red[16 + warp] = mx; }
         asm volatile("bar.sync 1, 256;" ::: "memory");
         mx = 0.f;
+        float t = 0.f;
 #pragma unroll
-        for (int w = 8; w < 16; w++) mx = fmaxf(mx, red[16 + w]);
+        for (int w = 8; w < 16; w++) { mx = fmaxf(mx, red[16 + w]); t += red[w]; }
+        if (a.norm_w) {
+            const float r = 1.0f / sqrtf(t / (float)D + a.eps);
+#pragma unroll
+            for (int j = 0; j < XC; j++)
+#pragma unroll
+                for (int i = 0; i < 8; i++) xv[j][i] *= r;
+            mx *= r;
+        }
         const float inv = mx > 1e-30f ? 127.0f / mx : 0.f;
         if (xt == 0) s_scale = mx / 127.0f;
 #pragma unroll

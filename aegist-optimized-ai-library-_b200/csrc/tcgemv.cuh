@@ -169,6 +169,7 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
             xv[b][0] = v0.x; xv[b][1] = v0.y; xv[b][2] = v0.z; xv[b][3] = v0.w;
             xv[b][4] = v1.x; xv[b][5] = v1.y; xv[b][6] = v1.z; xv[b][7] = v1.w;
         }
+        const bool znorm = a.gn_w == nullptr && a.norm_w != nullptr;
         if (a.gn_w) {
             // DeltaNet output projection: w * rmsnorm_DV(o) * silu(z) per value head (aegist/hybrid.py:133-147);
             // a head is DV / 8 neighbouring lanes
@@ -192,6 +193,8 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
                 for (int i = 0; i < 8; i++) xv[b][i] = (gw[i] * (xv[b][i] * r)) * zz[i];
             }
         } else if (a.norm_w) {
+            // (1 + w) * x / rms(x) (aegist/hybrid.py:119-130). The rms is one factor for the whole vector, so the sum of
+            // squares and the largest |(1 + w) x| are reduced together, behind one barrier, and the factor joins after it
             uint4 wv = make_uint4(0u, 0u, 0u, 0u);
             if (has) wv = *reinterpret_cast<const uint4*>(a.norm_w + kc);
             const float nw[8] = {1.0f + bflo(wv.x), 1.0f + bfhi(wv.x), 1.0f + bflo(wv.y), 1.0f + bfhi(wv.y),
@@ -200,19 +203,9 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
             for (int b = 0; b < NB; b++) {
                 float ss = 0.f;
 #pragma unroll
-                for (int i = 0; i < 8; i++) ss = fmaf(xv[b][i], xv[b][i], ss);
+                for (int i = 0; i < 8; i++) { ss = fmaf(xv[b][i], xv[b][i], ss); xv[b][i] *= nw[i]; }
                 ss = warp_sum(ss);
                 if (lane == 0) red[0][warp][b] = ss;
-            }
-            __syncthreads();
-#pragma unroll
-            for (int b = 0; b < NB; b++) {
-                float t = 0.f;
-#pragma unroll
-                for (int w = 0; w < WT; w++) t += red[0][w][b];
-                const float rn = 1.0f / sqrtf(t / (float)a.K + a.eps);
-#pragma unroll
-                for (int i = 0; i < 8; i++) xv[b][i] = xv[b][i] * rn * nw[i];
             }
         }
 #pragma unroll
@@ -229,6 +222,15 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
             float mx = 0.f;
 #pragma unroll
             for (int w = 0; w < WT; w++) mx = fmaxf(mx, red[1][w][b]);
+            if (znorm) {
+                float t = 0.f;
+#pragma unroll
+                for (int w = 0; w < WT; w++) t += red[0][w][b];
+                const float rn = 1.0f / sqrtf(t / (float)a.K + a.eps);
+#pragma unroll
+                for (int i = 0; i < 8; i++) xv[b][i] *= rn;
+                mx *= rn;
+            }
             const float inv = mx > 1e-30f ? 127.0f / mx : 0.f;
             if (threadIdx.x == 0) s_xscale[b] = mx / 127.0f;
             if (has) {
