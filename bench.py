@@ -301,11 +301,11 @@ def run_b64(args):
 
 
 # DRAM bytes (read + write) per launch from the ncu launch list of the 4-layer full-width case, averaged over the
-# launches of a role in the 40-layer model (30 DeltaNet + 10 attention layers): in_proj = (30 x 26.59 + 10 x 19.58 +
+# launches of a role in the 40-layer model (30 DeltaNet + 10 attention layers): in_proj = (30 x 26.02 + 10 x 19.90 +
 # 40 x 3.33) / 80 MB, and so on; the per-launch figures are in the file named below.
 NCU_DRAM_SOURCE = "profiles/decode_step_launch_list_4layer_case.md"
-NCU_DRAM_BYTES_PER_LAUNCH = {"in_proj": 14.08e6, "out_proj": 8.77e6, "expert_gate_up": 10.07e6, "expert_down": 6.05e6,
-                             "head": 322.0e6, "delta_step": 2.13e6, "attention": 4.72e6}
+NCU_DRAM_BYTES_PER_LAUNCH = {"in_proj": 13.91e6, "out_proj": 8.76e6, "expert_gate_up": 10.13e6, "expert_down": 6.00e6,
+                             "head": 321.4e6, "delta_step": 2.14e6, "attention": 4.64e6}
 
 
 def graph_timeline(eng, prof):
