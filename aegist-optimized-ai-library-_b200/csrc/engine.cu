@@ -1285,6 +1285,18 @@ int b2_feed(b2_engine* e, const uint32_t* ids, int n, float* logits_out) {
     return 0;
 }
 
+void* b2_host_alloc(size_t bytes) {
+    void* p = nullptr;
+    if (cudaHostAlloc(&p, bytes ? bytes : 1, cudaHostAllocDefault) != cudaSuccess) {
+        cudaGetLastError();
+        return nullptr;
+    }
+    return p;
+}
+void b2_host_free(void* p) {
+    if (p) cudaFreeHost(p);
+}
+
 int b2_feed_batch(b2_engine* e, const uint32_t* ids, uint32_t* next_greedy, float* logits_out) {
     if (feed_checks(e, 1)) return 1;
     for (int b = 0; b < e->B; b++)

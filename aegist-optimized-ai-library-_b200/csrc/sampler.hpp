@@ -21,11 +21,27 @@ inline double splitmix_next_f64(uint64_t* s) {
 extern "C" uint32_t b2_sample(const float* logits, int vocab, float temperature, float top_p, int top_k, uint64_t* rng_state) {
     if (vocab <= 0) return 0;
     if (temperature <= 0.0f) {
-        int best = 0;
-        float bv = -INFINITY;
-        for (int i = 0; i < vocab; i++)
-            if (logits[i] > bv) { bv = logits[i]; best = i; }
-        return (uint32_t)best;
+        // first maximum wins. Two levels, so that the long pass is eight independent running maxima the compiler
+        // turns into vector compares: the largest value of every block of 512, the first block that holds the
+        // overall maximum, then the first position inside it. A NaN never wins a '>' and is never picked.
+        constexpr int BL = 512;
+        float gmax = -INFINITY;
+        int gblock = -1;
+        for (int b0 = 0; b0 < vocab; b0 += BL) {
+            const int n = std::min(BL, vocab - b0);
+            float m[8] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            int i = 0;
+            for (; i + 8 <= n; i += 8)
+                for (int l = 0; l < 8; l++) m[l] = logits[b0 + i + l] > m[l] ? logits[b0 + i + l] : m[l];
+            for (; i < n; i++) m[0] = logits[b0 + i] > m[0] ? logits[b0 + i] : m[0];
+            float bm = m[0];
+            for (int l = 1; l < 8; l++) bm = m[l] > bm ? m[l] : bm;
+            if (bm > gmax) { gmax = bm; gblock = b0; }
+        }
+        if (gblock < 0) return 0;
+        for (int i = gblock; i < std::min(gblock + BL, vocab); i++)
+            if (logits[i] == gmax) return (uint32_t)i;
+        return 0;
     }
     const int k = std::max(1, std::min(top_k, vocab));
     std::vector<uint32_t> idx(vocab);

@@ -53,6 +53,8 @@ SYMBOLS = {
     "b2_verify_file": (_I, [C.c_char_p, C.POINTER(_I), C.c_char_p, C.c_size_t]),
     "b2_close": (None, [_P]),
     "b2_feed": (_I, [_P, _P, _I, _P]),
+    "b2_host_alloc": (_P, [C.c_size_t]),
+    "b2_host_free": (None, [_P]),
     "b2_feed_batch": (_I, [_P, _P, _P, _P]),
     "b2_decode_greedy": (_I, [_P, _P, _I, _P, C.POINTER(_F)]),
     "b2_crop": (_I, [_P, _I]),
@@ -182,8 +184,23 @@ class HybridEngine:
 
     def close(self):
         if self._h:
+            for p in getattr(self, "_host_bufs", []):
+                self._lib.b2_host_free(p)
+            self._host_bufs = []
             self._lib.b2_close(self._h)
             self._h = None
+
+    def host_buffer(self, n: int, dtype=np.float32) -> np.ndarray:
+        """A page-locked numpy array of n values for feed(out=...): the logits then arrive by plain DMA. It lives
+        until close(); do not use it afterwards."""
+        dt = np.dtype(dtype)
+        p = self._lib.b2_host_alloc(int(n) * dt.itemsize)
+        if not p:
+            raise EngineError("b2_host_alloc failed")
+        if not hasattr(self, "_host_bufs"):
+            self._host_bufs = []
+        self._host_bufs.append(p)
+        return np.frombuffer((C.c_char * (int(n) * dt.itemsize)).from_address(p), dtype=dt)
 
     def __del__(self):
         try:
@@ -192,11 +209,17 @@ class HybridEngine:
             pass
 
     # --- trait Lm ---------------------------------------------------------------------------
-    def feed(self, ids, want_logits: bool = True):
-        """Feed tokens; return the logits after the last one."""
+    def feed(self, ids, want_logits: bool = True, out=None):
+        """Feed tokens; return the logits after the last one (in `out`, a float32[vocab] array such as
+        host_buffer(vocab), when given: a loop that reuses one page-locked array saves the allocation and
+        the staged copy of a fresh one)."""
         ids = np.ascontiguousarray(np.asarray(ids, dtype=np.uint32).reshape(-1))
-        out = np.empty(self.vocab, dtype=np.float32) if want_logits else None
-        self._check(self._lib.b2_feed(self._h, _ptr(ids), len(ids), _ptr(out) if want_logits else None))
+        if out is not None:
+            if out.dtype != np.float32 or out.size != self.vocab or not out.flags.c_contiguous:
+                raise EngineError("feed(out=...) needs a contiguous float32 array of vocab values")
+        elif want_logits:
+            out = np.empty(self.vocab, dtype=np.float32)
+        self._check(self._lib.b2_feed(self._h, _ptr(ids), len(ids), _ptr(out) if out is not None else None))
         return out
 
     def feed_batch(self, ids, want_logits: bool = True):

@@ -66,6 +66,13 @@ void b2_close(b2_engine* e);
  * "context full" when length + n > cap, and on a token id outside the vocabulary. */
 int b2_feed(b2_engine* e, const uint32_t* ids, int n, float* logits_out);
 
+/* Page-locked host memory for `logits_out` and `ids`: copies to and from it are plain DMA, where pageable memory
+ * is staged by the driver (0.1 ms per feed for the 35B vocabulary's 608 KB of logits). Not part of the reference
+ * interface, whose feed returns a fresh Vec<f32>; a binding keeps one such buffer per engine and copies out of it
+ * only if its caller keeps the logits. NULL when the allocation fails. */
+void* b2_host_alloc(size_t bytes);
+void b2_host_free(void* p);
+
 /* One token for each of the `batch` sequences. `next_greedy` (u32[batch], host, optional) receives
  * the arg-max of each row (first maximum wins, as chat.rs:239); `logits_out` (f32[batch][vocab],
  * host, optional). New entry point: the reference engine has no batch. */

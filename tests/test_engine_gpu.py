@@ -156,6 +156,22 @@ def test_device_greedy_loop_equals_feed_loop(E, micro, micro_path):
     e.close()
 
 
+def test_feed_into_a_page_locked_buffer(E, micro, micro_path):
+    """feed(out=host_buffer) returns the same logits as feed() into a fresh array, and refuses a wrong array."""
+    prompt = micro["prompt"].tolist()
+    a = E.HybridEngine.load(micro_path, max_context=64)
+    b = E.HybridEngine.load(micro_path, max_context=64)
+    ids_h, out_h = b.host_buffer(len(prompt), np.uint32), b.host_buffer(b.vocab)
+    ids_h[:] = prompt
+    want = a.feed(prompt)
+    got = b.feed(ids_h, out=out_h)
+    assert got is out_h and np.array_equal(got, want)
+    with pytest.raises(E.EngineError, match="vocab"):
+        b.feed([1], out=np.zeros(3, np.float32))
+    a.close()
+    b.close()
+
+
 def test_split_attention_long_context_and_bf16_cache(E, micro_path):
     """350 tokens with room for 4096: the attention runs as many slices (most of them empty at
     first), fp32 and bf16 caches, each against the oracle with the same cache rounding."""
