@@ -563,6 +563,18 @@ static cudaError_t opt_in_smem(F* f, size_t bytes) {
     return cudaFuncSetAttribute((const void*)f, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
 }
 
+// k_mma_i8 over `passes` groups of MM_TOK sequences. A grid that gives an SM at most one block (the out projections,
+// the MoE-in matrices) is bound by the latency of its K chunks, one after the other: it takes the deeper ring.
+static cudaError_t launch_mma_i8(const MmaArgs& m, int passes, int nsm, cudaStream_t st) {
+    const dim3 grid(m.total_blocks, passes), block(MM_THREADS);
+    const bool deep = m.total_blocks * passes <= nsm && m.K / MM_KC >= MM_STAGES_DEEP;
+    const size_t smem = (size_t)(deep ? MM_STAGES_DEEP : MM_STAGES) * MM_STAGE_BYTES;
+    cudaError_t e;
+    if (deep) { if ((e = opt_in_smem(k_mma_i8<MM_STAGES_DEEP>, smem)) == cudaSuccess) e = launch_k(k_mma_i8<MM_STAGES_DEEP>, grid, block, smem, st, m); }
+    else { if ((e = opt_in_smem(k_mma_i8<MM_STAGES>, smem)) == cudaSuccess) e = launch_k(k_mma_i8<MM_STAGES>, grid, block, smem, st, m); }
+    return e;
+}
+
 // Tensor-core path for 8 or more sequences (B2_MMA=0 switches it off): scratch for the fp16 activations.
 static bool g_mma = [] { const char* v = getenv("B2_MMA"); return !(v && v[0] == '0'); }();
 struct BatchCtx { __half* xh; int Tpad; };
@@ -609,9 +621,7 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
             e = launch_k(k_prep_x, dim3(p.Tpad), dim3(256), 0, st, p);
             if (e != cudaSuccess) return e;
             m.xh = bc->xh; m.K = a.K; m.T = B; m.conv_w = a.conv_w; m.conv_state = a.conv_state; m.a_log = a.a_log; m.dt_bias = a.dt_bias;
-            const size_t smem = (size_t)MM_STAGES * MM_STAGE_BYTES;
-            e = opt_in_smem(k_mma_i8, smem);
-            if (e == cudaSuccess) e = launch_k(k_mma_i8, dim3(m.total_blocks, p.Tpad / MM_TOK), dim3(MM_THREADS), smem, st, m);
+            e = launch_mma_i8(m, p.Tpad / MM_TOK, nsm, st);
             if (e != cudaSuccess) return e;
             if (argmax_logits) {
                 e = launch_k(k_argmax_rows, dim3(B), dim3(1024), 0, st, argmax_logits, argmax_rows, argmax_stride, a.next_tok, a.pos);
@@ -773,9 +783,9 @@ static cudaError_t launch_q4(Q4Args q, const ChunkTable& small, const ChunkTable
     const int gs = std::max(1, std::min(small.cap, (5 * nsm + row_blocks - 1) / row_blocks));
     const int gb = std::max(1, std::min(big.cap, (2 * nsm + row_blocks - 1) / row_blocks));
     q.chunks = small;
-    if ((e = launch_k(k_mma_q4<1>, dim3(row_blocks, gs), dim3(MM_THREADS), sm1, st, q)) != cudaSuccess) return e;
+    if ((e = launch_k(k_mma_q4<1>, dim3(row_blocks, gs), dim3(Q4_THREADS), sm1, st, q)) != cudaSuccess) return e;
     q.chunks = big;
-    return launch_k(k_mma_q4<4>, dim3(row_blocks, gb), dim3(MM_THREADS), sm4, st, q);
+    return launch_k(k_mma_q4<4>, dim3(row_blocks, gb), dim3(Q4_THREADS), sm4, st, q);
 }
 static cudaError_t launch_experts_mma(const ExpertArgs& a, int T, const ExpertMmaCtx& m, int nsm, cudaStream_t st, b2_engine* prof) {
     cudaError_t e;
@@ -811,9 +821,7 @@ static cudaError_t launch_experts_mma(const ExpertArgs& a, int T, const ExpertMm
     d.seg[0].out = a.ypart + ((size_t)a.local0 * (a.topk + 1) + a.topk) * a.D; d.seg[0].out_stride = (a.topk + 1) * a.D;
     d.seg[0].blocks = (a.D + MM_ROWS - 1) / MM_ROWS;
     d.nseg = 1; d.total_blocks = d.seg[0].blocks; d.xh = m.xh; d.K = a.SH; d.T = a.nlocal;
-    const size_t smem2 = (size_t)MM_STAGES * MM_STAGE_BYTES;
-    if ((e = opt_in_smem(k_mma_i8, smem2)) != cudaSuccess) return e;
-    if ((e = launch_k(k_mma_i8, dim3(d.total_blocks, p3.Tpad / MM_TOK), dim3(MM_THREADS), smem2, st, d)) != cudaSuccess) return e;
+    if ((e = launch_mma_i8(d, p3.Tpad / MM_TOK, nsm, st)) != cudaSuccess) return e;
     if (prof) prof->mark(6, st);
     return cudaSuccess;
 }

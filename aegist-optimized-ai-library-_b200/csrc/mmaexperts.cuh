@@ -102,6 +102,7 @@ __global__ void __launch_bounds__(1024) k_group_picks(const GroupArgs a) {
     trace_out(a.trace);
 }
 
+constexpr int Q4_THREADS = 128;             // 4 warps, one 16-row slab each
 constexpr int Q4_ROWS = 64;                 // weight rows per tile (16 per warp); a pair tile = 32 gate + 32 up
 constexpr int Q4_PA = 160;                  // bytes between code rows in shared memory (128 used)
 constexpr int Q4_STAGE_A = Q4_ROWS * Q4_PA; // 10240
@@ -150,7 +151,7 @@ __device__ __forceinline__ void q4x8_to_h2x4(uint32_t w, uint32_t& p0, uint32_t&
 
 // grid (row blocks, blocks per row block); NT = 8-pick tiles per chunk (1: small table, 4: big table)
 template <int NT>
-__global__ void __launch_bounds__(MM_THREADS) k_mma_q4(const Q4Args a) {
+__global__ void __launch_bounds__(Q4_THREADS) k_mma_q4(const Q4Args a) {
     constexpr int STAGE = q4_stage_bytes(NT);
     constexpr int NCOL = 8 * NT;                  // picks per chunk
     extern __shared__ __align__(128) unsigned char q4_smem[];
@@ -181,7 +182,7 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_q4(const Q4Args a) {
     const int rows_per_tile = a.pair ? Q4_ROWS / 2 : Q4_ROWS;
     const int row0 = blockIdx.x * rows_per_tile * a.row_tiles;
     const int ngroup = a.K >> 6;                 // <= 32
-    for (int p = threadIdx.x; p < n * ngroup; p += MM_THREADS) {
+    for (int p = threadIdx.x; p < n * ngroup; p += Q4_THREADS) {
         const int c = p / ngroup, g = p % ngroup;
         s_xsum[c][g] = a.xsum[(size_t)s_src[c] * ngroup + g];
     }
@@ -200,7 +201,7 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_q4(const Q4Args a) {
         unsigned char* sa = q4_smem + (size_t)st * STAGE;
         unsigned char* ss = sa + Q4_STAGE_A;
         unsigned char* sb = ss + Q4_STAGE_S;
-        for (int p = threadIdx.x; p < Q4_ROWS * 8; p += MM_THREADS) {          // codes: 64 rows x 128 B
+        for (int p = threadIdx.x; p < Q4_ROWS * 8; p += Q4_THREADS) {          // codes: 64 rows x 128 B
             const int r = p >> 3, c = p & 7;
             cp_async16(sa + r * Q4_PA + c * 16, base + a.off_q + (size_t)weight_row(rt, r) * rowbytes + (size_t)kc * 128 + c * 16);
         }
@@ -211,7 +212,7 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_q4(const Q4Args a) {
         }
         // activations of the chunk's picks only: columns 0..NCOL-1 hi, NCOL..2 NCOL-1 lo; the other
         // columns keep whatever shared memory held (their products are never stored)
-        for (int p = threadIdx.x; p < 2 * n * (MM_KC / 8); p += MM_THREADS) {
+        for (int p = threadIdx.x; p < 2 * n * (MM_KC / 8); p += Q4_THREADS) {
             const int j = p / (MM_KC / 8), c = p % (MM_KC / 8);
             const int part = j >= n, tc = part ? j - n : j;
             const int src_row = s_src[tc];

@@ -28,8 +28,9 @@ constexpr int MM_TOK = 32;           // sequences per pass (64 columns: hi and l
 constexpr int MM_PA = 320;           // bytes between weight rows in shared memory
 constexpr int MM_PB = 528;           // bytes between activation columns in shared memory
 constexpr int MM_STAGES = 2;          // two blocks of 4 warps fit an SM (2 x 106 KB); with 3 stages only one did, and it ran slower
+constexpr int MM_STAGES_DEEP = 4;     // for grids of at most one block per SM: 212 KB, three K chunks in flight
 constexpr int MM_STAGE_BYTES = MM_ROWS * MM_PA + 2 * MM_TOK * MM_PB;   // 20480 + 33792
-constexpr int MM_THREADS = 128;
+constexpr int MM_THREADS = 256;       // 8 warps: warp = (half of the sequences) x (16-row slab)
 
 struct PrepArgs {
     unsigned long long* trace;   // step timeline slot of this launch, or null
@@ -193,12 +194,18 @@ __device__ __forceinline__ void i8x4_to_h2x2(uint32_t w, uint32_t& h01, uint32_t
     h23 = *reinterpret_cast<uint32_t*>(&hb);
 }
 
-// grid (total_blocks, passes of MM_TOK sequences). NMAT = 2 for gate/up pairs handled by one warp.
+// grid (total_blocks, passes of MM_TOK sequences). NS = stages of the K-chunk ring (the same sums in the same
+// order for every NS). Warps 0-3 take sequences 0-15 of the pass, warps 4-7 sequences 16-31, each its 16-row slab:
+// a block alone on an SM (matrices of few rows) then still has two warps per scheduler to hide the conversion and
+// mma latencies, which is what bounds these launches.
+template <int NS>
 __global__ void __launch_bounds__(MM_THREADS) k_mma_i8(const MmaArgs a) {
     extern __shared__ __align__(128) unsigned char mm_smem[];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31, warp = (threadIdx.x >> 5) & 3, half = threadIdx.x >> 7;
     const int gid = lane >> 2, tid = lane & 3;
     const int t0 = blockIdx.y * MM_TOK;
+    // this warp's four n-tiles of the 64 columns: hi parts 2 half, 2 half + 1, lo parts 4 + 2 half, 5 + 2 half
+    const int ntile[4] = {2 * half, 2 * half + 1, 2 * half + 4, 2 * half + 5};
     grid_dep_launch();
     trace_in(a.trace, 10, gridDim.x);
     // which matrix and which 64 rows
@@ -237,20 +244,20 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_i8(const MmaArgs a) {
     };
 
     grid_dep_wait();          // the activations are the previous kernel's output
-    for (int i = 0; i < MM_STAGES - 1; i++) {
+    for (int i = 0; i < NS - 1; i++) {
         if (i < nk) load_stage(i, i); else cp_async_commit();
     }
-    float acc[8][4];
+    float acc[4][4];
 #pragma unroll
-    for (int j = 0; j < 8; j++)
+    for (int j = 0; j < 4; j++)
 #pragma unroll
         for (int q = 0; q < 4; q++) acc[j][q] = 0.f;
 
     for (int kc = 0; kc < nk; kc++) {
-        cp_async_wait<MM_STAGES - 2>();
+        cp_async_wait<NS - 2>();
         __syncthreads();
-        if (kc + MM_STAGES - 1 < nk) load_stage(kc + MM_STAGES - 1, (kc + MM_STAGES - 1) % MM_STAGES); else cp_async_commit();
-        const unsigned char* sa = mm_smem + (size_t)(kc % MM_STAGES) * MM_STAGE_BYTES;
+        if (kc + NS - 1 < nk) load_stage(kc + NS - 1, (kc + NS - 1) % NS); else cp_async_commit();
+        const unsigned char* sa = mm_smem + (size_t)(kc % NS) * MM_STAGE_BYTES;
         const unsigned char* sb = sa + MM_ROWS * MM_PA;
         const unsigned char* ar0 = sa + (warp * 16 + gid) * MM_PA;
         const unsigned char* ar1 = ar0 + 8 * MM_PA;
@@ -265,10 +272,10 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_i8(const MmaArgs a) {
                 bf16x8_to_h2x4(w1, h1);
                 const uint32_t afa[4] = {h0[0], h1[0], h0[1], h1[1]}, afb[4] = {h0[2], h1[2], h0[3], h1[3]};
 #pragma unroll
-                for (int nt = 0; nt < 8; nt++) {
-                    const uint4 x0 = *reinterpret_cast<const uint4*>(sb + (nt * 8 + gid) * MM_PB + sbk * 64 + tid * 16);
-                    mma16816(acc[nt], afa, x0.x, x0.y);
-                    mma16816(acc[nt], afb, x0.z, x0.w);
+                for (int j = 0; j < 4; j++) {
+                    const uint4 x0 = *reinterpret_cast<const uint4*>(sb + (ntile[j] * 8 + gid) * MM_PB + sbk * 64 + tid * 16);
+                    mma16816(acc[j], afa, x0.x, x0.y);
+                    mma16816(acc[j], afb, x0.z, x0.w);
                 }
             }
             continue;
@@ -286,44 +293,44 @@ __global__ void __launch_bounds__(MM_THREADS) k_mma_i8(const MmaArgs a) {
                 i8x4_to_h2x2(wb[j], af[j][1], af[j][3]);
             }
 #pragma unroll
-            for (int nt = 0; nt < 8; nt++) {
+            for (int j = 0; j < 4; j++) {
                 // column 8 nt + gid: 16 halves = this thread's k range of the super-block
-                const unsigned char* bp = sb + (nt * 8 + gid) * MM_PB + sbk * 128 + tid * 32;
+                const unsigned char* bp = sb + (ntile[j] * 8 + gid) * MM_PB + sbk * 128 + tid * 32;
                 const uint4 x0 = *reinterpret_cast<const uint4*>(bp);
                 const uint4 x1 = *reinterpret_cast<const uint4*>(bp + 16);
-                mma16816(acc[nt], af[0], x0.x, x0.y);
-                mma16816(acc[nt], af[1], x0.z, x0.w);
-                mma16816(acc[nt], af[2], x1.x, x1.y);
-                mma16816(acc[nt], af[3], x1.z, x1.w);
+                mma16816(acc[j], af[0], x0.x, x0.y);
+                mma16816(acc[j], af[1], x0.z, x0.w);
+                mma16816(acc[j], af[2], x1.x, x1.y);
+                mma16816(acc[j], af[3], x1.z, x1.w);
             }
         }
     }
     cp_async_wait<0>();
 
     // epilogue. Thread holds rows (gid, gid + 8) of its warp's slab and, in n-tile nt, columns 2 tid, 2 tid + 1:
-    // sequences 8 nt + 2 tid (+1) for nt < 4 (hi) and the same sequences' lo parts in nt + 4.
+    // sequences 8 nt + 2 tid (+1) for nt < 4 (hi, acc[0], acc[1]) and the same sequences' lo parts (acc[2], acc[3]).
     __shared__ float gate_s[2][16][MM_TOK + 1];     // pairs: the gate warps hand their sums to the up warps
     if (pair && warp < 2) {
 #pragma unroll
-        for (int nt = 0; nt < 4; nt++)
+        for (int j = 0; j < 2; j++)
 #pragma unroll
             for (int q = 0; q < 4; q++) {
-                const int r = gid + (q >> 1) * 8, col = nt * 8 + 2 * tid + (q & 1);
-                gate_s[warp][r][col] = acc[nt][q] + acc[nt + 4][q];
+                const int r = gid + (q >> 1) * 8, col = ntile[j] * 8 + 2 * tid + (q & 1);
+                gate_s[warp][r][col] = acc[j][q] + acc[j + 2][q];
             }
     }
     if (pair) __syncthreads();
     if (pair && warp < 2) { trace_out(a.trace); return; }
 #pragma unroll
-    for (int nt = 0; nt < 4; nt++) {
+    for (int j = 0; j < 2; j++) {
 #pragma unroll
         for (int q = 0; q < 4; q++) {
             const int rl = gid + (q >> 1) * 8;                               // row inside the warp's slab
-            const int col = nt * 8 + 2 * tid + (q & 1);
+            const int col = ntile[j] * 8 + 2 * tid + (q & 1);
             const int tok = t0 + col;
             const int row = pair ? row0 + (warp - 2) * 16 + rl : row0 + warp * 16 + rl;
             if (tok >= a.T || row >= sg.rows) continue;
-            const float dot = acc[nt][q] + acc[nt + 4][q];
+            const float dot = acc[j][q] + acc[j + 2][q];
             float* out = sg.out + (size_t)tok * sg.out_stride;
             switch (sg.kind) {
             case SEG_I8: out[row] = bf(sg.s[row]) * dot; break;
