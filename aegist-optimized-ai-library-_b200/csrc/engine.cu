@@ -93,17 +93,7 @@ static size_t dtype_size(const std::string& d) {
     return 0;
 }
 
-// Blocks per SM of the streaming GEMV kernel (B2_GEMV_CTAS overrides; for experiments).
-// Row-per-lane GEMV kernel (k_rowgemv) instead of the row-per-warp one (B2_ROWGEMV=0 switches back).
-static bool g_rowgemv = [] { const char* v = getenv("B2_ROWGEMV"); return !(v && v[0] == '0'); }();
-// Tensor-core GEMV (k_tcgemv) for the int8 matrices of small batches (B2_TCGEMV=0 switches back to k_rowgemv).
-// Expert kernels for fewer than 8 tokens (k_moe_gu1 / k_moe_down1; B2_MOE1=0 switches back to the per-pick kernels).
-static bool g_moe1 = [] { const char* v = getenv("B2_MOE1"); return !(v && v[0] == '0'); }();
-// Tensor-core decode attention for a bf16 cache (k_attn_mma; B2_ATTN_MMA=0 switches back to k_attn).
-static bool g_attn_mma = [] { const char* v = getenv("B2_ATTN_MMA"); return !(v && v[0] == '0'); }();
-static bool g_tcgemv = [] { const char* v = getenv("B2_TCGEMV"); return !(v && v[0] == '0'); }();
-constexpr int g_tc_warps = 16;   // compute warps per block
-static int g_gemv_ctas_per_sm = [] { const char* v = getenv("B2_GEMV_CTAS"); return v ? atoi(v) : 2; }();
+constexpr int g_tc_warps = 16;   // compute warps per block of k_tcgemv
 static int down_row_blocks(int D) { return (D + DOWN_ROWS - 1) / DOWN_ROWS; }
 
 }  // namespace b2
@@ -478,7 +468,7 @@ int b2_engine::finish() {
     CU(dalloc(&top_ptr, (size_t)B * c.TOPK));
     CU(dalloc(&actq, (size_t)B * c.TOPK * M1_PLANES * c.I));
     CU(dalloc(&asc, (size_t)B * c.TOPK * std::max(1, c.I / 32))); CU(dalloc(&asum, (size_t)B * c.TOPK * std::max(1, c.I / 32)));
-    head_grid = g_rowgemv ? std::min((c.V + 31) / 32, nsm) : std::min((c.V + 7) / 8, g_gemv_ctas_per_sm * nsm);
+    head_grid = std::min((c.V + 31) / 32, nsm);
     CU(dalloc(&part_val, (size_t)B * head_grid)); CU(dalloc(&part_idx, (size_t)B * head_grid));
     // attention: enough slices to fill the GPU, but at least 64 positions each at full context
     nsplit = std::max(1, std::min({64, (2 * nsm) / std::max(1, c.KV * B), (cap + 63) / 64}));
@@ -505,7 +495,7 @@ int b2_engine::finish() {
         CU(dalloc(&rec_all, Bg * rw));
         CU(dalloc(&recv_y, Bg * (c.TOPK + 1) * c.D));
     }
-    CU(cudaMallocHost((void**)&h_pin, std::max(B, 1) * sizeof(uint32_t) * 2));
+    CU(cudaMallocHost((void**)&h_pin, (std::max(B, 1) * 2 + 1) * sizeof(uint32_t)));   // ids | arg-max | device error word
     CU(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
     CU(cudaEventCreate(&ev0));
     CU(cudaEventCreate(&ev1));
@@ -521,8 +511,6 @@ int b2_engine::finish() {
     return build_graph();
 }
 
-// Programmatic dependent launch for every kernel of a step (B2_PDL=0 turns it off).
-static bool g_pdl = [] { const char* v = getenv("B2_PDL"); return !(v && v[0] == '0'); }();
 
 static int g_launch_count = 0;   // kernels launched so far (a step's count is the difference)
 
@@ -553,7 +541,7 @@ static cudaError_t launch_k(void (*kernel)(KArgs...), dim3 grid, dim3 block, siz
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = g_pdl ? 1 : 0;
+    cfg.numAttrs = 1;   // programmatic dependent launch for every kernel of a step
     return cudaLaunchKernelEx(&cfg, kernel, with_trace(args, 0)...);
 }
 
@@ -575,8 +563,7 @@ static cudaError_t launch_mma_i8(const MmaArgs& m, int passes, int nsm, cudaStre
     return e;
 }
 
-// Tensor-core path for 8 or more sequences (B2_MMA=0 switches it off): scratch for the fp16 activations.
-static bool g_mma = [] { const char* v = getenv("B2_MMA"); return !(v && v[0] == '0'); }();
+// Tensor-core path for 8 or more sequences: scratch for the fp16 activations.
 struct BatchCtx { __half* xh; int Tpad; };
 static void seal(GemvArgs& a, int K);
 
@@ -585,7 +572,7 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
     GemvArgs a = a0;
     if (a.x_stride == 0) a.x_stride = a.K;
     cudaError_t e;
-    if (g_rowgemv && g_mma && bc && bc->xh && B >= 8 && B <= bc->Tpad && a.K % MM_KC == 0) {
+    if (bc && bc->xh && B >= 8 && B <= bc->Tpad && a.K % MM_KC == 0) {
         // int8 matrices (except the head with its arg-max) go to the tensor cores; bf16 rows stay on k_rowgemv
         MmaArgs m{};
         GemvArgs rest = a;
@@ -639,7 +626,7 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
             grid_override = 0;
         }
     }
-    if (g_rowgemv && g_tcgemv && tc_shape_ok(a.K, g_tc_warps)) {
+    if (tc_shape_ok(a.K, g_tc_warps)) {
         // int8 products on the tensor cores; one block per SM, NB sequences per pass. Rows per tile (r for
         // 2048-byte slots, r / 2 for wide rows and pairs) such that the longest block has the least to stream.
         int best_r = 32;
@@ -676,8 +663,8 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
 #undef TCG
         return e;
     }
-    if (g_rowgemv) {
-        // one block of 1024 threads per SM, NB sequences per pass
+    {
+        // shapes the tensor-core kernel does not take: one block of 1024 threads per SM, NB sequences per pass
         const int grid = grid_override ? grid_override : std::max(1, std::min(a.total_jobs, nsm));
         if (B >= 2) {
             const size_t smem = (size_t)2 * RL_STAGE_BYTES + (size_t)4 * a.K * 4 + (size_t)2 * 4 * RL_WARPS * 32 * 4;
@@ -690,14 +677,6 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
         }
         return e;
     }
-    const int grid = grid_override ? grid_override : std::max(1, std::min(a.total_jobs, g_gemv_ctas_per_sm * nsm));
-    const size_t smem = (size_t)RING_STAGES * RING_STAGE_BYTES;
-    const int maxc = (a.K + 511) / 512;
-    dim3 g(grid, B);
-    if (maxc <= 1) { e = opt_in_smem(k_gemv_norm<1>, smem); if (e == cudaSuccess) e = launch_k(k_gemv_norm<1>, g, GEMV_THREADS, smem, st, a); }
-    else if (maxc == 2) { e = opt_in_smem(k_gemv_norm<2>, smem); if (e == cudaSuccess) e = launch_k(k_gemv_norm<2>, g, GEMV_THREADS, smem, st, a); }
-    else { e = opt_in_smem(k_gemv_norm<4>, smem); if (e == cudaSuccess) e = launch_k(k_gemv_norm<4>, g, GEMV_THREADS, smem, st, a); }
-    return e;
 }
 
 static Seg make_seg(int kind, const void* w, const uint16_t* s, int rows, float* out, int out_stride) {
@@ -711,9 +690,7 @@ static void seal(GemvArgs& a, int K) {
     a.total_jobs = 0;
     for (int i = 0; i < a.nseg; i++) {
         Seg& g = a.seg[i];
-        const bool i8 = g.kind == SEG_I8 || g.kind == SEG_I8_CONV || g.kind == SEG_I8_ARGMAX || g.kind == SEG_I8_SILU || g.kind == SEG_I8_ACC;
-        if (g_rowgemv) g.jobs = (g.rows + rl_tile_rows(g.kind, K) - 1) / rl_tile_rows(g.kind, K);
-        else g.jobs = i8 ? (g.rows + 7) / 8 : (g.rows + 3) / 4;
+        g.jobs = (g.rows + rl_tile_rows(g.kind, K) - 1) / rl_tile_rows(g.kind, K);
         a.total_jobs += g.jobs;
     }
 }
@@ -722,25 +699,13 @@ static void seal(GemvArgs& a, int K);
 static Seg make_seg(int kind, const void* w, const uint16_t* s, int rows, float* out, int out_stride);
 
 static void launch_proj(const ProjArgs& a, int B, int nsm, cudaStream_t st, const BatchCtx* bc = nullptr) {
-    if (g_rowgemv) {
-        GemvArgs g{};
-        g.seg[0] = make_seg(SEG_I8_ACC, a.w, a.s, a.N, a.x, a.N);
-        g.nseg = 1;
-        seal(g, a.K);
-        g.x = a.in; g.x_stride = a.K; g.norm_w = nullptr; g.eps = a.eps;
-        if (a.mode == 0) { g.gn_w = a.gn_w; g.z = a.z; g.DV = a.DV; }
-        launch_gemv(g, B, nsm, st, 0, bc);
-        return;
-    }
-    // rows per block a multiple of 4 (four warp pairs per block), one wave of blocks
-    const int rpb = 4 * PROJ_RPW;     // the kernel covers exactly this many rows per block
-    const int grid = (a.N + rpb - 1) / rpb;
-    const size_t smem = (size_t)(2 * rpb) * 4;
-    const int maxc = (a.K / 2 + 511) / 512;
-    dim3 g(grid, B);
-    if (maxc <= 1) launch_k(k_proj_out<1>, g, THREADS, smem, st, a);
-    else if (maxc == 2) launch_k(k_proj_out<2>, g, THREADS, smem, st, a);
-    else launch_k(k_proj_out<4>, g, THREADS, smem, st, a);
+    GemvArgs g{};
+    g.seg[0] = make_seg(SEG_I8_ACC, a.w, a.s, a.N, a.x, a.N);
+    g.nseg = 1;
+    seal(g, a.K);
+    g.x = a.in; g.x_stride = a.K; g.norm_w = nullptr; g.eps = a.eps;
+    if (a.mode == 0) { g.gn_w = a.gn_w; g.z = a.z; g.DV = a.DV; }
+    launch_gemv(g, B, nsm, st, 0, bc);
 }
 
 static void launch_delta(const DeltaArgs& a, int DK, int B, cudaStream_t st) {
@@ -838,7 +803,7 @@ static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaS
     }
     const int hr = a.RD / 2;
     const bool rope_ok = hr % 32 == 0 || (hr > 0 && hr < 32 && (hr & (hr - 1)) == 0);   // pairs in one lane, or a power of two lanes apart
-    if (!f32 && g_attn_mma && G <= 8 && rope_ok && (HD == 256 || HD == 128 || HD == 64)) {
+    if (!f32 && G <= 8 && rope_ok && (HD == 256 || HD == 128 || HD == 64)) {
         // bf16 cache: both contractions on the tensor cores; two tile buffers when a slice can span several tiles
         const int nbuf = tiles_per_slice > 1 ? 2 : 1;
         cudaError_t e;
@@ -859,6 +824,37 @@ static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaS
 #undef ATT
     launch_k(k_attn_merge, dim3(a.H, B), THREADS, 0, st, a, HD);
     return cudaSuccess;
+}
+
+// The expert kernels for fewer than 8 tokens (moe1.cuh): shapes they take, and their two launches. `x_in` rows are
+// normalised with `norm_w` when it is given; the result is added into `xout`.
+static bool moe1_shape_ok(const Cfg& c) {
+    return (c.D == 512 || c.D == 1024 || c.D == 2048 || c.D == 4096) && c.I >= 128 && c.I <= 2048 && (c.I & (c.I - 1)) == 0 &&
+           c.SH % 128 == 0 && c.TOPK <= 8 && c.E <= 256;
+}
+struct Moe1Ctx { const uint8_t** top_ptr; int8_t* actq; float* asc; float* asum; };
+static cudaError_t launch_moe1(const Cfg& c, const float* rlogits, const float* x_in, const uint16_t* norm_w, const uint8_t* const* eptr,
+                               int* top_idx, float* top_w, const Moe1Ctx& m, const float* sh_act, const float* sgate, const int8_t* shd_w,
+                               const uint16_t* shd_s, float* xout, int* err, int B, cudaStream_t st, b2_engine* prof) {
+    Gu1Args g{};
+    g.logits = rlogits; g.x = x_in; g.norm_w = norm_w; g.eps = c.eps; g.eptr = eptr;
+    g.off_gu_s = c.off_gu_s(); g.off_gu_m = c.off_gu_m(); g.D = c.D; g.I = c.I; g.E = c.E; g.topk = c.TOPK;
+    g.top_idx = top_idx; g.top_w = top_w; g.top_ptr = m.top_ptr; g.actq = m.actq; g.asc = m.asc; g.asum = m.asum; g.err = err;
+    const int gx = c.TOPK * c.I / M1_GU_PAIRS;
+    cudaError_t ce = opt_in_smem(k_moe_gu1, m1_gu_smem(c.D));
+    if (ce == cudaSuccess) ce = launch_k(k_moe_gu1, dim3(gx, B), dim3(M1_GU_THREADS), m1_gu_smem(c.D), st, g);
+    if (prof) prof->mark(5, st);
+    Down1Args d{};
+    d.top_ptr = m.top_ptr; d.top_w = top_w; d.actq = m.actq; d.asc = m.asc; d.asum = m.asum; d.sh_act = sh_act; d.sg = sgate;
+    d.shd_w = shd_w; d.shd_s = shd_s;
+    d.off_dn_q = c.off_dn_q(); d.off_dn_s = c.off_dn_s(); d.off_dn_m = c.off_dn_m();
+    d.D = c.D; d.I = c.I; d.SH = c.SH; d.topk = c.TOPK; d.xout = xout;
+    const size_t dsm = m1_down_smem(c.I, c.SH, c.TOPK);
+    if (ce == cudaSuccess) ce = opt_in_smem(k_moe_down1, dsm);
+    if (ce == cudaSuccess)
+        ce = launch_k(k_moe_down1, dim3((c.D + M1_DOWN_ROWS - 1) / M1_DOWN_ROWS, B), dim3(2 * (c.TOPK + 1) * 32), dsm, st, d);
+    if (prof) prof->mark(6, st);
+    return ce;
 }
 
 // One decode step for all B sequences: token ids in d_tok, positions in d_pos.
@@ -931,32 +927,16 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.nseg = 3; seal(a, c.D);
             a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D; a.err = d_err;
             // fewer than 8 tokens on one GPU: the top-8 moves into the expert kernel and the experts are spread over all SMs
-            const bool moe1 = g_moe1 && ep_world == 1 && B < 8 && (c.D == 512 || c.D == 1024 || c.D == 2048 || c.D == 4096) && c.I >= 128 && c.I <= 2048 && (c.I & (c.I - 1)) == 0 &&
-                              c.SH % 128 == 0 && c.TOPK <= 8 && c.E <= 256;
+            const bool moe1 = ep_world == 1 && B < 8 && moe1_shape_ok(c);
             a.finisher = moe1 ? FIN_NONE : FIN_TOPK; a.counter = d_counter; a.E = c.E; a.topk = c.TOPK;
             a.top_idx = top_idx + (size_t)li * B * c.TOPK; a.top_w = top_w + (size_t)li * B * c.TOPK;
             launch_gemv(a, B, nsm, st, 0, bc);
             mark(1, st);
             if (moe1) {
-                Gu1Args g{};
-                g.logits = rlogits; g.x = x; g.norm_w = l.norm2; g.eps = c.eps; g.eptr = l.eptr;
-                g.off_gu_s = c.off_gu_s(); g.off_gu_m = c.off_gu_m(); g.D = c.D; g.I = c.I; g.E = c.E; g.topk = c.TOPK;
-                g.top_idx = a.top_idx; g.top_w = a.top_w; g.top_ptr = top_ptr; g.actq = actq; g.asc = asc; g.asum = asum; g.err = d_err;
-                const int gx = c.TOPK * c.I / M1_GU_PAIRS;
-                cudaError_t ce = opt_in_smem(k_moe_gu1, m1_gu_smem(c.D));
-                if (ce == cudaSuccess) ce = launch_k(k_moe_gu1, dim3(gx, B), dim3(M1_GU_THREADS), m1_gu_smem(c.D), st, g);
-                mark(5, st);
-                Down1Args d{};
-                d.top_ptr = top_ptr; d.top_w = a.top_w; d.actq = actq; d.asc = asc; d.asum = asum; d.sh_act = sh_act; d.sg = sgate;
-                d.shd_w = (const int8_t*)l.sh_down.w; d.shd_s = l.sh_down.s;
-                d.off_dn_q = c.off_dn_q(); d.off_dn_s = c.off_dn_s(); d.off_dn_m = c.off_dn_m();
-                d.D = c.D; d.I = c.I; d.SH = c.SH; d.topk = c.TOPK; d.xout = x;
-                const size_t dsm = m1_down_smem(c.I, c.SH, c.TOPK);
-                if (ce == cudaSuccess) ce = opt_in_smem(k_moe_down1, dsm);
-                if (ce == cudaSuccess)
-                    ce = launch_k(k_moe_down1, dim3((c.D + M1_DOWN_ROWS - 1) / M1_DOWN_ROWS, B), dim3(2 * (c.TOPK + 1) * 32), dsm, st, d);
+                const Moe1Ctx mc{top_ptr, actq, asc, asum};
+                cudaError_t ce = launch_moe1(c, rlogits, x, l.norm2, l.eptr, a.top_idx, a.top_w, mc, sh_act, sgate, (const int8_t*)l.sh_down.w,
+                                             l.sh_down.s, x, d_err, B, st, this);
                 if (ce != cudaSuccess) return fail("expert kernels: %s", cudaGetErrorString(ce));
-                mark(6, st);
                 n += 3;
             } else {
             ExpertArgs x2{};
@@ -964,9 +944,9 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             x2.off_gu_s = c.off_gu_s(); x2.off_gu_m = c.off_gu_m(); x2.off_dn_q = c.off_dn_q(); x2.off_dn_s = c.off_dn_s(); x2.off_dn_m = c.off_dn_m();
             x2.norm_w = l.norm2; x2.eps = c.eps; x2.act = act; x2.sh_act = sh_act; x2.sg = sgate;
             x2.shd_w = l.sh_down.w; x2.shd_s = l.sh_down.s; x2.SH = c.SH; x2.xout = x; x2.err = d_err;
-            x2.ypart = ypart; x2.counter = d_dcounter;
+            x2.ypart = ypart; x2.counter = d_dcounter; x2.null_is_error = ep_world == 1;
             const int Tg = B * ep_world;
-            const bool grouped = g_mma && xh && Tg >= 16 && Tg * c.TOPK <= GQ_MAXP && c.D % MM_KC == 0 && c.I % MM_KC == 0 &&
+            const bool grouped = xh && Tg >= 16 && Tg * c.TOPK <= GQ_MAXP && c.D % MM_KC == 0 && c.I % MM_KC == 0 &&
                                  c.SH % MM_KC == 0 && c.D <= 2048 && c.I <= 2048 && c.E <= 256;
             const ExpertMmaCtx mctx{g_list, g_chunk, cap_small, cap_big, xh, acth, xsum_tok, xsum_act};
             if (ep_world == 1) {
@@ -1041,15 +1021,19 @@ int b2_engine::build_graph() {
     return 0;
 }
 
+// The device error word travels to page-locked memory on the stream, so a feed pays one synchronisation for its
+// results and the check together.
 int b2_engine::check_device_error() {
-    int h = 0;
-    CU(cudaMemcpyAsync(&h, d_err, 4, cudaMemcpyDeviceToHost, stream));
+    uint32_t* slot = h_pin + 2 * std::max(B, 1);
+    CU(cudaMemcpyAsync(slot, d_err, 4, cudaMemcpyDeviceToHost, stream));
     CU(cudaStreamSynchronize(stream));
+    const int h = (int)*slot;
     if (h) {
         cudaMemsetAsync(d_err, 0, 4, stream);
         cudaStreamSynchronize(stream);
         if (h == 1) return fail("a token id is outside the vocabulary (%d)", c.V);
         if (h == 3) return fail("a bulk copy into shared memory did not complete (bounded wait gave up)");
+        if (h == 4) return fail("a block waited too long for another block's results (bounded wait gave up)");
         return fail("router returned an expert outside 0..%d", c.E - 1);
     }
     return 0;
@@ -1289,8 +1273,7 @@ int b2_feed(b2_engine* e, const uint32_t* ids, int n, float* logits_out) {
         if (e->run_steps(1)) return 1;
     }
     if (logits_out) CUE(cudaMemcpyAsync(logits_out, e->logits, (size_t)e->c.V * 4, cudaMemcpyDeviceToHost, e->stream));
-    CUE(cudaStreamSynchronize(e->stream));
-    return 0;
+    return e->check_device_error();
 }
 
 void* b2_host_alloc(size_t bytes) {
@@ -1314,7 +1297,7 @@ int b2_feed_batch(b2_engine* e, const uint32_t* ids, uint32_t* next_greedy, floa
     if (e->run_steps(1)) return 1;
     if (next_greedy) CUE(cudaMemcpyAsync(e->h_pin + e->B, e->d_next, (size_t)e->B * 4, cudaMemcpyDeviceToHost, e->stream));
     if (logits_out) CUE(cudaMemcpyAsync(logits_out, e->logits, (size_t)e->B * e->c.V * 4, cudaMemcpyDeviceToHost, e->stream));
-    CUE(cudaStreamSynchronize(e->stream));
+    if (e->check_device_error()) return 1;
     if (next_greedy) memcpy(next_greedy, e->h_pin + e->B, (size_t)e->B * 4);
     return 0;
 }

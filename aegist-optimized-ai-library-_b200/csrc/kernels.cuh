@@ -1,29 +1,28 @@
 // Decode-step kernels for the hybrid-MoE token loop, written for sm_100a.
 //
 // One decode step of one layer is six launches (the reference's CUDA engine uses 16-18,
-// aegist_rs/src/hybrid.rs:787-993):
+// aegist_rs/src/hybrid.rs:787-993); which kernel fills a role depends on the number of sequences:
 //
-//   DeltaNet layer                                   attention layer
-//   k_gemv_norm   norm1 + in_qkv(+conv+SiLU) + in_z   k_gemv_norm   norm1 + q, k, v
+//   DeltaNet layer                                    attention layer
+//   GEMV group    norm1 + in_qkv(+conv+SiLU) + in_z    GEMV group    norm1 + q, k, v
 //                 + in_b(sigmoid) + in_a(decay)
-//   k_delta_step  L2 norm + gated delta rule          k_attn        q/k norm + RoPE + KV append +
-//                                                                   split-K attention + merge + gate
-//   k_proj_out    gated RMSNorm + out, += residual    k_proj_out    o, += residual
+//   k_delta_step  L2 norm + gated delta rule           k_attn(_mma)  q/k norm + RoPE + KV append +
+//                                                      k_attn_merge  split-K attention, merge, gate
+//   GEMV group    gated RMSNorm + out, += residual     GEMV group    o, += residual
 //   -- then, for every layer --
-//   k_gemv_norm   norm2 + router logits + shared gate/up(+SiLU) + shared_gate, then top-8 in the
-//                 last block to finish
-//   k_expert_gu   4-bit gate/up GEMV + SiLU for the 8 picked experts
-//   k_expert_down 4-bit down GEMV of the 8 picks (weighted, fixed order) + shared down, += residual
+//   GEMV group    norm2 + router logits + shared gate/up(+SiLU) + shared_gate (+ top-8)
+//   expert gate/up, expert down + shared down, += residual
 //
-// All arithmetic is fp32 with fp32 accumulation (the reference's kernels do the same,
-// aegist_rs/kernels/aegist.cu:1-6). Weights stream from HBM exactly once per sequence with 128-bit
-// loads and are widened in registers; the activation vector of a GEMV lives in registers (each lane
-// always owns the same 16-value slices of it, read straight from L2, normalised per warp), because
-// at one byte of weight per FMA the shared-memory port could not feed fp32 activations at HBM
-// speed. Integer-to-float conversion instructions run at a sixteenth of the FMA rate on this part,
-// so weights are widened with byte permutes into the mantissa of a magic constant instead
-// (i8_to_f32x4, q4 codes as 1 + code/16). Each kernel covers one sequence per blockIdx.y; grids
-// are sized in multiples of the SM count by the host.
+// A GEMV group is k_tcgemv (tcgemv.cuh; k_rowgemv, rowgemv.cuh, for shapes it does not take) up to 7
+// sequences and k_prep_x + k_mma_i8 (mmagemm.cuh) from 8 on; the experts are k_moe_gu1 / k_moe_down1
+// (moe1.cuh) up to 7 sequences, k_expert_gu / k_expert_down (this file) for 8 to 15 tokens and wherever
+// the faster kernels do not take the shape, and the grouped GEMM (mmaexperts.cuh) from 16 tokens on.
+//
+// All arithmetic is fp32 with fp32 accumulation or exact integer products (the reference's kernels
+// are fp32, aegist_rs/kernels/aegist.cu:1-6). Weights stream from HBM exactly once per step.
+// Integer-to-float conversion instructions run at a sixteenth of the FMA rate on this part, so the
+// CUDA-core kernels widen weights with byte permutes into the mantissa of a magic constant instead
+// (q4 codes as 1 + code/16). Grids are sized in multiples of the SM count by the host.
 //
 // Cross-block steps (router top-8, arg-max over the vocabulary, summing the expert picks) are done
 // by whichever block finishes last (a counter and a fence), never by waiting on another block.
@@ -126,16 +125,6 @@ __device__ __forceinline__ float dot16_i8(const int4& w, const float* x) {
     }
     return (a[0] + a[1]) + (a[2] + a[3]);
 }
-__device__ __forceinline__ float dot8_bf16(const int4& w, const float* x) {
-    float a = 0.f;
-    const uint32_t v[4] = {(uint32_t)w.x, (uint32_t)w.y, (uint32_t)w.z, (uint32_t)w.w};
-#pragma unroll
-    for (int i = 0; i < 4; i++) {
-        a = fmaf(x[2 * i], bflo(v[i]), a);
-        a = fmaf(x[2 * i + 1], bfhi(v[i]), a);
-    }
-    return a;
-}
 // 32 four-bit codes (even index in the low nibble) against 32 activations. Each code is placed in
 // the top four mantissa bits of 1.0 (a shift and one logic op), giving f = 1 + code/16 exactly; the
 // function returns sum f * x, and the caller recovers sum code * x = 16 * (result - sum x).
@@ -152,53 +141,6 @@ __device__ __forceinline__ float dot32_q4f(const int4& w, const float* x) {
         }
     }
     return (a[0] + a[1]) + (a[2] + a[3]);
-}
-
-// This lane's 16-value slices of a vector in global memory: slice j is values [16*(lane + 32*j), +16)
-// of `x` (zeros past the end), optionally followed by the zero-centred RMSNorm of the whole vector
-// (aegist/hybrid.py:119-130: x * rsqrt(mean x^2 + eps) * (1 + w)). One warp covers K <= 512 * MAXC
-// values, so the mean needs one shuffle reduction and no shared memory.
-template <int MAXC>
-__device__ __forceinline__ void load_x_znorm(float (&xr)[MAXC][16], const float* __restrict__ x,
-                                             const uint16_t* __restrict__ w, float eps, int K, int lane) {
-    const int nchunk = K >> 4;
-    float ss = 0.f;
-#pragma unroll
-    for (int j = 0; j < MAXC; j++) {
-        const int c = lane + 32 * j;
-        if (c < nchunk) {
-            const float4* p = reinterpret_cast<const float4*>(x + 16 * c);
-#pragma unroll
-            for (int q = 0; q < 4; q++) {
-                const float4 t = p[q];
-                xr[j][4 * q] = t.x; xr[j][4 * q + 1] = t.y; xr[j][4 * q + 2] = t.z; xr[j][4 * q + 3] = t.w;
-                ss = fmaf(t.x, t.x, ss); ss = fmaf(t.y, t.y, ss); ss = fmaf(t.z, t.z, ss); ss = fmaf(t.w, t.w, ss);
-            }
-        } else {
-#pragma unroll
-            for (int q = 0; q < 16; q++) xr[j][q] = 0.f;
-        }
-    }
-    if (w == nullptr) return;
-    ss = warp_sum(ss);
-    const float r = 1.0f / sqrtf(ss / (float)K + eps);
-#pragma unroll
-    for (int j = 0; j < MAXC; j++) {
-        const int c = lane + 32 * j;
-        if (c < nchunk) {
-            const uint4* pw = reinterpret_cast<const uint4*>(w + 16 * c);
-#pragma unroll
-            for (int q = 0; q < 2; q++) {
-                const uint4 t = pw[q];
-                const uint32_t u[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-                for (int i = 0; i < 4; i++) {
-                    xr[j][8 * q + 2 * i] = xr[j][8 * q + 2 * i] * r * (1.0f + bflo(u[i]));
-                    xr[j][8 * q + 2 * i + 1] = xr[j][8 * q + 2 * i + 1] * r * (1.0f + bfhi(u[i]));
-                }
-            }
-        }
-    }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -219,7 +161,7 @@ __global__ void k_embed(const uint16_t* __restrict__ embed, const int* __restric
 }
 
 // ------------------------------------------------------------------------------------------
-// k_gemv_norm: norm prologue + several weight matrices against the same normalised vector.
+// A GEMV group: norm prologue + several weight matrices against the same normalised vector.
 enum SegKind : int {
     SEG_I8 = 0,        // int8 rows, out = scale * dot
     SEG_I8_CONV = 1,   // int8 rows, then the depthwise causal conv (kernel 4) + SiLU with its state
@@ -352,8 +294,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // Wait for a phase of an mbarrier of this block. The wait is bounded: if the phase has not completed
 // after a very long time (a copy that never lands), *err is set and the caller goes on with whatever
 // the buffer holds, so that the kernel always terminates.
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
-    for (int spin = 0; spin < (1 << 22); spin++) {
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* err, int limit = 1 << 22) {
+    for (int spin = 0; spin < limit; spin++) {
         uint32_t ok;
         asm volatile(
             "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
@@ -369,214 +311,6 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_u32(dst)),
                  "l"(src), "r"(bytes), "r"(smem_u32(bar))
                  : "memory");
-}
-
-constexpr int RING_STAGE_BYTES = 16384;   // one tile: 8 int8 rows of 2048, or 4 bf16 rows, or 4 + 4 rows of a pair
-constexpr int RING_STAGES = 6;            // 96 KB per block: two kernels of a PDL pair fit one SM
-constexpr int GEMV_THREADS = THREADS + 32;   // 8 consumer warps + 1 producer warp
-
-__device__ __forceinline__ int seg_tile_rows(int kind) {
-    return (kind == SEG_BF_SIGMOID || kind == SEG_BF_DECAY || kind == SEG_BF || kind == SEG_I8_GATEUP) ? 4 : 8;
-}
-
-// The block's tiles [t0, t1) of the launch are streamed by one producer thread through the ring with
-// bulk copies; each of the 8 consumer warps takes one row of a tile (a row pair for gate/up), reads
-// its 16-byte slices from shared memory and reduces. Weights do not depend on the previous kernel, so
-// the producer starts before grid_dep_wait(): the ring fills while the predecessor is still running.
-template <int MAXC>
-__global__ void __launch_bounds__(GEMV_THREADS, 2) k_gemv_norm(const GemvArgs a) {
-    extern __shared__ __align__(128) unsigned char ring[];
-    __shared__ __align__(8) uint64_t full_bar[RING_STAGES], empty_bar[RING_STAGES];
-    __shared__ int s_last;
-    __shared__ float s_bv[WARPS];
-    __shared__ int s_bi[WARPS];
-    const int b = blockIdx.y;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int nchunk = a.K >> 4;
-    const int t0 = (int)((long long)blockIdx.x * a.total_jobs / gridDim.x);
-    const int t1 = (int)((long long)(blockIdx.x + 1) * a.total_jobs / gridDim.x);
-    grid_dep_launch();
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < RING_STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], WARPS); }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-
-    float best_v = -INFINITY;
-    int best_i = 0x7fffffff;
-
-    if (warp == WARPS) {
-        // ---- producer ----
-        if (lane == 0) {
-            int s = 0, tile_in_seg = t0;
-            while (s + 1 < a.nseg && tile_in_seg >= a.seg[s].jobs) { tile_in_seg -= a.seg[s].jobs; s++; }
-            for (int t = t0, i = 0; t < t1; t++, i++) {
-                const int st = i % RING_STAGES;
-                if (i >= RING_STAGES) mbar_wait(&empty_bar[st], ((i / RING_STAGES) - 1) & 1, a.err);
-                const Seg& sg = a.seg[s];
-                const int tr = seg_tile_rows(sg.kind);
-                const int row0 = tile_in_seg * tr;
-                const int nrows = min(tr, sg.rows - row0);
-                unsigned char* dst = ring + (size_t)st * RING_STAGE_BYTES;
-                if (sg.kind == SEG_I8_GATEUP) {
-                    const uint32_t bytes = (uint32_t)nrows * a.K;
-                    mbar_expect_tx(&full_bar[st], 2 * bytes);
-                    bulk_load(dst, (const char*)sg.w + (size_t)row0 * a.K, bytes, &full_bar[st]);
-                    bulk_load(dst + 4 * a.K, (const char*)sg.w2 + (size_t)row0 * a.K, bytes, &full_bar[st]);
-                } else {
-                    const int rb = (tr == 4) ? 2 * a.K : a.K;     // bytes per row
-                    const uint32_t bytes = (uint32_t)nrows * rb;
-                    mbar_expect_tx(&full_bar[st], bytes);
-                    bulk_load(dst, (const char*)sg.w + (size_t)row0 * rb, bytes, &full_bar[st]);
-                }
-                if (++tile_in_seg >= sg.jobs && s + 1 < a.nseg) { tile_in_seg = 0; s++; }
-            }
-        }
-    } else {
-        // ---- consumers ----
-        grid_dep_wait();
-        float xr[MAXC][16];
-        load_x_znorm<MAXC>(xr, a.x + (size_t)b * a.K, a.norm_w, a.eps, a.K, lane);
-        int s = 0, tile_in_seg = t0;
-        while (s + 1 < a.nseg && tile_in_seg >= a.seg[s].jobs) { tile_in_seg -= a.seg[s].jobs; s++; }
-        for (int t = t0, i = 0; t < t1; t++, i++) {
-            const int st = i % RING_STAGES;
-            const Seg& sg = a.seg[s];
-            const int tr = seg_tile_rows(sg.kind);
-            const int row = tile_in_seg * tr + warp;
-            const bool mine = warp < tr && row < sg.rows;
-            // what the epilogue needs from global memory is requested before the tile is waited for
-            float e0 = 0.f, e1 = 0.f, e2 = 0.f, e3 = 0.f;
-            uint2 ecw = make_uint2(0u, 0u);
-            if (mine && lane == 0) {
-                switch (sg.kind) {
-                case SEG_I8: case SEG_I8_ARGMAX: case SEG_I8_SILU: e0 = bf(sg.s[row]); break;
-                case SEG_I8_GATEUP: e0 = bf(sg.s[row]); e1 = bf(sg.s2[row]); break;
-                case SEG_I8_CONV: {
-                    e0 = bf(sg.s[row]);
-                    const float* stt = a.conv_state + ((size_t)b * sg.rows + row) * 3;
-                    e1 = stt[0]; e2 = stt[1]; e3 = stt[2];
-                    ecw = *reinterpret_cast<const uint2*>(a.conv_w + (size_t)row * 4);
-                } break;
-                case SEG_BF_DECAY: e0 = bf(a.a_log[row]); e1 = bf(a.dt_bias[row]); break;
-                case SEG_BF: e0 = sg.bias ? sg.bias[row] : 0.f; break;
-                default: break;
-                }
-            }
-            mbar_wait(&full_bar[st], (i / RING_STAGES) & 1, a.err);
-            const unsigned char* src = ring + (size_t)st * RING_STAGE_BYTES;
-            float accA = 0.f, accB = 0.f;
-            if (mine) {
-                if (tr == 8) {
-                    const int4* p = reinterpret_cast<const int4*>(src + (size_t)warp * a.K);
-#pragma unroll
-                    for (int jj = 0; jj < MAXC; jj++) {
-                        const int c = lane + 32 * jj;
-                        if (c < nchunk) accA += dot16_i8(p[c], &xr[jj][0]);
-                    }
-                } else if (sg.kind == SEG_I8_GATEUP) {
-                    const int4* pg = reinterpret_cast<const int4*>(src + (size_t)warp * a.K);
-                    const int4* pu = reinterpret_cast<const int4*>(src + (size_t)(4 + warp) * a.K);
-#pragma unroll
-                    for (int jj = 0; jj < MAXC; jj++) {
-                        const int c = lane + 32 * jj;
-                        if (c < nchunk) { accA += dot16_i8(pg[c], &xr[jj][0]); accB += dot16_i8(pu[c], &xr[jj][0]); }
-                    }
-                } else {
-                    const int4* p = reinterpret_cast<const int4*>(src + (size_t)warp * 2 * a.K);
-#pragma unroll
-                    for (int jj = 0; jj < MAXC; jj++) {
-                        const int c = lane + 32 * jj;
-                        if (c < nchunk) { accA += dot8_bf16(p[2 * c], &xr[jj][0]); accA += dot8_bf16(p[2 * c + 1], &xr[jj][8]); }
-                    }
-                }
-            }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&empty_bar[st]);      // this warp is done with the stage
-            if (mine) {
-                accA = warp_sum(accA);
-                if (sg.kind == SEG_I8_GATEUP) accB = warp_sum(accB);
-                if (lane == 0) {
-                    float* out = sg.out + (size_t)b * sg.out_stride;
-                    switch (sg.kind) {
-                    case SEG_I8: out[row] = e0 * accA; break;
-                    case SEG_I8_SILU: out[row] = siluf_(e0 * accA); break;
-                    case SEG_I8_ARGMAX: {
-                        const float v0 = e0 * accA;
-                        out[row] = v0;
-                        if (v0 > best_v || (v0 == best_v && row < best_i)) { best_v = v0; best_i = row; }
-                    } break;
-                    case SEG_I8_CONV: {
-                        // hybrid.py:393-398: y = silu(sum_j w[c][j] * taps[j]), taps = 3 previous inputs + the new one
-                        const float raw = e0 * accA;
-                        float* stt = a.conv_state + ((size_t)b * sg.rows + row) * 3;
-                        float y = bflo(ecw.x) * e1;
-                        y = fmaf(bfhi(ecw.x), e2, y);
-                        y = fmaf(bflo(ecw.y), e3, y);
-                        y = fmaf(bfhi(ecw.y), raw, y);
-                        stt[0] = e2; stt[1] = e3; stt[2] = raw;
-                        out[row] = siluf_(y);
-                    } break;
-                    case SEG_BF_SIGMOID: out[row] = sigmoidf_(accA); break;
-                    case SEG_BF_DECAY: out[row] = -expf(e0) * softplusf_(accA + e1); break;
-                    case SEG_BF: out[row] = accA + e0; break;
-                    case SEG_I8_GATEUP: out[row] = siluf_(e0 * accA) * (e1 * accB); break;
-                    }
-                }
-            }
-            if (++tile_in_seg >= sg.jobs && s + 1 < a.nseg) { tile_in_seg = 0; s++; }
-        }
-    }
-
-    if (a.finisher == FIN_NONE) return;
-
-    if (a.finisher == FIN_ARGMAX) {
-        if (lane == 0 && warp < WARPS) { s_bv[warp] = best_v; s_bi[warp] = best_i; }
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            float v = s_bv[0];
-            int i = s_bi[0];
-            for (int w = 1; w < WARPS; w++)
-                if (s_bv[w] > v || (s_bv[w] == v && s_bi[w] < i)) { v = s_bv[w]; i = s_bi[w]; }
-            a.part_val[(size_t)b * gridDim.x + blockIdx.x] = v;
-            a.part_idx[(size_t)b * gridDim.x + blockIdx.x] = i;
-        }
-    }
-    __threadfence();
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        const unsigned int n = atomicAdd(a.counter + b, 1u);
-        s_last = (n == gridDim.x - 1);
-    }
-    __syncthreads();
-    if (!s_last) return;
-    __threadfence();
-    if (a.finisher == FIN_TOPK) {
-        if (warp == 0)
-            router_topk_warp(a.seg[0].out + (size_t)b * a.seg[0].out_stride, a.E, a.topk, a.top_idx + (size_t)b * a.topk,
-                             a.top_w + (size_t)b * a.topk, lane);
-    } else {
-        if (warp == 0) {
-            float v = -INFINITY;
-            int i = 0x7fffffff;
-            for (int g = lane; g < (int)gridDim.x; g += 32) {
-                const float pv = __ldcg(a.part_val + (size_t)b * gridDim.x + g);
-                const int pi = __ldcg(a.part_idx + (size_t)b * gridDim.x + g);
-                if (pv > v || (pv == v && pi < i)) { v = pv; i = pi; }
-            }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) {
-                const float ov = __shfl_xor_sync(0xffffffffu, v, o);
-                const int oi = __shfl_xor_sync(0xffffffffu, i, o);
-                if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
-            }
-            if (lane == 0) {
-                a.next_tok[b] = i;
-                if (a.pos) a.pos[b] += 1;
-            }
-        }
-    }
-    if (threadIdx.x == 0) a.counter[b] = 0;
 }
 
 }  // namespace b2
@@ -600,7 +334,7 @@ struct DeltaArgs {
     const float* beta;   // [B][HV]
     const float* g;      // [B][HV]
     float* state;        // [B][HV][DK][DV]
-    float* o;            // [B][HV*DV] raw readout (the gated norm is applied by k_proj_out)
+    float* o;            // [B][HV*DV] raw readout (the gated norm is applied by the out projection's prologue)
     int C, HK, HV, DV;
     int prenormed;       // 1: q and k come in already normalised and scaled (the bare delta-rule op)
 };
@@ -681,7 +415,7 @@ __global__ void __launch_bounds__(THREADS) k_delta_step(const DeltaArgs a) {
 }
 
 // ------------------------------------------------------------------------------------------
-// k_proj_out: the mixer's output projection, accumulated into the residual stream.
+// The mixer's output projection, accumulated into the residual stream (run as a GEMV group).
 //   mode 0 (DeltaNet): input = w * rmsnorm_DV(o) * silu(z) per value head (aegist/hybrid.py:133-147);
 //                      silu(z) arrives ready-made from the in_z rows' epilogue
 //   mode 1 (attention): input is used as it is (already merged and gated by k_attn_merge)
@@ -700,89 +434,6 @@ struct ProjArgs {
     float* x;             // [B][N] residual stream, += result
     int N, K;
 };
-
-constexpr int PROJ_RPW = 2;     // rows per warp pair: a block covers 4 * PROJ_RPW rows
-
-template <int MAXC>
-__global__ void __launch_bounds__(THREADS, 2) k_proj_out(const ProjArgs a) {
-    extern __shared__ float smem[];
-    float* part = smem;             // [2][rows per block]
-    const int b = blockIdx.y;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int half = warp & 1, pair = warp >> 1;          // 4 row-pairs of warps per block
-    const int nchunk_half = a.K >> 5;                      // 16-value slices per half row
-    const int rows_per_block = (a.N + gridDim.x - 1) / gridDim.x;
-    const int row0 = blockIdx.x * rows_per_block;
-    const int row1 = min(a.N, row0 + rows_per_block);
-    grid_dep_launch();
-
-    // every row of this warp pair is requested before anything else: one round trip to HBM, not one per row
-    int4 wbuf[PROJ_RPW][MAXC];
-#pragma unroll
-    for (int u = 0; u < PROJ_RPW; u++) {
-        const int row = row0 + pair + 4 * u;
-        const char* p = (const char*)a.w + (size_t)row * a.K + (size_t)half * (a.K >> 1);
-#pragma unroll
-        for (int jj = 0; jj < MAXC; jj++) {
-            const int c = lane + 32 * jj;
-            wbuf[u][jj] = (row < row1 && c < nchunk_half) ? ldw(p + (size_t)c * 16) : make_int4(0, 0, 0, 0);
-        }
-    }
-    grid_dep_wait();
-
-    const int koff = half * (a.K >> 1);
-    const float* in = a.in + (size_t)b * a.K + koff;
-    float xr[MAXC][16];
-    load_x_znorm<MAXC>(xr, in, nullptr, 0.f, a.K >> 1, lane);
-    if (a.mode == 0) {
-        const float* z = a.z + (size_t)b * a.K + koff;
-        const int lanes_per_head = a.DV >> 4;
-#pragma unroll
-        for (int jj = 0; jj < MAXC; jj++) {
-            const int c = lane + 32 * jj;
-            float ss = 0.f;
-#pragma unroll
-            for (int q = 0; q < 16; q++) ss = fmaf(xr[jj][q], xr[jj][q], ss);
-            for (int o = 1; o < lanes_per_head; o <<= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-            if (c < nchunk_half) {
-                const float r = 1.0f / sqrtf(ss / (float)a.DV + a.eps);
-                const int k0 = 16 * c;                       // offset inside this half
-                const int d0 = (koff + k0) % a.DV;           // position inside the value head
-                const float4* pz = reinterpret_cast<const float4*>(z + k0);
-#pragma unroll
-                for (int q = 0; q < 4; q++) {
-                    const float4 t = pz[q];
-                    const float zz[4] = {t.x, t.y, t.z, t.w};
-#pragma unroll
-                    for (int i = 0; i < 4; i++)
-                        xr[jj][4 * q + i] = (bf(a.gn_w[d0 + 4 * q + i]) * (xr[jj][4 * q + i] * r)) * zz[i];
-                }
-            }
-        }
-    }
-
-    float acc[PROJ_RPW];
-#pragma unroll
-    for (int u = 0; u < PROJ_RPW; u++) {
-        acc[u] = 0.f;
-#pragma unroll
-        for (int jj = 0; jj < MAXC; jj++) acc[u] += dot16_i8(wbuf[u][jj], &xr[jj][0]);
-    }
-#pragma unroll
-    for (int u = 0; u < PROJ_RPW; u++) acc[u] = warp_sum(acc[u]);
-    if (lane == 0) {
-#pragma unroll
-        for (int u = 0; u < PROJ_RPW; u++) {
-            const int row = row0 + pair + 4 * u;
-            if (row < row1) part[half * rows_per_block + (row - row0)] = acc[u];
-        }
-    }
-    __syncthreads();
-    for (int r = threadIdx.x; r < row1 - row0; r += THREADS) {
-        const float d = part[r] + part[rows_per_block + r];
-        a.x[(size_t)b * a.N + row0 + r] += bf(a.s[row0 + r]) * d;
-    }
-}
 
 // ------------------------------------------------------------------------------------------
 // Experts. One expert's bytes (aegist/hybrid.py:472-480):
@@ -816,6 +467,7 @@ struct ExpertArgs {
     unsigned int* counter;        // [B][row blocks]
     float* xout;                  // [B][D] residual stream, += result
     int* err;
+    int null_is_error;            // 1: every expert must be in the table (one GPU); 0: a null entry is another rank's expert
 };
 
 // act[pick][i] = silu(gate_i . h) * (up_i . h), one warp per (gate, up) row pair.
@@ -833,7 +485,7 @@ __global__ void __launch_bounds__(THREADS, 2) k_expert_gu(const ExpertArgs a) {
     const int e = a.top_idx[(size_t)b * a.idx_stride + pick % a.topk];
     const uint8_t* base = (e >= 0 && e < a.E) ? a.eptr[e] : nullptr;
     if (base == nullptr) {   // not resident here (another rank's expert) or a bad pick
-        if (e < 0 || e >= a.E) { if (threadIdx.x == 0) atomicExch(a.err, 2); }
+        if (e < 0 || e >= a.E || a.null_is_error) { if (threadIdx.x == 0) atomicExch(a.err, 2); }
         return;
     }
     const int nchunk = a.D >> 5;          // 16-byte slices per row
@@ -1477,6 +1129,19 @@ __global__ void __launch_bounds__(1024) k_argmax_rows(const float* __restrict__ 
             if (pos) pos[b] += 1;
         }
     }
+}
+
+// A wait that cannot succeed, for testing the bounded wait: the barrier expects bytes that no copy delivers, so
+// mbar_wait gives up after `polls` polls, sets *err to 3 and the kernel ends normally.
+__global__ void k_wait_never(int polls, int* err) {
+    __shared__ __align__(8) uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        mbar_expect_tx(&bar, 16);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_wait(&bar, 0, err, polls);
 }
 
 __global__ void k_fill_i32(int* p, int v, int n) {

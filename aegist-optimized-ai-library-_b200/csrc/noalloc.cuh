@@ -17,7 +17,12 @@
 //    kernels add into are cleared at the start of every call;
 //  * two calls that overlap on one GPU (two streams, two threads) use the same memory and race;
 //  * the first call on a device looks the array's device address up (cudaGetSymbolAddress with that
-//    device current); make that first call before any stream capture begins.
+//    device current); make that first call before any stream capture begins;
+//  * every call ends by synchronising `stream` and reading the kernels' error word back, so it must
+//    never be made on a stream that is being captured;
+//  * every device pointer (h, y, idx, wts and the nine inside *w) must be non-null where required and
+//    16-byte aligned: the kernels read them with 128-bit loads. A pointer that fails this is refused
+//    with code 3 before anything is launched.
 #pragma once
 
 #define B2_STATIC_MAX_TOKENS 8
@@ -85,6 +90,19 @@ extern "C" int b2_moe_forward_static(const b2_moe_device_weights* w, const float
         fprintf(stderr, "b200moe: b2_moe_forward_static: unsupported shape\n");
         return 3;
     }
+    {
+        // the kernels use 128-bit loads on all of these; a null or misaligned one must be an error code, not a fault
+        const void* must[] = {h, y, w->router_bf16, w->expert_ptrs, w->sh_gate_q, w->sh_gate_s, w->sh_up_q, w->sh_up_s,
+                              w->sh_down_q, w->sh_down_s, w->shared_gate_bf16};
+        const char* names[] = {"h", "y", "router_bf16", "expert_ptrs", "sh_gate_q", "sh_gate_s", "sh_up_q", "sh_up_s",
+                               "sh_down_q", "sh_down_s", "shared_gate_bf16"};
+        for (int i = 0; i < 11; i++)
+            if (!must[i] || ((uintptr_t)must[i] & 15)) {
+                fprintf(stderr, "b200moe: b2_moe_forward_static: %s is %s\n", names[i], must[i] ? "not 16-byte aligned" : "null");
+                return 3;
+            }
+        if (((uintptr_t)idx & 3) || ((uintptr_t)wts & 3)) { fprintf(stderr, "b200moe: b2_moe_forward_static: idx / wts misaligned\n"); return 3; }
+    }
     float* s = nullptr;
     if (int rc = na_scratch(&s)) return rc;
     cudaStream_t st = (cudaStream_t)stream;
@@ -111,11 +129,20 @@ extern "C" int b2_moe_forward_static(const b2_moe_device_weights* w, const float
     x.off_gu_s = c.off_gu_s(); x.off_gu_m = c.off_gu_m(); x.off_dn_q = c.off_dn_q(); x.off_dn_s = c.off_dn_s(); x.off_dn_m = c.off_dn_m();
     x.x = h; x.norm_w = nullptr; x.act = s + NA_ACT; x.sh_act = s + NA_SHACT; x.sg = s + NA_SGATE;
     x.shd_w = w->sh_down_q; x.shd_s = w->sh_down_s; x.SH = c.SH; x.xout = y; x.err = (int*)(s + NA_ERR);
-    x.ypart = s + NA_YPART; x.counter = (unsigned int*)(s + NA_DCOUNTER);
+    x.null_is_error = 1; x.ypart = s + NA_YPART; x.counter = (unsigned int*)(s + NA_DCOUNTER);
     launch_experts(x, tokens, nsm, st);
     OPCU(cudaGetLastError());
     if (idx) OPCU(cudaMemcpyAsync(idx, top_idx, (size_t)tokens * c.TOPK * sizeof(int), cudaMemcpyDeviceToDevice, st));
     if (wts) OPCU(cudaMemcpyAsync(wts, top_w, (size_t)tokens * c.TOPK * sizeof(float), cudaMemcpyDeviceToDevice, st));
+    // the error word the kernels set (a pick outside the table, a copy that never landed): 4 bytes into a local, no allocation
+    int herr = 0;
+    OPCU(cudaMemcpyAsync(&herr, s + NA_ERR, sizeof(int), cudaMemcpyDeviceToHost, st));
     OPCU(cudaStreamSynchronize(st));
+    if (herr) {
+        fprintf(stderr, "b200moe: b2_moe_forward_static: %s\n",
+                herr == 3 ? "a bulk copy into shared memory did not complete (bounded wait gave up)"
+                          : "the router picked an expert whose table entry is null or out of range");
+        return 4;
+    }
     return 0;
 }

@@ -33,9 +33,30 @@ struct b2_moe {
     unsigned int* counter = nullptr;
     float* ypart = nullptr;
     unsigned int* dcounter = nullptr;
+    // fewer than 8 tokens: the engine's small-batch expert kernels (k_moe_gu1 / k_moe_down1)
+    const uint8_t** top_ptr = nullptr;
+    int8_t* actq = nullptr;
+    float *asc = nullptr, *asum = nullptr;
+    int* h_err = nullptr;                    // page-locked copy of the device error word
     cudaStream_t st = nullptr;
     cudaEvent_t e0 = nullptr, e1 = nullptr;
 };
+
+// The device error word after an operator's kernels: 2 = a pick outside the expert table, 3 = a bulk copy that
+// never landed (bounded wait gave up). Returns non-zero with a message when it is set, and clears it.
+static int op_check_err(int* d_err, int* h_err, cudaStream_t st, const char* who) {
+    OPCU(cudaMemcpyAsync(h_err, d_err, 4, cudaMemcpyDeviceToHost, st));
+    OPCU(cudaStreamSynchronize(st));
+    if (*h_err == 0) return 0;
+    const int code = *h_err;
+    cudaMemsetAsync(d_err, 0, 4, st);
+    cudaStreamSynchronize(st);
+    snprintf(g_op_err.msg, sizeof(g_op_err.msg), "%s: %s", who,
+             code == 3 ? "a bulk copy into shared memory did not complete (bounded wait gave up)"
+                       : "the router picked an expert that is not in the table");
+    fprintf(stderr, "b200moe: %s\n", g_op_err.msg);
+    return 4;
+}
 
 struct b2_delta {
     int device, B, H, dk, dv;
@@ -75,6 +96,18 @@ int b2_op_linear_i8(int device, const int8_t* q, const uint16_t* scale, int n, i
     return 0;
 }
 
+int b2_debug_wait_timeout(int device, int polls, int* status) {
+    if (!status || polls < 1 || polls > (1 << 22)) return 1;
+    OPCU(cudaSetDevice(device));
+    int* d = nullptr;
+    OPCU(dalloc(&d, 1));
+    k_wait_never<<<1, 32>>>(polls, d);
+    OPCU(cudaGetLastError());
+    OPCU(cudaMemcpy(status, d, sizeof(int), cudaMemcpyDeviceToHost));
+    cudaFree(d);
+    return 0;
+}
+
 int b2_moe_create(int device, const b2_moe_weights* w, int max_tokens, b2_moe** out) {
     b2_moe* m = new b2_moe();
     *out = m;
@@ -105,6 +138,10 @@ int b2_moe_create(int device, const b2_moe_weights* w, int max_tokens, b2_moe** 
     OPCU(dalloc(&m->counter, T));
     OPCU(dalloc(&m->ypart, (size_t)T * (c.TOPK + 1) * c.D));
     OPCU(dalloc(&m->dcounter, (size_t)T * down_row_blocks(c.D)));
+    OPCU(dalloc(&m->top_ptr, (size_t)T * c.TOPK));
+    OPCU(dalloc(&m->actq, (size_t)T * c.TOPK * M1_PLANES * c.I));
+    OPCU(dalloc(&m->asc, (size_t)T * c.TOPK * std::max(1, c.I / 32))); OPCU(dalloc(&m->asum, (size_t)T * c.TOPK * std::max(1, c.I / 32)));
+    OPCU(cudaMallocHost((void**)&m->h_err, sizeof(int)));
     OPCU(cudaStreamCreateWithFlags(&m->st, cudaStreamNonBlocking));
     OPCU(cudaEventCreate(&m->e0)); OPCU(cudaEventCreate(&m->e1));
     return 0;
@@ -123,23 +160,31 @@ int b2_moe_forward(b2_moe* m, const float* h, int tokens, float* y, int32_t* idx
     a.seg[1].w2 = m->su_q; a.seg[1].s2 = m->su_s;
     a.seg[2] = make_seg(SEG_BF_SIGMOID, m->shared_gate, nullptr, 1, m->sgate, 1);
     a.nseg = 3; seal(a, c.D);
-    a.x = m->h; a.norm_w = nullptr; a.K = c.D;
-    a.finisher = FIN_TOPK; a.counter = m->counter; a.E = c.E; a.topk = c.TOPK; a.top_idx = m->top_idx; a.top_w = m->top_w;
+    a.x = m->h; a.norm_w = nullptr; a.K = c.D; a.err = m->err;
+    // the kernels the engine would run for this many tokens: below 8 the top-8 happens inside the expert kernel
+    const bool moe1 = tokens < 8 && moe1_shape_ok(c);
+    a.finisher = moe1 ? FIN_NONE : FIN_TOPK; a.counter = m->counter; a.E = c.E; a.topk = c.TOPK; a.top_idx = m->top_idx; a.top_w = m->top_w;
     launch_gemv(a, tokens, m->nsm, m->st);
+    if (moe1) {
+        const Moe1Ctx mc{m->top_ptr, m->actq, m->asc, m->asum};
+        OPCU(launch_moe1(c, m->rlogits, m->h, nullptr, m->eptr, m->top_idx, m->top_w, mc, m->sh_act, m->sgate, m->sd_q, m->sd_s, m->y, m->err,
+                         tokens, m->st, nullptr));
+    } else {
     ExpertArgs x{};
     x.eptr = m->eptr; x.top_idx = m->top_idx; x.top_w = m->top_w; x.topk = c.TOPK; x.E = c.E; x.D = c.D; x.I = c.I;
     x.idx_stride = c.TOPK; x.x_stride = c.D; x.combine = 1; x.local0 = 0; x.nlocal = tokens;
     x.off_gu_s = c.off_gu_s(); x.off_gu_m = c.off_gu_m(); x.off_dn_q = c.off_dn_q(); x.off_dn_s = c.off_dn_s(); x.off_dn_m = c.off_dn_m();
     x.x = m->h; x.norm_w = nullptr; x.act = m->act; x.sh_act = m->sh_act; x.sg = m->sgate;
     x.shd_w = m->sd_q; x.shd_s = m->sd_s; x.SH = c.SH; x.xout = m->y; x.err = m->err;
-    x.ypart = m->ypart; x.counter = m->dcounter;
+    x.null_is_error = 1; x.ypart = m->ypart; x.counter = m->dcounter;
     launch_experts(x, tokens, m->nsm, m->st);
+    }
     OPCU(cudaEventRecord(m->e1, m->st));
     OPCU(cudaGetLastError());
     OPCU(cudaMemcpyAsync(y, m->y, (size_t)tokens * c.D * 4, cudaMemcpyDeviceToHost, m->st));
     if (idx) OPCU(cudaMemcpyAsync(idx, m->top_idx, (size_t)tokens * c.TOPK * 4, cudaMemcpyDeviceToHost, m->st));
     if (wts) OPCU(cudaMemcpyAsync(wts, m->top_w, (size_t)tokens * c.TOPK * 4, cudaMemcpyDeviceToHost, m->st));
-    OPCU(cudaStreamSynchronize(m->st));
+    if (int rc = op_check_err(m->err, m->h_err, m->st, "b2_moe_forward")) return rc;
     if (device_ms) OPCU(cudaEventElapsedTime(device_ms, m->e0, m->e1));
     return 0;
 }
@@ -148,8 +193,10 @@ void b2_moe_destroy(b2_moe* m) {
     if (!m) return;
     cudaSetDevice(m->device);
     void* bufs[] = {m->router, m->sg_s, m->su_s, m->sd_s, m->shared_gate, m->experts, m->sg_q, m->su_q, m->sd_q, (void*)m->eptr, m->h, m->y,
-                    m->rlogits, m->sh_act, m->sgate, m->act, m->top_w, m->top_idx, m->err, m->counter, m->ypart, m->dcounter};
+                    m->rlogits, m->sh_act, m->sgate, m->act, m->top_w, m->top_idx, m->err, m->counter, m->ypart, m->dcounter,
+                    (void*)m->top_ptr, m->actq, m->asc, m->asum};
     for (void* p : bufs) cudaFree(p);
+    if (m->h_err) cudaFreeHost(m->h_err);
     if (m->e0) cudaEventDestroy(m->e0);
     if (m->e1) cudaEventDestroy(m->e1);
     if (m->st) cudaStreamDestroy(m->st);

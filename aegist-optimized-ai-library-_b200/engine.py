@@ -80,6 +80,7 @@ SYMBOLS = {
     "b2_profile_step": (_I, [_P, _I, C.POINTER(_F), C.POINTER(C.c_double), C.POINTER(_I)]),
     "b2_debug_trace_step": (_I, [_P, C.POINTER(C.c_uint64), _I, C.POINTER(_I)]),
     "b2_op_linear_i8": (_I, [_I, _P, _P, _I, _I, _P, _I, _P]),
+    "b2_debug_wait_timeout": (_I, [_I, _I, C.POINTER(_I)]),
     "b2_moe_create": (_I, [_I, C.POINTER(MoeWeights), _I, C.POINTER(_P)]),
     "b2_moe_forward": (_I, [_P, _P, _I, _P, _P, _P, C.POINTER(_F)]),
     "b2_moe_destroy": (None, [_P]),

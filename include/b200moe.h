@@ -158,7 +158,9 @@ int b2_op_linear_i8(int device, const int8_t* q, const uint16_t* scale_bf16, int
                     const float* x, int tokens, float* y);
 /* MoE.forward (aegist/hybrid.py:641-652; router_topk + moe_*_gemv + shared expert, hybrid.rs:863-975)
  * on `tokens` rows of h: y = experts(h) + sigmoid(shared_gate h) * shared(h). Weight pointers are
- * host memory in the .nx layouts. idx/wts (optional) receive the router's picks. */
+ * host memory in the .nx layouts. idx/wts (optional) receive the router's picks. It runs the kernels the
+ * engine runs for that many tokens (below 8 the top-8 happens inside the expert kernel). Returns 4 when
+ * the kernels set their error word (a bad pick, a copy that never landed). */
 typedef struct {
     int d_model, n_experts, top_k, expert_hidden, shared_hidden, group;
     const uint16_t* router_bf16;      /* [E][D] */
@@ -184,8 +186,12 @@ void b2_moe_destroy(b2_moe* m);
  * (3: bad argument, 1: CUDA error). All calls share that array, which keeps the last call's contents
  * (the function clears what must start at zero, y included): calls that overlap on one GPU race, so
  * run them one after the other. The first call on a device looks the array's address up; make it
- * before any stream capture begins. Work is queued on `stream` (a cudaStream_t, NULL = default) and the
- * function returns after it has completed. idx / wts are optional outputs. */
+ * before any stream capture begins. Work is queued on `stream` (a cudaStream_t, NULL = default); every
+ * call then synchronises that stream and reads the kernels' error word back, so it must never be made on
+ * a stream that is being captured. h, y and the nine pointers inside *w must be non-null and 16-byte
+ * aligned (the kernels use 128-bit loads), idx / wts 4-byte aligned: otherwise 3 is returned and nothing
+ * runs. 4 = the kernels reported an error (a pick whose table entry is null, a copy that never landed).
+ * idx / wts are optional outputs. */
 typedef struct {
     int d_model, n_experts, top_k, expert_hidden, shared_hidden;
     const uint16_t* router_bf16;            /* [E][D] */
@@ -197,6 +203,12 @@ typedef struct {
 } b2_moe_device_weights;
 int b2_moe_forward_static(const b2_moe_device_weights* w, const float* h, int tokens, float* y, int32_t* idx,
                           float* wts, void* stream);
+
+/* Runs a kernel whose only wait can never succeed (an mbarrier that expects bytes no copy delivers) with a
+ * limit of `polls` polls, and returns the device error word in *status: 3 = the bounded wait gave up and the
+ * kernel ended normally. This is how the time-out path of every bulk-copy wait is tested without a hang.
+ * No counterpart in the reference. */
+int b2_debug_wait_timeout(int device, int polls, int* status);
 
 /* delta_rule_step (aegist/hybrid.py:318-324; delta_scan, kernels/hybrid.cu:240-300) with the state
  * kept on the device between calls. q, k [B][H][dk] (already normalised and scaled), v [B][H][dv],

@@ -72,6 +72,16 @@ def test_moe_layer_op(E, moe_layer, tokens):
     layer.close()
 
 
+def test_bounded_wait_gives_up_with_an_error_code(E):
+    """Every wait on a bulk copy is bounded. A kernel whose barrier expects bytes that no copy delivers must end
+    by itself with error word 3 (never a hang), here after 20,000 polls."""
+    import ctypes as C
+    lib = E.load_library()
+    status = C.c_int(-1)
+    assert lib.b2_debug_wait_timeout(0, 20000, C.byref(status)) == 0
+    assert status.value == 3
+
+
 @pytest.mark.parametrize("batch,steps", [(1, 1000), (16, 120), (64, 30)])
 def test_delta_rule_steps(E, batch, steps):
     """hidden 2048-shaped DeltaNet state: 32 value heads, 128 x 128, fp32 state from N(0, 0.1), bf16
