@@ -8,6 +8,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200moe.so")
+CLI = os.path.join(HERE, "b2-debug-logits")        # the reference's `aegist debug-logits` over the C ABI
 SOURCES = ["engine.cu"]
 HEADERS = ["kernels.cuh", "rowgemv.cuh", "mmagemm.cuh", "mmaexperts.cuh", "digits.cuh", "attnmma.cuh", "tcgemv.cuh", "moe1.cuh", "ops.cuh", "noalloc.cuh", "sampler.hpp", "nxfile.hpp", "json.hpp", "sha256.hpp", "../../include/b200moe.h"]
 
@@ -20,10 +21,10 @@ def nvcc() -> str:
 
 
 def stale() -> bool:
-    if not os.path.exists(LIB):
+    if not os.path.exists(LIB) or not os.path.exists(CLI):
         return True
-    t = os.path.getmtime(LIB)
-    return any(os.path.getmtime(os.path.join(CSRC, f)) > t for f in SOURCES + HEADERS)
+    t = min(os.path.getmtime(LIB), os.path.getmtime(CLI))
+    return any(os.path.getmtime(os.path.join(CSRC, f)) > t for f in SOURCES + HEADERS + ["debug_logits.cpp"])
 
 
 def build(verbose: bool = False, force: bool = False) -> str:
@@ -37,6 +38,14 @@ def build(verbose: bool = False, force: bool = False) -> str:
         sys.stderr.write(r.stdout + r.stderr)
     if r.returncode != 0:
         raise RuntimeError("nvcc failed")
+    # the command-line parity driver: plain C++ over the C ABI, finds the library beside itself
+    cmd = ["g++", "-O2", "-std=c++17", "-o", CLI, os.path.join(CSRC, "debug_logits.cpp"), "-L" + HERE, "-lb200moe",
+           "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if verbose or r.returncode != 0:
+        sys.stderr.write(r.stdout + r.stderr)
+    if r.returncode != 0:
+        raise RuntimeError("g++ failed on debug_logits.cpp")
     return LIB
 
 

@@ -6,10 +6,10 @@
 //   S = Q K^T    mma.sync.m16n8k16.bf16: Q as three bf16 planes (hi + mid + lo = the fp32 value to 2^-24),
 //                K as it lies in the cache; warp w takes positions 8 w .. 8 w + 7
 //   softmax      online, base-2, maxima and sums of the 8 warps meet in shared memory
-//   O += P V     P as two bf16 planes, V through ldmatrix.trans; warp w takes HD / 8 output dims
+//   O += P V     P as three bf16 planes (exact to 2^-24), V through ldmatrix.trans; warp w takes HD / 8 output dims
 // K and V tiles come in by 16-byte cp.async, double-buffered when the slice has more than one tile. The
-// exact fp32 arithmetic of k_attn (used for an fp32 cache) differs from this by the bf16 split of Q and P,
-// below 2^-16 relative.
+// exact fp32 arithmetic of k_attn (used for an fp32 cache) differs from this only by summation order: the
+// three-plane splits of Q and P carry all 24 significant bits.
 #pragma once
 
 namespace b2 {
@@ -37,10 +37,10 @@ template <int HD>
 __host__ __device__ constexpr int am_kpitch() { return HD * 2 + 64; }   // rows r, r + 1 in different halves of the banks
 template <int HD>
 __host__ __device__ constexpr int am_vpitch() { return HD * 2 + 16; }   // 8 consecutive rows cover all banks (ldmatrix)
-// dynamic shared memory: [nbuf] K tiles | [nbuf] V tiles | Q planes [3][8][HD + 32] bf16 | P planes [2][8][72] bf16
+// dynamic shared memory: [nbuf] K tiles | [nbuf] V tiles | Q planes [3][8][HD + 32] bf16 | P planes [3][8][72] bf16
 template <int HD>
 __host__ __device__ constexpr size_t am_smem(int nbuf) {
-    return (size_t)nbuf * AM_TILE * (am_kpitch<HD>() + am_vpitch<HD>()) + (size_t)3 * 8 * (HD + 32) * 2 + (size_t)2 * 8 * 72 * 2;
+    return (size_t)nbuf * AM_TILE * (am_kpitch<HD>() + am_vpitch<HD>()) + (size_t)3 * 8 * (HD + 32) * 2 + (size_t)3 * 8 * 72 * 2;
 }
 
 // grid (nsplit, KV, B); the slice length is a multiple of 64
@@ -57,11 +57,12 @@ __global__ void __launch_bounds__(THREADS) k_attn_mma(const AttnArgs a, int nbuf
     unsigned char* Ks = am_smem_raw;                                         // [nbuf][64][KP]
     unsigned char* Vs = Ks + (size_t)nbuf * AM_TILE * KP;                    // [nbuf][64][VP]
     uint16_t* Qh = reinterpret_cast<uint16_t*>(Vs + (size_t)nbuf * AM_TILE * VP);   // [3][8][QP]
-    uint16_t* Ps = Qh + 3 * 8 * QP;                                          // [2][8][PP]
+    uint16_t* Ps = Qh + 3 * 8 * QP;                                          // [3][8][PP]
     __shared__ float knew[HD], vnew[HD];
     __shared__ float s_max[WARPS][8], s_sum[WARPS][8];
     grid_dep_launch();
     trace_in(a.trace, 7, gridDim.x);
+    if (warp == WARPS - 1 && blockIdx.z == 0) l2_prefetch_share(a.pf, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, lane);
     grid_dep_wait();
     trace_pt(a.trace, 1);
     const int pos = a.pos[b];
@@ -217,12 +218,14 @@ __global__ void __launch_bounds__(THREADS) k_attn_mma(const AttnArgs a, int nbuf
         ps += __shfl_xor_sync(0xffffffffu, ps, 1);
         ps += __shfl_xor_sync(0xffffffffu, ps, 2);
         if (tid == 0) s_sum[warp][gid] = ps;
-        {   // P as hi + lo bf16 planes, [plane][head][position in the tile]
-            const uint32_t h0 = __float_as_uint(e0) & 0xFFFF0000u, h1 = __float_as_uint(e1) & 0xFFFF0000u;
-            const float r0 = e0 - __uint_as_float(h0), r1 = e1 - __uint_as_float(h1);
+        {   // P as hi + mid + lo bf16 planes (truncations, so the remainders are exact), [plane][head][position in the tile]
+            uint16_t a0, a1, a2, b0, b1, b2;
+            split3_bf16(e0, a0, a1, a2);
+            split3_bf16(e1, b0, b1, b2);
             const int pc = warp * 8 + 2 * tid;
-            *reinterpret_cast<uint32_t*>(Ps + (0 * 8 + gid) * PP + pc) = (h0 >> 16) | h1;
-            *reinterpret_cast<uint32_t*>(Ps + (1 * 8 + gid) * PP + pc) = (__float_as_uint(r0) >> 16) | (__float_as_uint(r1) & 0xFFFF0000u);
+            *reinterpret_cast<uint32_t*>(Ps + (0 * 8 + gid) * PP + pc) = (uint32_t)a0 | ((uint32_t)b0 << 16);
+            *reinterpret_cast<uint32_t*>(Ps + (1 * 8 + gid) * PP + pc) = (uint32_t)a1 | ((uint32_t)b1 << 16);
+            *reinterpret_cast<uint32_t*>(Ps + (2 * 8 + gid) * PP + pc) = (uint32_t)a2 | ((uint32_t)b2 << 16);
         }
         __syncthreads();
         float lt = 0.f;
@@ -239,13 +242,16 @@ __global__ void __launch_bounds__(THREADS) k_attn_mma(const AttnArgs a, int nbuf
             const uint32_t ph2 = *reinterpret_cast<const uint32_t*>(Ps + (0 * 8 + gid) * PP + ks * 16 + 8 + 2 * tid);
             const uint32_t pl0 = *reinterpret_cast<const uint32_t*>(Ps + (1 * 8 + gid) * PP + ks * 16 + 2 * tid);
             const uint32_t pl2 = *reinterpret_cast<const uint32_t*>(Ps + (1 * 8 + gid) * PP + ks * 16 + 8 + 2 * tid);
+            const uint32_t pm0 = *reinterpret_cast<const uint32_t*>(Ps + (2 * 8 + gid) * PP + ks * 16 + 2 * tid);
+            const uint32_t pm2 = *reinterpret_cast<const uint32_t*>(Ps + (2 * 8 + gid) * PP + ks * 16 + 8 + 2 * tid);
             const unsigned char* vr = Vs + ((size_t)buf * AM_TILE + ks * 16 + (lane & 15)) * VP + (size_t)warp * (HD / 8) * 2;
 #pragma unroll
             for (int n = 0; n < NTV; n++) {
                 uint32_t b0, b1;
                 ldmatrix_x2_trans(b0, b1, vr + n * 16);
-                mma_bf16(o[n], ph0, 0u, ph2, 0u, b0, b1);
+                mma_bf16(o[n], pm0, 0u, pm2, 0u, b0, b1);       // smallest parts first
                 mma_bf16(o[n], pl0, 0u, pl2, 0u, b0, b1);
+                mma_bf16(o[n], ph0, 0u, ph2, 0u, b0, b1);
             }
         }
         __syncthreads();                     // the tile, P and the per-warp maxima may be overwritten

@@ -130,6 +130,10 @@ struct b2_engine {
     int pages_per_seq = 0;
     float *rope_cos = nullptr, *rope_sin = nullptr;
     int length = 0;
+    // the tokens fed so far (one sequence), for saved states; unknown after steps whose tokens stayed on the device
+    std::vector<uint32_t> toks;
+    bool toks_known = true;
+    std::string fingerprint;      // names the weights (NxFile::fingerprint); empty when built from tensors
 
     // per-step device scalars and work buffers
     int *d_tok = nullptr, *d_next = nullptr, *d_pos = nullptr, *d_err = nullptr;
@@ -213,6 +217,9 @@ struct b2_engine {
     int run_steps(int n);
     int check_device_error();
     int reset_state();
+    std::string state_key() const;
+    struct Piece { char* p; size_t bytes; };
+    std::vector<Piece> state_pieces(int n) const;
 };
 
 b2_engine::~b2_engine() {
@@ -698,8 +705,9 @@ static void seal(GemvArgs& a, int K) {
 static void seal(GemvArgs& a, int K);
 static Seg make_seg(int kind, const void* w, const uint16_t* s, int rows, float* out, int out_stride);
 
-static void launch_proj(const ProjArgs& a, int B, int nsm, cudaStream_t st, const BatchCtx* bc = nullptr) {
+static void launch_proj(const ProjArgs& a, int B, int nsm, cudaStream_t st, const BatchCtx* bc = nullptr, const PrefetchList* pf = nullptr) {
     GemvArgs g{};
+    if (pf) g.pf = *pf;
     g.seg[0] = make_seg(SEG_I8_ACC, a.w, a.s, a.N, a.x, a.N);
     g.nseg = 1;
     seal(g, a.K);
@@ -835,8 +843,11 @@ static bool moe1_shape_ok(const Cfg& c) {
 struct Moe1Ctx { const uint8_t** top_ptr; int8_t* actq; float* asc; float* asum; };
 static cudaError_t launch_moe1(const Cfg& c, const float* rlogits, const float* x_in, const uint16_t* norm_w, const uint8_t* const* eptr,
                                int* top_idx, float* top_w, const Moe1Ctx& m, const float* sh_act, const float* sgate, const int8_t* shd_w,
-                               const uint16_t* shd_s, float* xout, int* err, int B, cudaStream_t st, b2_engine* prof) {
+                               const uint16_t* shd_s, float* xout, int* err, int B, cudaStream_t st, b2_engine* prof,
+                               const PrefetchList* pf = nullptr) {
     Gu1Args g{};
+    g.off_dn_q = c.off_dn_q(); g.dn_bytes = (unsigned int)(c.dn_q() + 2 * c.dn_sm());
+    if (pf) g.pf = *pf;
     g.logits = rlogits; g.x = x_in; g.norm_w = norm_w; g.eps = c.eps; g.eptr = eptr;
     g.off_gu_s = c.off_gu_s(); g.off_gu_m = c.off_gu_m(); g.D = c.D; g.I = c.I; g.E = c.E; g.topk = c.TOPK;
     g.top_idx = top_idx; g.top_w = top_w; g.top_ptr = m.top_ptr; g.actq = m.actq; g.asc = m.asc; g.asum = m.asum; g.err = err;
@@ -857,6 +868,19 @@ static cudaError_t launch_moe1(const Cfg& c, const float* rlogits, const float* 
     return ce;
 }
 
+static PrefetchList pf_of(std::initializer_list<std::pair<const void*, size_t>> regions) {
+    PrefetchList l{};
+    int i = 0;
+    for (auto& r : regions)
+        if (i < PF_MAX && r.first) { l.r[i].p = (const char*)r.first; l.r[i].bytes = (unsigned int)std::min<size_t>(r.second, 0xFFFFF000u); i++; }
+    return l;
+}
+// the int8 input projections of layer `l`, which the launch after the previous layer's experts streams
+static PrefetchList pf_in_proj(const LayerW& l, const Cfg& c) {
+    if (l.attn) return pf_of({{l.q.w, (size_t)l.q.n * c.D}, {l.k.w, (size_t)l.k.n * c.D}, {l.v.w, (size_t)l.v.n * c.D}});
+    return pf_of({{l.in_qkv.w, (size_t)l.in_qkv.n * c.D}, {l.in_z.w, (size_t)l.in_z.n * c.D}});
+}
+
 // One decode step for all B sequences: token ids in d_tok, positions in d_pos.
 int b2_engine::enqueue_step(cudaStream_t st, bool count) {
     int n = 0;
@@ -869,10 +893,18 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
     mark(0, st);
     n++;
     const size_t kv_layer = (size_t)B * pages_per_seq * c.KV * KV_PAGE * c.HD * (kv_f32 ? 4 : 2);
+    // fewer than 8 sequences: the launches ask the weights of later launches of the step into L2 (see Prefetch). One layer's
+    // dense weights and experts are half of L2, so what is asked for is still there when its launch comes.
+    const bool pfon = B < 8 && ep_world == 1;
+    const PrefetchList none{};
     for (int li = 0; li < c.L; li++) {
         const LayerW& l = layers[li];
+        const PrefetchList pf_moe_in = pfon ? pf_of({{l.router, (size_t)c.E * c.D * 2}, {l.sh_gate.w, (size_t)c.SH * c.D}, {l.sh_up.w, (size_t)c.SH * c.D}}) : none;
+        const PrefetchList pf_shdown = pfon ? pf_of({{l.sh_down.w, (size_t)c.D * c.SH}}) : none;
+        const PrefetchList pf_next = pfon && li + 1 < c.L ? pf_in_proj(layers[li + 1], c) : none;
         if (l.attn) {
             GemvArgs a{};
+            if (pfon) a.pf = pf_of({{l.o.w, (size_t)c.D * c.H * c.HD}});
             a.seg[0] = make_seg(SEG_I8, l.q.w, l.q.s, l.q.n, big, 2 * c.H * c.HD);
             a.seg[1] = make_seg(SEG_I8, l.k.w, l.k.s, l.k.n, kraw, c.KV * c.HD);
             a.seg[2] = make_seg(SEG_I8, l.v.w, l.v.s, l.v.n, vraw, c.KV * c.HD);
@@ -886,15 +918,16 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             t.kpool = (char*)kpool + kv_layer * l.slot; t.vpool = (char*)vpool + kv_layer * l.slot;
             t.page_table = page_table; t.pages_per_seq = pages_per_seq;
             t.H = c.H; t.KV = c.KV; t.RD = c.RD; t.eps = c.eps; t.scale = 1.0f / std::sqrt((float)c.HD);
-            t.part = attn_part; t.out = att; t.nsplit = nsplit;
+            t.part = attn_part; t.out = att; t.nsplit = nsplit; t.pf = pf_moe_in;
             cudaError_t e = launch_attn(t, c.HD, kv_f32, B, st, attn_tiles);
             if (e != cudaSuccess) return fail("attention launch: %s", cudaGetErrorString(e));
             mark(3, st);
             ProjArgs p{};
             p.in = att; p.mode = 1; p.w = l.o.w; p.s = l.o.s; p.x = x; p.N = c.D; p.K = c.H * c.HD; p.eps = c.eps; p.DV = c.DV;
-            launch_proj(p, B, nsm, st, bc);
+            launch_proj(p, B, nsm, st, bc, &pf_shdown);
         } else {
             GemvArgs a{};
+            if (pfon) a.pf = pf_of({{l.out.w, (size_t)c.D * c.VD()}});
             a.seg[0] = make_seg(SEG_I8_CONV, l.in_qkv.w, l.in_qkv.s, l.in_qkv.n, big, c.C());
             a.seg[1] = make_seg(SEG_I8_SILU, l.in_z.w, l.in_z.s, l.in_z.n, zbuf, c.VD());
             a.seg[2] = make_seg(SEG_BF_SIGMOID, l.in_b, nullptr, c.HV, beta, c.HV);
@@ -907,13 +940,13 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             mark(1, st);
             DeltaArgs d{};
             d.y = big; d.beta = beta; d.g = gdec; d.state = state + (size_t)l.slot * B * c.HV * c.DK * c.DV;
-            d.o = obuf; d.C = c.C(); d.HK = c.HK; d.HV = c.HV; d.DV = c.DV; d.prenormed = 0;
+            d.o = obuf; d.C = c.C(); d.HK = c.HK; d.HV = c.HV; d.DV = c.DV; d.prenormed = 0; d.pf = pf_moe_in;
             launch_delta(d, c.DK, B, st);
             mark(2, st);
             ProjArgs p{};
             p.in = obuf; p.z = zbuf; p.gn_w = l.gnorm; p.eps = c.eps; p.DV = c.DV; p.mode = 0;
             p.w = l.out.w; p.s = l.out.s; p.x = x; p.N = c.D; p.K = c.VD();
-            launch_proj(p, B, nsm, st, bc);
+            launch_proj(p, B, nsm, st, bc, &pf_shdown);
         }
         mark(4, st);
         n += l.attn ? 4 : 3;
@@ -925,7 +958,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.seg[1].w2 = l.sh_up.w; a.seg[1].s2 = l.sh_up.s;
             a.seg[2] = make_seg(SEG_BF_SIGMOID, l.sh_gw, nullptr, 1, sgate, 1);
             a.nseg = 3; seal(a, c.D);
-            a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D; a.err = d_err;
+            a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D; a.err = d_err; a.pf = pf_next;
             // fewer than 8 tokens on one GPU: the top-8 moves into the expert kernel and the experts are spread over all SMs
             const bool moe1 = ep_world == 1 && B < 8 && moe1_shape_ok(c);
             a.finisher = moe1 ? FIN_NONE : FIN_TOPK; a.counter = d_counter; a.E = c.E; a.topk = c.TOPK;
@@ -1051,6 +1084,8 @@ int b2_engine::reset_state() {
     CU(cudaMemsetAsync(state, 0, state_bytes, stream));
     CU(cudaMemsetAsync(d_pos, 0, B * 4, stream));
     length = 0;
+    toks.clear();
+    toks_known = true;
     snap_pos[0] = snap_pos[1] = -1;
     return 0;
 }
@@ -1226,6 +1261,7 @@ int b2_open(const char* nx_path, int max_context, int device, int batch, int kv_
     int rc = b2_create(js.c_str(), max_context, device, batch, kv_dtype, 0, 1, out);
     if (rc) return rc;
     b2_engine* e = *out;
+    e->fingerprint = nx.fingerprint();
     for (auto& kv : nx.tensors) {
         const NxTensor& t = kv.second;
         if (e->put(kv.first, t.dtype, t.shape, nx.data(t), t.nbytes, false)) return 1;
@@ -1271,6 +1307,7 @@ int b2_feed(b2_engine* e, const uint32_t* ids, int n, float* logits_out) {
         // the id travels as a kernel-independent 4-byte copy ordered on the stream
         CUE(cudaMemcpyAsync(e->d_tok, ids + i, 4, cudaMemcpyHostToDevice, e->stream));
         if (e->run_steps(1)) return 1;
+        e->toks.push_back(ids[i]);
     }
     if (logits_out) CUE(cudaMemcpyAsync(logits_out, e->logits, (size_t)e->c.V * 4, cudaMemcpyDeviceToHost, e->stream));
     return e->check_device_error();
@@ -1295,6 +1332,7 @@ int b2_feed_batch(b2_engine* e, const uint32_t* ids, uint32_t* next_greedy, floa
     memcpy(e->h_pin, ids, (size_t)e->B * 4);
     CUE(cudaMemcpyAsync(e->d_tok, e->h_pin, (size_t)e->B * 4, cudaMemcpyHostToDevice, e->stream));
     if (e->run_steps(1)) return 1;
+    if (e->B == 1) e->toks.push_back(ids[0]); else e->toks_known = false;
     if (next_greedy) CUE(cudaMemcpyAsync(e->h_pin + e->B, e->d_next, (size_t)e->B * 4, cudaMemcpyDeviceToHost, e->stream));
     if (logits_out) CUE(cudaMemcpyAsync(logits_out, e->logits, (size_t)e->B * e->c.V * 4, cudaMemcpyDeviceToHost, e->stream));
     if (e->check_device_error()) return 1;
@@ -1323,6 +1361,10 @@ int b2_decode_greedy(b2_engine* e, const uint32_t* first, int steps, uint32_t* t
     CUE(cudaMemcpyAsync(tokens_out, hist, (size_t)steps * B * 4, cudaMemcpyDeviceToHost, e->stream));
     CUE(cudaStreamSynchronize(e->stream));
     cudaFree(hist);
+    if (B == 1) {                       // fed: the first token, then every arg-max but the last
+        e->toks.push_back(first[0]);
+        for (int s = 0; s + 1 < steps; s++) e->toks.push_back(tokens_out[s]);
+    } else e->toks_known = false;
     if (device_ms) CUE(cudaEventElapsedTime(device_ms, e->ev0, e->ev1));
     return e->check_device_error();
 }
@@ -1343,6 +1385,7 @@ int b2_crop(b2_engine* e, int n) {
     if (ok) {
         const int p = (int)e->snap_pos[best];
         e->length = p;
+        if ((int)e->toks.size() >= p) e->toks.resize(p);
         k_fill_i32<<<(e->B + 255) / 256, 256, 0, e->stream>>>(e->d_pos, p, e->B);
         for (int i = 0; i < 2; i++) if (e->snap_pos[i] > p) e->snap_pos[i] = -1;
     } else {
@@ -1362,6 +1405,116 @@ int b2_snapshot(b2_engine* e) {
     CUE(cudaMemcpyAsync(e->snap_state[i], e->state, e->state_bytes, cudaMemcpyDeviceToDevice, e->stream));
     CUE(cudaStreamSynchronize(e->stream));
     e->snap_pos[i] = e->length;
+    return 0;
+}
+
+// ---- saved states (trait Lm::state_key / save_state / load_state, aegist_rs/src/model.rs:375-387) ----
+// File format of the reference's engines that save states (aegist_rs/src/next.rs:2442-2548): "AEGSTATE", u64 LE
+// header length, JSON {"key", "toks"}, then layer by layer what the first n tokens left behind: an attention
+// layer's keys and values per KV head (n rows each), a DeltaNet layer's conv taps [C][3] and state [HV][DK][DV].
+std::string b2_engine::state_key() const {
+    char buf[96];
+    snprintf(buf, sizeof(buf), "-%dx%dx%d%s", c.L, c.KV, c.HD, kv_f32 ? "-kvf32" : "");
+    return (fingerprint.empty() ? std::string("tensors") : fingerprint) + buf;
+}
+// (device address, bytes) of every piece in file order; the KV rows of a head are contiguous within a 64-token page
+std::vector<b2_engine::Piece> b2_engine::state_pieces(int n) const {
+    std::vector<Piece> v;
+    const size_t esz = kv_f32 ? 4 : 2;
+    const size_t kv_layer = (size_t)B * pages_per_seq * c.KV * KV_PAGE * c.HD * esz;
+    for (const LayerW& l : layers) {
+        if (l.attn) {
+            for (int h = 0; h < c.KV; h++)
+                for (int which = 0; which < 2; which++)
+                    for (int p0 = 0; p0 < n; p0 += KV_PAGE) {
+                        const int rows = std::min(KV_PAGE, n - p0);
+                        char* pool = (char*)(which ? vpool : kpool) + kv_layer * l.slot;
+                        v.push_back({pool + (((size_t)(p0 / KV_PAGE) * c.KV + h) * KV_PAGE) * c.HD * esz, (size_t)rows * c.HD * esz});
+                    }
+        } else {
+            v.push_back({(char*)(conv + (size_t)l.slot * B * c.C() * 3), (size_t)c.C() * 3 * 4});
+            v.push_back({(char*)(state + (size_t)l.slot * B * c.HV * c.DK * c.DV), (size_t)c.HV * c.DK * c.DV * 4});
+        }
+    }
+    return v;
+}
+
+const char* b2_state_key(const b2_engine* e) {
+    static thread_local std::string k;
+    k = e ? e->state_key() : "";
+    return k.c_str();
+}
+
+int b2_save_state(b2_engine* e, const char* path) {
+    if (!e || !e->finished) return 1;
+    if (e->B != 1) return e->fail("states are saved for one sequence (this engine has %d)", e->B);
+    if (!e->toks_known || (int)e->toks.size() != e->length) return e->fail("the tokens of this context are not all known to the host (device-side steps were run)");
+    CUE(cudaSetDevice(e->device));
+    CUE(cudaStreamSynchronize(e->stream));
+    const int n = e->length;
+    std::string head = "{\"key\":\"" + e->state_key() + "\",\"toks\":[";
+    for (int i = 0; i < n; i++) head += (i ? "," : "") + std::to_string(e->toks[i]);
+    head += "]}";
+    const std::string tmp = std::string(path) + ".tmp";
+    FILE* f = fopen(tmp.c_str(), "wb");
+    if (!f) return e->fail("%s: %s", tmp.c_str(), strerror(errno));
+    const uint64_t hl = head.size();
+    bool ok = fwrite("AEGSTATE", 1, 8, f) == 8 && fwrite(&hl, 8, 1, f) == 1 && fwrite(head.data(), 1, head.size(), f) == head.size();
+    std::vector<char> buf;
+    for (auto& pc : e->state_pieces(n)) {
+        if (!ok) break;
+        buf.resize(pc.bytes);
+        if (cudaMemcpy(buf.data(), pc.p, pc.bytes, cudaMemcpyDeviceToHost) != cudaSuccess) { ok = false; break; }
+        ok = fwrite(buf.data(), 1, pc.bytes, f) == pc.bytes;
+    }
+    ok = (fclose(f) == 0) && ok;
+    if (!ok) { remove(tmp.c_str()); cudaGetLastError(); return e->fail("%s: could not write the state", tmp.c_str()); }
+    if (rename(tmp.c_str(), path) != 0) return e->fail("%s: %s", path, strerror(errno));
+    return 0;
+}
+
+int b2_load_state(b2_engine* e, const char* path, uint32_t* toks_out, int cap_toks, int* n_out) {
+    if (!e || !e->finished) return 1;
+    if (e->B != 1) return e->fail("states are loaded for one sequence (this engine has %d)", e->B);
+    CUE(cudaSetDevice(e->device));
+    // on any error the engine is left empty (model.rs:383-384)
+    e->reset_state();
+    cudaStreamSynchronize(e->stream);
+    FILE* f = fopen(path, "rb");
+    if (!f) return e->fail("%s: %s", path, strerror(errno));
+    char magic[16];
+    if (fread(magic, 1, 16, f) != 16 || memcmp(magic, "AEGSTATE", 8) != 0) { fclose(f); return e->fail("%s: not a saved state", path); }
+    uint64_t hl;
+    memcpy(&hl, magic + 8, 8);
+    if (hl > (1ull << 30)) { fclose(f); return e->fail("%s: not a saved state", path); }
+    std::string head(hl, 0);
+    if (fread(&head[0], 1, hl, f) != hl) { fclose(f); return e->fail("%s: truncated", path); }
+    JValue j;
+    std::string jerr;
+    JParser parser(head.data(), head.size());
+    if (!parser.parse(j, jerr)) { fclose(f); return e->fail("%s: %s", path, jerr.c_str()); }
+    const JValue* key = j.get("key");
+    if (!key || key->type != JValue::Str || key->str != e->state_key()) { fclose(f); return e->fail("%s: saved by another brain", path); }
+    std::vector<uint32_t> toks;
+    if (const JValue* t = j.get("toks")) for (auto& x : t->arr) toks.push_back((uint32_t)x.num);
+    const int n = (int)toks.size();
+    if (n == 0 || n >= e->cap) { fclose(f); return e->fail("%s: %d tokens do not fit a context of %d", path, n, e->cap); }
+    std::vector<char> buf;
+    for (auto& pc : e->state_pieces(n)) {
+        buf.resize(pc.bytes);
+        if (fread(buf.data(), 1, pc.bytes, f) != pc.bytes) { fclose(f); e->reset_state(); return e->fail("%s: truncated", path); }
+        if (cudaMemcpy(pc.p, buf.data(), pc.bytes, cudaMemcpyHostToDevice) != cudaSuccess) { fclose(f); cudaGetLastError(); e->reset_state(); return e->fail("%s: upload failed", path); }
+    }
+    fclose(f);
+    k_fill_i32<<<1, 32, 0, e->stream>>>(e->d_pos, n, 1);
+    CUE(cudaStreamSynchronize(e->stream));
+    e->length = n;
+    e->toks = toks;
+    e->toks_known = true;
+    e->snap_pos[0] = e->snap_pos[1] = -1;
+    if (b2_snapshot(e)) return 1;
+    if (n_out) *n_out = n;
+    if (toks_out) memcpy(toks_out, toks.data(), (size_t)std::min(n, cap_toks) * 4);
     return 0;
 }
 
@@ -1446,6 +1599,7 @@ int b2_debug_seek(b2_engine* e, int n) {
     k_fill_i32<<<(e->B + 255) / 256, 256, 0, e->stream>>>(e->d_pos, n, e->B);
     CUE(cudaStreamSynchronize(e->stream));
     e->length = n;
+    e->toks_known = false;
     return 0;
 }
 
@@ -1456,6 +1610,15 @@ double b2_step_bytes(const b2_engine* e) {
     double s = 0;
     for (double v : cls) s += v;
     return s;
+}
+
+double b2_ep_bytes_per_step(const b2_engine* e) {
+    if (!e || e->ep_world <= 1) return 0;
+    const Cfg& c = e->c;
+    const double peers = e->ep_world - 1;
+    const double gather = peers * e->B * (c.D + 2.0 * c.TOPK) * 4;       // this GPU's records, to every peer
+    const double back = peers * e->B * (c.TOPK + 1.0) * c.D * 4;         // pick outputs computed here, to their owners
+    return c.L * (gather + back);
 }
 
 int b2_debug_trace_step(b2_engine* e, unsigned long long* out, int cap_launches, int* n_launches) {
@@ -1484,6 +1647,7 @@ int b2_debug_trace_step(b2_engine* e, unsigned long long* out, int cap_launches,
     cudaGraphExecDestroy(ge);
     if (ce != cudaSuccess) return e->fail("trace step: %s", cudaGetErrorString(ce));
     e->length += 1;
+    e->toks_known = false;
     const int m = std::min(std::min(n, cap_launches), TRACE_MAX_LAUNCHES);
     cudaMemcpy(out, e->d_trace, (size_t)m * 128, cudaMemcpyDeviceToHost);
     *n_launches = m;
@@ -1502,6 +1666,7 @@ int b2_profile_step(b2_engine* e, int iters, float ms[8], double bytes[8], int l
         cudaError_t ce = cudaStreamSynchronize(e->stream);
         if (ce != cudaSuccess) { e->profiling = false; return e->fail("profile step: %s", cudaGetErrorString(ce)); }
         e->length += 1;
+        e->toks_known = false;
         for (size_t k = 1; k < e->prof_used; k++) {
             float t = 0;
             cudaEventElapsedTime(&t, e->prof_ev[k - 1], e->prof_ev[k]);

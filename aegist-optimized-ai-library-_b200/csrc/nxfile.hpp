@@ -1,6 +1,10 @@
 // Reader for the .nx brain format (writer: aegist/nx.py:70-143; Rust reader: aegist_rs/src/nx.rs).
 //   bytes 0..8 magic "AEGISTNX" | 8..12 u32 LE version | 12..20 u64 LE header length H | H bytes JSON
 //   data section from the next 64-byte boundary; every tensor 64-byte aligned.
+// A cores file (aegist_rs/src/nx.rs:82-110) is an .nx file whose header names a base file
+// ("base": {"path", "sha256"}) and whose tensors, all of group "cores", replace the base's tensors of the same
+// names: opening it opens the base, checks that the base's weights are the ones the cores were learned on, and
+// lays the cores over them.
 #pragma once
 #include <fcntl.h>
 #include <sys/mman.h>
@@ -23,6 +27,7 @@ struct NxTensor {
     std::vector<int64_t> shape;
     size_t offset = 0, nbytes = 0;
     std::string group;
+    bool overlay = false;     // the bytes live in the cores file laid over this base
 };
 
 class NxFile {
@@ -38,8 +43,70 @@ public:
         if (fd_ >= 0) ::close(fd_);
         map_ = nullptr;
         fd_ = -1;
+        delete over_;
+        over_ = nullptr;
     }
+    // open `p`; when it is a cores file, this object becomes its base with the cores laid over it
     bool open(const std::string& p, std::string& err) {
+        if (!open_one(p, err)) return false;
+        const JValue* base = header.get("base");
+        if (!base || base->type != JValue::Obj) return true;
+        const JValue* bp = base->get("path");
+        if (!bp || bp->type != JValue::Str) { err = p + ": base has no path"; return false; }
+        NxFile* top = new NxFile();
+        // this object's mapping moves into `top`; then the base is opened in place
+        top->path = path; top->header = header; top->tensors = tensors; top->data_start = data_start;
+        top->fd_ = fd_; top->map_ = map_; top->size_ = size_;
+        fd_ = -1; map_ = nullptr; size_ = 0;
+        const std::string base_path = bp->str;
+        tensors.clear();
+        if (!open_one(base_path, err)) { err = p + " is learned cores over " + base_path + ": " + err; delete top; return false; }
+        const JValue* nested = header.get("base");
+        if (nested && nested->type == JValue::Obj) { err = p + ": its base " + base_path + " is itself a cores file"; delete top; return false; }
+        const JValue* have = header.get("sha256");
+        const JValue* hb = have ? have->get("base") : nullptr;
+        const JValue* want = base->get("sha256");
+        if (!hb || !want || hb->type != JValue::Str || want->type != JValue::Str || hb->str != want->str) {
+            err = p + " was learned on a different " + base_path + " (its weights changed since)";
+            delete top;
+            return false;
+        }
+        for (auto& kv : top->tensors) {
+            NxTensor t = kv.second;
+            if (t.group != "cores") { err = p + ": a cores file may only hold cores, not " + kv.first; delete top; return false; }
+            auto it = tensors.find(kv.first);
+            bool fits = it != tensors.end() && it->second.dtype == t.dtype && it->second.shape.size() == t.shape.size();
+            for (size_t i = 1; fits && i < t.shape.size(); i++) fits = it->second.shape[i] == t.shape[i];
+            if (!fits) { err = p + ": " + kv.first + " does not fit " + base_path; delete top; return false; }
+            t.overlay = true;
+            tensors[kv.first] = t;
+        }
+        over_ = top;
+        return true;
+    }
+    // sha256 over the header's hash object in compact JSON with sorted keys (what serde_json prints), then over the
+    // cores file's, first 12 bytes in hex (NxFile::fingerprint, aegist_rs/src/nx.rs:114-124); empty without hashes
+    std::string fingerprint() const {
+        auto dump = [](const JValue* o) {
+            std::vector<std::pair<std::string, std::string>> kv;
+            for (auto& e : o->obj) kv.emplace_back(e.first, e.second.str);
+            std::sort(kv.begin(), kv.end());
+            std::string s = "{";
+            for (size_t i = 0; i < kv.size(); i++) s += std::string(i ? "," : "") + "\"" + kv[i].first + "\":\"" + kv[i].second + "\"";
+            return s + "}";
+        };
+        const JValue* h = header.get("sha256");
+        if (!h || h->type != JValue::Obj) return "";
+        Sha256 sh;
+        std::string a = dump(h);
+        sh.update((const uint8_t*)a.data(), a.size());
+        if (over_) {
+            const JValue* oh = over_->header.get("sha256");
+            if (oh && oh->type == JValue::Obj) { std::string b = dump(oh); sh.update((const uint8_t*)b.data(), b.size()); }
+        }
+        return sh.hex().substr(0, 24);
+    }
+    bool open_one(const std::string& p, std::string& err) {
         path = p;
         fd_ = ::open(p.c_str(), O_RDONLY);
         if (fd_ < 0) { err = "cannot open " + p + ": " + strerror(errno); return false; }
@@ -77,7 +144,10 @@ public:
         }
         return true;
     }
-    const uint8_t* data(const NxTensor& t) const { return map_ + data_start + t.offset; }
+    const uint8_t* data(const NxTensor& t) const {
+        if (t.overlay && over_) return over_->map_ + over_->data_start + t.offset;
+        return map_ + data_start + t.offset;
+    }
 
     // group -> matches the header's sha256; order (group, name) as the writer hashes
     std::map<std::string, bool> verify() const {
@@ -105,6 +175,7 @@ private:
     int fd_ = -1;
     const uint8_t* map_ = nullptr;
     size_t size_ = 0;
+    NxFile* over_ = nullptr;      // the cores file laid over this base, if any
 };
 
 }  // namespace b2

@@ -59,6 +59,9 @@ SYMBOLS = {
     "b2_decode_greedy": (_I, [_P, _P, _I, _P, C.POINTER(_F)]),
     "b2_crop": (_I, [_P, _I]),
     "b2_snapshot": (_I, [_P]),
+    "b2_state_key": (C.c_char_p, [_P]),
+    "b2_save_state": (_I, [_P, C.c_char_p]),
+    "b2_load_state": (_I, [_P, C.c_char_p, _P, _I, C.POINTER(_I)]),
     "b2_length": (_I, [_P]),
     "b2_cap": (_I, [_P]),
     "b2_set_taps": (_I, [_P, C.POINTER(_I), _I]),
@@ -77,6 +80,7 @@ SYMBOLS = {
     "b2_debug_seek": (_I, [_P, _I]),
     "b2_launches_per_step": (_I, [_P]),
     "b2_step_bytes": (C.c_double, [_P]),
+    "b2_ep_bytes_per_step": (C.c_double, [_P]),
     "b2_profile_step": (_I, [_P, _I, C.POINTER(_F), C.POINTER(C.c_double), C.POINTER(_I)]),
     "b2_debug_trace_step": (_I, [_P, C.POINTER(C.c_uint64), _I, C.POINTER(_I)]),
     "b2_op_linear_i8": (_I, [_I, _P, _P, _I, _I, _P, _I, _P]),
@@ -250,6 +254,21 @@ class HybridEngine:
     def snapshot(self):
         self._check(self._lib.b2_snapshot(self._h))
 
+    def state_key(self) -> str:
+        """Lm::state_key (aegist_rs/src/model.rs:375-378)."""
+        return self._lib.b2_state_key(self._h).decode()
+
+    def save_state(self, path: str):
+        """Lm::save_state: what the tokens fed so far left behind, in the reference's AEGSTATE file format."""
+        self._check(self._lib.b2_save_state(self._h, os.fsencode(path)))
+
+    def load_state(self, path: str):
+        """Lm::load_state -> the saved tokens; on an error the engine is left empty."""
+        toks = np.zeros(max(self.cap(), 1), dtype=np.uint32)
+        n = C.c_int(0)
+        self._check(self._lib.b2_load_state(self._h, os.fsencode(path), _ptr(toks), len(toks), C.byref(n)))
+        return toks[: n.value].tolist()
+
     def length(self) -> int:
         return self._lib.b2_length(self._h)
 
@@ -311,6 +330,10 @@ class HybridEngine:
 
     def step_bytes(self) -> float:
         return self._lib.b2_step_bytes(self._h)
+
+    def ep_bytes_per_step(self) -> float:
+        """Bytes this GPU sends to its peers over NVLink in one decode step (expert parallelism)."""
+        return self._lib.b2_ep_bytes_per_step(self._h)
 
     # roles of the launches of a decode step; which kernel fills a role depends on the batch:
     #   1-7 sequences: k_tcgemv (in_proj, out_proj, head), k_moe_gu1, k_moe_down1

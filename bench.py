@@ -86,63 +86,137 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def oracle_sample(cfg_full, steps: int, warmup: int, device: str):
-    """The CPU port of the reference path on a bounded sample of the workload: one period of the
-    layer pattern (3 DeltaNet + 1 attention layers at full width, all 256 experts of each) plus the
-    head, single-token steps after a 4-token prompt; a full-model token costs ten such periods plus
-    one head. Weights are re-materialised on every call, as the reference's QLinear does."""
+SAMPLE_LAYERS = 4          # one period of the layer pattern: 3 DeltaNet + 1 attention, at full width
+
+
+def sample_brain(device: str):
+    """The first four layers of the benchmarked model (seed 0, full width, full vocabulary) as device tensors for the
+    engine and as host arrays for the CPU legs."""
     import torch
     from __graft_entry__ import load_package
     load_package()
     from b200moe import brain
     from b200moe.config import HybridConfig
-    from oracle import hybrid_oracle as O
+    cfg4 = HybridConfig.full(n_layers=SAMPLE_LAYERS)
+    dev = list(brain.random_brain(cfg4, seed=0, device=device))
+    host = {}
+    for name, dt, t in dev:
+        c = t.detach().contiguous().cpu()
+        host[name] = (dt, c.view(torch.int16).numpy().view(np.uint16) if dt == "bf16" else c.numpy())
+    return cfg4, dev, host
 
-    cfg4 = HybridConfig.full(n_layers=4)
-    tensors = {}
-    for name, dt, t in brain.random_brain(cfg4, seed=0, device=device):
-        t = t.detach().contiguous().cpu()
-        tensors[name] = (dt, t.view(torch.int16).numpy().view(np.uint16) if dt == "bf16" else t.numpy())
-    model = O.HybridOracle(O.DictBrain(cfg4.to_dict(), tensors), hold_weights=False)
-    cache = model.new_cache(1, 8 + warmup + steps, kv_dtype="bf16")
-    lg = model.forward(np.asarray([[11, 22, 33, 44]]), cache)[0]
-    tok = int(np.argmax(lg))
-    for _ in range(warmup):
-        tok = int(np.argmax(model.forward(np.asarray([[tok]]), cache)[0]))
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        tok = int(np.argmax(model.forward(np.asarray([[tok]]), cache)[0]))
-    t_fwd = (time.perf_counter() - t0) / steps
-    h = np.zeros((1, cfg4.d_model), dtype=np.float32)
-    t0 = time.perf_counter()
-    for _ in range(max(1, min(steps, 3))):
-        model.qlinear(h, "lm_head")
-    t_head = (time.perf_counter() - t0) / max(1, min(steps, 3))
-    periods = cfg_full.n_layers / 4
-    t_full = (t_fwd - t_head) * periods + t_head
+
+def parity_check(E, cfg4, dev, host, tokens: int = 6):
+    """The engine (bf16 cache, the kernels of the timed run) against the CPU oracle on the sample brain: a few
+    single-token steps, compared on logits, router picks of every layer and greedy tokens."""
+    from oracle import hybrid_oracle as O
+    model = O.HybridOracle(O.DictBrain(cfg4.to_dict(), host), hold_weights=True)
+    cache = model.new_cache(1, tokens + 8, kv_dtype="bf16")
+    eng = E.HybridEngine.from_tensors(cfg4.to_dict(), dev, max_context=PROMPT, device=0, batch=1, kv_dtype=E.KV_BF16)
+    tok, worst, routes, greedy = 11, 0.0, True, True
+    for _ in range(tokens):
+        want = model.forward(np.asarray([[tok]]), cache)[0]
+        got = eng.feed([tok])
+        worst = max(worst, float(np.abs(got - want).max()))
+        for layer in range(cfg4.n_layers):
+            routes = routes and bool(np.array_equal(eng.router(layer, cfg4.experts_active)[0], model.last_route[layer][0]))
+        greedy = greedy and int(np.argmax(got)) == int(np.argmax(want))
+        tok = int(np.argmax(want))
+    eng.close()
+    return {"against": f"CPU oracle, {SAMPLE_LAYERS}-layer full-width sample brain, {tokens} greedy steps, bf16 cache",
+            "max_abs": worst, "routes_equal": routes, "greedy_equal": greedy}, model
+
+
+REF_DIR = os.path.join(ROOT, "oracle", "_ref")
+
+
+def cpu_sample(cfg_full, cfg4, host, model, steps: int, warmup: int):
+    """The reference path on the host cores over a bounded sample of the workload: single-token steps through one
+    period of the layer pattern (3 DeltaNet + 1 attention layers at full width, 256 experts each) plus the head after
+    a 4-token prompt; a full-model token costs ten such periods plus one head. With the reference's own Python
+    package present under oracle/_ref (placed there by oracle/make_ref.py; it never enters the repository's history)
+    this runs the reference's HybridLM in torch fp32 exactly as its parity test does
+    (tests/test_hybrid_rust.py:96-116), kind "reference"; otherwise the numpy port, kind "port"."""
     cores = os.cpu_count() or 1
-    return {"value": 1.0 / t_full, "unit": "tok/s", "cores": cores, "kind": "port",
-            "sample": (f"numpy port of aegist/hybrid.py, fp32, {steps} single-token steps through 4 full-width layers "
-                       f"(3 DeltaNet + 1 attention, 256 experts each) + lm_head at context < 16, "
+    periods = cfg_full.n_layers / SAMPLE_LAYERS
+    if os.path.exists(os.path.join(REF_DIR, "aegist", "hybrid.py")):
+        import torch
+        from b200moe import nxfile
+        from b200moe.brain import Bf16
+        sys.path.insert(0, REF_DIR)
+        from aegist import nx as NX
+        torch.set_num_threads(cores)
+        with tempfile.TemporaryDirectory() as tmp:
+            path = os.path.join(tmp, "sample.nx")
+            state = {n: (Bf16(a) if dt == "bf16" else a) for n, (dt, a) in host.items()}
+            from tokenizers import Tokenizer, models
+            tk = Tokenizer(models.WordLevel({"hi": 0, "there": 1, "[UNK]": 2}, unk_token="[UNK]"))
+            tk.add_special_tokens(["<|im_start|>", "<|im_end|>", "<|endoftext|>"])
+            nxfile.save(path, state, cfg4.to_dict(), tk.to_str(),
+                        extra={"quant": "int8", "dtype": "bf16", "experts": "q4a-g64", "seed": 0})
+            ref, _, nx = NX.load_model(path, device="cpu", slots=cfg4.n_experts)
+            ref.float()
+            cache = ref.new_cache(1, 16 + warmup + steps, dtype=torch.float32)
+            with torch.no_grad():
+                fwd = lambda ids: ref(torch.tensor([ids]), cache=cache, last_only=True)["logits"][0, -1].float()
+                tok = int(fwd([11, 22, 33, 44]).argmax())
+                for _ in range(warmup):
+                    tok = int(fwd([tok]).argmax())
+                t0 = time.perf_counter()
+                for _ in range(steps):
+                    tok = int(fwd([tok]).argmax())
+                t_fwd = (time.perf_counter() - t0) / steps
+                h = torch.zeros(1, cfg4.d_model)
+                t0 = time.perf_counter()
+                for _ in range(3):
+                    ref.lm_head(h)
+                t_head = (time.perf_counter() - t0) / 3
+            del ref, cache
+            nx.close()
+        kind, what = "reference", f"the reference's HybridLM (torch fp32, {cores} threads)"
+    else:
+        from oracle import hybrid_oracle as O
+        model = O.HybridOracle(model.b, hold_weights=False)      # weights re-materialised per call, as the reference's QLinear does
+        cache = model.new_cache(1, 16 + warmup + steps, kv_dtype="bf16")
+        tok = int(np.argmax(model.forward(np.asarray([[11, 22, 33, 44]]), cache)[0]))
+        for _ in range(warmup):
+            tok = int(np.argmax(model.forward(np.asarray([[tok]]), cache)[0]))
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            tok = int(np.argmax(model.forward(np.asarray([[tok]]), cache)[0]))
+        t_fwd = (time.perf_counter() - t0) / steps
+        h = np.zeros((1, cfg4.d_model), dtype=np.float32)
+        t0 = time.perf_counter()
+        for _ in range(3):
+            model.qlinear(h, "lm_head")
+        t_head = (time.perf_counter() - t0) / 3
+        kind, what = "port", f"numpy port of aegist/hybrid.py (fp32, {cores} threads available to BLAS)"
+    t_full = (t_fwd - t_head) * periods + t_head
+    return {"value": 1.0 / t_full, "unit": "tok/s", "cores": cores, "kind": kind,
+            "sample": (f"{what}: {steps} single-token steps through {SAMPLE_LAYERS} full-width layers "
+                       f"(3 DeltaNet + 1 attention, 256 experts each) + lm_head at context < 32, "
                        f"{t_fwd * 1e3:.0f} ms per sampled token of which head {t_head * 1e3:.0f} ms, "
-                       f"scaled to 40 layers + head = {t_full * 1e3:.0f} ms per token")}
+                       f"scaled to {cfg_full.n_layers} layers + head = {t_full * 1e3:.0f} ms per token")}
 
 
 def run_reference(args):
-    """The reference arm: the reference's own CPU implementation of the path (its Python model cannot
-    travel to the GPU box, so the numpy port stands in), on all host cores, same metric and config."""
+    """The reference arm: the reference's own CPU implementation of the path on all host cores, same metric and
+    config (see cpu_sample for what runs and what the bounded sample is)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     import torch
     from __graft_entry__ import load_package
     pkg = load_package()
+    from oracle import hybrid_oracle as O
     cfg = pkg.HybridConfig.full()
     steps = max(1, min(args.steps, 4))
     warm = max(0, min(args.warmup, 1))
     dev = "cuda" if torch.cuda.is_available() else "cpu"   # building the weights is set-up, not the timed path
     t0 = time.perf_counter()
-    cb = oracle_sample(cfg, steps, warm, dev)
+    cfg4, _, host = sample_brain(dev)
+    model = O.HybridOracle(O.DictBrain(cfg4.to_dict(), host), hold_weights=False)
+    cb = cpu_sample(cfg, cfg4, host, model, steps, warm)
     line = {"impl": "reference", "metric": METRIC, "value": cb["value"], "unit": "tok/s", "n_gpus": args.gpus,
             "steps": steps, "warmup": warm, "ms_per_step": 1e3 / cb["value"], "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
@@ -193,24 +267,14 @@ def run_profile_case(args):
             prev = e
 
 
-def run_b64(args):
-    """Batched decode of 64 sequences, expert-parallel over the ranks (256/N experts of every layer per
-    GPU, the routed tokens exchanged by NCCL), router bias for Zipf(1.1) expert popularity."""
+def b64_measure(pkg, K: int, W: int, world: int, rank: int, local: int, dist):
+    """Batched decode of 64 sequences at context 8192 with Zipf(1.1) expert popularity, expert-parallel over `world`
+    ranks (256/world experts of every layer per GPU, the routed tokens exchanged by NCCL). Returns rank 0's line."""
+    import hashlib
     import torch
-    import torch.distributed as dist
-    from __graft_entry__ import load_package
-    pkg = load_package()
     from b200moe import brain, ep
     from b200moe import engine as E
-
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     cfg = pkg.HybridConfig.full()
-    K, W = args.steps, max(args.warmup, 3)
     Bt = 64
     B = Bt // world
     fed = 16
@@ -224,8 +288,8 @@ def run_b64(args):
     for layer in range(cfg.n_layers):
         eng.set_router_bias(layer, brain.router_popularity_bias(cfg, layer, 0, 1.1).numpy())
     t_build = time.perf_counter() - t0
-    # context: the prefill kernels are not built, and feeding 64 x 8192 tokens through the decode path would
-    # take minutes, so the length is set directly and only the last `fed` prompt tokens are real
+    # context: feeding 64 x 8192 tokens through the decode path would take minutes, so the length is set directly and
+    # only the last `fed` prompt tokens are real; the bytes read per step are those of a real prompt
     eng.seek(B64_PROMPT - fed)
     g = torch.Generator().manual_seed(1234)
     prompt = torch.randint(0, cfg.vocab_size, (Bt, fed), generator=g).numpy().astype(np.uint32)[rank * B:(rank + 1) * B]
@@ -238,24 +302,29 @@ def run_b64(args):
             dist.barrier()
             torch.cuda.synchronize()
 
-    toks, _ = eng.decode_greedy(prompt[:, -1], W)
+    toks_w, _ = eng.decode_greedy(prompt[:, -1], W)
     barrier()
     clocks = ClockSampler(local)
     clocks.start()
     barrier()
-    toks, ms = eng.decode_greedy(toks[-1], K)
+    toks, ms = eng.decode_greedy(toks_w[-1], K)
     barrier()
     clk = clocks.stop()
     bytes_step = eng.step_bytes()
     # picks per rank in the last step, all layers
     picks = np.stack([eng.router(layer, cfg.experts_active)[0] for layer in range(cfg.n_layers)])
+    all_toks = np.concatenate([toks_w, toks], 0)                      # [W + K][B] greedy tokens of this rank's sequences
     if world > 1:
         t = torch.tensor([ms], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-        allp = [None] * world
+        allp, allt = [None] * world, [None] * world
         dist.all_gather_object(allp, picks)
+        dist.all_gather_object(allt, all_toks)
         picks = np.concatenate(allp, 1)
+        all_toks = np.concatenate(allt, 1)
+    # the same sums in the same order on every number of GPUs: this hash must not depend on N
+    tokens_sha1 = hashlib.sha1(np.ascontiguousarray(all_toks.astype("<u4")).tobytes()).hexdigest()
     load = np.stack([ep.load_per_rank(picks[l], cfg.n_experts, world) for l in range(cfg.n_layers)]).sum(0)
     uniq = float(np.mean([len(np.unique(picks[l])) for l in range(cfg.n_layers)]))
     value = Bt * K / (ms / 1e3)
@@ -273,28 +342,47 @@ def run_b64(args):
         t = torch.tensor([e2e_s], device="cuda")
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_s = float(t.item())
+    n_launch = eng.launches_per_step()
+    nvlink = eng.ep_bytes_per_step() if world > 1 else 0
+    eng.close()
+    torch.cuda.empty_cache()
     peak, peak_kind = peaks()
     step_gbs = bytes_step / (ms / K * 1e-3) / 1e9
+    return {"metric": METRIC_B64, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "full-b64: the 40-layer 35B-A3B-shaped model, 64 sequences at context 8192, greedy decode, "
+                                   "router bias for Zipf(1.1) expert popularity",
+                       "batch": Bt, "sequences_per_gpu": B, "context": B64_PROMPT,
+                       "context_note": f"length set to {B64_PROMPT - fed} directly, then {fed} real tokens fed",
+                       "kv_cache": "bf16", "parallelism": f"ep{world}: {cfg.n_experts // world} experts of every layer per GPU, "
+                                                          "sequences split over the GPUs, NCCL all-gather + all-to-all per layer",
+                       "l2": "per-step traffic exceeds L2 (126 MB); no flush needed"},
+            "e2e": {"value": Bt * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
+                    "timing": "host wall clock around K feed_batch() calls (ids in, arg-max out), max over ranks"},
+            "gpu_launches": n_launch * K,
+            "tokens_sha1": tokens_sha1, "nvlink_bytes_per_step_per_gpu": nvlink,
+            "roofline": {"bound": "hbm", "kernel": "whole step, per GPU", "achieved": step_gbs, "peak": peak, "unit": "GB/s",
+                         "frac": step_gbs / peak, "peak_kind": peak_kind, "traffic": None,
+                         "bytes_per_step_per_gpu": bytes_step},
+            "expert_load": {"picks_per_rank": load.tolist(), "max_over_mean": float(load.max() / load.mean()),
+                            "unique_experts_per_layer": uniq},
+            "cpu_baseline": None, "clocks": clk, "setup": {"build_s": round(t_build, 1)}}
+
+
+def run_b64(args):
+    import torch
+    import torch.distributed as dist
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    line = b64_measure(pkg, args.steps, max(args.warmup, 3), world, rank, local, dist)
     if rank == 0:
-        line = {"metric": METRIC_B64, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
-                "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
-                "data": "synthetic",
-                "config": {"workload": "full-b64: the 40-layer 35B-A3B-shaped model, 64 sequences at context 8192, greedy decode, "
-                                       "router bias for Zipf(1.1) expert popularity",
-                           "batch": Bt, "sequences_per_gpu": B, "context": B64_PROMPT,
-                           "context_note": f"length set to {B64_PROMPT - fed} directly, then {fed} real tokens fed (no prefill kernels yet)",
-                           "kv_cache": "bf16", "parallelism": f"ep{world}: {cfg.n_experts // world} experts of every layer per GPU, "
-                                                              "sequences split over the GPUs, NCCL all-gather + all-to-all per layer",
-                           "l2": "per-step traffic exceeds L2 (126 MB); no flush needed"},
-                "e2e": {"value": Bt * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
-                        "timing": "host wall clock around K feed_batch() calls (ids in, arg-max out), max over ranks"},
-                "gpu_launches": eng.launches_per_step() * K,
-                "roofline": {"bound": "hbm", "kernel": "whole step, per GPU", "achieved": step_gbs, "peak": peak, "unit": "GB/s",
-                             "frac": step_gbs / peak, "peak_kind": peak_kind, "traffic": None,
-                             "bytes_per_step_per_gpu": bytes_step},
-                "expert_load": {"picks_per_rank": load.tolist(), "max_over_mean": float(load.max() / load.mean()),
-                                "unique_experts_per_layer": uniq},
-                "cpu_baseline": None, "clocks": clk, "setup": {"build_s": round(t_build, 1)}}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -402,31 +490,47 @@ def run_ours(args):
         e2e_s = float(t.item())
     e2e = world * K / e2e_s
 
-    # per-role times for the roofline object: CUDA events around every launch of un-graphed steps (which include the
-    # host's launch gaps), and the device-side timeline of a graph-run step (what the timed loop above executes)
+    # per-role times for the roofline object: the device-side timeline of a graph-run step (what the timed loop above
+    # executes; device global timer, from the end of the previous launch to the end of this one), and as a side key
+    # CUDA events around every launch of un-graphed steps (which include the host's launch gaps)
     prof = eng.profile_step(8)
     peak, peak_kind = peaks()
-    name = max((n for n in prof if prof[n]["launches"]), key=lambda n: prof[n]["ms"])
-    dom = prof[name]
-    achieved = dom["bytes"] / (dom["ms"] * 1e-3) / 1e9
-    step_gbs = bytes_step / (ms / K * 1e-3) / 1e9
     in_graph = graph_timeline(eng, prof)
+    roles = {n: v for n, v in in_graph.items() if n in prof and prof[n]["launches"] and v["us_per_step"] > 0}
+    name = max(roles, key=lambda n: roles[n]["us_per_step"])
+    dom, dom_us = prof[name], roles[name]["us_per_step"]
+    achieved = dom["bytes"] / (dom_us * 1e-6) / 1e9
+    step_gbs = bytes_step / (ms / K * 1e-3) / 1e9
+    roles_sum_ms = sum(v["us_per_step"] for v in in_graph.values()) / 1e3
+    consistent = abs(roles_sum_ms - ms / K) <= 0.10 * (ms / K)
+    if not consistent:
+        print(f"warning: the roles' in-graph times sum to {roles_sum_ms:.3f} ms, the timed step is {ms / K:.3f} ms", file=sys.stderr)
     roof = {"bound": "hbm", "kernel": f"{name} ({E.HybridEngine.KERNELS_SMALL_BATCH[name]})", "achieved": achieved, "peak": peak,
             "unit": "GB/s", "frac": achieved / peak, "peak_kind": peak_kind,
             "traffic": NCU_DRAM_BYTES_PER_LAUNCH.get(name), "traffic_source": NCU_DRAM_SOURCE,
             "launches_per_step": dom["launches"], "bytes_per_launch": dom["bytes"] / max(dom["launches"], 1),
-            "ms_per_launch": dom["ms"] / max(dom["launches"], 1),
-            "timing": "CUDA events around each launch of 8 un-graphed steps; in_graph = device global timer inside the CUDA graph",
+            "ms_per_launch": dom_us / 1e3 / max(dom["launches"], 1),
+            "timing": "device global timer inside the CUDA graph of one decode step (b2_debug_trace_step); "
+                      "ungraphed_events = CUDA events around each launch of 8 un-graphed steps",
             "whole_step": {"bytes": bytes_step, "achieved": step_gbs, "frac": step_gbs / peak},
-            "per_kernel": {n: {"ms_per_step": round(v["ms"], 4), "GBps": round(v["bytes"] / max(v["ms"], 1e-9) / 1e6, 1),
-                               "launches": v["launches"], "kernel": E.HybridEngine.KERNELS_SMALL_BATCH[n]} for n, v in prof.items()},
-            "in_graph": in_graph}
-    cb = None
+            "in_graph": in_graph,
+            "consistency": {"roles_sum_ms": round(roles_sum_ms, 4), "ms_per_step": round(ms / K, 4), "within_10_percent": consistent},
+            "ungraphed_events": {n: {"ms_per_step": round(v["ms"], 4), "GBps": round(v["bytes"] / max(v["ms"], 1e-9) / 1e6, 1),
+                                     "launches": v["launches"], "kernel": E.HybridEngine.KERNELS_SMALL_BATCH[n]} for n, v in prof.items()}}
+    cb = parity = b64 = None
     n_launch = eng.launches_per_step()
+    eng.close()
+    torch.cuda.empty_cache()
+    if rank == 0 and world == 1 and not args.no_b64:
+        # the single-GPU point of the expert-parallel series (the lines of --gpus 2/4/8 carry the other points)
+        full = b64_measure(pkg, min(K, 64), 3, 1, 0, local, None)
+        b64 = {k: full[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "tokens_sha1", "roofline", "expert_load", "e2e", "config")}
     if rank == 0 and world == 1 and not args.no_cpu:
-        eng.close()
+        cfg4, dev, host = sample_brain(f"cuda:{local}")
+        parity, model = parity_check(E, cfg4, dev, host)
+        del dev
         torch.cuda.empty_cache()
-        cb = oracle_sample(cfg, 3, 1, f"cuda:{local}")
+        cb = cpu_sample(cfg, cfg4, host, model, 3, 1)
     if rank == 0:
         line = {"metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": W,
                 "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32",
@@ -434,9 +538,9 @@ def run_ours(args):
                 "e2e": {"value": e2e, "unit": "tok/s", "h2d_bytes_per_step": 4, "d2h_bytes_per_step": cfg.vocab_size * 4,
                         "timing": "host wall clock around K feed() calls (id and logits in page-locked host arrays, b2_sample arg-max on the host), synchronised on both sides"},
                 "gpu_launches": n_launch * K,
-                "roofline": roof, "cpu_baseline": cb, "clocks": clk,
+                "roofline": roof, "cpu_baseline": cb, "parity": parity, "b64": b64, "clocks": clk,
                 "setup": {"build_s": round(t_build, 1), "prefill_s": round(t_prefill, 1),
-                          "prefill": "prompt fed through the decode path, untimed"}}
+                          "prefill": "prompt fed through the engine's feed(), untimed"}}
         if world > 1:
             line["config"]["parallelism"] = f"{world} independent replicas (batch-1 decode does not shard)"
         print(json.dumps(line), flush=True)
@@ -450,7 +554,8 @@ if __name__ == "__main__":
     ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the parity check and the CPU baseline leg")
+    ap.add_argument("--no-b64", action="store_true", help="one GPU: skip the batch-64 point of the expert-parallel series")
     ap.add_argument("--workload", default="auto", choices=["auto", "b1", "b64"],
                     help="b1: batch-1 decode (the default on one GPU); b64: 64 sequences, expert-parallel (the default on several)")
     ap.add_argument("--timeline", action="store_true",

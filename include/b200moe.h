@@ -88,6 +88,19 @@ int b2_decode_greedy(b2_engine* e, const uint32_t* first, int steps, uint32_t* t
  * (>= 0) or a negative error. */
 int b2_crop(b2_engine* e, int n);
 int b2_snapshot(b2_engine* e);
+
+/* Lm::state_key / save_state / load_state (aegist_rs/src/model.rs:375-387). The reference's hybrid engine
+ * keeps the trait's defaults (it cannot save); its other engines write the file format used here
+ * (aegist_rs/src/next.rs:2442-2548): "AEGSTATE", u64 LE header length, JSON {"key", "toks"}, then per layer the
+ * keys and values of the first n positions (per KV head) or the conv taps [C][3] and the recurrent state
+ * [HV][DK][DV]. The key is `<fingerprint of the brain file>-<layers>x<kv heads>x<head dim>` (+ "-kvf32" for an
+ * fp32 cache), so a state only loads into the brain that wrote it. One sequence only. b2_load_state returns the
+ * saved tokens (`toks_out` holds up to `cap_toks`, `*n_out` their number), takes a snapshot at that length, and
+ * leaves the engine empty on any error. b2_save_state needs every token of the context to have passed through
+ * the host (b2_feed, b2_feed_batch, b2_decode_greedy). */
+const char* b2_state_key(const b2_engine* e);
+int b2_save_state(b2_engine* e, const char* path);
+int b2_load_state(b2_engine* e, const char* path, uint32_t* toks_out, int cap_toks, int* n_out);
 int b2_length(const b2_engine* e);
 int b2_cap(const b2_engine* e);
 
@@ -142,6 +155,10 @@ double b2_step_bytes(const b2_engine* e);
  * groups, 2 DeltaNet step, 3 attention, 4 output projections, 5 expert gate/up, 6 expert down +
  * shared down, 7 head. */
 int b2_profile_step(b2_engine* e, int iters, float ms[8], double bytes[8], int launches[8]);
+/* Bytes this GPU sends to its peers in one decode step of an expert-parallel engine (0 on one GPU): the per-layer
+ * records (all-gather) and the pick outputs computed here for other GPUs' sequences. No counterpart in the reference. */
+double b2_ep_bytes_per_step(const b2_engine* e);
+
 /* Timeline of one decode step as the CUDA graph runs it (debugging aid, no reference counterpart; the step
  * feeds the current tokens and advances the length by one). Per launch 16 words: [0] first block entered and
  * [4] last block left, in ns of the GPU's global timer; [5] kernel code (1 GEMV, 3 DeltaNet step, 5 expert

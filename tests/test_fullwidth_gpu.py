@@ -62,14 +62,14 @@ def full4(pkg):
     return cfg, dev, model
 
 
-def check_step(e, model, cfg, got, want, tag, wtol=1e-5):
+def check_step(e, model, cfg, got, want, tag, wtol=1e-5, tol=TOL):
     for layer in range(cfg.n_layers):
         idx, w = e.router(layer, cfg.experts_active)
         widx, ww = model.last_route[layer]
         assert np.array_equal(idx, widx), (tag, layer, idx, widx)
         assert np.abs(w - ww).max() < wtol, (tag, layer)
     err = float(np.abs(got - want).max())
-    assert err < TOL, (tag, err)
+    assert err < tol, (tag, err)
     assert np.array_equal(got.argmax(-1), want.argmax(-1)), tag
     reference_accepts(want, got)
     return err
@@ -91,9 +91,12 @@ def test_batch1_decode_at_full_width(E, full4, kv):
         t = ids[j] if j < len(ids) else tok
         want = model.forward(np.asarray([[t]]), cache)
         got = e.feed([t])[None]
-        # bf16 cache: the tensor-core attention kernel also carries the softmax weights as two bf16 planes (2^-16
-        # relative), which shows in the router weights after an attention layer: measured 1.3e-5
-        check_step(e, model, cfg, got, want, (kv, j), 1e-5 if kv == "f32" else 5e-5)
+        # bf16 cache: keys and values are ROUNDED to bfloat16 when they are stored, by the engine and by the oracle
+        # alike. A key that the two compute 1e-7 apart can fall on either side of a rounding boundary, and then it
+        # differs by a whole bf16 step (2^-8 relative) in the two caches; with 1024 stored values per token and layer
+        # that happens once every few tokens and moves the logits by a few 1e-4 (measured 3.9e-4 at the seventh
+        # token, 1.3e-5 on a router weight). The fp32 cache has no such step and keeps the tight bounds.
+        check_step(e, model, cfg, got, want, (kv, j), *((1e-5, TOL) if kv == "f32" else (1e-4, 2e-3)))
         tok = int(got.argmax())
     hid = e.hidden()
     assert np.abs(hid[0] - model.final_hidden[0]).max() < TOL
