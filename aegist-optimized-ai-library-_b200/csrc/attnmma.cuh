@@ -62,7 +62,6 @@ __global__ void __launch_bounds__(THREADS) k_attn_mma(const AttnArgs a, int nbuf
     __shared__ float s_max[WARPS][8], s_sum[WARPS][8];
     grid_dep_launch();
     trace_in(a.trace, 7, gridDim.x);
-    if (warp == WARPS - 1 && blockIdx.z == 0) l2_prefetch_share(a.pf, blockIdx.y * gridDim.x + blockIdx.x, gridDim.x * gridDim.y, lane);
     grid_dep_wait();
     trace_pt(a.trace, 1);
     const int pos = a.pos[b];

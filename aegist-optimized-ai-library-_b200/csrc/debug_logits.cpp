@@ -128,7 +128,7 @@ int main(int argc, char** argv) {
     uint64_t hits = 0, page_ins = 0;
     b2_expert_counters(e, &hits, &page_ins);
     fprintf(stderr, "%s; prefill %zu tokens in %.3fs; %zu rows; %zu decode steps in %.3fs (%.1f tok/s); experts %llu hits, %llu copied in\n",
-            b2_describe(e), prompt.size(), 1 + steps.size(), steps.size(), dt, steps.size() / (dt > 1e-9 ? dt : 1e-9),
+            b2_describe(e), prompt.size(), prefill, 1 + steps.size(), steps.size(), dt, steps.size() / (dt > 1e-9 ? dt : 1e-9),
             (unsigned long long)hits, (unsigned long long)page_ins);
     b2_close(e);
     return 0;

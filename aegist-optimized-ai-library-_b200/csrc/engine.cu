@@ -7,6 +7,8 @@
 //     token ids, positions, router picks and the arg-max stay on the device (the reference crosses
 //     the host boundary 82 times per token, hybrid.rs:743-758, 875, 919, 1000);
 //   * the KV cache is paged (64-token pages through a page table) and stored as bf16 or fp32.
+#include <cuda.h>
+#include <cudaTypedefs.h>
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 #include <nccl.h>
@@ -148,6 +150,10 @@ struct b2_engine {
     float* attn_part = nullptr;
     __half* xh = nullptr;                    // [Tpad][2][4096] fp16 activations for the tensor-core path
     int xh_tpad = 0;
+    int8_t* uq_i = nullptr;                  // [passes][3][64][4096] int8 digit planes for the tcgen05 GEMM
+    uint16_t* uq_b = nullptr;                // [passes][3][64][4096] bf16 planes
+    float* uq_scale = nullptr;               // [passes * 64]
+    int uq_passes = 0;
     // grouped expert GEMM: picks sorted by expert, chunk table, fp16 expert activations, group sums
     int *g_list = nullptr, *g_chunk = nullptr;
     __half* acth = nullptr;
@@ -230,7 +236,7 @@ b2_engine::~b2_engine() {
     for (auto& l : layers) { cudaFree((void*)l.eptr); cudaFree(l.router_bias); }
     void* bufs[] = {conv, state, snap_conv[0], snap_conv[1], snap_state[0], snap_state[1], kpool, vpool, page_table, rope_cos,
                     rope_sin, d_tok, d_next, d_pos, d_err, d_counter, d_acounter, x, big, zbuf, kraw, vraw, beta, gdec, obuf, att,
-                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh, g_list, g_chunk, acth, xsum_tok, xsum_act, d_trace, (void*)top_ptr, actq, asc, asum};
+                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh, g_list, g_chunk, acth, xsum_tok, xsum_act, d_trace, (void*)top_ptr, actq, asc, asum, uq_i, uq_b, uq_scale};
     for (void* p : bufs) cudaFree(p);
     if (h_pin) cudaFreeHost(h_pin);
     if (ev0) cudaEventDestroy(ev0);
@@ -485,6 +491,10 @@ int b2_engine::finish() {
     if (B >= 8) {
         xh_tpad = ((int)Bg + MM_TOK - 1) / MM_TOK * MM_TOK;
         CU(dalloc((uint16_t**)&xh, (size_t)xh_tpad * 2 * 4096));
+        uq_passes = ((int)Bg + UM_TOK - 1) / UM_TOK;
+        CU(dalloc(&uq_i, (size_t)uq_passes * UM_PI * UM_TOK * 4096));
+        CU(dalloc(&uq_b, (size_t)uq_passes * UM_PB * UM_TOK * 4096));
+        CU(dalloc(&uq_scale, (size_t)uq_passes * UM_TOK));
         const size_t P = Bg * c.TOPK;
         cap_small = (int)std::min<size_t>(P, c.E / ep_world);
         cap_big = (int)(P / (GQ_SMALL + 1)) + 1;
@@ -570,8 +580,80 @@ static cudaError_t launch_mma_i8(const MmaArgs& m, int passes, int nsm, cudaStre
     return e;
 }
 
-// Tensor-core path for 8 or more sequences: scratch for the fp16 activations.
-struct BatchCtx { __half* xh; int Tpad; };
+// Tensor-core paths for 8 or more tokens: scratch for the fp16 activations of k_mma_i8, and for the activation planes of
+// the tcgen05 GEMM (k_umma: int8 digit planes qi, bf16 planes qb, per-token scales; `passes_max` groups of 64 tokens).
+struct BatchCtx { __half* xh; int Tpad; int8_t* qi; uint16_t* qb; float* xscale; int passes_max; };
+
+// cuTensorMapEncodeTiled through the runtime's driver entry point table (no link against libcuda)
+static PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) p = nullptr;
+        cudaGetLastError();
+        return (PFN_cuTensorMapEncodeTiled_v12000)p;
+    }();
+    return fn;
+}
+// a [rows][row_bytes] byte matrix as a 2-D tensor of bytes; box = 128 bytes x box_rows, 128-byte swizzle, zeros outside
+static bool byte_matrix_map(CUtensorMap* m, const void* p, uint64_t rows, uint64_t row_bytes, uint32_t box_rows) {
+    auto enc = tensor_map_encoder();
+    if (!enc || !p || ((uintptr_t)p & 15) || row_bytes % 128 != 0 || box_rows > 256) return false;
+    const cuuint64_t dims[2] = {row_bytes, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {UM_BK, box_rows};
+    const cuuint32_t es[2] = {1, 1};
+    return enc(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(p), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+static bool umma_kind(int k) {
+    return k == SEG_I8 || k == SEG_I8_CONV || k == SEG_I8_SILU || k == SEG_I8_ACC || k == SEG_I8_GATEUP || k == SEG_I8_ARGMAX ||
+           k == SEG_BF || k == SEG_BF_SIGMOID || k == SEG_BF_DECAY;
+}
+// All segments of a GEMV group for T tokens on the tcgen05 GEMM: planes, then one persistent launch. false = this group
+// does not fit it (the caller takes another path); *err carries a launch error.
+static long g_umma_launches = 0;      // how many GEMV groups went to k_umma (tests check that the tcgen05 path is the one that runs)
+static bool launch_umma(const GemvArgs& a, int T, int nsm, cudaStream_t st, const BatchCtx& bc, cudaError_t* err) {
+    *err = cudaSuccess;
+    const int passes = (T + UM_TOK - 1) / UM_TOK;
+    if (!bc.qi || passes > bc.passes_max || a.K % UM_BK != 0 || a.K > 4096 || a.nseg > 4 || !tensor_map_encoder()) return false;
+    UmmaArgs u{};
+    bool any_i8 = false, any_bf = false;
+    for (int i = 0; i < a.nseg; i++) {
+        const Seg& g = a.seg[i];
+        if (!umma_kind(g.kind)) return false;
+        const bool isbf = g.kind == SEG_BF || g.kind == SEG_BF_SIGMOID || g.kind == SEG_BF_DECAY;
+        const bool pair = g.kind == SEG_I8_GATEUP;
+        (isbf ? any_bf : any_i8) = true;
+        UmmaSeg& d = u.seg[i];
+        d.s = g.s; d.s2 = g.s2; d.bias = g.bias; d.out = g.out; d.rows = g.rows; d.out_stride = g.out_stride;
+        d.kind = g.kind == SEG_I8_ARGMAX ? (int)SEG_I8 : g.kind;
+        d.units = pair ? (g.rows + 63) / 64 : (g.rows + UM_M - 1) / UM_M;
+        u.total_units += d.units;
+        const uint64_t rb = isbf ? 2ull * a.K : (uint64_t)a.K;
+        if (!byte_matrix_map(&u.wmap[i], g.w, g.rows, rb, 64)) return false;
+        if (pair && !byte_matrix_map(&u.wmap2[i], g.w2, g.rows, rb, 64)) return false;
+    }
+    u.nseg = a.nseg;
+    // tokens per unit: a block pulls about 110 GB/s out of L2, so few row blocks are split over the tokens too
+    int tt = UM_TOK;
+    while (tt > 16 && u.total_units * passes * (UM_TOK / tt) * 2 <= nsm && T > tt / 2) tt /= 2;
+    u.tt = tt;
+    if (const char* v = getenv("B2_UMMA_DBG")) u.dbg = atoi(v);
+    if (!byte_matrix_map(&u.xmap_i8, bc.qi, (uint64_t)passes * UM_PI * UM_TOK, a.K, tt)) return false;
+    if (!byte_matrix_map(&u.xmap_bf, bc.qb, (uint64_t)passes * UM_PB * UM_TOK, 2ull * a.K, tt)) return false;
+    PrepQArgs p{};
+    p.x = a.x; p.x_stride = a.x_stride; p.norm_w = a.norm_w; p.gn_w = a.gn_w; p.z = a.z; p.DV = a.DV; p.eps = a.eps;
+    p.K = a.K; p.T = T; p.qi = any_i8 ? bc.qi : nullptr; p.qb = any_bf ? bc.qb : nullptr; p.xscale = bc.xscale;
+    if ((*err = launch_k(k_prep_q, dim3(passes * UM_TOK), dim3(256), 0, st, p)) != cudaSuccess) return true;
+    u.K = a.K; u.T = T; u.passes = passes; u.xscale = bc.xscale;
+    u.conv_w = a.conv_w; u.conv_state = a.conv_state; u.a_log = a.a_log; u.dt_bias = a.dt_bias; u.err = a.err;
+    if ((*err = opt_in_smem(k_umma, UM_SMEM)) != cudaSuccess) return true;
+    const int grid = std::max(1, std::min(u.total_units * passes * (UM_TOK / tt), nsm));
+    *err = launch_k(k_umma, dim3(grid), dim3(UM_THREADS), UM_SMEM, st, u);
+    g_umma_launches++;
+    return true;
+}
 static void seal(GemvArgs& a, int K);
 
 static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t st, int grid_override = 0,
@@ -579,6 +661,19 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
     GemvArgs a = a0;
     if (a.x_stride == 0) a.x_stride = a.K;
     cudaError_t e;
+    if (bc && B >= 8 && launch_umma(a, B, nsm, st, *bc, &e)) {
+        // every matrix of the group went to the tcgen05 GEMM; the head's arg-max and the router's top-8 are launches of their own
+        if (e != cudaSuccess) return e;
+        for (int i = 0; i < a.nseg; i++)
+            if (a.seg[i].kind == SEG_I8_ARGMAX && a.finisher == FIN_ARGMAX) {
+                e = launch_k(k_argmax_rows, dim3(B), dim3(1024), 0, st, (const float*)a.seg[i].out, a.seg[i].rows, a.seg[i].out_stride, a.next_tok, a.pos);
+                if (e != cudaSuccess) return e;
+            }
+        if (a.finisher == FIN_TOPK)
+            e = launch_k(k_router_topk, dim3((B + 7) / 8), dim3(256), 0, st, (const float*)a.seg[0].out, a.seg[0].out_stride, a.E, a.topk,
+                         a.top_idx, a.top_w, B);
+        return e;
+    }
     if (bc && bc->xh && B >= 8 && B <= bc->Tpad && a.K % MM_KC == 0) {
         // int8 matrices (except the head with its arg-max) go to the tensor cores; bf16 rows stay on k_rowgemv
         MmaArgs m{};
@@ -705,9 +800,8 @@ static void seal(GemvArgs& a, int K) {
 static void seal(GemvArgs& a, int K);
 static Seg make_seg(int kind, const void* w, const uint16_t* s, int rows, float* out, int out_stride);
 
-static void launch_proj(const ProjArgs& a, int B, int nsm, cudaStream_t st, const BatchCtx* bc = nullptr, const PrefetchList* pf = nullptr) {
+static void launch_proj(const ProjArgs& a, int B, int nsm, cudaStream_t st, const BatchCtx* bc = nullptr) {
     GemvArgs g{};
-    if (pf) g.pf = *pf;
     g.seg[0] = make_seg(SEG_I8_ACC, a.w, a.s, a.N, a.x, a.N);
     g.nseg = 1;
     seal(g, a.K);
@@ -843,11 +937,8 @@ static bool moe1_shape_ok(const Cfg& c) {
 struct Moe1Ctx { const uint8_t** top_ptr; int8_t* actq; float* asc; float* asum; };
 static cudaError_t launch_moe1(const Cfg& c, const float* rlogits, const float* x_in, const uint16_t* norm_w, const uint8_t* const* eptr,
                                int* top_idx, float* top_w, const Moe1Ctx& m, const float* sh_act, const float* sgate, const int8_t* shd_w,
-                               const uint16_t* shd_s, float* xout, int* err, int B, cudaStream_t st, b2_engine* prof,
-                               const PrefetchList* pf = nullptr) {
+                               const uint16_t* shd_s, float* xout, int* err, int B, cudaStream_t st, b2_engine* prof) {
     Gu1Args g{};
-    g.off_dn_q = c.off_dn_q(); g.dn_bytes = (unsigned int)(c.dn_q() + 2 * c.dn_sm());
-    if (pf) g.pf = *pf;
     g.logits = rlogits; g.x = x_in; g.norm_w = norm_w; g.eps = c.eps; g.eptr = eptr;
     g.off_gu_s = c.off_gu_s(); g.off_gu_m = c.off_gu_m(); g.D = c.D; g.I = c.I; g.E = c.E; g.topk = c.TOPK;
     g.top_idx = top_idx; g.top_w = top_w; g.top_ptr = m.top_ptr; g.actq = m.actq; g.asc = m.asc; g.asum = m.asum; g.err = err;
@@ -868,24 +959,11 @@ static cudaError_t launch_moe1(const Cfg& c, const float* rlogits, const float* 
     return ce;
 }
 
-static PrefetchList pf_of(std::initializer_list<std::pair<const void*, size_t>> regions) {
-    PrefetchList l{};
-    int i = 0;
-    for (auto& r : regions)
-        if (i < PF_MAX && r.first) { l.r[i].p = (const char*)r.first; l.r[i].bytes = (unsigned int)std::min<size_t>(r.second, 0xFFFFF000u); i++; }
-    return l;
-}
-// the int8 input projections of layer `l`, which the launch after the previous layer's experts streams
-static PrefetchList pf_in_proj(const LayerW& l, const Cfg& c) {
-    if (l.attn) return pf_of({{l.q.w, (size_t)l.q.n * c.D}, {l.k.w, (size_t)l.k.n * c.D}, {l.v.w, (size_t)l.v.n * c.D}});
-    return pf_of({{l.in_qkv.w, (size_t)l.in_qkv.n * c.D}, {l.in_z.w, (size_t)l.in_z.n * c.D}});
-}
-
 // One decode step for all B sequences: token ids in d_tok, positions in d_pos.
 int b2_engine::enqueue_step(cudaStream_t st, bool count) {
     int n = 0;
     const int launches0 = g_launch_count;
-    const BatchCtx bctx{xh, xh_tpad};
+    const BatchCtx bctx{xh, xh_tpad, uq_i, uq_b, uq_scale, uq_passes};
     const BatchCtx* bc = xh ? &bctx : nullptr;
     cudaGetLastError();   // a stale error of an earlier, unrelated call must not be blamed on these launches
     mark(-1, st);
@@ -893,18 +971,10 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
     mark(0, st);
     n++;
     const size_t kv_layer = (size_t)B * pages_per_seq * c.KV * KV_PAGE * c.HD * (kv_f32 ? 4 : 2);
-    // fewer than 8 sequences: the launches ask the weights of later launches of the step into L2 (see Prefetch). One layer's
-    // dense weights and experts are half of L2, so what is asked for is still there when its launch comes.
-    const bool pfon = B < 8 && ep_world == 1;
-    const PrefetchList none{};
     for (int li = 0; li < c.L; li++) {
         const LayerW& l = layers[li];
-        const PrefetchList pf_moe_in = pfon ? pf_of({{l.router, (size_t)c.E * c.D * 2}, {l.sh_gate.w, (size_t)c.SH * c.D}, {l.sh_up.w, (size_t)c.SH * c.D}}) : none;
-        const PrefetchList pf_shdown = pfon ? pf_of({{l.sh_down.w, (size_t)c.D * c.SH}}) : none;
-        const PrefetchList pf_next = pfon && li + 1 < c.L ? pf_in_proj(layers[li + 1], c) : none;
         if (l.attn) {
             GemvArgs a{};
-            if (pfon) a.pf = pf_of({{l.o.w, (size_t)c.D * c.H * c.HD}});
             a.seg[0] = make_seg(SEG_I8, l.q.w, l.q.s, l.q.n, big, 2 * c.H * c.HD);
             a.seg[1] = make_seg(SEG_I8, l.k.w, l.k.s, l.k.n, kraw, c.KV * c.HD);
             a.seg[2] = make_seg(SEG_I8, l.v.w, l.v.s, l.v.n, vraw, c.KV * c.HD);
@@ -918,16 +988,15 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             t.kpool = (char*)kpool + kv_layer * l.slot; t.vpool = (char*)vpool + kv_layer * l.slot;
             t.page_table = page_table; t.pages_per_seq = pages_per_seq;
             t.H = c.H; t.KV = c.KV; t.RD = c.RD; t.eps = c.eps; t.scale = 1.0f / std::sqrt((float)c.HD);
-            t.part = attn_part; t.out = att; t.nsplit = nsplit; t.pf = pf_moe_in;
+            t.part = attn_part; t.out = att; t.nsplit = nsplit;
             cudaError_t e = launch_attn(t, c.HD, kv_f32, B, st, attn_tiles);
             if (e != cudaSuccess) return fail("attention launch: %s", cudaGetErrorString(e));
             mark(3, st);
             ProjArgs p{};
             p.in = att; p.mode = 1; p.w = l.o.w; p.s = l.o.s; p.x = x; p.N = c.D; p.K = c.H * c.HD; p.eps = c.eps; p.DV = c.DV;
-            launch_proj(p, B, nsm, st, bc, &pf_shdown);
+            launch_proj(p, B, nsm, st, bc);
         } else {
             GemvArgs a{};
-            if (pfon) a.pf = pf_of({{l.out.w, (size_t)c.D * c.VD()}});
             a.seg[0] = make_seg(SEG_I8_CONV, l.in_qkv.w, l.in_qkv.s, l.in_qkv.n, big, c.C());
             a.seg[1] = make_seg(SEG_I8_SILU, l.in_z.w, l.in_z.s, l.in_z.n, zbuf, c.VD());
             a.seg[2] = make_seg(SEG_BF_SIGMOID, l.in_b, nullptr, c.HV, beta, c.HV);
@@ -940,13 +1009,13 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             mark(1, st);
             DeltaArgs d{};
             d.y = big; d.beta = beta; d.g = gdec; d.state = state + (size_t)l.slot * B * c.HV * c.DK * c.DV;
-            d.o = obuf; d.C = c.C(); d.HK = c.HK; d.HV = c.HV; d.DV = c.DV; d.prenormed = 0; d.pf = pf_moe_in;
+            d.o = obuf; d.C = c.C(); d.HK = c.HK; d.HV = c.HV; d.DV = c.DV; d.prenormed = 0;
             launch_delta(d, c.DK, B, st);
             mark(2, st);
             ProjArgs p{};
             p.in = obuf; p.z = zbuf; p.gn_w = l.gnorm; p.eps = c.eps; p.DV = c.DV; p.mode = 0;
             p.w = l.out.w; p.s = l.out.s; p.x = x; p.N = c.D; p.K = c.VD();
-            launch_proj(p, B, nsm, st, bc, &pf_shdown);
+            launch_proj(p, B, nsm, st, bc);
         }
         mark(4, st);
         n += l.attn ? 4 : 3;
@@ -958,7 +1027,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             a.seg[1].w2 = l.sh_up.w; a.seg[1].s2 = l.sh_up.s;
             a.seg[2] = make_seg(SEG_BF_SIGMOID, l.sh_gw, nullptr, 1, sgate, 1);
             a.nseg = 3; seal(a, c.D);
-            a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D; a.err = d_err; a.pf = pf_next;
+            a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D; a.err = d_err;
             // fewer than 8 tokens on one GPU: the top-8 moves into the expert kernel and the experts are spread over all SMs
             const bool moe1 = ep_world == 1 && B < 8 && moe1_shape_ok(c);
             a.finisher = moe1 ? FIN_NONE : FIN_TOPK; a.counter = d_counter; a.E = c.E; a.topk = c.TOPK;
@@ -1591,6 +1660,7 @@ int b2_set_router_bias(b2_engine* e, int layer, const float* bias) {
 }
 
 int b2_launches_per_step(const b2_engine* e) { return e ? e->launches : 0; }
+long b2_debug_umma_launches(void) { return g_umma_launches; }
 
 int b2_debug_seek(b2_engine* e, int n) {
     if (!e || !e->finished) return 1;

@@ -56,31 +56,6 @@ __device__ __forceinline__ float h2f(uint16_t h) { return __half2float(__ushort_
 __device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-// Weights that a LATER launch of the step will stream can be asked into L2 now (cp.async.bulk.prefetch.L2): HBM is idle
-// through most of a decode step's hand-overs and prologues, and a kernel whose tiles come from L2 starts computing
-// sooner. A launch carries up to three regions; every block asks for its own slice of each, in 4 KB pieces issued by
-// the lanes of one warp that is off the critical path. Nothing waits on a prefetch and nothing depends on it.
-struct Prefetch { const char* p; unsigned int bytes; };
-constexpr int PF_MAX = 3;
-struct PrefetchList { Prefetch r[PF_MAX]; };
-__device__ __forceinline__ void l2_prefetch(const void* p, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void l2_prefetch_share(const PrefetchList& pf, int blk, int nblk, int lane) {
-#pragma unroll
-    for (int i = 0; i < PF_MAX; i++) {
-        const unsigned int bytes = pf.r[i].bytes;
-        if (pf.r[i].p == nullptr || bytes == 0) continue;
-        unsigned int share = (bytes + nblk - 1) / nblk;
-        share = (share + 4095u) & ~4095u;
-        const unsigned int lo = (unsigned int)blk * share;
-        if (lo >= bytes) continue;
-        const unsigned int hi = min(bytes, lo + share);
-        for (unsigned int o = lo + lane * 4096u; o < hi; o += 32u * 4096u)
-            l2_prefetch(pf.r[i].p + o, (min(hi, o + 4096u) - o) & ~15u);
-    }
-}
-
 // Time stamps of a launch for the step timeline (debugging aid; trace is null in normal runs). Per launch
 // 16 words: [0] first block in and [4] last block out (ns of the global timer, which is slow to read, so it is
 // read only there), [5] kernel code, [6] a shape hint, [7] last block in, [8] block 0's SM cycle counter when it came in,
@@ -248,7 +223,6 @@ struct GemvArgs {
     int* next_tok;           // [B]
     int* pos;                // [B] advanced by one by the finisher (may be null)
     int* err;                // set to 3 if a bulk copy never landed (bounded wait gave up)
-    PrefetchList pf;         // weights of later launches to ask into L2 (k_tcgemv)
 };
 
 // Softmax over E router logits and the `topk` largest in descending order, ties to the lower
@@ -320,7 +294,7 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // Wait for a phase of an mbarrier of this block. The wait is bounded: if the phase has not completed
 // after a very long time (a copy that never lands), *err is set and the caller goes on with whatever
 // the buffer holds, so that the kernel always terminates.
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* err, int limit = 1 << 22) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* err, int limit = 1 << 22) {
     for (int spin = 0; spin < limit; spin++) {
         uint32_t ok;
         asm volatile(
@@ -328,9 +302,10 @@ __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* e
             : "=r"(ok)
             : "r"(smem_u32(bar)), "r"(parity)
             : "memory");
-        if (ok) return;
+        if (ok) return true;
     }
     if (err) atomicExch(err, 3);
+    return false;
 }
 // One contiguous copy global -> shared; src, dst 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
@@ -363,7 +338,6 @@ struct DeltaArgs {
     float* o;            // [B][HV*DV] raw readout (the gated norm is applied by the out projection's prologue)
     int C, HK, HV, DV;
     int prenormed;       // 1: q and k come in already normalised and scaled (the bare delta-rule op)
-    PrefetchList pf;     // weights of later launches to ask into L2
 };
 
 template <int DK>
@@ -379,7 +353,6 @@ __global__ void __launch_bounds__(THREADS) k_delta_step(const DeltaArgs a) {
     const int col = slab * 32 + lane;
     grid_dep_launch();
     trace_in(a.trace, 3, gridDim.x);
-    if (warp == WARPS - 1 && blockIdx.y == 0) l2_prefetch_share(a.pf, blockIdx.x, gridDim.x, lane);
     grid_dep_wait();        // the state itself is written by this kernel's previous launch
     trace_pt(a.trace, 1);
 
@@ -799,7 +772,6 @@ struct AttnArgs {
     float* part;              // [B][KV][nsplit][G][HD + 2]  scratch
     float* out;               // [B][H*HD]
     int nsplit;
-    PrefetchList pf;          // weights of later launches to ask into L2 (k_attn_mma)
 };
 
 constexpr int ATT_PPW = 4;    // positions a warp loads at once
@@ -1063,6 +1035,7 @@ __global__ void __launch_bounds__(THREADS) k_attn_merge(const AttnArgs a, int HD
 
 }  // namespace b2
 #include "attnmma.cuh"
+#include "ummagemm.cuh"
 namespace b2 {
 
 // ------------------------------------------------------------------------------------------

@@ -128,9 +128,6 @@ struct Gu1Args {
     float* asc;                   // [B * topk][I / 32] out: scale of each 32-value group of act
     float* asum;                  // [B * topk][I / 32] out: sum of each 32-value group of act
     int* err;
-    size_t off_dn_q;              // where a pick's down projection starts inside its blob, and its size: once the picks are
-    unsigned int dn_bytes;        // known, every block asks for a slice of its pick's down matrix into L2 for k_moe_down1
-    PrefetchList pf;              // weights of later launches to ask into L2
 };
 
 // dynamic shared memory: rows | scales | digit planes of x | group sums of x
@@ -167,7 +164,6 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
     // the expert table is written at load time only: read it while the previous kernel still runs
     if (threadIdx.x < a.E && threadIdx.x < 256) s_eptr[threadIdx.x] = a.eptr[threadIdx.x];
     if (threadIdx.x < 8) { s_top[threadIdx.x] = -1; s_topv[threadIdx.x] = 0.f; }
-    if (warp == M1_GU_WARPS - 1 && b == 0) l2_prefetch_share(a.pf, blockIdx.x, gridDim.x, lane);
     grid_dep_wait();
     trace_pt(a.trace, 1);
 
@@ -317,14 +313,6 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
         if (threadIdx.x == 0) atomicExch(a.err, 2);
         trace_out(a.trace);
         return;
-    }
-    // the pick's down projection is what k_moe_down1 reads next: the blocks of a pick ask for it, a slice each
-    if (warp == M1_GU_WARPS - 1 && a.dn_bytes) {
-        const int per_pick = a.I / M1_GU_PAIRS;                 // blocks that share this pick
-        PrefetchList dn{};
-        dn.r[0].p = reinterpret_cast<const char*>(base) + a.off_dn_q;
-        dn.r[0].bytes = a.dn_bytes;
-        l2_prefetch_share(dn, blockIdx.x % per_pick, per_pick, lane);
     }
     // slot of pair s: block s / 8, gate in row s % 8 of the block's 16 rows, up in row 8 + s % 8; a warp
     // fetches two whole rows, a lane 16-byte pieces of them

@@ -150,7 +150,6 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
     };
     if (warp == W)
         for (int i = 0; i < NST && t0 + i < t1; i++) request(t0 + i, i);
-    if (warp == W + 1 && blockIdx.y == 0) l2_prefetch_share(a.pf, blockIdx.x, gridDim.x, lane);
     grid_dep_wait();
     trace_pt(a.trace, 1);
 

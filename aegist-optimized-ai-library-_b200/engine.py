@@ -79,6 +79,7 @@ SYMBOLS = {
     "b2_set_router_bias": (_I, [_P, _I, _P]),
     "b2_debug_seek": (_I, [_P, _I]),
     "b2_launches_per_step": (_I, [_P]),
+    "b2_debug_umma_launches": (C.c_long, []),
     "b2_step_bytes": (C.c_double, [_P]),
     "b2_ep_bytes_per_step": (C.c_double, [_P]),
     "b2_profile_step": (_I, [_P, _I, C.POINTER(_F), C.POINTER(C.c_double), C.POINTER(_I)]),

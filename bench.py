@@ -130,6 +130,12 @@ def parity_check(E, cfg4, dev, host, tokens: int = 6):
 REF_DIR = os.path.join(ROOT, "oracle", "_ref")
 
 
+def timed(f) -> float:
+    t0 = time.perf_counter()
+    f()
+    return time.perf_counter() - t0
+
+
 def cpu_sample(cfg_full, cfg4, host, model, steps: int, warmup: int):
     """The reference path on the host cores over a bounded sample of the workload: single-token steps through one
     period of the layer pattern (3 DeltaNet + 1 attention layers at full width, 256 experts each) plus the head after
@@ -167,10 +173,8 @@ def cpu_sample(cfg_full, cfg4, host, model, steps: int, warmup: int):
                     tok = int(fwd([tok]).argmax())
                 t_fwd = (time.perf_counter() - t0) / steps
                 h = torch.zeros(1, cfg4.d_model)
-                t0 = time.perf_counter()
-                for _ in range(3):
-                    ref.lm_head(h)
-                t_head = (time.perf_counter() - t0) / 3
+                ref.lm_head(h)                                   # first call: allocations
+                t_head = min(timed(lambda: ref.lm_head(h)) for _ in range(3))
             del ref, cache
             nx.close()
         kind, what = "reference", f"the reference's HybridLM (torch fp32, {cores} threads)"
@@ -186,11 +190,10 @@ def cpu_sample(cfg_full, cfg4, host, model, steps: int, warmup: int):
             tok = int(np.argmax(model.forward(np.asarray([[tok]]), cache)[0]))
         t_fwd = (time.perf_counter() - t0) / steps
         h = np.zeros((1, cfg4.d_model), dtype=np.float32)
-        t0 = time.perf_counter()
-        for _ in range(3):
-            model.qlinear(h, "lm_head")
-        t_head = (time.perf_counter() - t0) / 3
+        model.qlinear(h, "lm_head")
+        t_head = min(timed(lambda: model.qlinear(h, "lm_head")) for _ in range(3))
         kind, what = "port", f"numpy port of aegist/hybrid.py (fp32, {cores} threads available to BLAS)"
+    t_head = min(t_head, 0.75 * t_fwd)                           # the head is part of every sampled token
     t_full = (t_fwd - t_head) * periods + t_head
     return {"value": 1.0 / t_full, "unit": "tok/s", "cores": cores, "kind": kind,
             "sample": (f"{what}: {steps} single-token steps through {SAMPLE_LAYERS} full-width layers "

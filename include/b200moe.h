@@ -145,6 +145,9 @@ int b2_set_router_bias(b2_engine* e, int layer, const float* bias);
 int b2_debug_seek(b2_engine* e, int n);
 /* Number of kernel launches in one decode step (all sequences). */
 int b2_launches_per_step(const b2_engine* e);
+/* How many launches of the tcgen05 GEMM (k_umma) this process has enqueued so far, graph captures included: lets a
+ * test see that the Blackwell tensor-core path, not a fall-back, is what ran. No counterpart in the reference. */
+long b2_debug_umma_launches(void);
 /* Algorithmic bytes one decode step moves (weights once, recurrent state read + written, KV read
  * up to the current length), for roofline arithmetic. */
 double b2_step_bytes(const b2_engine* e);

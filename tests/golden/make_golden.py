@@ -1,6 +1,6 @@
 """Generate the golden fixtures in this directory by running the UNMODIFIED reference.
 
-    python tests/golden/make_golden.py [/path/to/reference/aegist-fast-35b]
+    python tests/golden/make_golden.py /path/to/reference/aegist-fast-35b
 
 The reference's Python model (aegist/hybrid.py) is imported from its own tree; nothing of it is
 copied. Master weights come from this repo's seeded generator (`brain.normal`, keyed by tensor
@@ -26,7 +26,9 @@ import torch
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 ROOT = os.path.dirname(os.path.dirname(HERE))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference/aegist-fast-35b"
+if len(sys.argv) < 2:
+    raise SystemExit(__doc__)
+REF = sys.argv[1]
 sys.path.insert(0, ROOT)
 sys.path.insert(0, REF)
 sys.dont_write_bytecode = True
