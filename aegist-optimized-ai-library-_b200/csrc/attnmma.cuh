@@ -81,7 +81,7 @@ __global__ void __launch_bounds__(THREADS) k_attn_mma(const AttnArgs a, int nbuf
     // a tile is one cache page: 64 rows of HD bf16 for this KV head, contiguous; rows past the slice are not needed
     // but must hold finite numbers (their probabilities are zero), so the last valid row is loaded in their place
     auto load_tile = [&](int t0, int buf) {
-        const int page = a.page_table[(size_t)b * a.pages_per_seq + t0 / KV_PAGE];
+        const int page = a.page_table[(size_t)b * a.pt_stride + t0 / KV_PAGE];
         const size_t base = ((size_t)page * a.KV + kvh) * KV_PAGE * HD;
         constexpr int CPR = HD * 2 / 16;        // 16-byte pieces per row
         const int last = min(AM_TILE, p1 - t0) - 1;
@@ -154,9 +154,14 @@ __global__ void __launch_bounds__(THREADS) k_attn_mma(const AttnArgs a, int nbuf
     __syncthreads();
     // the block that owns the newest position appends it
     if (pos >= p0 && pos < p1) {
-        const int page = a.page_table[(size_t)b * a.pages_per_seq + pos / KV_PAGE];
+        const int page = a.page_table[(size_t)b * a.pt_stride + pos / KV_PAGE];
         const size_t off = (((size_t)page * a.KV + kvh) * KV_PAGE + pos % KV_PAGE) * HD;
         for (int i = threadIdx.x; i < HD; i += THREADS) { ((uint16_t*)a.kpool)[off + i] = f2bf(knew[i]); ((uint16_t*)a.vpool)[off + i] = f2bf(vnew[i]); }
+    }
+    if (a.append_only) {
+        cp_async_wait<0>();                     // the first tile's copies were already sent
+        trace_out(a.trace);
+        return;
     }
     trace_pt(a.trace, 2);
 

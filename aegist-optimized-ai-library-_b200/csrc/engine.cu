@@ -189,6 +189,26 @@ struct b2_engine {
     int ep_exchange_records(cudaStream_t st);
     int ep_exchange_outputs(cudaStream_t st);
 
+    // Prompt chunks (b2_feed of 16 or more tokens): the step's kernels with the chunk's tokens as the columns, on a work
+    // buffer set of its own that is allocated when the first such feed arrives.
+    struct ChunkBufs {
+        int W = 0;                                  // tokens per chunk
+        int *tok = nullptr, *vpos = nullptr;        // [W] token ids, positions pos0 + t
+        float *x = nullptr, *big = nullptr, *zbuf = nullptr, *kraw = nullptr, *vraw = nullptr, *beta = nullptr, *gdec = nullptr;
+        float *obuf = nullptr, *att = nullptr, *rlogits = nullptr, *sh_act = nullptr, *sgate = nullptr, *act = nullptr;
+        int* top_idx = nullptr; float* top_w = nullptr;
+        float *ypart = nullptr, *attn_part = nullptr;
+        unsigned int *dcounter = nullptr, *counter = nullptr;
+        __half *xh = nullptr, *acth = nullptr;
+        int xh_tpad = 0;
+        int8_t* uq_i = nullptr; uint16_t* uq_b = nullptr; float* uq_scale = nullptr; int uq_passes = 0;
+        int *g_list = nullptr, *g_chunk = nullptr;
+        float *xsum_tok = nullptr, *xsum_act = nullptr;
+        int cap_small = 0, cap_big = 0, nsplit = 1, attn_tiles = 1;
+    } pc;
+    int ensure_chunk_bufs();
+    int feed_chunk(const uint32_t* ids, int T, bool want_head);
+
     // per-kernel timing (b2_profile_step): one event after every launch of an un-graphed step
     bool profiling = false;
     std::vector<cudaEvent_t> prof_ev;
@@ -219,7 +239,7 @@ struct b2_engine {
     int need(const std::string& name, const std::string& dtype, std::vector<int64_t> shape, const void** out);
     int qw(const std::string& prefix, int n, int k, QWd* out);
     int build_graph();
-    int enqueue_step(cudaStream_t st, bool count);
+    int enqueue_step(cudaStream_t st, bool count, int chunk_T = 0, bool chunk_head = false);
     int run_steps(int n);
     int check_device_error();
     int reset_state();
@@ -238,6 +258,10 @@ b2_engine::~b2_engine() {
                     rope_sin, d_tok, d_next, d_pos, d_err, d_counter, d_acounter, x, big, zbuf, kraw, vraw, beta, gdec, obuf, att,
                     rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh, g_list, g_chunk, acth, xsum_tok, xsum_act, d_trace, (void*)top_ptr, actq, asc, asum, uq_i, uq_b, uq_scale};
     for (void* p : bufs) cudaFree(p);
+    void* cb[] = {pc.tok, pc.vpos, pc.x, pc.big, pc.zbuf, pc.kraw, pc.vraw, pc.beta, pc.gdec, pc.obuf, pc.att, pc.rlogits, pc.sh_act, pc.sgate,
+                  pc.act, pc.top_idx, pc.top_w, pc.ypart, pc.attn_part, pc.dcounter, pc.counter, pc.xh, pc.acth, pc.uq_i, pc.uq_b, pc.uq_scale,
+                  pc.g_list, pc.g_chunk, pc.xsum_tok, pc.xsum_act};
+    for (void* p : cb) cudaFree(p);
     if (h_pin) cudaFreeHost(h_pin);
     if (ev0) cudaEventDestroy(ev0);
     if (ev1) cudaEventDestroy(ev1);
@@ -639,7 +663,6 @@ static bool launch_umma(const GemvArgs& a, int T, int nsm, cudaStream_t st, cons
     int tt = UM_TOK;
     while (tt > 16 && u.total_units * passes * (UM_TOK / tt) * 2 <= nsm && T > tt / 2) tt /= 2;
     u.tt = tt;
-    if (const char* v = getenv("B2_UMMA_DBG")) u.dbg = atoi(v);
     if (!byte_matrix_map(&u.xmap_i8, bc.qi, (uint64_t)passes * UM_PI * UM_TOK, a.K, tt)) return false;
     if (!byte_matrix_map(&u.xmap_bf, bc.qb, (uint64_t)passes * UM_PB * UM_TOK, 2ull * a.K, tt)) return false;
     PrepQArgs p{};
@@ -960,17 +983,53 @@ static cudaError_t launch_moe1(const Cfg& c, const float* rlogits, const float* 
 }
 
 // One decode step for all B sequences: token ids in d_tok, positions in d_pos.
-int b2_engine::enqueue_step(cudaStream_t st, bool count) {
+// chunk_T > 0: a prompt chunk of chunk_T tokens of the engine's one sequence instead (the tokens are the columns of
+// every matrix product; conv, delta rule and attention walk them in order; the head runs for the last token only,
+// and only when chunk_head is set).
+int b2_engine::enqueue_step(cudaStream_t st, bool count, int chunk_T, bool chunk_head) {
     int n = 0;
     const int launches0 = g_launch_count;
-    const BatchCtx bctx{xh, xh_tpad, uq_i, uq_b, uq_scale, uq_passes};
+    const bool chunk = chunk_T > 0;
+    const int NSEQ = this->B;                     // sequences: what the recurrent state, the conv taps and the KV pages are laid out by
+    const int B = chunk ? chunk_T : this->B;      // columns of this step's matrix products
+    // the work buffers of this step: the members, or the chunk's own set under the same names
+    int* const d_tok = chunk ? pc.tok : this->d_tok;
+    int* const d_pos = chunk ? pc.vpos : this->d_pos;
+    float* const x = chunk ? pc.x : this->x;
+    float* const big = chunk ? pc.big : this->big;
+    float* const zbuf = chunk ? pc.zbuf : this->zbuf;
+    float* const kraw = chunk ? pc.kraw : this->kraw;
+    float* const vraw = chunk ? pc.vraw : this->vraw;
+    float* const beta = chunk ? pc.beta : this->beta;
+    float* const gdec = chunk ? pc.gdec : this->gdec;
+    float* const obuf = chunk ? pc.obuf : this->obuf;
+    float* const att = chunk ? pc.att : this->att;
+    float* const rlogits = chunk ? pc.rlogits : this->rlogits;
+    float* const sh_act = chunk ? pc.sh_act : this->sh_act;
+    float* const sgate = chunk ? pc.sgate : this->sgate;
+    float* const act = chunk ? pc.act : this->act;
+    float* const ypart = chunk ? pc.ypart : this->ypart;
+    float* const attn_part = chunk ? pc.attn_part : this->attn_part;
+    unsigned int* const d_dcounter = chunk ? pc.dcounter : this->d_dcounter;
+    unsigned int* const d_counter = chunk ? pc.counter : this->d_counter;
+    __half* const xh = chunk ? pc.xh : this->xh;
+    __half* const acth = chunk ? pc.acth : this->acth;
+    int* const g_list = chunk ? pc.g_list : this->g_list;
+    int* const g_chunk = chunk ? pc.g_chunk : this->g_chunk;
+    float* const xsum_tok = chunk ? pc.xsum_tok : this->xsum_tok;
+    float* const xsum_act = chunk ? pc.xsum_act : this->xsum_act;
+    const int cap_small = chunk ? pc.cap_small : this->cap_small, cap_big = chunk ? pc.cap_big : this->cap_big;
+    const int nsplit = chunk ? pc.nsplit : this->nsplit, attn_tiles = chunk ? pc.attn_tiles : this->attn_tiles;
+    const BatchCtx bctx = chunk ? BatchCtx{pc.xh, pc.xh_tpad, pc.uq_i, pc.uq_b, pc.uq_scale, pc.uq_passes}
+                                : BatchCtx{this->xh, xh_tpad, uq_i, uq_b, uq_scale, uq_passes};
     const BatchCtx* bc = xh ? &bctx : nullptr;
     cudaGetLastError();   // a stale error of an earlier, unrelated call must not be blamed on these launches
     mark(-1, st);
     launch_k(k_embed, dim3(B), dim3(256), 0, st, embed, (const int*)d_tok, x, c.D, c.V, d_err);
+    if (chunk) launch_k(k_iota_from, dim3((B + 255) / 256), dim3(256), 0, st, d_pos, (const int*)this->d_pos, B);
     mark(0, st);
     n++;
-    const size_t kv_layer = (size_t)B * pages_per_seq * c.KV * KV_PAGE * c.HD * (kv_f32 ? 4 : 2);
+    const size_t kv_layer = (size_t)NSEQ * pages_per_seq * c.KV * KV_PAGE * c.HD * (kv_f32 ? 4 : 2);
     for (int li = 0; li < c.L; li++) {
         const LayerW& l = layers[li];
         if (l.attn) {
@@ -986,10 +1045,18 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             t.qraw = big; t.kraw = kraw; t.vraw = vraw; t.qn_w = l.q_norm; t.kn_w = l.k_norm;
             t.rope_cos = rope_cos; t.rope_sin = rope_sin; t.pos = d_pos;
             t.kpool = (char*)kpool + kv_layer * l.slot; t.vpool = (char*)vpool + kv_layer * l.slot;
-            t.page_table = page_table; t.pages_per_seq = pages_per_seq;
+            t.page_table = page_table; t.pages_per_seq = pages_per_seq; t.pt_stride = chunk ? 0 : pages_per_seq;
             t.H = c.H; t.KV = c.KV; t.RD = c.RD; t.eps = c.eps; t.scale = 1.0f / std::sqrt((float)c.HD);
             t.part = attn_part; t.out = att; t.nsplit = nsplit;
-            cudaError_t e = launch_attn(t, c.HD, kv_f32, B, st, attn_tiles);
+            cudaError_t e = cudaSuccess;
+            if (chunk) {
+                // every token's key and value row goes into the cache first: a token's blocks then find the rows of the
+                // chunk's earlier tokens there (they write their own row again, with the same bytes)
+                AttnArgs ap = t;
+                ap.append_only = 1;
+                e = launch_attn(ap, c.HD, kv_f32, B, st, attn_tiles);
+            }
+            if (e == cudaSuccess) e = launch_attn(t, c.HD, kv_f32, B, st, attn_tiles);
             if (e != cudaSuccess) return fail("attention launch: %s", cudaGetErrorString(e));
             mark(3, st);
             ProjArgs p{};
@@ -997,20 +1064,30 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             launch_proj(p, B, nsm, st, bc);
         } else {
             GemvArgs a{};
-            a.seg[0] = make_seg(SEG_I8_CONV, l.in_qkv.w, l.in_qkv.s, l.in_qkv.n, big, c.C());
+            a.seg[0] = make_seg(chunk ? SEG_I8 : SEG_I8_CONV, l.in_qkv.w, l.in_qkv.s, l.in_qkv.n, big, c.C());
             a.seg[1] = make_seg(SEG_I8_SILU, l.in_z.w, l.in_z.s, l.in_z.n, zbuf, c.VD());
             a.seg[2] = make_seg(SEG_BF_SIGMOID, l.in_b, nullptr, c.HV, beta, c.HV);
             a.seg[3] = make_seg(SEG_BF_DECAY, l.in_a, nullptr, c.HV, gdec, c.HV);
             a.nseg = 4; seal(a, c.D);
             a.x = x; a.norm_w = l.norm1; a.eps = c.eps; a.K = c.D; a.err = d_err;
-            a.conv_w = l.conv; a.conv_state = conv + (size_t)l.slot * B * c.C() * 3;
+            a.conv_w = l.conv; a.conv_state = conv + (size_t)l.slot * NSEQ * c.C() * 3;
             a.a_log = l.a_log; a.dt_bias = l.dt_bias;
             launch_gemv(a, B, nsm, st, 0, bc);
             mark(1, st);
+            float* const lstate = state + (size_t)l.slot * NSEQ * c.HV * c.DK * c.DV;
+            if (chunk) {
+                ConvScanArgs cs{big, l.conv, a.conv_state, c.C(), B};
+                launch_k(k_conv_scan, dim3((c.C() + 255) / 256), dim3(256), 0, st, cs);
+                DeltaScanArgs ds{big, beta, gdec, lstate, obuf, c.C(), c.HK, c.HV, c.DV, B};
+                const dim3 g(c.HV * (c.DV / 32));
+                if (c.DK == 64) launch_k(k_delta_scan<64>, g, dim3(THREADS), 0, st, ds);
+                else launch_k(k_delta_scan<128>, g, dim3(THREADS), 0, st, ds);
+            } else {
             DeltaArgs d{};
-            d.y = big; d.beta = beta; d.g = gdec; d.state = state + (size_t)l.slot * B * c.HV * c.DK * c.DV;
+            d.y = big; d.beta = beta; d.g = gdec; d.state = lstate;
             d.o = obuf; d.C = c.C(); d.HK = c.HK; d.HV = c.HV; d.DV = c.DV; d.prenormed = 0;
             launch_delta(d, c.DK, B, st);
+            }
             mark(2, st);
             ProjArgs p{};
             p.in = obuf; p.z = zbuf; p.gn_w = l.gnorm; p.eps = c.eps; p.DV = c.DV; p.mode = 0;
@@ -1031,8 +1108,14 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             // fewer than 8 tokens on one GPU: the top-8 moves into the expert kernel and the experts are spread over all SMs
             const bool moe1 = ep_world == 1 && B < 8 && moe1_shape_ok(c);
             a.finisher = moe1 ? FIN_NONE : FIN_TOPK; a.counter = d_counter; a.E = c.E; a.topk = c.TOPK;
-            a.top_idx = top_idx + (size_t)li * B * c.TOPK; a.top_w = top_w + (size_t)li * B * c.TOPK;
+            // a chunk's picks live in its own scratch; the last token's are kept where a decode step's are (b2_debug_router)
+            a.top_idx = chunk ? pc.top_idx : top_idx + (size_t)li * B * c.TOPK;
+            a.top_w = chunk ? pc.top_w : top_w + (size_t)li * B * c.TOPK;
             launch_gemv(a, B, nsm, st, 0, bc);
+            if (chunk) {
+                cudaMemcpyAsync(top_idx + (size_t)li * NSEQ * c.TOPK, pc.top_idx + (size_t)(B - 1) * c.TOPK, c.TOPK * sizeof(int), cudaMemcpyDeviceToDevice, st);
+                cudaMemcpyAsync(top_w + (size_t)li * NSEQ * c.TOPK, pc.top_w + (size_t)(B - 1) * c.TOPK, c.TOPK * sizeof(float), cudaMemcpyDeviceToDevice, st);
+            }
             mark(1, st);
             if (moe1) {
                 const Moe1Ctx mc{top_ptr, actq, asc, asum};
@@ -1087,24 +1170,82 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count) {
             }
         }
         for (size_t j = 0; j < tap_layers.size(); j++)
-            if (tap_layers[j] == li)
-                cudaMemcpyAsync(tap_buf + j * (size_t)B * c.D, x, (size_t)B * c.D * 4, cudaMemcpyDeviceToDevice, st);
+            if (tap_layers[j] == li) {
+                // the hidden state after this layer, of every sequence's token; of a chunk's last token
+                if (chunk) cudaMemcpyAsync(tap_buf + j * (size_t)NSEQ * c.D, x + (size_t)(B - 1) * c.D, (size_t)c.D * 4, cudaMemcpyDeviceToDevice, st);
+                else cudaMemcpyAsync(tap_buf + j * (size_t)B * c.D, x, (size_t)B * c.D * 4, cudaMemcpyDeviceToDevice, st);
+            }
     }
-    {
+    if (!chunk || chunk_head) {
         GemvArgs a{};
         a.seg[0] = make_seg(SEG_I8_ARGMAX, lm_head.w, lm_head.s, c.V, logits, c.V);
         a.nseg = 1; seal(a, c.D);
-        a.x = x; a.norm_w = norm; a.eps = c.eps; a.K = c.D; a.err = d_err;
-        a.finisher = FIN_ARGMAX; a.counter = d_counter; a.part_val = part_val; a.part_idx = part_idx;
-        a.next_tok = d_next; a.pos = d_pos;
-        launch_gemv(a, B, nsm, st, head_grid, bc);
+        a.x = chunk ? x + (size_t)(B - 1) * c.D : x; a.norm_w = norm; a.eps = c.eps; a.K = c.D; a.err = d_err;
+        a.finisher = FIN_ARGMAX; a.counter = this->d_counter; a.part_val = part_val; a.part_idx = part_idx;
+        a.next_tok = d_next; a.pos = chunk ? nullptr : d_pos;
+        // a chunk's head runs for its last token alone (the decode GEMV), and leaves the residual row where a decode step does
+        launch_gemv(a, chunk ? 1 : B, nsm, st, head_grid, chunk ? nullptr : bc);
         mark(7, st);
         n++;
+    }
+    if (chunk) {
+        cudaMemcpyAsync(this->x, x + (size_t)(B - 1) * c.D, (size_t)c.D * 4, cudaMemcpyDeviceToDevice, st);
+        k_add_i32<<<1, 32, 0, st>>>(this->d_pos, B, NSEQ);                  // the sequence is B positions further
     }
     (void)n;
     if (count) launches = g_launch_count - launches0;
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail("kernel launch: %s", cudaGetErrorString(e));
+    return 0;
+}
+
+// ---- prompt chunks ------------------------------------------------------------------------------------------------
+constexpr int CHUNK_TOKENS = 128;        // tokens per chunk: what the pick grouping handles at once (GQ_MAXP picks)
+constexpr int CHUNK_MIN = 16;            // shorter feeds (and the rest of a longer one) go token by token
+
+int b2_engine::ensure_chunk_bufs() {
+    if (pc.W) return 0;
+    const int W = CHUNK_TOKENS;
+    const int bigw = std::max(2 * c.H * c.HD, c.C());
+    const size_t P = (size_t)W * c.TOPK;
+    CU(dalloc(&pc.tok, W)); CU(dalloc(&pc.vpos, W));
+    CU(dalloc(&pc.x, (size_t)W * c.D)); CU(dalloc(&pc.big, (size_t)W * bigw)); CU(dalloc(&pc.zbuf, (size_t)W * c.VD()));
+    CU(dalloc(&pc.kraw, (size_t)W * c.KV * c.HD)); CU(dalloc(&pc.vraw, (size_t)W * c.KV * c.HD));
+    CU(dalloc(&pc.beta, (size_t)W * c.HV)); CU(dalloc(&pc.gdec, (size_t)W * c.HV));
+    CU(dalloc(&pc.obuf, (size_t)W * c.VD())); CU(dalloc(&pc.att, (size_t)W * c.H * c.HD));
+    CU(dalloc(&pc.rlogits, (size_t)W * c.E)); CU(dalloc(&pc.sh_act, (size_t)W * c.SH)); CU(dalloc(&pc.sgate, W));
+    CU(dalloc(&pc.act, P * c.I)); CU(dalloc(&pc.top_idx, P)); CU(dalloc(&pc.top_w, P));
+    CU(dalloc(&pc.ypart, (size_t)W * (c.TOPK + 1) * c.D));
+    CU(dalloc(&pc.dcounter, (size_t)W * down_row_blocks(c.D))); CU(dalloc(&pc.counter, W));
+    // one block set per token already fills the GPU: few, long slices
+    pc.nsplit = std::max(1, std::min({64, (2 * nsm) / std::max(1, c.KV * W), (cap + 63) / 64}));
+    pc.attn_tiles = ((cap + pc.nsplit - 1) / pc.nsplit + AM_TILE - 1) / AM_TILE;
+    CU(dalloc(&pc.attn_part, (size_t)W * c.KV * pc.nsplit * (c.H / c.KV) * (c.HD + 2)));
+    pc.xh_tpad = (W + MM_TOK - 1) / MM_TOK * MM_TOK;
+    CU(dalloc((uint16_t**)&pc.xh, (size_t)pc.xh_tpad * 2 * 4096));
+    pc.uq_passes = (W + UM_TOK - 1) / UM_TOK;
+    CU(dalloc(&pc.uq_i, (size_t)pc.uq_passes * UM_PI * UM_TOK * 4096));
+    CU(dalloc(&pc.uq_b, (size_t)pc.uq_passes * UM_PB * UM_TOK * 4096));
+    CU(dalloc(&pc.uq_scale, (size_t)pc.uq_passes * UM_TOK));
+    pc.cap_small = (int)std::min<size_t>(P, c.E);
+    pc.cap_big = (int)(P / (GQ_SMALL + 1)) + 1;
+    CU(dalloc(&pc.g_list, P));
+    CU(dalloc(&pc.g_chunk, (size_t)3 * (pc.cap_small + pc.cap_big) + 2));
+    CU(dalloc((uint16_t**)&pc.acth, P * 2 * c.I));
+    CU(dalloc(&pc.xsum_tok, (size_t)W * (c.D / 64)));
+    CU(dalloc(&pc.xsum_act, P * std::max(1, c.I / 64)));
+    pc.W = W;
+    return 0;
+}
+
+// T (16 .. CHUNK_TOKENS) tokens of the sequence in one pass over the layers (forward_chunk, aegist_rs/src/hybrid.rs:1023-1025)
+int b2_engine::feed_chunk(const uint32_t* ids, int T, bool want_head) {
+    if (ensure_chunk_bufs()) return 1;
+    CU(cudaMemcpyAsync(pc.tok, ids, (size_t)T * 4, cudaMemcpyHostToDevice, stream));
+    if (enqueue_step(stream, false, T, want_head)) return 1;
+    length += T;
+    hits += (uint64_t)T * c.TOPK * c.L;
+    for (int i = 0; i < T; i++) toks.push_back(ids[i]);
     return 0;
 }
 
@@ -1372,7 +1513,14 @@ int b2_feed(b2_engine* e, const uint32_t* ids, int n, float* logits_out) {
     if (feed_checks(e, n)) return 1;
     for (int i = 0; i < n; i++)
         if (ids[i] >= (uint32_t)e->c.V) return e->fail("token id %u is outside the vocabulary (%d)", ids[i], e->c.V);
-    for (int i = 0; i < n; i++) {
+    int i0 = 0;
+    // whole chunks of the prompt go through the layers together; what is left (fewer than 16 tokens) token by token
+    while (n - i0 >= CHUNK_MIN && e->ep_world == 1) {
+        const int T = std::min(CHUNK_TOKENS, n - i0);
+        if (e->feed_chunk(ids + i0, T, i0 + T == n)) return 1;
+        i0 += T;                     // (the caller's ids are read by stream-ordered copies; the stream is drained before we return)
+    }
+    for (int i = i0; i < n; i++) {
         // the id travels as a kernel-independent 4-byte copy ordered on the stream
         CUE(cudaMemcpyAsync(e->d_tok, ids + i, 4, cudaMemcpyHostToDevice, e->stream));
         if (e->run_steps(1)) return 1;

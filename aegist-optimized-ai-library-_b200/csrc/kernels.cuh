@@ -767,6 +767,9 @@ struct AttnArgs {
     void* vpool;
     const int* page_table;    // [B][pages per sequence]
     int pages_per_seq;
+    int pt_stride;            // page-table row stride per block set: pages_per_seq, or 0 when the block sets are the tokens
+                              // of ONE sequence's prompt chunk (position pos[b] each, all on the same pages)
+    int append_only;          // 1: write the new key and value rows into the cache and leave
     int H, KV, RD;
     float eps, scale;
     float* part;              // [B][KV][nsplit][G][HD + 2]  scratch
@@ -842,13 +845,14 @@ __global__ void __launch_bounds__(THREADS) k_attn(const AttnArgs a) {
     __syncthreads();
     // the block that owns the newest position appends it
     if (pos >= p0 && pos < p1) {
-        const int page = a.page_table[(size_t)b * a.pages_per_seq + pos / KV_PAGE];
+        const int page = a.page_table[(size_t)b * a.pt_stride + pos / KV_PAGE];
         const size_t off = (((size_t)page * a.KV + kvh) * KV_PAGE + pos % KV_PAGE) * HD;
         for (int i = threadIdx.x; i < HD; i += THREADS) {
             if (KVF32) { ((float*)a.kpool)[off + i] = knew[i]; ((float*)a.vpool)[off + i] = vnew[i]; }
             else { ((uint16_t*)a.kpool)[off + i] = f2bf(knew[i]); ((uint16_t*)a.vpool)[off + i] = f2bf(vnew[i]); }
         }
     }
+    if (a.append_only) return;
 
     // scores are kept in the base-2 domain: q carries 1/sqrt(HD) * log2(e), so p = 2^(s - m)
     float q[MAXG][DPL];
@@ -876,7 +880,7 @@ __global__ void __launch_bounds__(THREADS) k_attn(const AttnArgs a) {
         for (int u = 0; u < ATT_PPW; u++) {
             const int p = pb + u;
             if (p < w1 && p != pos) {
-                const int page = a.page_table[(size_t)b * a.pages_per_seq + p / KV_PAGE];
+                const int page = a.page_table[(size_t)b * a.pt_stride + p / KV_PAGE];
                 const size_t off = (((size_t)page * a.KV + kvh) * KV_PAGE + p % KV_PAGE) * HD + lane * DPL;
                 load_kv<DPL, KVF32>(a.kpool, off, kk[u]);
                 load_kv<DPL, KVF32>(a.vpool, off, vv[u]);
@@ -1036,6 +1040,7 @@ __global__ void __launch_bounds__(THREADS) k_attn_merge(const AttnArgs a, int HD
 }  // namespace b2
 #include "attnmma.cuh"
 #include "ummagemm.cuh"
+#include "prefill.cuh"
 namespace b2 {
 
 // ------------------------------------------------------------------------------------------

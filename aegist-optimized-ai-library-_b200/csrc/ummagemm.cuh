@@ -23,8 +23,8 @@
 // The K loop walks 128-byte chunks of a row (128 int8 or 64 bf16 weights). A unit of work is (128 weight rows, tt
 // tokens), tt = 64, 32 or 16: a block pulls at most about 110 GB/s out of L2, so a matrix of few rows is split over
 // the tokens as well until the units fill the SMs. A block walks units blockIdx.x, + gridDim.x, ... Every wait is a bounded mbarrier wait (mbar_wait): on a
-// time-out the error word is set, every later wait of the block is skipped, the producer stops issuing copies and waits
-// (bounded) for those in flight, and the kernel runs to its end, frees its tensor memory and returns.
+// time-out the error word is set and the thread skips its later waits; the producer stops issuing copies and waits
+// (bounded) for those in flight; the kernel runs to its end, frees its tensor memory and returns.
 #pragma once
 #include <cuda.h>
 
@@ -38,11 +38,14 @@ constexpr int UM_PI = 3;                   // int8 digit planes: x = s (d0 + d1/
 constexpr int UM_PB = 3;                   // bf16 planes
 constexpr int UM_A_BYTES = UM_M * UM_BK;                     // 16 KB
 constexpr int UM_RING_BYTES = 200 * 1024;
-__host__ __device__ constexpr int um_stage_bytes(int tt) { return UM_A_BYTES + tt * UM_PI * UM_BK; }      // 40, 28 or 22 KB
+// A stage holds KC K chunks (each a 128-row x 128-byte weight box + the tokens' planes): the hand-over of a stage between
+// the producer and the MMA lane (two mbarrier operations on either side) costs about 400 cycles whatever it carries, more
+// than four products over few tokens take, so units of 32 or 16 tokens move two chunks per stage.
+__host__ __device__ constexpr int um_kc(int tt) { return tt >= 64 ? 1 : 2; }
+__host__ __device__ constexpr int um_chunk_bytes(int tt) { return UM_A_BYTES + tt * UM_PI * UM_BK; }      // 40, 28 or 22 KB
+__host__ __device__ constexpr int um_stage_bytes(int tt) { return um_kc(tt) * um_chunk_bytes(tt); }       // 40, 56 or 44 KB
 __host__ __device__ constexpr int um_stages(int tt) { return UM_RING_BYTES / um_stage_bytes(tt) < UM_MAX_STAGES ? UM_RING_BYTES / um_stage_bytes(tt) : UM_MAX_STAGES; }
 static_assert(UM_PI == UM_PB, "int8 and bf16 rows share the stage layout");
-// independent accumulators per unit (1, 2 or 4): as many as fit the 256 columns of one of the two accumulator buffers
-__host__ __device__ constexpr int um_chains(int tt) { return tt >= 64 ? 1 : (tt >= 32 ? 2 : 4); }
 constexpr int UM_THREADS = 320;            // producer, MMA, 8 epilogue warps (two per quarter of the TMEM lanes)
 constexpr int UM_TMEM_COLS = 512;          // two accumulators of up to 256 columns
 constexpr size_t UM_SMEM = (size_t)UM_RING_BYTES + 1024;                // + room to align the ring to 1024 bytes
@@ -66,7 +69,6 @@ struct UmmaArgs {
     int nseg, total_units;   // total_units = sum of seg units
     int K, T, passes;        // passes = ceil(T / 64)
     int tt;                  // tokens per unit of work: 64, 32 or 16 (the planes' tensor maps have boxes of `tt` rows)
-    int dbg;                 // timing experiments (B2_UMMA_DBG): 1 = no copies are issued, 2 = no products are issued
     const float* xscale;     // [passes * 64] scale of each token's int8 planes
     const uint16_t* conv_w;  // SEG_I8_CONV (decode: one token per sequence, state per sequence)
     float* conv_state;       // [T][C][3]
@@ -130,14 +132,12 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_umma(const __grid_constant__ 
     extern __shared__ unsigned char um_raw[];
     __shared__ __align__(8) uint64_t full_bar[UM_MAX_STAGES], empty_bar[UM_MAX_STAGES], acc_full[2], acc_empty[2];
     __shared__ uint32_t tmem_slot;
-    __shared__ volatile int s_abort;                 // set by the first wait that gives up
     __shared__ float gate_x[2][64][17];              // gate/up pairs: the gate rows' values of 16 tokens, per half of the tokens
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     unsigned char* ring = um_raw + ((1024u - (smem_u32(um_raw) & 1023u)) & 1023u);
     grid_dep_launch();
     trace_in(a.trace, 14, gridDim.x);
     if (threadIdx.x == 0) {
-        s_abort = 0;
         for (int s = 0; s < UM_MAX_STAGES; s++) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], 1); }
         for (int b = 0; b < 2; b++) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -147,7 +147,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_umma(const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
-    const int NST = um_stages(a.tt), STAGE = um_stage_bytes(a.tt);
+    const int NST = um_stages(a.tt), STAGE = um_stage_bytes(a.tt), KC = um_kc(a.tt), CHUNK = um_chunk_bytes(a.tt);
     const int nsub = UM_TOK / a.tt;                  // token groups of a pass
     const int nwork = a.total_units * a.passes * nsub;       // (row block, pass of 64 tokens, token group), token groups innermost
     // work item w -> unit, pass, first token; false when the group holds no token at all (every role skips it alike)
@@ -166,9 +166,11 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_umma(const __grid_constant__ 
         if (a.trace && blockIdx.x == 0) a.trace[8 + i] = (unsigned long long)clock64();
     };
     if (threadIdx.x == 0) stamp(1);
-    auto wait = [&](uint64_t* bar, uint32_t parity) {
-        if (s_abort) return;
-        if (!mbar_wait(bar, parity, a.err, 1 << 21)) s_abort = 1;
+    // A bounded wait. `dead` is the caller's own flag: after one of its waits has given up, a thread skips the rest
+    // and runs to the end of its loops; the other roles' waits then give up the same way.
+    auto wait = [&](uint64_t* bar, uint32_t parity, bool& dead) {
+        if (dead) return;
+        if (!mbar_wait(bar, parity, a.err, 1 << 21)) dead = true;
     };
     auto locate = [&](int unit, int& s, int& blk) {
         s = 0; blk = unit;
@@ -176,11 +178,13 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_umma(const __grid_constant__ 
     };
 
     if (warp == 0) {
-        // ---- producer: lane 0 waits for the stage and announces the bytes, then lanes 0..4 issue one tensor copy each
-        // (a thread needs about 180 cycles to issue one, which would otherwise bound a block at five per K chunk) ----
+        // ---- producer: lane 0 waits for the stage and announces the bytes, then lanes 0 .. 5 KC - 1 issue one tensor copy
+        // each: per K chunk the two 64-row halves of the weight box and the three planes ----
         int st = 0, ph = 0;
+        bool dead = false;
         uint32_t armed_mask = 0, armed_par = 0;     // stages with a copy group sent, and the parity of the latest one
-        for (int w = blockIdx.x; w < nwork && !s_abort; w += gridDim.x) {
+        const int ck = lane / 5, which = lane - ck * 5;      // this lane's chunk of the stage and its copy within the chunk
+        for (int w = blockIdx.x; w < nwork; w += gridDim.x) {
             int unit, pass, sub;
             if (!decode(w, unit, pass, sub)) continue;
             int s, blk;
@@ -188,36 +192,37 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_umma(const __grid_constant__ 
             const int kind = a.seg[s].kind;
             const bool isbf = kind == SEG_BF || kind == SEG_BF_SIGMOID || kind == SEG_BF_DECAY;
             const bool pair = kind == SEG_I8_GATEUP;
-            const int nk = (isbf ? 2 * a.K : a.K) / UM_BK;
-            const uint32_t bytes = UM_A_BYTES + (uint32_t)a.tt * UM_PI * UM_BK;
-            // this lane's copy: 0, 1 the two 64-row halves of the weight box, 2..4 the three planes
-            const CUtensorMap* map = lane >= 2 ? (isbf ? &a.xmap_bf : &a.xmap_i8) : (pair && lane == 1 ? &a.wmap2[s] : &a.wmap[s]);
-            const int y = lane >= 2 ? (pass * UM_PI + (lane - 2)) * UM_TOK + sub * a.tt : (pair ? blk * 64 : blk * UM_M + lane * 64);
-            const int off = lane >= 2 ? UM_A_BYTES + (lane - 2) * a.tt * UM_BK : lane * 64 * UM_BK;
-            for (int kc = 0; kc < nk; kc++) {
+            const int nk = (isbf ? 2 * a.K : a.K) / UM_BK;             // K chunks of the unit
+            const CUtensorMap* map = which >= 2 ? (isbf ? &a.xmap_bf : &a.xmap_i8) : (pair && which == 1 ? &a.wmap2[s] : &a.wmap[s]);
+            const int y = which >= 2 ? (pass * UM_PI + (which - 2)) * UM_TOK + sub * a.tt : (pair ? blk * 64 : blk * UM_M + which * 64);
+            const int off = ck * CHUNK + (which >= 2 ? UM_A_BYTES + (which - 2) * a.tt * UM_BK : which * 64 * UM_BK);
+            for (int k0 = 0; k0 < nk; k0 += KC) {
+                const int nch = min(KC, nk - k0);                       // chunks in this stage
                 if (lane == 0) {
-                    wait(&empty_bar[st], ph ^ 1);
-                    if (!s_abort) { if (a.dbg & 1) mbar_arrive(&full_bar[st]); else mbar_expect_tx(&full_bar[st], bytes); }
+                    wait(&empty_bar[st], ph ^ 1, dead);
+                    if (!dead) mbar_expect_tx(&full_bar[st], (uint32_t)nch * CHUNK);
                 }
-                __syncwarp();
-                if (s_abort) break;
-                if (lane < 2 + UM_PI && !(a.dbg & 1)) tma_load_2d(ring + (size_t)st * STAGE + off, map, kc * UM_BK, y, &full_bar[st]);
+                dead = __shfl_sync(0xffffffffu, (int)dead, 0) != 0;
+                if (dead) break;
+                if (lane < 5 * nch) tma_load_2d(ring + (size_t)st * STAGE + off, map, (k0 + ck) * UM_BK, y, &full_bar[st]);
                 armed_mask |= 1u << st;
                 armed_par = (armed_par & ~(1u << st)) | ((uint32_t)ph << st);
                 if (++st == NST) { st = 0; ph ^= 1; }
             }
+            if (dead) break;
         }
         __syncwarp();
         if (lane == 0) {
             stamp(2);
-            if (s_abort)                             // copies still in flight must land before the block may leave
+            if (dead)                                // copies still in flight must land before the block may leave
                 for (int i = 0; i < UM_MAX_STAGES; i++)
                     if (armed_mask >> i & 1) mbar_wait(&full_bar[i], (armed_par >> i) & 1u, nullptr, 1 << 16);
         }
     } else if (warp == 1) {
-        // ---- MMA issuer: the whole warp walks the loop and waits together, lane 0 issues ----
-        {
+        // ---- MMA issuer ----
+        if (lane == 0) {
             int st = 0, ph = 0, n = 0;
+            bool dead = false;
             for (int w = blockIdx.x; w < nwork; w += gridDim.x) {
                 int unit, pass, sub;
                 if (!decode(w, unit, pass, sub)) continue;
@@ -228,39 +233,31 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_umma(const __grid_constant__ 
                 const int nk = (isbf ? 2 * a.K : a.K) / UM_BK;
                 const uint32_t idesc = isbf ? umma_idesc(1, 1, UM_M, a.tt * UM_PB) : umma_idesc(2, 1, UM_M, a.tt * UM_PI);
                 const int buf = n & 1;
-                wait(&acc_empty[buf], ((n >> 1) & 1) ^ 1);                  // the epilogue has read this accumulator
+                wait(&acc_empty[buf], ((n >> 1) & 1) ^ 1, dead);            // the epilogue has read this accumulator
                 tc_fence_after();
                 const uint32_t d = tmem + (uint32_t)buf * 256u;
-                // consecutive products into ONE accumulator wait for one another; with few columns the four products of a
-                // K chunk go to separate accumulators (chains) that the epilogue adds
-                const int chains = um_chains(a.tt);
-                const uint32_t ncol = (uint32_t)a.tt * UM_PI;
-                for (int kc = 0; kc < nk; kc++) {
-                    wait(&full_bar[st], ph);
-                    if (!(a.dbg & 8)) tc_fence_after();
-                    const uint32_t sa = smem_u32(ring + (size_t)st * STAGE);
-                    const uint64_t ad = umma_desc_sw128(sa), bd = umma_desc_sw128(sa + UM_A_BYTES);
+                for (int k0 = 0; k0 < nk; k0 += KC) {
+                    wait(&full_bar[st], ph, dead);
+                    tc_fence_after();
+                    const int nch = min(KC, nk - k0);
+                    for (int c = 0; c < nch; c++) {
+                        const uint32_t sa = smem_u32(ring + (size_t)st * STAGE + (size_t)c * CHUNK);
+                        const uint64_t ad = umma_desc_sw128(sa), bd = umma_desc_sw128(sa + UM_A_BYTES);
 #pragma unroll
-                    for (int k = 0; k < UM_BK / 32; k++) {
-                        // 32 bytes further along K inside the swizzle span: + 2 in the descriptor's address field
-                        if ((a.dbg & 2) || lane != 0) continue;
-                        const uint32_t dc = d + (uint32_t)(k & (chains - 1)) * ncol;
-                        const uint32_t acc = (kc != 0 || k >= chains) ? 1u : 0u;
-                        if (isbf) umma_f16(dc, ad + 2 * k, bd + 2 * k, idesc, acc);
-                        else umma_i8(dc, ad + 2 * k, bd + 2 * k, idesc, acc);
+                        for (int k = 0; k < UM_BK / 32; k++) {
+                            // 32 bytes further along K inside the swizzle span: + 2 in the descriptor's address field
+                            const uint32_t acc = (k0 + c != 0 || k != 0) ? 1u : 0u;
+                            if (isbf) umma_f16(d, ad + 2 * k, bd + 2 * k, idesc, acc);
+                            else umma_i8(d, ad + 2 * k, bd + 2 * k, idesc, acc);
+                        }
                     }
-                    if (lane == 0) {
-                        if (a.dbg & 4) mbar_arrive(&empty_bar[st]);
-                        else umma_commit(&empty_bar[st]);                 // the stage may be refilled once these have read it
-                    }
-                    __syncwarp();
+                    umma_commit(&empty_bar[st]);                          // the stage may be refilled once these have read it
                     if (++st == NST) { st = 0; ph ^= 1; }
                 }
-                if (lane == 0) umma_commit(&acc_full[buf]);
-                __syncwarp();
+                umma_commit(&acc_full[buf]);
                 n++;
             }
-            if (lane == 0) stamp(3);
+            stamp(3);
         }
     } else {
         // ---- epilogue: warp w may touch TMEM lanes 32 (w % 4) .. + 31 ----
@@ -269,6 +266,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_umma(const __grid_constant__ 
         const int vrow = q * 32 + lane;                                  // row of the unit = TMEM lane
         const uint32_t lane_addr = (uint32_t)(q * 32) << 16;
         int n = 0;
+        bool dead = false;
         for (int w = blockIdx.x; w < nwork; w += gridDim.x) {
             int unit, pass, sub;
             if (!decode(w, unit, pass, sub)) continue;
@@ -290,17 +288,7 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_umma(const __grid_constant__ 
                 if (kind == SEG_BF_DECAY) { rs = bf(a.a_log[row]); e1 = bf(a.dt_bias[row]); }
                 if (kind == SEG_I8_CONV) cw = *reinterpret_cast<const uint2*>(a.conv_w + (size_t)row * 4);
             }
-            if (a.dbg & 16) {
-                // one lane per warp polls, with a pause between polls; the others wait at the warp barrier
-                if (lane == 0) {
-                    for (int spin = 0; spin < (1 << 16) && !s_abort; spin++) {
-                        if (mbar_wait(&acc_full[buf], (n >> 1) & 1, nullptr, 1)) break;
-                        __nanosleep(500);
-                    }
-                }
-                __syncwarp();
-            } else
-            wait(&acc_full[buf], (n >> 1) & 1);
+            wait(&acc_full[buf], (n >> 1) & 1, dead);
             tc_fence_after();
             if (n == 0 && threadIdx.x == 64) stamp(4);
             const uint32_t base = tmem + lane_addr + (uint32_t)buf * 256u;
@@ -309,42 +297,22 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_umma(const __grid_constant__ 
                 if (n == 0 && c == 1 && threadIdx.x == 64) stamp(7);
                 if (t0 >= a.T) break;                                    // uniform over the block
                 float v[16];
-                const int chains = um_chains(a.tt);
-                const uint32_t ncol = (uint32_t)a.tt * UM_PI;
-                if (isbf) {
-                    float f0[16], f1[16], f2[16];
-#pragma unroll
-                    for (int i = 0; i < 16; i++) f0[i] = f1[i] = f2[i] = 0.f;
-                    for (int ch = 0; ch < chains; ch++) {
-                        uint32_t d0[16], d1[16], d2[16];
-                        tmem_ld16(base + ch * ncol + 0 * a.tt + c * 16, d0);
-                        tmem_ld16(base + ch * ncol + 1 * a.tt + c * 16, d1);
-                        tmem_ld16(base + ch * ncol + 2 * a.tt + c * 16, d2);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 16; i++) { f0[i] += __uint_as_float(d0[i]); f1[i] += __uint_as_float(d1[i]); f2[i] += __uint_as_float(d2[i]); }
-                    }
+                {
+                    uint32_t d0[16], d1[16], d2[16];
+                    tmem_ld16(base + 0 * a.tt + c * 16, d0);
+                    tmem_ld16(base + 1 * a.tt + c * 16, d1);
+                    tmem_ld16(base + 2 * a.tt + c * 16, d2);
+                    tmem_ld_wait();
                     if (n == 0 && c == 0 && threadIdx.x == 64) stamp(6);
+                    if (isbf) {
 #pragma unroll
-                    for (int i = 0; i < 16; i++) v[i] = (f2[i] + f1[i]) + f0[i];
-                } else {
-                    int s0[16], s1[16], s2[16];
+                        for (int i = 0; i < 16; i++) v[i] = (__uint_as_float(d2[i]) + __uint_as_float(d1[i])) + __uint_as_float(d0[i]);
+                    } else {
 #pragma unroll
-                    for (int i = 0; i < 16; i++) s0[i] = s1[i] = s2[i] = 0;
-                    for (int ch = 0; ch < chains; ch++) {
-                        uint32_t d0[16], d1[16], d2[16];
-                        tmem_ld16(base + ch * ncol + 0 * a.tt + c * 16, d0);
-                        tmem_ld16(base + ch * ncol + 1 * a.tt + c * 16, d1);
-                        tmem_ld16(base + ch * ncol + 2 * a.tt + c * 16, d2);
-                        tmem_ld_wait();
-#pragma unroll
-                        for (int i = 0; i < 16; i++) { s0[i] += (int)d0[i]; s1[i] += (int)d1[i]; s2[i] += (int)d2[i]; }
-                    }
-                    if (n == 0 && c == 0 && threadIdx.x == 64) stamp(6);
-#pragma unroll
-                    for (int i = 0; i < 16; i++) {
-                        const float f = (float)s2[i] * (1.0f / 128.0f) + (float)s1[i];
-                        v[i] = (f * (1.0f / 128.0f) + (float)s0[i]) * __ldg(a.xscale + t0 + i);
+                        for (int i = 0; i < 16; i++) {
+                            const float f = (float)(int)d2[i] * (1.0f / 128.0f) + (float)(int)d1[i];
+                            v[i] = (f * (1.0f / 128.0f) + (float)(int)d0[i]) * __ldg(a.xscale + t0 + i);
+                        }
                     }
                 }
                 if (pair) {

@@ -139,6 +139,48 @@ def test_batched_decode_at_full_width(E, full4, batch):
     e.close()
 
 
+@pytest.mark.parametrize("kv", ["f32", "bf16"])
+def test_prompt_chunks_at_full_width(E, full4, kv):
+    """A 300-token prompt in one feed: two chunks of 128 tokens and one of 44 go through the layers with their tokens as
+    the columns of the tcgen05 GEMMs and of the grouped expert GEMM, conv / delta rule / attention walk them in order;
+    then single-token steps continue from the state the chunks left. Against the oracle, which runs the prompt through
+    the reference's chunked DeltaNet form: the reference's own acceptance, logits within tolerance, same greedy tokens;
+    and bit-for-bit the same continuation as an engine that was fed the prompt token by token is NOT required (the sums
+    run in another order), only agreement within the same bounds."""
+    cfg, dev, model = full4
+    rng = np.random.default_rng(11)
+    prompt = rng.integers(0, cfg.vocab_size, 300)
+    e = E.HybridEngine.from_tensors(cfg.to_dict(), dev, max_context=512, device=0, batch=1,
+                                    kv_dtype=E.KV_F32 if kv == "f32" else E.KV_BF16)
+    cache = model.new_cache(1, 400, kv_dtype=kv)
+    want = model.forward(prompt[None, :], cache)
+    got = e.feed(prompt)[None]
+    tol = TOL if kv == "f32" else 2e-3
+    assert e.length() == 300
+    reference_accepts(want, got)
+    assert np.abs(got - want).max() < tol, float(np.abs(got - want).max())
+    for layer in range(cfg.n_layers):                      # the last token's picks are where a decode step leaves them
+        assert np.array_equal(e.router(layer, cfg.experts_active)[0][0], model.last_route[layer][0][-1]), layer
+    tok = int(want.argmax())
+    for j in range(4):
+        want = model.forward(np.asarray([[tok]]), cache)
+        got = e.feed([tok])[None]
+        assert np.abs(got - want).max() < tol, (j, float(np.abs(got - want).max()))
+        assert int(got.argmax()) == int(want.argmax())
+        tok = int(want.argmax())
+    # a second engine fed the same prompt token by token agrees with the chunked one
+    e2 = E.HybridEngine.from_tensors(cfg.to_dict(), dev, max_context=512, device=0, batch=1,
+                                     kv_dtype=E.KV_F32 if kv == "f32" else E.KV_BF16)
+    for t in prompt[:-1]:
+        e2.feed([int(t)], want_logits=False)
+    one = e2.feed([int(prompt[-1])])
+    e3 = E.HybridEngine.from_tensors(cfg.to_dict(), dev, max_context=512, device=0, batch=1,
+                                     kv_dtype=E.KV_F32 if kv == "f32" else E.KV_BF16)
+    assert np.abs(e3.feed(prompt) - one).max() < tol
+    for eng in (e, e2, e3):
+        eng.close()
+
+
 def test_router_ties_and_bias_at_256_experts(E, full4):
     """A router bias that makes groups of experts exactly equal must still give the reference's order (ties to the
     lower index), and the bias must act as in the oracle."""
