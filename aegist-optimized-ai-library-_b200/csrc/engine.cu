@@ -85,6 +85,11 @@ struct LayerW {
     const uint8_t* experts = nullptr;       // [local experts][expert_bytes]
     const uint8_t** eptr = nullptr;         // device [E]
     float* router_bias = nullptr;           // device [E] or null
+    // core engine + the layer's live switchable cores (live_bank, aegist_rs/src/hybrid.rs:1122-1150)
+    const uint16_t *key1 = nullptr, *key2 = nullptr;      // [n1][D], [n2][D]; null: the brain has no core engine tensors
+    int* live = nullptr;                    // device [n1 * n2]: core id -> index into the bank, or -1
+    int n_live = 0;
+    const uint16_t *cg = nullptr, *cu = nullptr, *cd = nullptr;   // bank: gate, up [n][D][r], down [n][r][D]
 };
 
 static size_t dtype_size(const std::string& d) {
@@ -171,6 +176,11 @@ struct b2_engine {
     std::vector<int> tap_layers;
     float* tap_buf = nullptr;
     uint64_t hits = 0;
+    // core engine: switch-on counts per layer and core, the picks of the current layer, its score rows, the live cores' output
+    int* d_counts = nullptr;                 // [L][n1 * n2]
+    int* csel = nullptr; float* cselw = nullptr;      // [B][cores_active]
+    float *cscore = nullptr, *core_y = nullptr;       // [B][n1 + n2], [B][D]
+    int live_cores = 0;
     // expert parallelism (ep_world > 1): NCCL is resolved at run time from the library the process
     // already has loaded (torch's), so that one process never holds two NCCL versions
     void* nccl_lib = nullptr;
@@ -205,7 +215,9 @@ struct b2_engine {
         int *g_list = nullptr, *g_chunk = nullptr;
         float *xsum_tok = nullptr, *xsum_act = nullptr;
         int cap_small = 0, cap_big = 0, nsplit = 1, attn_tiles = 1;
+        int* csel = nullptr; float *cselw = nullptr, *cscore = nullptr, *core_y = nullptr;
     } pc;
+    cudaGraphExec_t chunk_graph = nullptr;          // a full chunk without the head, captured at its first use
     int ensure_chunk_bufs();
     int feed_chunk(const uint32_t* ids, int T, bool want_head);
 
@@ -252,15 +264,16 @@ b2_engine::~b2_engine() {
     if (t.empty() && !finished) return;   // nothing was ever allocated (e.g. creation was refused)
     cudaSetDevice(device);
     if (graph) cudaGraphExecDestroy(graph);
+    if (chunk_graph) cudaGraphExecDestroy(chunk_graph);
     for (auto& kv : t) cudaFree(kv.second.p);
-    for (auto& l : layers) { cudaFree((void*)l.eptr); cudaFree(l.router_bias); }
+    for (auto& l : layers) { cudaFree((void*)l.eptr); cudaFree(l.router_bias); cudaFree(l.live); }
     void* bufs[] = {conv, state, snap_conv[0], snap_conv[1], snap_state[0], snap_state[1], kpool, vpool, page_table, rope_cos,
                     rope_sin, d_tok, d_next, d_pos, d_err, d_counter, d_acounter, x, big, zbuf, kraw, vraw, beta, gdec, obuf, att,
-                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh, g_list, g_chunk, acth, xsum_tok, xsum_act, d_trace, (void*)top_ptr, actq, asc, asum, uq_i, uq_b, uq_scale};
+                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh, g_list, g_chunk, acth, xsum_tok, xsum_act, d_trace, (void*)top_ptr, actq, asc, asum, uq_i, uq_b, uq_scale, d_counts, csel, cselw, cscore, core_y};
     for (void* p : bufs) cudaFree(p);
     void* cb[] = {pc.tok, pc.vpos, pc.x, pc.big, pc.zbuf, pc.kraw, pc.vraw, pc.beta, pc.gdec, pc.obuf, pc.att, pc.rlogits, pc.sh_act, pc.sgate,
                   pc.act, pc.top_idx, pc.top_w, pc.ypart, pc.attn_part, pc.dcounter, pc.counter, pc.xh, pc.acth, pc.uq_i, pc.uq_b, pc.uq_scale,
-                  pc.g_list, pc.g_chunk, pc.xsum_tok, pc.xsum_act};
+                  pc.g_list, pc.g_chunk, pc.xsum_tok, pc.xsum_act, pc.csel, pc.cselw, pc.cscore, pc.core_y};
     for (void* p : cb) cudaFree(p);
     if (h_pin) cudaFreeHost(h_pin);
     if (ev0) cudaEventDestroy(ev0);
@@ -320,6 +333,8 @@ int b2_engine::parse_config(const JValue& j) {
     if (c.E > 256 || c.E < 1 || c.TOPK > 8 || c.TOPK < 1 || c.TOPK > c.E || c.G != 64 || c.I % 64 != 0 || c.I > 512 || c.I < 64) add("experts need n_experts <= 256, top-k <= 8, group 64, hidden a multiple of 64 up to 512");
     if (c.SH % 16 != 0 || c.SH > 512 || c.SH < 16) add("shared_hidden must be a multiple of 16 up to 512");
     if (c.E % ep_world != 0) add("n_experts not divisible by the number of expert-parallel ranks");
+    if (c.n1 < 1 || c.n2 < 1 || c.n1 > 128 || c.n2 > 128 || c.cores_active < 1 || c.cores_active > 8 || c.rank < 1 || c.rank > 256)
+        add("core engine needs a grid of at most 128 x 128, 1 to 8 active cores, rank up to 256");
     if (!bad.empty()) return fail("this engine build does not support this brain's shape: %s", bad.c_str());
     return 0;
 }
@@ -332,12 +347,6 @@ int b2_engine::put(const std::string& name, const std::string& dtype, const std:
     size_t n = es;
     for (auto s : shape) n *= (size_t)s;
     if (n != nbytes) return fail("%s: %zu bytes given, shape says %zu", name.c_str(), nbytes, n);
-    // tensors the decode path does not read are not kept (the embedding IS kept: it is gathered on the device)
-    if (name.find(".engine.") != std::string::npos || name.find(".cores.") != std::string::npos) {
-        if (name.size() > 10 && name.rfind(".cores.ids") == name.size() - 10 && nbytes != 0)
-            return fail("%s: this brain has live switchable cores, which this engine build does not run", name.c_str());
-        return 0;
-    }
     CU(cudaSetDevice(device));
     DevTensor d;
     d.dtype = dtype;
@@ -443,6 +452,32 @@ int b2_engine::finish() {
         CU(cudaMalloc((void**)&l.eptr, c.E * sizeof(void*)));
         CU(cudaMemcpy((void*)l.eptr, tab.data(), c.E * sizeof(void*), cudaMemcpyHostToDevice));
         CU(dalloc(&l.router_bias, c.E));   // zeros: adding them changes no logit; b2_set_router_bias fills them
+        if (t.count(b + "engine.key1.weight")) {
+            NEED(l.key1, b + "engine.key1.weight", "bf16", c.n1, c.D)
+            NEED(l.key2, b + "engine.key2.weight", "bf16", c.n2, c.D)
+            // the sparse bank: ids [n] name the cores that are stored; everything else adds nothing
+            const int nc = c.n1 * c.n2;
+            std::vector<int> map(nc, -1);
+            auto it = t.find(b + "cores.ids");
+            int n = 0;
+            if (it != t.end() && it->second.nbytes) {
+                if (it->second.dtype != "i64") return fail("%scores.ids must be i64", b.c_str());
+                n = (int)(it->second.nbytes / 8);
+                std::vector<int64_t> ids(n);
+                CU(cudaMemcpy(ids.data(), it->second.p, (size_t)n * 8, cudaMemcpyDeviceToHost));
+                for (int j = 0; j < n; j++) {
+                    if (ids[j] < 0 || ids[j] >= nc) return fail("%scores.ids: core id %lld is outside the %d x %d grid", b.c_str(), (long long)ids[j], c.n1, c.n2);
+                    map[(size_t)ids[j]] = j;
+                }
+                NEED(l.cg, b + "cores.gate", "bf16", n, c.D, c.rank)
+                NEED(l.cu, b + "cores.up", "bf16", n, c.D, c.rank)
+                NEED(l.cd, b + "cores.down", "bf16", n, c.rank, c.D)
+            }
+            l.n_live = n;
+            live_cores += n;
+            CU(dalloc(&l.live, nc, false));
+            CU(cudaMemcpy(l.live, map.data(), (size_t)nc * 4, cudaMemcpyHostToDevice));
+        }
         layers.push_back(l);
     }
 #undef NEED
@@ -530,6 +565,9 @@ int b2_engine::finish() {
     }
     CU(dalloc(&ypart, Bg * (c.TOPK + 1) * c.D));
     CU(dalloc(&d_dcounter, Bg * down_row_blocks(c.D)));
+    CU(dalloc(&d_counts, (size_t)c.L * c.n1 * c.n2));
+    CU(dalloc(&csel, (size_t)B * c.cores_active)); CU(dalloc(&cselw, (size_t)B * c.cores_active));
+    CU(dalloc(&cscore, (size_t)B * (c.n1 + c.n2))); CU(dalloc(&core_y, (size_t)B * c.D));
     if (ep_world > 1) {
         const size_t rw = c.D + 2 * c.TOPK;
         CU(dalloc(&rec_local, (size_t)B * rw));
@@ -545,7 +583,7 @@ int b2_engine::finish() {
     char buf[512];
     size_t kv_bytes = 2 * kv_elems * kvb;
     snprintf(buf, sizeof(buf), "%s: %.2f GB of weights in HBM (%d of %d experts resident%s), %d live cores, context %d tokens x %d, KV %s %.2f GB",
-             gpu_name.c_str(), weight_bytes / 1e9, c.L * per, c.L * c.E, ep_world > 1 ? " on this rank" : "", 0, cap, B,
+             gpu_name.c_str(), weight_bytes / 1e9, c.L * per, c.L * c.E, ep_world > 1 ? " on this rank" : "", live_cores, cap, B,
              kv_f32 ? "fp32" : "bf16", kv_bytes / 1e9);
     desc = buf;
     if (ep_world > 1) return 0;   // the step graph holds NCCL calls: it is built by b2_ep_init
@@ -640,7 +678,7 @@ static long g_umma_launches = 0;      // how many GEMV groups went to k_umma (te
 static bool launch_umma(const GemvArgs& a, int T, int nsm, cudaStream_t st, const BatchCtx& bc, cudaError_t* err) {
     *err = cudaSuccess;
     const int passes = (T + UM_TOK - 1) / UM_TOK;
-    if (!bc.qi || passes > bc.passes_max || a.K % UM_BK != 0 || a.K > 4096 || a.nseg > 4 || !tensor_map_encoder()) return false;
+    if (!bc.qi || passes > bc.passes_max || a.K % UM_BK != 0 || a.K > 4096 || a.nseg > GEMV_MAX_SEG || !tensor_map_encoder()) return false;
     UmmaArgs u{};
     bool any_i8 = false, any_bf = false;
     for (int i = 0; i < a.nseg; i++) {
@@ -694,7 +732,7 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
             }
         if (a.finisher == FIN_TOPK)
             e = launch_k(k_router_topk, dim3((B + 7) / 8), dim3(256), 0, st, (const float*)a.seg[0].out, a.seg[0].out_stride, a.E, a.topk,
-                         a.top_idx, a.top_w, B);
+                         a.top_idx, a.top_w, B, a.core);
         return e;
     }
     if (bc && bc->xh && B >= 8 && B <= bc->Tpad && a.K % MM_KC == 0) {
@@ -740,10 +778,15 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
                 if (e != cudaSuccess) return e;
             }
             if (topk_moved) {
-                e = launch_k(k_router_topk, dim3((B + 7) / 8), dim3(256), 0, st, (const float*)a.seg[0].out, a.seg[0].out_stride, a.E, a.topk,
-                             a.top_idx, a.top_w, B);
-                if (e != cudaSuccess) return e;
-                rest.finisher = FIN_NONE;
+                // the picks need every score row: what this kernel did not take (beyond its four matrices) is multiplied first
+                if (rest.nseg > 0) {
+                    rest.finisher = FIN_NONE;
+                    rest.core.score = nullptr;
+                    seal(rest, a.K);
+                    if ((e = launch_gemv(rest, B, nsm, st, 0, nullptr)) != cudaSuccess) return e;
+                }
+                return launch_k(k_router_topk, dim3((B + 7) / 8), dim3(256), 0, st, (const float*)a.seg[0].out, a.seg[0].out_stride, a.E, a.topk,
+                                a.top_idx, a.top_w, B, a.core);
             }
             if (rest.nseg == 0) return cudaSuccess;
             seal(rest, a.K);
@@ -960,8 +1003,10 @@ static bool moe1_shape_ok(const Cfg& c) {
 struct Moe1Ctx { const uint8_t** top_ptr; int8_t* actq; float* asc; float* asum; };
 static cudaError_t launch_moe1(const Cfg& c, const float* rlogits, const float* x_in, const uint16_t* norm_w, const uint8_t* const* eptr,
                                int* top_idx, float* top_w, const Moe1Ctx& m, const float* sh_act, const float* sgate, const int8_t* shd_w,
-                               const uint16_t* shd_s, float* xout, int* err, int B, cudaStream_t st, b2_engine* prof) {
+                               const uint16_t* shd_s, float* xout, int* err, int B, cudaStream_t st, b2_engine* prof,
+                               const CoreRoute* core = nullptr, const CoresLiveArgs* live = nullptr) {
     Gu1Args g{};
+    if (core) g.core = *core;
     g.logits = rlogits; g.x = x_in; g.norm_w = norm_w; g.eps = c.eps; g.eptr = eptr;
     g.off_gu_s = c.off_gu_s(); g.off_gu_m = c.off_gu_m(); g.D = c.D; g.I = c.I; g.E = c.E; g.topk = c.TOPK;
     g.top_idx = top_idx; g.top_w = top_w; g.top_ptr = m.top_ptr; g.actq = m.actq; g.asc = m.asc; g.asum = m.asum; g.err = err;
@@ -969,6 +1014,8 @@ static cudaError_t launch_moe1(const Cfg& c, const float* rlogits, const float* 
     cudaError_t ce = opt_in_smem(k_moe_gu1, m1_gu_smem(c.D));
     if (ce == cudaSuccess) ce = launch_k(k_moe_gu1, dim3(gx, B), dim3(M1_GU_THREADS), m1_gu_smem(c.D), st, g);
     if (prof) prof->mark(5, st);
+    // the gate/up kernel has made the core engine's picks; the live cores read x before the down kernel writes it
+    if (live && ce == cudaSuccess) ce = launch_k(k_cores_live, dim3(B), dim3(256), (size_t)(live->D + live->r) * 4, st, *live);
     Down1Args d{};
     d.top_ptr = m.top_ptr; d.top_w = top_w; d.actq = m.actq; d.asc = m.asc; d.asum = m.asum; d.sh_act = sh_act; d.sg = sgate;
     d.shd_w = shd_w; d.shd_s = shd_s;
@@ -1103,7 +1150,32 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count, int chunk_T, bool chunk
             a.seg[1] = make_seg(SEG_I8_GATEUP, l.sh_gate.w, l.sh_gate.s, c.SH, sh_act, c.SH);
             a.seg[1].w2 = l.sh_up.w; a.seg[1].s2 = l.sh_up.s;
             a.seg[2] = make_seg(SEG_BF_SIGMOID, l.sh_gw, nullptr, 1, sgate, 1);
-            a.nseg = 3; seal(a, c.D);
+            a.nseg = 3;
+            // the core engine's two key tables ride along: their scores, then the picks where the router's are made
+            float* const cscore = chunk ? pc.cscore : this->cscore;
+            int* const csel = chunk ? pc.csel : this->csel;
+            float* const cselw = chunk ? pc.cselw : this->cselw;
+            float* const core_y = chunk ? pc.core_y : this->core_y;
+            CoreRoute cr{};
+            if (l.key1) {
+                a.seg[3] = make_seg(SEG_BF, l.key1, nullptr, c.n1, cscore, c.n1 + c.n2);
+                a.seg[4] = make_seg(SEG_BF, l.key2, nullptr, c.n2, cscore + c.n1, c.n1 + c.n2);
+                a.nseg = 5;
+                cr.score = cscore; cr.n1 = c.n1; cr.n2 = c.n2; cr.k = c.cores_active;
+                cr.counts = d_counts + (size_t)li * c.n1 * c.n2; cr.sel = csel; cr.selw = cselw;
+            }
+            seal(a, c.D);
+            a.core = cr;
+            // the layer's live cores: their output goes to core_y once the picks are known and before the experts write x
+            CoresLiveArgs cl{};
+            const bool has_live = l.key1 && l.n_live > 0;
+            if (has_live) {
+                cl.x = x; cl.norm_w = l.norm2; cl.eps = c.eps; cl.live = l.live; cl.cg = l.cg; cl.cu = l.cu; cl.cd = l.cd;
+                cl.sel = csel; cl.selw = cselw; cl.y = core_y; cl.D = c.D; cl.r = c.rank; cl.k = c.cores_active;
+            }
+            auto launch_live = [&]() {
+                if (has_live) launch_k(k_cores_live, dim3(B), dim3(256), (size_t)(c.D + c.rank) * 4, st, cl);
+            };
             a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D; a.err = d_err;
             // fewer than 8 tokens on one GPU: the top-8 moves into the expert kernel and the experts are spread over all SMs
             const bool moe1 = ep_world == 1 && B < 8 && moe1_shape_ok(c);
@@ -1117,10 +1189,11 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count, int chunk_T, bool chunk
                 cudaMemcpyAsync(top_w + (size_t)li * NSEQ * c.TOPK, pc.top_w + (size_t)(B - 1) * c.TOPK, c.TOPK * sizeof(float), cudaMemcpyDeviceToDevice, st);
             }
             mark(1, st);
+            if (!moe1) launch_live();              // the picks were made by the launch above (its finisher, or k_router_topk)
             if (moe1) {
                 const Moe1Ctx mc{top_ptr, actq, asc, asum};
                 cudaError_t ce = launch_moe1(c, rlogits, x, l.norm2, l.eptr, a.top_idx, a.top_w, mc, sh_act, sgate, (const int8_t*)l.sh_down.w,
-                                             l.sh_down.s, x, d_err, B, st, this);
+                                             l.sh_down.s, x, d_err, B, st, this, &cr, has_live ? &cl : nullptr);
                 if (ce != cudaSuccess) return fail("expert kernels: %s", cudaGetErrorString(ce));
                 n += 3;
             } else {
@@ -1168,6 +1241,10 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count, int chunk_T, bool chunk
             }
             n += 3;
             }
+        }
+        if (l.key1 && l.n_live > 0) {
+            float* const cy = chunk ? pc.core_y : this->core_y;
+            launch_k(k_add_rows, dim3((B * c.D + 255) / 256), dim3(256), 0, st, x, (const float*)cy, B * c.D);
         }
         for (size_t j = 0; j < tap_layers.size(); j++)
             if (tap_layers[j] == li) {
@@ -1234,6 +1311,8 @@ int b2_engine::ensure_chunk_bufs() {
     CU(dalloc((uint16_t**)&pc.acth, P * 2 * c.I));
     CU(dalloc(&pc.xsum_tok, (size_t)W * (c.D / 64)));
     CU(dalloc(&pc.xsum_act, P * std::max(1, c.I / 64)));
+    CU(dalloc(&pc.csel, (size_t)W * c.cores_active)); CU(dalloc(&pc.cselw, (size_t)W * c.cores_active));
+    CU(dalloc(&pc.cscore, (size_t)W * (c.n1 + c.n2))); CU(dalloc(&pc.core_y, (size_t)W * c.D));
     pc.W = W;
     return 0;
 }
@@ -1242,7 +1321,21 @@ int b2_engine::ensure_chunk_bufs() {
 int b2_engine::feed_chunk(const uint32_t* ids, int T, bool want_head) {
     if (ensure_chunk_bufs()) return 1;
     CU(cudaMemcpyAsync(pc.tok, ids, (size_t)T * 4, cudaMemcpyHostToDevice, stream));
-    if (enqueue_step(stream, false, T, want_head)) return 1;
+    if (T == CHUNK_TOKENS && !want_head) {
+        // the common case of a long prompt: one graph launch instead of some fifteen launches per layer
+        if (!chunk_graph) {
+            cudaGraph_t g;
+            CU(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+            const int rc = enqueue_step(stream, false, T, false);
+            const cudaError_t ce = cudaStreamEndCapture(stream, &g);
+            if (rc) return rc;
+            if (ce != cudaSuccess) return fail("chunk graph capture: %s", cudaGetErrorString(ce));
+            const cudaError_t ci = cudaGraphInstantiate(&chunk_graph, g, 0);
+            cudaGraphDestroy(g);
+            if (ci != cudaSuccess) { chunk_graph = nullptr; return fail("chunk graph instantiate: %s", cudaGetErrorString(ci)); }
+        }
+        CU(cudaGraphLaunch(chunk_graph, stream));
+    } else if (enqueue_step(stream, false, T, want_head)) return 1;
     length += T;
     hits += (uint64_t)T * c.TOPK * c.L;
     for (int i = 0; i < T; i++) toks.push_back(ids[i]);
@@ -1361,7 +1454,7 @@ void b2_engine::class_bytes(double out[8]) const {
             out[2] += nb * 2.0 * c.HV * c.DK * c.DV * 4;
             out[4] += qwb(c.D, c.VD()) + c.DV * 2.0;
         }
-        out[1] += c.D * 2.0 + (double)c.E * c.D * 2 + c.D * 2.0 + 2 * qwb(c.SH, c.D);
+        out[1] += c.D * 2.0 + (double)c.E * c.D * 2 + c.D * 2.0 + 2 * qwb(c.SH, c.D) + (layers[i].key1 ? (c.n1 + c.n2) * c.D * 2.0 : 0.0);
         out[5] += uniq * (double)(c.gu_q() + 2 * c.gu_sm()) + c.D * 2.0;
         out[6] += uniq * (double)(c.dn_q() + 2 * c.dn_sm()) + qwb(c.D, c.SH);
     }
@@ -1750,6 +1843,7 @@ int b2_set_taps(b2_engine* e, const int* layers, int n) {
     e->tap_buf = nullptr;
     e->tap_layers.assign(layers, layers + n);
     if (n) CUE(dalloc(&e->tap_buf, (size_t)n * e->B * e->c.D));
+    if (e->chunk_graph) { cudaGraphExecDestroy(e->chunk_graph); e->chunk_graph = nullptr; }      // it holds the old taps' copies
     return e->build_graph();
 }
 
@@ -1763,11 +1857,19 @@ int b2_taps(b2_engine* e, float* out) {
 }
 
 int b2_core_counts(b2_engine* e, int32_t* out) {
-    if (!e) return 1;
-    memset(out, 0, (size_t)e->c.L * e->c.n1 * e->c.n2 * 4);
+    if (!e || !e->finished) return 1;
+    CUE(cudaSetDevice(e->device));
+    CUE(cudaStreamSynchronize(e->stream));
+    CUE(cudaMemcpy(out, e->d_counts, (size_t)e->c.L * e->c.n1 * e->c.n2 * 4, cudaMemcpyDeviceToHost));
     return 0;
 }
-int b2_reset_counts(b2_engine* e) { return e ? 0 : 1; }
+int b2_reset_counts(b2_engine* e) {
+    if (!e || !e->finished) return 1;
+    CUE(cudaSetDevice(e->device));
+    CUE(cudaMemsetAsync(e->d_counts, 0, (size_t)e->c.L * e->c.n1 * e->c.n2 * 4, e->stream));
+    CUE(cudaStreamSynchronize(e->stream));
+    return 0;
+}
 
 void b2_expert_counters(const b2_engine* e, uint64_t* hits, uint64_t* page_ins) {
     if (hits) *hits = e ? e->hits : 0;

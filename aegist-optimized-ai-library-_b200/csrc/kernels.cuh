@@ -189,9 +189,84 @@ struct Seg {
     int tr;            // k_tcgemv: rows per tile chosen by the host (0 = as many as a stage holds)
 };
 
+
+// The core engine (CoreEngine.forward, aegist/model.py:214-224; the routing half of cores_apply,
+// aegist_rs/kernels/aegist.cu:283-322): two score tables of n1 and n2 entries address n1 * n2 switchable cores. The k
+// best of each table, the k1 * k2 sums of their pairs, the k best sums (ties to the earlier one), softmax over those.
+// Every pick is tallied in counts[core] (Lm::core_counts); picks and weights are kept for the live cores' kernel.
+struct CoreRoute {
+    const float* score;      // [T][n1 + n2] the two tables' scores of every token (null: this brain has no core engine)
+    int n1, n2, k;
+    int* counts;             // [n1 * n2] of this layer
+    int* sel;                // [T][k]
+    float* selw;             // [T][k]
+};
+// one warp per token; n1 <= 128, n2 <= 128, k <= 8
+__device__ __forceinline__ void core_route_warp(const CoreRoute& cr, int t, int lane) {
+    const float* s = cr.score + (size_t)t * (cr.n1 + cr.n2);
+    float v[2][8];
+    int ix[2][8];
+    const int kk[2] = {min(cr.k, cr.n1), min(cr.k, cr.n2)};
+#pragma unroll
+    for (int tab = 0; tab < 2; tab++) {
+        const int n = tab ? cr.n2 : cr.n1;
+        const float* st = s + (tab ? cr.n1 : 0);
+        float mine[4];
+#pragma unroll
+        for (int j = 0; j < 4; j++) mine[j] = lane + 32 * j < n ? __ldcg(st + lane + 32 * j) : -INFINITY;
+        for (int r = 0; r < kk[tab]; r++) {
+            float bv = -INFINITY;
+            int bi = 0x7fffffff;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                if (lane + 32 * j < n && mine[j] > bv) { bv = mine[j]; bi = lane + 32 * j; }      // '>' keeps the lower index
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            v[tab][r] = bv; ix[tab][r] = bi;
+            if ((bi & 31) == lane) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) if (j == (bi >> 5)) mine[j] = -INFINITY;
+            }
+        }
+    }
+    if (lane == 0) {
+        // candidate order: first table's pick outermost (as the reference lists them); at most 64 candidates
+        float cv[64];
+        int ci[64], nc = 0;
+        for (int a = 0; a < kk[0]; a++)
+            for (int b = 0; b < kk[1]; b++) { cv[nc] = v[0][a] + v[1][b]; ci[nc++] = ix[0][a] * cr.n2 + ix[1][b]; }
+        float tv[8];
+        int ti[8];
+        const int k = min(cr.k, nc);
+        for (int j = 0; j < k; j++) {
+            int best = -1;
+            for (int i = 0; i < nc; i++) {
+                bool taken = false;
+                for (int p = 0; p < j; p++) taken |= ti[p] == i;
+                if (!taken && (best < 0 || cv[i] > cv[best])) best = i;
+            }
+            ti[j] = best; tv[j] = cv[best];
+        }
+        float sum = 0.f;
+        for (int j = 0; j < k; j++) sum += expf(tv[j] - tv[0]);
+        for (int j = 0; j < k; j++) {
+            const int core = ci[ti[j]];
+            cr.sel[(size_t)t * cr.k + j] = core;
+            cr.selw[(size_t)t * cr.k + j] = expf(tv[j] - tv[0]) / sum;
+            atomicAdd(cr.counts + core, 1);
+        }
+    }
+}
+
+constexpr int GEMV_MAX_SEG = 6;     // router + shared gate/up + shared gate + the core engine's two key tables
+
 struct GemvArgs {
     unsigned long long* trace;   // step timeline slot of this launch, or null
-    Seg seg[4];
+    Seg seg[GEMV_MAX_SEG];
     int nseg;
     int total_jobs;
     int jq, jr;              // k_tcgemv: total_jobs = jq * grid + jr; block b starts at b * jq + min(b, jr)
@@ -223,6 +298,7 @@ struct GemvArgs {
     int* next_tok;           // [B]
     int* pos;                // [B] advanced by one by the finisher (may be null)
     int* err;                // set to 3 if a bulk copy never landed (bounded wait gave up)
+    CoreRoute core;          // FIN_TOPK: the core engine's picks follow the router's (scores = two of the segments)
 };
 
 // Softmax over E router logits and the `topk` largest in descending order, ties to the lower
@@ -1149,6 +1225,81 @@ __global__ void k_wait_never(int polls, int* err) {
     }
     __syncthreads();
     if (threadIdx.x == 0) mbar_wait(&bar, 0, err, polls);
+}
+
+// The live switchable cores of one layer (SparseCoreBank.forward, aegist/hybrid.py:745-771; the second half of
+// cores_apply, aegist_rs/kernels/aegist.cu:323-349): for every pick whose core is stored, w * down^T (silu(h gate) * (h up))
+// with h = norm2(x), summed into y[t] (which k_add_rows later adds to the residual stream). grid (T), 256 threads,
+// dynamic shared memory D + r floats. Launched only for layers that have live cores.
+struct CoresLiveArgs {
+    const float* x;           // [T][D] residual rows before the experts wrote them
+    const uint16_t* norm_w;   // [D]
+    float eps;
+    const int* live;          // [n cores] index into the bank, or -1
+    const uint16_t *cg, *cu, *cd;   // bank: gate [n][D][r], up [n][D][r], down [n][r][D] bf16
+    const int* sel;           // [T][k]
+    const float* selw;        // [T][k]
+    float* y;                 // [T][D]
+    int D, r, k;
+};
+__global__ void __launch_bounds__(256) k_cores_live(const CoresLiveArgs a) {
+    extern __shared__ float cl_smem[];
+    float* h = cl_smem;              // [D]
+    float* z = cl_smem + a.D;        // [r]
+    __shared__ float red[8];
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    grid_dep_launch();
+    grid_dep_wait();
+    const float* xr = a.x + (size_t)t * a.D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < a.D; i += 256) { const float v = xr[i]; ss = fmaf(v, v, ss); }
+    ss = block_sum(ss, red);
+    const float rn = 1.0f / sqrtf(ss / (float)a.D + a.eps);
+    for (int i = threadIdx.x; i < a.D; i += 256) h[i] = xr[i] * rn * (1.0f + bf(a.norm_w[i]));
+    float acc[8];                    // this thread's output dims i = threadIdx.x + 256 j (D <= 2048)
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[j] = 0.f;
+    __syncthreads();
+    for (int c = 0; c < a.k; c++) {
+        const int li = a.live[a.sel[(size_t)t * a.k + c]];
+        if (li < 0) continue;        // the same for the whole block
+        const uint16_t* G = a.cg + (size_t)li * a.D * a.r;
+        const uint16_t* U = a.cu + (size_t)li * a.D * a.r;
+        const uint16_t* Dn = a.cd + (size_t)li * a.r * a.D;
+        for (int j = warp; j < a.r; j += 8) {
+            float g = 0.f, u = 0.f;
+            for (int i = lane; i < a.D; i += 32) {
+                g = fmaf(h[i], bf(G[(size_t)i * a.r + j]), g);
+                u = fmaf(h[i], bf(U[(size_t)i * a.r + j]), u);
+            }
+            g = warp_sum(g);
+            u = warp_sum(u);
+            if (lane == 0) z[j] = siluf_(g) * u;
+        }
+        __syncthreads();
+        const float wc = a.selw[(size_t)t * a.k + c];
+#pragma unroll
+        for (int j = 0; j < 8; j++) {
+            const int i = threadIdx.x + 256 * j;
+            if (i >= a.D) break;
+            float s = 0.f;
+            for (int q = 0; q < a.r; q++) s = fmaf(z[q], bf(Dn[(size_t)q * a.D + i]), s);
+            acc[j] = fmaf(wc, s, acc[j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int i = threadIdx.x + 256 * j;
+        if (i < a.D) a.y[(size_t)t * a.D + i] = acc[j];
+    }
+}
+// x[t][i] += y[t][i]
+__global__ void k_add_rows(float* x, const float* y, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    grid_dep_launch();
+    grid_dep_wait();
+    if (i < n) x[i] += y[i];
 }
 
 __global__ void k_fill_i32(int* p, int v, int n) {

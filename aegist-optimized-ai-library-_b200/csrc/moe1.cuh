@@ -101,7 +101,7 @@ __device__ __forceinline__ void router_topk_lanes(const float* __restrict__ logi
 // top-k of every sequence's router logits, one warp per sequence (batched decode, after the logits came from a
 // matrix product). grid (ceil(B / 8)), 256 threads.
 __global__ void __launch_bounds__(256) k_router_topk(const float* __restrict__ logits, int stride, int E, int topk, int* __restrict__ top_idx,
-                                                     float* __restrict__ top_w, int B) {
+                                                     float* __restrict__ top_w, int B, const CoreRoute core) {
     const int lane = threadIdx.x & 31, b = blockIdx.x * 8 + (threadIdx.x >> 5);
     grid_dep_launch();
     grid_dep_wait();
@@ -110,6 +110,7 @@ __global__ void __launch_bounds__(256) k_router_topk(const float* __restrict__ l
     float w;
     router_topk_lanes(logits + (size_t)b * stride, E, topk, lane, e, w);
     if (lane < topk) { top_idx[(size_t)b * topk + lane] = e; top_w[(size_t)b * topk + lane] = w; }
+    if (core.score) core_route_warp(core, b, lane);       // the core engine's picks of the same token
 }
 
 struct Gu1Args {
@@ -128,6 +129,7 @@ struct Gu1Args {
     float* asc;                   // [B * topk][I / 32] out: scale of each 32-value group of act
     float* asum;                  // [B * topk][I / 32] out: sum of each 32-value group of act
     int* err;
+    CoreRoute core;               // the core engine's picks: one otherwise idle warp of every token's first block makes them
 };
 
 // dynamic shared memory: rows | scales | digit planes of x | group sums of x
@@ -231,6 +233,8 @@ __global__ void __launch_bounds__(M1_GU_THREADS) k_moe_gu1(const Gu1Args a) {
             a.top_ptr[(size_t)b * a.topk + threadIdx.x] = (ex >= 0 && ex < a.E) ? s_eptr[ex] : nullptr;
         }
         trace_pt(a.trace, 2);
+    } else if (warp == 16) {
+        if (blockIdx.x == 0 && a.core.score) core_route_warp(a.core, b, lane);
     } else if (warp < 16) {
         // norm2(x) -> digit planes and group sums; D / 8 chunks over 256 threads
         const int xt = threadIdx.x - 256;

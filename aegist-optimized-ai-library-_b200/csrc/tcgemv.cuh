@@ -452,6 +452,7 @@ __global__ void __launch_bounds__((W + TC_EPI) * 32, 1) k_tcgemv(const GemvArgs 
         if (a.finisher == FIN_TOPK) {
             router_topk_warp(a.seg[0].out + (size_t)b * a.seg[0].out_stride, a.E, a.topk, a.top_idx + (size_t)b * a.topk,
                              a.top_w + (size_t)b * a.topk, lane);
+            if (a.core.score) core_route_warp(a.core, b, lane);
         } else {
             float v = -INFINITY;
             int ix = 0x7fffffff;

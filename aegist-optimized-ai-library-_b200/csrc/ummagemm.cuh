@@ -60,12 +60,12 @@ struct UmmaSeg {
 };
 
 struct UmmaArgs {
-    CUtensorMap wmap[4];     // weights of each segment as a [rows][K bytes] tensor, box 128 bytes x 64 rows
-    CUtensorMap wmap2[4];    // SEG_I8_GATEUP: the up matrix
+    CUtensorMap wmap[GEMV_MAX_SEG];     // weights of each segment as a [rows][K bytes] tensor, box 128 bytes x 64 rows
+    CUtensorMap wmap2[GEMV_MAX_SEG];    // SEG_I8_GATEUP: the up matrix
     CUtensorMap xmap_i8;     // int8 planes [passes * 3 * 64][K], box 128 bytes x tt rows (one box per plane)
     CUtensorMap xmap_bf;     // bf16 planes [passes * 3 * 64][2 K bytes], box 128 bytes x tt rows
     unsigned long long* trace;
-    UmmaSeg seg[4];
+    UmmaSeg seg[GEMV_MAX_SEG];
     int nseg, total_units;   // total_units = sum of seg units
     int K, T, passes;        // passes = ceil(T / 64)
     int tt;                  // tokens per unit of work: 64, 32 or 16 (the planes' tensor maps have boxes of `tt` rows)

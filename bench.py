@@ -226,7 +226,7 @@ def run_reference(args):
             "config": workload_config(cfg), "cpu_baseline": cb,
             "e2e": {"value": cb["value"], "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
             "wall_s": time.perf_counter() - t0}
-    print(json.dumps(line), flush=True)
+    print(json.dumps(line, default=lambda o: o.item() if hasattr(o, 'item') else str(o)), flush=True)
 
 
 def workload_config(cfg):
@@ -386,7 +386,7 @@ def run_b64(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     line = b64_measure(pkg, args.steps, max(args.warmup, 3), world, rank, local, dist)
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line, default=lambda o: o.item() if hasattr(o, 'item') else str(o)), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
@@ -505,7 +505,7 @@ def run_ours(args):
     achieved = dom["bytes"] / (dom_us * 1e-6) / 1e9
     step_gbs = bytes_step / (ms / K * 1e-3) / 1e9
     roles_sum_ms = sum(v["us_per_step"] for v in in_graph.values()) / 1e3
-    consistent = abs(roles_sum_ms - ms / K) <= 0.10 * (ms / K)
+    consistent = bool(abs(roles_sum_ms - ms / K) <= 0.10 * (ms / K))
     if not consistent:
         print(f"warning: the roles' in-graph times sum to {roles_sum_ms:.3f} ms, the timed step is {ms / K:.3f} ms", file=sys.stderr)
     roof = {"bound": "hbm", "kernel": f"{name} ({E.HybridEngine.KERNELS_SMALL_BATCH[name]})", "achieved": achieved, "peak": peak,
@@ -546,7 +546,7 @@ def run_ours(args):
                           "prefill": "prompt fed through the engine's feed(), untimed"}}
         if world > 1:
             line["config"]["parallelism"] = f"{world} independent replicas (batch-1 decode does not shard)"
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line, default=lambda o: o.item() if hasattr(o, 'item') else str(o)), flush=True)
     if world > 1:
         dist.destroy_process_group()
 

@@ -110,7 +110,9 @@ int b2_set_taps(b2_engine* e, const int* layers, int n);
 int b2_taps(b2_engine* e, float* out);
 
 /* Lm::core_counts / reset_counts (hybrid.rs:1095-1101): per-layer switch-on counts of the core
- * engine, i32[layers][n_cores]. */
+ * engine, i32[layers][n_cores]. The engine runs the reference's core engine in every layer of every token
+ * (cores_apply, kernels/aegist.cu:283-350): product-key routing over the two key tables, one count per pick, and the
+ * output of the picks whose core is live (stored in the brain file or a cores file laid over it). */
 int b2_core_counts(b2_engine* e, int32_t* out);
 int b2_reset_counts(b2_engine* e);
 

@@ -316,9 +316,9 @@ class HybridOracle:
         self.last_route = {}      # layer -> (idx [N,k], weights [N,k]) of the latest forward
         self.last_hidden = {}     # layer -> x after that layer, last position [B, D]
         self.router_bias = {}     # layer -> [E] added to the router output (expert-popularity shaping)
-        for i in range(c["n_layers"]):
-            if brain.has(f"blocks.{i}.cores.ids") and brain.raw(f"blocks.{i}.cores.ids").size:
-                raise NotImplementedError("live switchable cores are outside this oracle (a fresh brain has none)")
+        n_cores = int(c["core_grid"][0]) * int(c["core_grid"][1])
+        self.core_counts = np.zeros((c["n_layers"], n_cores), dtype=np.int64)   # switch-ons per core (HybridLM.core_usage)
+        self.last_cores = {}      # layer -> (ids [N,k], weights [N,k]) of the latest forward
 
     # int8 linear: y = x @ (q * scale)^T, the product q * scale rounded to fp32 first (model.py:92-93)
     def qlinear(self, x, prefix):
@@ -436,6 +436,48 @@ class HybridOracle:
         sg = sigmoid((hf @ self.b.f32(p + "shared_gate.weight").T).astype(F32))
         return (out + sg * sh).astype(F32)
 
+    # CoreEngine.forward (aegist/model.py:214-224): product-key routing. Two score tables of n1 and n2 entries address
+    # n1 * n2 cores; the k best of each, their k1 * k2 sums, the k best sums (ties to the earlier candidate), softmax.
+    def core_route(self, i, hf):
+        c, p = self.cfg, f"blocks.{i}.engine."
+        n1, n2 = int(c["core_grid"][0]), int(c["core_grid"][1])
+        k = int(c["cores_active"])
+        s1 = (hf @ self.b.f32(p + "key1.weight").T).astype(F32)
+        s2 = (hf @ self.b.f32(p + "key2.weight").T).astype(F32)
+        k1, k2 = min(k, n1), min(k, n2)
+        i1 = np.argsort(-s1, -1, kind="stable")[:, :k1]
+        i2 = np.argsort(-s2, -1, kind="stable")[:, :k2]
+        v1, v2 = np.take_along_axis(s1, i1, -1), np.take_along_axis(s2, i2, -1)
+        cand = (v1[:, :, None] + v2[:, None, :]).astype(F32).reshape(len(hf), -1)
+        ids = (i1[:, :, None] * n2 + i2[:, None, :]).reshape(len(hf), -1)
+        pos = np.argsort(-cand, -1, kind="stable")[:, :k]
+        top = np.take_along_axis(cand, pos, -1)
+        e = np.exp(top - top[:, :1], dtype=F32)
+        return np.take_along_axis(ids, pos, -1).astype(np.int32), (e / e.sum(-1, keepdims=True, dtype=F32)).astype(F32)
+
+    # SparseCoreBank.forward (aegist/hybrid.py:745-771) and the tally of HybridBlock.forward (:830-840): every pick is
+    # counted; a pick whose core is live adds w * (silu(x g) * (x u)) d, any other adds nothing
+    def cores(self, i, hf):
+        ids, w = self.core_route(i, hf)
+        self.last_cores[i] = (ids, w)
+        np.add.at(self.core_counts[i], ids.reshape(-1), 1)
+        out = np.zeros_like(hf)
+        p = f"blocks.{i}.cores."
+        if not self.b.has(p + "ids"):
+            return out
+        live = {int(cid): j for j, cid in enumerate(np.asarray(self.b.raw(p + "ids")).reshape(-1).tolist())}
+        if not live:
+            return out
+        G, U, Dn = self.b.f32(p + "gate"), self.b.f32(p + "up"), self.b.f32(p + "down")
+        for t in range(len(hf)):
+            for r in range(ids.shape[1]):
+                j = live.get(int(ids[t, r]))
+                if j is None:
+                    continue
+                z = (silu((hf[t] @ G[j]).astype(F32)) * (hf[t] @ U[j]).astype(F32)).astype(F32)
+                out[t] += (z @ Dn[j]).astype(F32) * w[t, r]
+        return out
+
     # aegist/hybrid.py:812-843 and 896-924
     def forward(self, ids, cache):
         c = self.cfg
@@ -454,7 +496,11 @@ class HybridOracle:
                 y = self.deltanet(i, h, cache)
             x = (x + y).astype(F32)
             h = znorm(x, self.b.f32(f"blocks.{i}.norm2.weight"), self.eps)
-            x = (x + self.moe(i, h.reshape(-1, c["d_model"])).reshape(B, T, -1)).astype(F32)
+            hf = h.reshape(-1, c["d_model"])
+            out = self.moe(i, hf)
+            if self.b.has(f"blocks.{i}.engine.key1.weight"):
+                out = (out + self.cores(i, hf)).astype(F32)
+            x = (x + out.reshape(B, T, -1)).astype(F32)
             self.last_hidden[i] = x[:, -1].copy()
         cache.length += T
         hN = znorm(x[:, -1], self.b.f32("norm.weight"), self.eps)

@@ -15,6 +15,8 @@ Outputs:
   tiny_golden.npz     the 4-layer hidden-512 vocab-32768 case: group hashes of the file the
                       reference wrote, router picks, greedy tokens and logits samples
   ops_golden.npz      per-op cases: quantisers, MoE layer, delta rule (step and chunked), RoPE
+  micro_cores.nx      the micro brain with a few live switchable cores (`--only cores` writes just this pair)
+  cores_golden.npz    logits, core picks and weights, per-core switch-on counts of the reference on that brain
 """
 import hashlib
 import os
@@ -196,6 +198,60 @@ def micro_cases(path, out):
     ref.nx.close()
 
 
+def cores_case(path, out):
+    """The micro brain with live switchable cores: a dry run finds which cores the engine picks on the test tokens, some
+    of those (and two that are never picked) are made live by the reference's own `make_live` and given seeded gate / up /
+    down weights, the reference writes and reloads the file, and its logits, picks, weights and switch-on counts are kept."""
+    reference_brain(OurConfig.micro(), 0, path, vary_1d=True)
+    model, _, nx = NX.load_model(path, device="cpu", slots=4096)
+    model.float().eval()
+    V = model.cfg.vocab_size
+    g = torch.Generator().manual_seed(7)
+    ids = torch.randint(0, V, (20,), generator=g).tolist()
+    with torch.no_grad():
+        model(torch.tensor([ids]), cache=model.new_cache(1, 64, dtype=torch.float32), last_only=True)
+    live = {}
+    for li in (0, 2, 3):
+        picked = model.blocks[li].last_core_ids.reshape(-1).tolist()
+        seen = list(dict.fromkeys(picked))[:4]
+        never = [c for c in range(model.cfg.n_cores) if c not in picked][:2]
+        live[li] = seen + never
+    nx.close()
+    # rebuild (the loaded model pages its experts from the file), make the cores live, give them weights, write again
+    cfg = H.HybridConfig.from_dict(OurConfig.micro().to_dict())
+    tmp = path + ".base"
+    os.replace(path, tmp)
+    model, _, nx = NX.load_model(tmp, device="cpu", slots=4096)
+    for li, cores in live.items():
+        bank = model.blocks[li].cores
+        bank.make_live(cores)
+        with torch.no_grad():
+            for name in ("gate", "up", "down"):
+                p = getattr(bank, name)
+                p.copy_(B.normal(f"blocks.{li}.cores.{name}", p.shape, 5, "cpu", 0.08 if name == "down" else cfg.d_model ** -0.5).to(p.dtype))
+    NX.save_model(path, model, tokenizer_json())
+    nx.close()
+    os.remove(tmp)
+    ref = Ref(path)
+    spy = {}
+    for i, b in enumerate(ref.model.blocks):
+        def hook(m, a, out, i=i):
+            spy[i] = (out[0].detach().clone(), out[1].detach().float().clone())
+        b.engine.register_forward_hook(hook)
+    cache = ref.cache(1, 64)
+    rows, cids, cw = [], [], []
+    lg, _, _ = ref.feed([ids[:8]], cache)                       # a prompt in one piece, then single tokens
+    rows.append(lg[0]); cids.append(np.stack([spy[i][0][-1].numpy() for i in range(4)])); cw.append(np.stack([spy[i][1][-1].numpy() for i in range(4)]))
+    for t in ids[8:]:
+        lg, _, _ = ref.feed([[t]], cache)
+        rows.append(lg[0]); cids.append(np.stack([spy[i][0][-1].numpy() for i in range(4)])); cw.append(np.stack([spy[i][1][-1].numpy() for i in range(4)]))
+    usage = ref.model.core_usage().numpy()
+    np.savez_compressed(out, ids=np.array(ids, dtype=np.int32), logits=np.stack(rows), core_ids=np.stack(cids).astype(np.int32),
+                        core_w=np.stack(cw), counts=usage.astype(np.int64),
+                        live=np.array([[li] + c for li, c in live.items()], dtype=np.int32))
+    ref.nx.close()
+
+
 def tiny_case(out):
     ours = OurConfig.tiny()
     with tempfile.TemporaryDirectory() as d:
@@ -302,6 +358,12 @@ def op_cases(micro_path, out):
 
 if __name__ == "__main__":
     torch.set_num_threads(8)
+    if sys.argv[2:4] == ["--only", "cores"]:
+        cores_case(os.path.join(HERE, "micro_cores.nx"), os.path.join(HERE, "cores_golden.npz"))
+        for f in ("micro_cores.nx", "cores_golden.npz"):
+            p = os.path.join(HERE, f)
+            print(f, os.path.getsize(p), hashlib.sha256(open(p, "rb").read()).hexdigest()[:16])
+        raise SystemExit(0)
     micro = os.path.join(HERE, "micro.nx")
     reference_brain(OurConfig.micro(), 0, micro, vary_1d=True)
     micro_cases(micro, os.path.join(HERE, "micro_golden.npz"))

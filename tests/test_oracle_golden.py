@@ -168,3 +168,23 @@ def test_sampler_known_answers():
     assert picks == {1, 2}                                        # top-k 2 never leaves the two largest
     counts = np.bincount([O.sample(logits, 0.7, 0.95, 20, O.Rng(s)) for s in range(2000)], minlength=5)
     assert counts[1] > counts[4] > counts[0] and counts[3] < 30
+
+
+def test_core_engine_and_live_cores_against_the_reference(golden_dir):
+    """The oracle's core engine (product-key routing, switch-on counts) and live cores on the brain the reference wrote
+    with live cores: logits, picks, weights and counts of the unmodified reference."""
+    g = np.load(os.path.join(golden_dir, "cores_golden.npz"))
+    m = O.HybridOracle(O.Brain(os.path.join(golden_dir, "micro_cores.nx")))
+    cache = m.new_cache(1, 64)
+    ids = g["ids"].tolist()
+    rows = [m.forward(np.asarray([ids[:8]]), cache)[0]]
+    cid = [np.stack([m.last_cores[i][0][-1] for i in range(4)])]
+    cw = [np.stack([m.last_cores[i][1][-1] for i in range(4)])]
+    for t in ids[8:]:
+        rows.append(m.forward(np.asarray([[t]]), cache)[0])
+        cid.append(np.stack([m.last_cores[i][0][-1] for i in range(4)]))
+        cw.append(np.stack([m.last_cores[i][1][-1] for i in range(4)]))
+    assert np.abs(np.stack(rows) - g["logits"]).max() < 2e-5
+    assert np.array_equal(np.stack(cid), g["core_ids"])
+    assert np.abs(np.stack(cw) - g["core_w"]).max() < 1e-5
+    assert np.array_equal(m.core_counts, g["counts"])
