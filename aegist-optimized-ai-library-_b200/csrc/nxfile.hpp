@@ -59,7 +59,10 @@ public:
         top->fd_ = fd_; top->map_ = map_; top->size_ = size_;
         fd_ = -1; map_ = nullptr; size_ = 0;
         const std::string base_path = bp->str;
+        const JValue top_base = *base;          // `base` points into the header that is about to be replaced
+        base = &top_base;
         tensors.clear();
+        header = JValue();
         if (!open_one(base_path, err)) { err = p + " is learned cores over " + base_path + ": " + err; delete top; return false; }
         const JValue* nested = header.get("base");
         if (nested && nested->type == JValue::Obj) { err = p + ": its base " + base_path + " is itself a cores file"; delete top; return false; }
@@ -163,8 +166,9 @@ public:
             it->second.update(data(t), t.nbytes);
         }
         std::map<std::string, bool> ok;
-        const JValue* want = header.get("sha256");
         for (auto& kv : h) {
+            // the cores of a cores file are hashed in that file's header, everything else in the base's
+            const JValue* want = (over_ && kv.first == "cores") ? over_->header.get("sha256") : header.get("sha256");
             const JValue* w = want ? want->get(kv.first) : nullptr;
             ok[kv.first] = w && w->type == JValue::Str && w->str == kv.second.hex();
         }

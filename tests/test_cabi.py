@@ -45,3 +45,21 @@ def test_sampler_and_verify_need_no_gpu(E, micro_path):
     for s in range(20):
         assert E.sample(logits, 0.9, 0.9, 10, E.Rng(s)) == O.sample(logits, 0.9, 0.9, 10, O.Rng(s))
     assert E.verify_file(micro_path) == {"base": True, "engine": True, "cores": True}
+
+
+def test_cores_file_is_read_over_its_base(E, pkg, micro_path, golden_dir, tmp_path):
+    """The .nx reader opens a cores file (aegist_rs/src/nx.rs:82-110) as its base with the cores laid over it, checks every
+    group's hash where it is recorded, and refuses a changed base or a cores file over a cores file. No GPU needed."""
+    from conftest import cores_file
+    src = os.path.join(golden_dir, "micro_cores.nx")
+    over = str(tmp_path / "learned.nx")
+    cores_file(pkg, micro_path, src, over)
+    assert E.verify_file(over) == {"base": True, "engine": True, "cores": True}
+    stale = str(tmp_path / "stale.nx")
+    cores_file(pkg, micro_path, src, stale, base_sha="0" * 64)
+    with pytest.raises(E.EngineError, match="learned on a different"):
+        E.verify_file(stale)
+    nested = str(tmp_path / "nested.nx")
+    cores_file(pkg, over, src, nested)
+    with pytest.raises(E.EngineError, match="itself a cores file"):
+        E.verify_file(nested)

@@ -7,6 +7,7 @@ import os
 import numpy as np
 import pytest
 
+from conftest import cores_file
 from oracle import hybrid_oracle as O
 
 pytestmark = pytest.mark.gpu
@@ -87,3 +88,28 @@ def test_prompt_chunk_with_live_cores(E, cores):
     assert np.abs(got - want).max() < TOL
     assert np.array_equal(e.core_counts(4, 512), model.core_counts)
     e.close()
+
+
+def test_cores_file_over_its_base(E, pkg, cores, micro_path, tmp_path):
+    """Opening a cores file opens its base with the cores laid over it: the fresh micro brain + the live cores of the
+    fixture = the reference's logits for the brain that stores both; a base whose weights changed is refused, and so
+    is a cores file that carries anything but cores."""
+    path, g = cores
+    over = str(tmp_path / "learned.nx")
+    cores_file(pkg, micro_path, path, over)
+    e = E.HybridEngine.load(over, max_context=64)
+    assert "18 live cores" in e.describe()
+    ids = g["ids"].tolist()
+    rows = [e.feed(ids[:8])] + [e.feed([t]) for t in ids[8:]]
+    assert np.abs(np.stack(rows) - g["logits"]).max() < TOL
+    key_over, key_plain = e.state_key(), E.HybridEngine.load(micro_path, max_context=8).state_key()
+    assert key_over != key_plain                         # a context computed with the cores is kept apart from one without
+    e.close()
+    bad = str(tmp_path / "stale.nx")
+    cores_file(pkg, micro_path, path, bad, base_sha="0" * 64)
+    with pytest.raises(E.EngineError, match="learned on a different"):
+        E.HybridEngine.load(bad)
+    nested = str(tmp_path / "nested.nx")
+    cores_file(pkg, over, path, nested)
+    with pytest.raises(E.EngineError, match="itself a cores file"):
+        E.HybridEngine.load(nested)
