@@ -10,7 +10,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200moe.so")
 CLI = os.path.join(HERE, "b2-debug-logits")        # the reference's `aegist debug-logits` over the C ABI
 SOURCES = ["engine.cu"]
-HEADERS = ["kernels.cuh", "rowgemv.cuh", "mmagemm.cuh", "mmaexperts.cuh", "digits.cuh", "attnmma.cuh", "tcgemv.cuh", "moe1.cuh", "ops.cuh", "noalloc.cuh", "sampler.hpp", "nxfile.hpp", "json.hpp", "sha256.hpp", "../../include/b200moe.h"]
+HEADERS = sorted(f for f in os.listdir(CSRC) if f.endswith((".cuh", ".hpp"))) + ["../../include/b200moe.h"]
 
 
 def nvcc() -> str:

@@ -163,6 +163,7 @@ struct b2_engine {
     int *g_list = nullptr, *g_chunk = nullptr;
     __half* acth = nullptr;
     float *xsum_tok = nullptr, *xsum_act = nullptr;
+    int8_t* sq = nullptr; float *sq_scale = nullptr, *sq_sum = nullptr;   // planes of the sorted picks (k_umma_q4)
     int cap_small = 0, cap_big = 0;
     const uint8_t** top_ptr = nullptr;       // [B][TOPK] expert blobs of the current layer's picks (k_moe_gu1 -> k_moe_down1)
     int8_t* actq = nullptr;                  // [B * TOPK][4][I] digit planes of act
@@ -214,6 +215,7 @@ struct b2_engine {
         int8_t* uq_i = nullptr; uint16_t* uq_b = nullptr; float* uq_scale = nullptr; int uq_passes = 0;
         int *g_list = nullptr, *g_chunk = nullptr;
         float *xsum_tok = nullptr, *xsum_act = nullptr;
+        int8_t* sq = nullptr; float *sq_scale = nullptr, *sq_sum = nullptr;
         int cap_small = 0, cap_big = 0, nsplit = 1, attn_tiles = 1;
         int* csel = nullptr; float *cselw = nullptr, *cscore = nullptr, *core_y = nullptr;
     } pc;
@@ -269,11 +271,11 @@ b2_engine::~b2_engine() {
     for (auto& l : layers) { cudaFree((void*)l.eptr); cudaFree(l.router_bias); cudaFree(l.live); }
     void* bufs[] = {conv, state, snap_conv[0], snap_conv[1], snap_state[0], snap_state[1], kpool, vpool, page_table, rope_cos,
                     rope_sin, d_tok, d_next, d_pos, d_err, d_counter, d_acounter, x, big, zbuf, kraw, vraw, beta, gdec, obuf, att,
-                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh, g_list, g_chunk, acth, xsum_tok, xsum_act, d_trace, (void*)top_ptr, actq, asc, asum, uq_i, uq_b, uq_scale, d_counts, csel, cselw, cscore, core_y};
+                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh, g_list, g_chunk, acth, xsum_tok, xsum_act, sq, sq_scale, sq_sum, d_trace, (void*)top_ptr, actq, asc, asum, uq_i, uq_b, uq_scale, d_counts, csel, cselw, cscore, core_y};
     for (void* p : bufs) cudaFree(p);
     void* cb[] = {pc.tok, pc.vpos, pc.x, pc.big, pc.zbuf, pc.kraw, pc.vraw, pc.beta, pc.gdec, pc.obuf, pc.att, pc.rlogits, pc.sh_act, pc.sgate,
                   pc.act, pc.top_idx, pc.top_w, pc.ypart, pc.attn_part, pc.dcounter, pc.counter, pc.xh, pc.acth, pc.uq_i, pc.uq_b, pc.uq_scale,
-                  pc.g_list, pc.g_chunk, pc.xsum_tok, pc.xsum_act, pc.csel, pc.cselw, pc.cscore, pc.core_y};
+                  pc.g_list, pc.g_chunk, pc.xsum_tok, pc.xsum_act, pc.sq, pc.sq_scale, pc.sq_sum, pc.csel, pc.cselw, pc.cscore, pc.core_y};
     for (void* p : cb) cudaFree(p);
     if (h_pin) cudaFreeHost(h_pin);
     if (ev0) cudaEventDestroy(ev0);
@@ -562,6 +564,7 @@ int b2_engine::finish() {
         CU(dalloc((uint16_t**)&acth, P * 2 * c.I));
         CU(dalloc(&xsum_tok, Bg * (c.D / 64)));
         CU(dalloc(&xsum_act, P * std::max(1, c.I / 64)));
+        CU(dalloc(&sq, (size_t)UM_PI * P * std::max(c.D, c.I))); CU(dalloc(&sq_scale, P)); CU(dalloc(&sq_sum, P * (size_t)(std::max(c.D, c.I) / 64 + 1)));
     }
     CU(dalloc(&ypart, Bg * (c.TOPK + 1) * c.D));
     CU(dalloc(&d_dcounter, Bg * down_row_blocks(c.D)));
@@ -898,6 +901,9 @@ static void launch_experts(const ExpertArgs& a, int B, int nsm, cudaStream_t st,
 struct ExpertMmaCtx {
     int* list; int* chunk; int cap_small, cap_big;
     __half* xh; __half* acth; float* xsum_tok; float* xsum_act;
+    // the tcgen05 kernel's operands: planes of the sorted picks, and where this GPU's expert blobs lie
+    int8_t* sq; float* sq_scale; float* sq_sum; int slots;
+    const uint8_t* experts; size_t expert_bytes; int per, e0;
 };
 static void chunk_tables(const ExpertMmaCtx& m, ChunkTable& small, ChunkTable& big) {
     int* p = m.chunk;
@@ -920,6 +926,46 @@ static cudaError_t launch_q4(Q4Args q, const ChunkTable& small, const ChunkTable
     q.chunks = big;
     return launch_k(k_mma_q4<4>, dim3(row_blocks, gb), dim3(Q4_THREADS), sm4, st, q);
 }
+// One matrix of the experts (gate/up pairs, or down) on k_umma_q4: planes of the sorted picks, then the grouped GEMM.
+static bool umma_q4_fits(const ExpertArgs& a, const ExpertMmaCtx& m, int P) {
+    auto ok = [&](int K, size_t off_q, size_t off_s, size_t off_m) {
+        return K % UQ_KB == 0 && K <= 64 * UQ_MAXG && (((uintptr_t)m.experts + off_q) & 15) == 0 && (off_s | off_m) % 8 == 0;
+    };
+    return tensor_map_encoder() && m.sq && m.experts && P <= m.slots && m.expert_bytes % 16 == 0 &&
+           ok(a.D, 0, a.off_gu_s, a.off_gu_m) && ok(a.I, a.off_dn_q, a.off_dn_s, a.off_dn_m);
+}
+// false: a tensor map could not be made, nothing was launched.
+static bool launch_umma_q4(const ExpertArgs& a, const ExpertMmaCtx& m, const GroupArgs& g, bool pair, int P, int nsm, cudaStream_t st, cudaError_t* err) {
+    auto enc = tensor_map_encoder();
+    const int K = pair ? a.D : a.I, rows = pair ? a.I : a.D;
+    const size_t off_q = pair ? 0 : a.off_dn_q;
+    const uint8_t* base = m.experts + off_q;
+    UmmaQ4Args u{};
+    {
+        const cuuint64_t dims[3] = {(cuuint64_t)K / 2, (cuuint64_t)(pair ? 2 * a.I : a.D), (cuuint64_t)m.per};
+        const cuuint64_t strides[2] = {(cuuint64_t)K / 2, (cuuint64_t)m.expert_bytes};
+        const cuuint32_t box[3] = {UQ_KB / 2, 64, 1};
+        const cuuint32_t es[3] = {1, 1, 1};
+        if (enc(&u.wmap, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<uint8_t*>(base), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) return false;
+    }
+    if (!byte_matrix_map(&u.xmap, m.sq, (uint64_t)(K / UM_BK) * m.slots * UM_PI, UM_BK, UQ_NCOL)) return false;
+    float* const xsum = m.sq_sum;                            // [slots][K / 64]
+    PrepSlotsArgs p{};
+    p.src = pair ? a.x : a.act; p.stride = pair ? a.x_stride : a.I; p.by_pick = pair ? 0 : 1; p.topk = a.topk;
+    p.norm_w = pair ? a.norm_w : nullptr; p.eps = a.eps; p.K = K; p.P = P; p.list = g.list; p.qi = m.sq; p.slots = m.slots;
+    p.xscale = m.sq_scale; p.xsum = xsum;
+    if ((*err = launch_k(k_prep_q_slots, dim3(P), dim3(256), 0, st, p)) != cudaSuccess) return true;
+    u.eptr = a.eptr; u.list = g.list; u.small = g.small; u.big = g.big; u.topk = a.topk; u.pair = pair ? 1 : 0; u.rows = rows; u.K = K;
+    u.up_row0 = a.I; u.e0 = m.e0; u.rbu = std::max(1, 2048 / K);     // about 8 ring steps per unit
+    u.off_s = pair ? a.off_gu_s : a.off_dn_s; u.off_m = pair ? a.off_gu_m : a.off_dn_m;
+    u.slots = m.slots; u.xscale = m.sq_scale; u.xsum = xsum; u.out = pair ? a.act : a.ypart; u.err = a.err;
+    if ((*err = opt_in_smem(k_umma_q4, UQ_SMEM)) != cudaSuccess) return true;
+    *err = launch_k(k_umma_q4, dim3(nsm), dim3(UQ_THREADS), UQ_SMEM, st, u);
+    g_umma_launches++;
+    return true;
+}
+
 static cudaError_t launch_experts_mma(const ExpertArgs& a, int T, const ExpertMmaCtx& m, int nsm, cudaStream_t st, b2_engine* prof) {
     cudaError_t e;
     const int P = T * a.topk;
@@ -927,24 +973,40 @@ static cudaError_t launch_experts_mma(const ExpertArgs& a, int T, const ExpertMm
     g.top_idx = a.top_idx; g.idx_stride = a.idx_stride; g.T = T; g.topk = a.topk; g.E = a.E; g.eptr = a.eptr;
     g.list = m.list;
     chunk_tables(m, g.small, g.big);
+    const bool q4_umma = umma_q4_fits(a, m, P);               // else (K not a multiple of 256, no tensor-map encoder): k_mma_q4
+    g.big_n = q4_umma ? UQ_TT : 0;
     if ((e = launch_k(k_group_picks, dim3(1), dim3(1024), 0, st, g)) != cudaSuccess) return e;
-    PrepArgs p{};
-    p.x = a.x; p.x_stride = a.x_stride; p.norm_w = a.norm_w; p.eps = a.eps; p.K = a.D; p.T = T; p.Tpad = T; p.out = m.xh;
-    p.xsum = m.xsum_tok; p.perm8 = 1;
-    if ((e = launch_k(k_prep_x, dim3(T), dim3(256), 0, st, p)) != cudaSuccess) return e;
+    bool gu_done = false, dn_done = false;
+    if (q4_umma) {
+        gu_done = launch_umma_q4(a, m, g, true, P, nsm, st, &e);
+        if (gu_done && e != cudaSuccess) return e;
+    }
+    if (gu_done) {
+        if (prof) prof->mark(5, st);
+        dn_done = launch_umma_q4(a, m, g, false, P, nsm, st, &e);
+        if (dn_done && e != cudaSuccess) return e;
+    }
     Q4Args q{};
     q.eptr = a.eptr; q.list = g.list; q.topk = a.topk;
-    q.pair = 1; q.rows = a.I; q.K = a.D; q.off_q = 0; q.off_s = a.off_gu_s; q.off_m = a.off_gu_m; q.up_row0 = a.I;
-    q.xh = m.xh; q.xsum = m.xsum_tok; q.by_pick = 0; q.out = a.act; q.row_tiles = 1;
-    if ((e = launch_q4(q, g.small, g.big, (a.I + 31) / 32, nsm, st)) != cudaSuccess) return e;
-    if (prof) prof->mark(5, st);
-    PrepArgs p2{};
-    p2.x = a.act; p2.x_stride = a.I; p2.K = a.I; p2.T = P; p2.Tpad = P; p2.out = m.acth; p2.xsum = m.xsum_act; p2.perm8 = 1;
-    if ((e = launch_k(k_prep_x, dim3(P), dim3(256), 0, st, p2)) != cudaSuccess) return e;
-    q.pair = 0; q.rows = a.D; q.K = a.I; q.off_q = a.off_dn_q; q.off_s = a.off_dn_s; q.off_m = a.off_dn_m; q.up_row0 = 0;
-    q.xh = m.acth; q.xsum = m.xsum_act; q.by_pick = 1; q.out = a.ypart;
-    q.row_tiles = std::max(1, std::min(4, 2048 / a.I));      // keep about 8 ring steps per block
-    if ((e = launch_q4(q, g.small, g.big, (a.D + Q4_ROWS * q.row_tiles - 1) / (Q4_ROWS * q.row_tiles), nsm, st)) != cudaSuccess) return e;
+    if (!gu_done) {
+        PrepArgs p{};
+        p.x = a.x; p.x_stride = a.x_stride; p.norm_w = a.norm_w; p.eps = a.eps; p.K = a.D; p.T = T; p.Tpad = T; p.out = m.xh;
+        p.xsum = m.xsum_tok; p.perm8 = 1;
+        if ((e = launch_k(k_prep_x, dim3(T), dim3(256), 0, st, p)) != cudaSuccess) return e;
+        q.pair = 1; q.rows = a.I; q.K = a.D; q.off_q = 0; q.off_s = a.off_gu_s; q.off_m = a.off_gu_m; q.up_row0 = a.I;
+        q.xh = m.xh; q.xsum = m.xsum_tok; q.by_pick = 0; q.out = a.act; q.row_tiles = 1;
+        if ((e = launch_q4(q, g.small, g.big, (a.I + 31) / 32, nsm, st)) != cudaSuccess) return e;
+        if (prof) prof->mark(5, st);
+    }
+    if (!dn_done) {
+        PrepArgs p2{};
+        p2.x = a.act; p2.x_stride = a.I; p2.K = a.I; p2.T = P; p2.Tpad = P; p2.out = m.acth; p2.xsum = m.xsum_act; p2.perm8 = 1;
+        if ((e = launch_k(k_prep_x, dim3(P), dim3(256), 0, st, p2)) != cudaSuccess) return e;
+        q.pair = 0; q.rows = a.D; q.K = a.I; q.off_q = a.off_dn_q; q.off_s = a.off_dn_s; q.off_m = a.off_dn_m; q.up_row0 = 0;
+        q.xh = m.acth; q.xsum = m.xsum_act; q.by_pick = 1; q.out = a.ypart;
+        q.row_tiles = std::max(1, std::min(4, 2048 / a.I));      // keep about 8 ring steps per block
+        if ((e = launch_q4(q, g.small, g.big, (a.D + Q4_ROWS * q.row_tiles - 1) / (Q4_ROWS * q.row_tiles), nsm, st)) != cudaSuccess) return e;
+    }
     // shared expert down for this GPU's own tokens: int8 [D][SH] on the dense tensor-core kernel
     PrepArgs p3{};
     p3.x = a.sh_act; p3.x_stride = a.SH; p3.K = a.SH; p3.T = a.nlocal; p3.Tpad = (a.nlocal + MM_TOK - 1) / MM_TOK * MM_TOK; p3.out = m.xh;
@@ -1206,7 +1268,9 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count, int chunk_T, bool chunk
             const int Tg = B * ep_world;
             const bool grouped = xh && Tg >= 16 && Tg * c.TOPK <= GQ_MAXP && c.D % MM_KC == 0 && c.I % MM_KC == 0 &&
                                  c.SH % MM_KC == 0 && c.D <= 2048 && c.I <= 2048 && c.E <= 256;
-            const ExpertMmaCtx mctx{g_list, g_chunk, cap_small, cap_big, xh, acth, xsum_tok, xsum_act};
+            const ExpertMmaCtx mctx{g_list, g_chunk, cap_small, cap_big, xh, acth, xsum_tok, xsum_act,
+                                    chunk ? pc.sq : sq, chunk ? pc.sq_scale : sq_scale, chunk ? pc.sq_sum : sq_sum, Tg * c.TOPK,
+                                    l.experts, c.expert_bytes(), c.E / ep_world, ep_rank * (c.E / ep_world)};
             if (ep_world == 1) {
                 x2.x = x; x2.x_stride = c.D; x2.top_idx = a.top_idx; x2.top_w = a.top_w; x2.idx_stride = c.TOPK;
                 x2.combine = 1; x2.local0 = 0; x2.nlocal = B;
@@ -1311,6 +1375,7 @@ int b2_engine::ensure_chunk_bufs() {
     CU(dalloc((uint16_t**)&pc.acth, P * 2 * c.I));
     CU(dalloc(&pc.xsum_tok, (size_t)W * (c.D / 64)));
     CU(dalloc(&pc.xsum_act, P * std::max(1, c.I / 64)));
+    CU(dalloc(&pc.sq, (size_t)UM_PI * P * std::max(c.D, c.I))); CU(dalloc(&pc.sq_scale, P)); CU(dalloc(&pc.sq_sum, P * (size_t)(std::max(c.D, c.I) / 64 + 1)));
     CU(dalloc(&pc.csel, (size_t)W * c.cores_active)); CU(dalloc(&pc.cselw, (size_t)W * c.cores_active));
     CU(dalloc(&pc.cscore, (size_t)W * (c.n1 + c.n2))); CU(dalloc(&pc.core_y, (size_t)W * c.D));
     pc.W = W;

@@ -1116,6 +1116,7 @@ __global__ void __launch_bounds__(THREADS) k_attn_merge(const AttnArgs a, int HD
 }  // namespace b2
 #include "attnmma.cuh"
 #include "ummagemm.cuh"
+#include "ummaq4.cuh"
 #include "prefill.cuh"
 namespace b2 {
 

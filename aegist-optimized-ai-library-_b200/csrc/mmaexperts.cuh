@@ -4,7 +4,7 @@
 //
 //   k_group_picks   counting sort of the step's picks by expert (the host code of
 //                   aegist_rs/src/hybrid.rs:875-900, on the device): per expert the list of its picks in
-//                   pick order, cut into chunks: runs of up to 32 picks go to the "big" table, a rest of
+//                   pick order, cut into chunks: runs of up to 32 picks (16 for k_umma_q4) go to the "big" table, a rest of
 //                   at most 8 picks to the "small" table (most experts of a step have only a few picks)
 //   k_mma_q4<NT>    for one chunk (one expert, <= 8 * NT of its picks) and a block of weight rows:
 //                   out = rows x picks, codes widened to fp16 (exact), activations as fp16 hi + lo,
@@ -40,6 +40,7 @@ struct GroupArgs {
     const uint8_t* const* eptr;   // only experts resident here are grouped
     int* list;                    // [P] pick ids (t * topk + r) sorted by expert, pick order inside an expert
     ChunkTable small, big;
+    int big_n;                    // picks per big chunk (0: GQ_BIG)
 };
 
 // one block of 1024 threads. The order of the picks inside an expert's list is whatever the shared-memory atomics
@@ -52,6 +53,7 @@ __global__ void __launch_bounds__(1024) k_group_picks(const GroupArgs a) {
     trace_in(a.trace, 11, gridDim.x);
     grid_dep_wait();
     const int P = a.T * a.topk;
+    const int BN = a.big_n > 0 ? a.big_n : GQ_BIG;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (threadIdx.x < 256) { s_cnt[threadIdx.x] = 0; s_fill[threadIdx.x] = 0; }
     __syncthreads();
@@ -68,8 +70,8 @@ __global__ void __launch_bounds__(1024) k_group_picks(const GroupArgs a) {
     if (threadIdx.x < 256) {
         const int e = threadIdx.x;
         cnt = e < a.E ? s_cnt[e] : 0;
-        nb = cnt > GQ_SMALL ? (cnt - GQ_SMALL + GQ_BIG - 1) / GQ_BIG : 0;
-        ns = (cnt - nb * GQ_BIG) > 0 ? 1 : 0;
+        nb = cnt > GQ_SMALL ? (cnt - GQ_SMALL + BN - 1) / BN : 0;
+        ns = (cnt - nb * BN) > 0 ? 1 : 0;
         x0 = cnt; x1 = nb; x2 = ns;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
@@ -87,7 +89,7 @@ __global__ void __launch_bounds__(1024) k_group_picks(const GroupArgs a) {
         s_off[e] = off;
         int s0 = 0, left = cnt;
         for (int k = 0; k < nb; k++) {
-            const int n = min(GQ_BIG, left);
+            const int n = min(BN, left);
             if (cb0 + k < a.big.cap) { a.big.expert[cb0 + k] = e; a.big.start[cb0 + k] = off + s0; a.big.n[cb0 + k] = n; }
             s0 += n; left -= n;
         }

@@ -124,9 +124,10 @@ def test_batched_decode_at_full_width(E, full4, batch):
     cfg, dev, model = full4
     before = E.load_library().b2_debug_umma_launches()
     e = E.HybridEngine.from_tensors(cfg.to_dict(), dev, max_context=64, device=0, batch=batch, kv_dtype=E.KV_F32)
-    # from 8 sequences on every GEMV group of the step graph is a tcgen05 GEMM: 3 per layer (mixer in, mixer out, MoE in) + the head
+    # from 8 sequences on every GEMV group of the step graph is a tcgen05 GEMM: 3 per layer (mixer in, mixer out, MoE in) + the head;
+    # from 16 on the 4-bit experts are two more per layer (gate/up, down)
     n_umma = E.load_library().b2_debug_umma_launches() - before
-    assert n_umma == (3 * cfg.n_layers + 1 if batch >= 8 else 0), n_umma
+    assert n_umma == ((5 if batch >= 16 else 3) * cfg.n_layers + 1 if batch >= 8 else 0), n_umma
     cache = model.new_cache(batch, 16)
     rng = np.random.default_rng(batch)
     tok = rng.integers(0, cfg.vocab_size, batch)
