@@ -201,64 +201,76 @@ struct CoreRoute {
     int* sel;                // [T][k]
     float* selw;             // [T][k]
 };
-// one warp per token; n1 <= 128, n2 <= 128, k <= 8
+// one warp per token; n1 <= 128, n2 <= 128, k <= 8. Everything stays in registers (lane r holds the r-th pick of a
+// table, lane c and c + 32 the candidates c): a local array here would give every kernel that calls this a stack frame.
 __device__ __forceinline__ void core_route_warp(const CoreRoute& cr, int t, int lane) {
     const float* s = cr.score + (size_t)t * (cr.n1 + cr.n2);
-    float v[2][8];
-    int ix[2][8];
-    const int kk[2] = {min(cr.k, cr.n1), min(cr.k, cr.n2)};
+    const int k0 = min(cr.k, cr.n1), k1 = min(cr.k, cr.n2);
+    float pv0 = 0.f, pv1 = 0.f;
+    int pi0 = 0, pi1 = 0;
 #pragma unroll
     for (int tab = 0; tab < 2; tab++) {
-        const int n = tab ? cr.n2 : cr.n1;
+        const int n = tab ? cr.n2 : cr.n1, kk = tab ? k1 : k0;
         const float* st = s + (tab ? cr.n1 : 0);
-        float mine[4];
-#pragma unroll
-        for (int j = 0; j < 4; j++) mine[j] = lane + 32 * j < n ? __ldcg(st + lane + 32 * j) : -INFINITY;
-        for (int r = 0; r < kk[tab]; r++) {
+        float m0 = lane < n ? __ldcg(st + lane) : -INFINITY, m1 = lane + 32 < n ? __ldcg(st + lane + 32) : -INFINITY;
+        float m2 = lane + 64 < n ? __ldcg(st + lane + 64) : -INFINITY, m3 = lane + 96 < n ? __ldcg(st + lane + 96) : -INFINITY;
+        for (int r = 0; r < kk; r++) {
             float bv = -INFINITY;
             int bi = 0x7fffffff;
-#pragma unroll
-            for (int j = 0; j < 4; j++)
-                if (lane + 32 * j < n && mine[j] > bv) { bv = mine[j]; bi = lane + 32 * j; }      // '>' keeps the lower index
+            if (lane < n && m0 > bv) { bv = m0; bi = lane; }                     // '>' keeps the lower index
+            if (lane + 32 < n && m1 > bv) { bv = m1; bi = lane + 32; }
+            if (lane + 64 < n && m2 > bv) { bv = m2; bi = lane + 64; }
+            if (lane + 96 < n && m3 > bv) { bv = m3; bi = lane + 96; }
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) {
                 const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
                 const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
                 if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
             }
-            v[tab][r] = bv; ix[tab][r] = bi;
+            if (lane == r) { if (tab) { pv1 = bv; pi1 = bi; } else { pv0 = bv; pi0 = bi; } }
             if ((bi & 31) == lane) {
-#pragma unroll
-                for (int j = 0; j < 4; j++) if (j == (bi >> 5)) mine[j] = -INFINITY;
+                const int j = bi >> 5;
+                if (j == 0) m0 = -INFINITY; else if (j == 1) m1 = -INFINITY; else if (j == 2) m2 = -INFINITY; else m3 = -INFINITY;
             }
         }
     }
-    if (lane == 0) {
-        // candidate order: first table's pick outermost (as the reference lists them); at most 64 candidates
-        float cv[64];
-        int ci[64], nc = 0;
-        for (int a = 0; a < kk[0]; a++)
-            for (int b = 0; b < kk[1]; b++) { cv[nc] = v[0][a] + v[1][b]; ci[nc++] = ix[0][a] * cr.n2 + ix[1][b]; }
-        float tv[8];
-        int ti[8];
-        const int k = min(cr.k, nc);
-        for (int j = 0; j < k; j++) {
-            int best = -1;
-            for (int i = 0; i < nc; i++) {
-                bool taken = false;
-                for (int p = 0; p < j; p++) taken |= ti[p] == i;
-                if (!taken && (best < 0 || cv[i] > cv[best])) best = i;
-            }
-            ti[j] = best; tv[j] = cv[best];
+    // candidate c = a k1 + b: the first table's pick a outermost (as the reference lists them); at most 64 candidates
+    const int nc = k0 * k1, k = min(cr.k, nc);
+    float c0, c1;
+    int core0, core1;
+    {
+        const int a0 = lane / k1, b0 = lane - a0 * k1, a1 = (lane + 32) / k1, b1 = (lane + 32) - a1 * k1;
+        const float va0 = __shfl_sync(0xffffffffu, pv0, a0 & 31), vb0 = __shfl_sync(0xffffffffu, pv1, b0 & 31);
+        const float va1 = __shfl_sync(0xffffffffu, pv0, a1 & 31), vb1 = __shfl_sync(0xffffffffu, pv1, b1 & 31);
+        const int ia0 = __shfl_sync(0xffffffffu, pi0, a0 & 31), ib0 = __shfl_sync(0xffffffffu, pi1, b0 & 31);
+        const int ia1 = __shfl_sync(0xffffffffu, pi0, a1 & 31), ib1 = __shfl_sync(0xffffffffu, pi1, b1 & 31);
+        c0 = lane < nc ? va0 + vb0 : -INFINITY; core0 = ia0 * cr.n2 + ib0;
+        c1 = lane + 32 < nc ? va1 + vb1 : -INFINITY; core1 = ia1 * cr.n2 + ib1;
+    }
+    float myv = 0.f;
+    int mycore = 0;
+    for (int j = 0; j < k; j++) {            // the j-th best sum goes to lane j; ties to the earlier candidate
+        float bv = c0;
+        int bc = lane;
+        if (c1 > bv) { bv = c1; bc = lane + 32; }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+            const int oc = __shfl_xor_sync(0xffffffffu, bc, o);
+            if (ov > bv || (ov == bv && oc < bc)) { bv = ov; bc = oc; }
         }
-        float sum = 0.f;
-        for (int j = 0; j < k; j++) sum += expf(tv[j] - tv[0]);
-        for (int j = 0; j < k; j++) {
-            const int core = ci[ti[j]];
-            cr.sel[(size_t)t * cr.k + j] = core;
-            cr.selw[(size_t)t * cr.k + j] = expf(tv[j] - tv[0]) / sum;
-            atomicAdd(cr.counts + core, 1);
-        }
+        const int core = __shfl_sync(0xffffffffu, (bc >> 5) ? core1 : core0, bc & 31);
+        if (lane == j) { myv = bv; mycore = core; }
+        if (lane == (bc & 31)) { if (bc >> 5) c1 = -INFINITY; else c0 = -INFINITY; }
+    }
+    const float top = __shfl_sync(0xffffffffu, myv, 0);
+    const float ex = lane < k ? expf(myv - top) : 0.f;
+    float sum = 0.f;
+    for (int j = 0; j < k; j++) sum += __shfl_sync(0xffffffffu, ex, j);        // summed in pick order, as one thread would
+    if (lane < k) {
+        cr.sel[(size_t)t * cr.k + lane] = mycore;
+        cr.selw[(size_t)t * cr.k + lane] = ex / sum;
+        atomicAdd(cr.counts + mycore, 1);
     }
 }
 
