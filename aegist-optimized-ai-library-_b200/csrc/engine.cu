@@ -564,7 +564,8 @@ int b2_engine::finish() {
         CU(dalloc((uint16_t**)&acth, P * 2 * c.I));
         CU(dalloc(&xsum_tok, Bg * (c.D / 64)));
         CU(dalloc(&xsum_act, P * std::max(1, c.I / 64)));
-        CU(dalloc(&sq, (size_t)UM_PI * P * std::max(c.D, c.I))); CU(dalloc(&sq_scale, P)); CU(dalloc(&sq_sum, P * (size_t)(std::max(c.D, c.I) / 64 + 1)));
+        CU(dalloc(&sq, (size_t)UM_PI * P * std::max(c.D, c.I)));
+        CU(dalloc(&sq_scale, P)); CU(dalloc(&sq_sum, P * (size_t)(std::max(c.D, c.I) / 64 + 1)));
     }
     CU(dalloc(&ypart, Bg * (c.TOPK + 1) * c.D));
     CU(dalloc(&d_dcounter, Bg * down_row_blocks(c.D)));

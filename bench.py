@@ -245,17 +245,24 @@ def run_profile_case(args):
     from b200moe import brain
     from b200moe import engine as E
     cfg = pkg.HybridConfig.full(n_layers=args.profile_case)
+    b64 = args.workload == "b64"             # the batched kernels: 64 sequences at context 8192, Zipf(1.1) expert popularity
+    batch, ctx = (64, B64_PROMPT) if b64 else (1, PROMPT)
     eng = E.HybridEngine.from_tensors(cfg.to_dict(), brain.random_brain(cfg, seed=0, device="cuda:0"),
-                                      max_context=PROMPT + 64, device=0, batch=1, kv_dtype=E.KV_BF16)
-    eng.seek(PROMPT)
-    toks, ms = eng.decode_greedy([1], max(args.warmup, 1))
-    toks, ms = eng.decode_greedy([toks[-1, 0]], args.steps)
-    print(json.dumps({"profile_case": True, "layers": args.profile_case, "steps": args.steps, "ms_per_step": ms / args.steps,
-                      "launches_per_step": eng.launches_per_step(), "note": "not a bench value"}), flush=True)
+                                      max_context=ctx + 64, device=0, batch=batch, kv_dtype=E.KV_BF16)
+    if b64:
+        for layer in range(cfg.n_layers):
+            eng.set_router_bias(layer, brain.router_popularity_bias(cfg, layer, 0, 1.1).numpy())
+    eng.seek(ctx)
+    toks, ms = eng.decode_greedy(np.arange(1, batch + 1), max(args.warmup, 1))
+    toks, ms = eng.decode_greedy(toks[-1], args.steps)
+    print(json.dumps({"profile_case": True, "layers": args.profile_case, "batch": batch, "context": ctx, "steps": args.steps,
+                      "ms_per_step": ms / args.steps, "launches_per_step": eng.launches_per_step(), "note": "not a bench value"}), flush=True)
     if args.timeline:
         # the step as the CUDA graph runs it: per launch, microseconds on the device global timer relative to the
         # first launch, and block 0's own progress (SM cycle counter at the sampled clock) at its points 1..7
-        names = {1: "k_tcgemv", 3: "k_delta_step", 5: "k_moe_gu1", 6: "k_moe_down1", 7: "k_attn(_mma)", 8: "k_attn_merge"}
+        names = {1: "k_tcgemv", 3: "k_delta_step", 5: "k_moe_gu1", 6: "k_moe_down1", 7: "k_attn(_mma)", 8: "k_attn_merge", 9: "k_prep_x",
+                 10: "k_mma_i8", 11: "k_group_picks", 12: "k_mma_q4", 13: "k_ep_combine", 14: "k_umma", 15: "k_prep_q", 16: "k_umma_q4",
+                 17: "k_prep_q_slots"}
         eng.trace_step()
         t = eng.trace_step().astype(np.int64)
         ghz = args.timeline_ghz
@@ -326,8 +333,10 @@ def b64_measure(pkg, K: int, W: int, world: int, rank: int, local: int, dist):
         dist.all_gather_object(allt, all_toks)
         picks = np.concatenate(allp, 1)
         all_toks = np.concatenate(allt, 1)
-    # the same sums in the same order on every number of GPUs: this hash must not depend on N
-    tokens_sha1 = hashlib.sha1(np.ascontiguousarray(all_toks.astype("<u4")).tobytes()).hexdigest()
+    # the same sums in the same order on every number of GPUs: this hash must not depend on N. It covers the first
+    # greedy steps only, so that runs with different --steps / --warmup can be compared too
+    n_hashed = min(8, all_toks.shape[0])
+    tokens_sha1 = hashlib.sha1(np.ascontiguousarray(all_toks[:n_hashed].astype("<u4")).tobytes()).hexdigest()
     load = np.stack([ep.load_per_rank(picks[l], cfg.n_experts, world) for l in range(cfg.n_layers)]).sum(0)
     uniq = float(np.mean([len(np.unique(picks[l])) for l in range(cfg.n_layers)]))
     value = Bt * K / (ms / 1e3)
@@ -364,7 +373,7 @@ def b64_measure(pkg, K: int, W: int, world: int, rank: int, local: int, dist):
             "e2e": {"value": Bt * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
                     "timing": "host wall clock around K feed_batch() calls (ids in, arg-max out), max over ranks"},
             "gpu_launches": n_launch * K,
-            "tokens_sha1": tokens_sha1, "nvlink_bytes_per_step_per_gpu": nvlink,
+            "tokens_sha1": tokens_sha1, "tokens_hashed": f"first {n_hashed} greedy steps of all {Bt} sequences", "nvlink_bytes_per_step_per_gpu": nvlink,
             "roofline": {"bound": "hbm", "kernel": "whole step, per GPU", "achieved": step_gbs, "peak": peak, "unit": "GB/s",
                          "frac": step_gbs / peak, "peak_kind": peak_kind, "traffic": None,
                          "bytes_per_step_per_gpu": bytes_step},
@@ -527,7 +536,7 @@ def run_ours(args):
     if rank == 0 and world == 1 and not args.no_b64:
         # the single-GPU point of the expert-parallel series (the lines of --gpus 2/4/8 carry the other points)
         full = b64_measure(pkg, min(K, 64), 3, 1, 0, local, None)
-        b64 = {k: full[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "tokens_sha1", "roofline", "expert_load", "e2e", "config")}
+        b64 = {k: full[k] for k in ("metric", "value", "unit", "ms_per_step", "steps", "tokens_sha1", "tokens_hashed", "roofline", "expert_load", "e2e", "config")}
     if rank == 0 and world == 1 and not args.no_cpu:
         cfg4, dev, host = sample_brain(f"cuda:{local}")
         parity, model = parity_check(E, cfg4, dev, host)
