@@ -544,8 +544,10 @@ int b2_engine::finish() {
     CU(dalloc(&asc, (size_t)B * c.TOPK * std::max(1, c.I / 32))); CU(dalloc(&asum, (size_t)B * c.TOPK * std::max(1, c.I / 32)));
     head_grid = std::min((c.V + 31) / 32, nsm);
     CU(dalloc(&part_val, (size_t)B * head_grid)); CU(dalloc(&part_idx, (size_t)B * head_grid));
-    // attention: enough slices to fill the GPU, but at least 64 positions each at full context
-    nsplit = std::max(1, std::min({64, (2 * nsm) / std::max(1, c.KV * B), (cap + 63) / 64}));
+    // attention: enough slices to fill the GPU, but at least 64 positions each at full context. With many sequences the
+    // GPU is full anyway; slices of about 8 tiles then keep the blocks short, so that they spread evenly over the SMs
+    // (an SM holds one block: 2 x 64 x 2 blocks of 64 tiles each were two uneven waves, 295 us per layer at context 8192)
+    nsplit = std::max(1, std::min({64, std::max((2 * nsm) / std::max(1, c.KV * B), (cap + 8 * AM_TILE - 1) / (8 * AM_TILE)), (cap + 63) / 64}));
     if (const char* v = getenv("B2_ATTN_SPLITS")) nsplit = std::max(1, std::min(64, atoi(v)));   // for tests: long slices at short contexts
     attn_tiles = ((cap + nsplit - 1) / nsplit + AM_TILE - 1) / AM_TILE;
     CU(dalloc(&attn_part, (size_t)B * c.KV * nsplit * (c.H / c.KV) * (c.HD + 2)));
@@ -1022,7 +1024,7 @@ static cudaError_t launch_experts_mma(const ExpertArgs& a, int T, const ExpertMm
     return cudaSuccess;
 }
 
-static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaStream_t st, int tiles_per_slice, b2_engine* prof = nullptr) {
+static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaStream_t st, int tiles_per_slice, int nsm, b2_engine* prof = nullptr) {
     const int G = a.H / a.KV;
     const size_t smem = (size_t)WARPS * G * HD * 4;
     dim3 g(a.nsplit, a.KV, B);
@@ -1036,7 +1038,9 @@ static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaS
     const bool rope_ok = hr % 32 == 0 || (hr > 0 && hr < 32 && (hr & (hr - 1)) == 0);   // pairs in one lane, or a power of two lanes apart
     if (!f32 && G <= 8 && rope_ok && (HD == 256 || HD == 128 || HD == 64)) {
         // bf16 cache: both contractions on the tensor cores; two tile buffers when a slice can span several tiles
-        const int nbuf = tiles_per_slice > 1 ? 2 : 1;
+        // with two or more blocks per SM to choose from, two single-buffered blocks on an SM (registers allow two) hide a
+        // tile's latency behind each other's products better than one double-buffered block does
+        const int nbuf = (tiles_per_slice > 1 && (long)a.nsplit * a.KV * B < 2L * nsm) ? 2 : 1;
         cudaError_t e;
 #define ATM(hd)                                                                                     \
     {                                                                                               \
@@ -1164,9 +1168,9 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count, int chunk_T, bool chunk
                 // chunk's earlier tokens there (they write their own row again, with the same bytes)
                 AttnArgs ap = t;
                 ap.append_only = 1;
-                e = launch_attn(ap, c.HD, kv_f32, B, st, attn_tiles);
+                e = launch_attn(ap, c.HD, kv_f32, B, st, attn_tiles, nsm);
             }
-            if (e == cudaSuccess) e = launch_attn(t, c.HD, kv_f32, B, st, attn_tiles);
+            if (e == cudaSuccess) e = launch_attn(t, c.HD, kv_f32, B, st, attn_tiles, nsm);
             if (e != cudaSuccess) return fail("attention launch: %s", cudaGetErrorString(e));
             mark(3, st);
             ProjArgs p{};

@@ -354,6 +354,34 @@ def test_bf16_cache_attention_over_several_tiles(E, tiny_path, splits, monkeypat
     e.close()
 
 
+def test_bf16_cache_attention_single_buffered_blocks(E, pkg, tmp_path, monkeypatch):
+    """With two or more blocks per SM to choose from (sequences x KV heads x slices) the attention kernel runs
+    single-buffered, two blocks to an SM; slices of two tiles here (32 sequences, 4 KV heads, 3 slices of a 320-token
+    cache), against the oracle with the same cache rounding."""
+    import dataclasses
+    from b200moe import brain
+    monkeypatch.setenv("B2_ATTN_SPLITS", "3")
+    cfg = dataclasses.replace(pkg.HybridConfig.micro(), n_layers=2, layer_types=["delta", "attn"], n_heads=8, n_kv_heads=4)
+    path = str(tmp_path / "kv4.nx")
+    brain.write_brain(path, cfg, seed=5)
+    B, T = 32, 150
+    assert 3 * cfg.n_kv_heads * B >= 2 * 148
+    rng = np.random.default_rng(77)
+    ids = rng.integers(0, cfg.vocab_size, (B, T))
+    e = E.HybridEngine.load(path, max_context=320, batch=B, kv_dtype=E.KV_BF16)
+    model = O.HybridOracle(O.Brain(path))
+    cache = model.new_cache(B, 320, kv_dtype="bf16")
+    worst = 0.0
+    for t in range(T):
+        want = model.forward(ids[:, t][:, None], cache)
+        nxt, got = e.feed_batch(ids[:, t])
+        if t % 16 == 0 or t > T - 6:
+            worst = max(worst, float(np.abs(got - want).max()))
+            assert (got.argmax(-1) == want.argmax(-1)).all()
+    assert worst < TOL, worst
+    e.close()
+
+
 def test_step_timeline(E, tiny_path):
     """b2_debug_trace_step: one row per launch of a graph-run step; the kernels that record stamp a first-in time,
     a last-out time after it, and launches follow one another in time; the step still advances the state."""
