@@ -196,6 +196,14 @@ struct b2_engine {
     ncclResult_t (*p_ncclGroupEnd)() = nullptr;
     const char* (*p_ncclGetErrorString)(ncclResult_t) = nullptr;
     float *rec_local = nullptr, *rec_all = nullptr, *recv_y = nullptr;
+    // exchange by peer stores: rec_all | recv_y | flags are one block that the other ranks map (cudaIpc)
+    float* ep_block = nullptr;
+    size_t ep_block_floats = 0, ep_flag_off = 0;
+    float* ep_peer[EP_MAX_WORLD] = {};
+    bool ep_peer_ready = false;
+    int* d_ep_seq = nullptr;
+    unsigned long long* d_ep_rows = nullptr;
+    long ep_steps = 0;
     int load_nccl();
     int ep_exchange_records(cudaStream_t st);
     int ep_exchange_outputs(cudaStream_t st);
@@ -265,13 +273,14 @@ struct b2_engine {
 b2_engine::~b2_engine() {
     if (t.empty() && !finished) return;   // nothing was ever allocated (e.g. creation was refused)
     cudaSetDevice(device);
+    if (ep_peer_ready) for (int p = 0; p < ep_world; p++) if (p != ep_rank && ep_peer[p]) cudaIpcCloseMemHandle(ep_peer[p]);
     if (graph) cudaGraphExecDestroy(graph);
     if (chunk_graph) cudaGraphExecDestroy(chunk_graph);
     for (auto& kv : t) cudaFree(kv.second.p);
     for (auto& l : layers) { cudaFree((void*)l.eptr); cudaFree(l.router_bias); cudaFree(l.live); }
     void* bufs[] = {conv, state, snap_conv[0], snap_conv[1], snap_state[0], snap_state[1], kpool, vpool, page_table, rope_cos,
                     rope_sin, d_tok, d_next, d_pos, d_err, d_counter, d_acounter, x, big, zbuf, kraw, vraw, beta, gdec, obuf, att,
-                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, rec_all, recv_y, xh, g_list, g_chunk, acth, xsum_tok, xsum_act, sq, sq_scale, sq_sum, d_trace, (void*)top_ptr, actq, asc, asum, uq_i, uq_b, uq_scale, d_counts, csel, cselw, cscore, core_y};
+                    rlogits, sh_act, sgate, act, logits, top_idx, top_w, part_val, part_idx, attn_part, tap_buf, ypart, d_dcounter, rec_local, ep_block, d_ep_seq, d_ep_rows, xh, g_list, g_chunk, acth, xsum_tok, xsum_act, sq, sq_scale, sq_sum, d_trace, (void*)top_ptr, actq, asc, asum, uq_i, uq_b, uq_scale, d_counts, csel, cselw, cscore, core_y};
     for (void* p : bufs) cudaFree(p);
     void* cb[] = {pc.tok, pc.vpos, pc.x, pc.big, pc.zbuf, pc.kraw, pc.vraw, pc.beta, pc.gdec, pc.obuf, pc.att, pc.rlogits, pc.sh_act, pc.sgate,
                   pc.act, pc.top_idx, pc.top_w, pc.ypart, pc.attn_part, pc.dcounter, pc.counter, pc.xh, pc.acth, pc.uq_i, pc.uq_b, pc.uq_scale,
@@ -577,8 +586,13 @@ int b2_engine::finish() {
     if (ep_world > 1) {
         const size_t rw = c.D + 2 * c.TOPK;
         CU(dalloc(&rec_local, (size_t)B * rw));
-        CU(dalloc(&rec_all, Bg * rw));
-        CU(dalloc(&recv_y, Bg * (c.TOPK + 1) * c.D));
+        const size_t nrec = (Bg * rw + 63) / 64 * 64, ny = Bg * (c.TOPK + 1) * c.D;
+        ep_flag_off = nrec + ny;
+        ep_block_floats = ep_flag_off + 2 * EP_MAX_WORLD * EP_MAX_BLOCKS;
+        CU(dalloc(&ep_block, ep_block_floats));
+        CU(cudaMemset(ep_block, 0, ep_block_floats * sizeof(float)));
+        rec_all = ep_block; recv_y = ep_block + nrec;
+        CU(dalloc(&d_ep_seq, 2)); CU(dalloc(&d_ep_rows, 1));
     }
     CU(cudaMallocHost((void**)&h_pin, (std::max(B, 1) * 2 + 1) * sizeof(uint32_t)));   // ids | arg-max | device error word
     CU(cudaStreamCreateWithFlags(&stream, cudaStreamNonBlocking));
@@ -1294,8 +1308,19 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count, int chunk_T, bool chunk
                 EpArgs ep{};
                 ep.x = x; ep.top_idx = a.top_idx; ep.top_w = a.top_w; ep.rec = rec_local; ep.recv_y = recv_y; ep.sg = sgate; ep.xout = x;
                 ep.D = c.D; ep.topk = c.TOPK; ep.B = B; ep.E = c.E; ep.world = ep_world; ep.rank = ep_rank; ep.has_shared = 1;
-                launch_k(k_ep_pack, dim3(B), dim3(256), 0, st, ep);
-                if (ep_exchange_records(st)) return 1;
+                EpPushArgs pa{};
+                if (ep_peer_ready) {
+                    for (int p = 0; p < ep_world; p++) pa.peers.base[p] = ep_peer[p];
+                    pa.peers.rec_off = 0; pa.peers.y_off = (size_t)(recv_y - ep_block); pa.peers.flag_off = ep_flag_off;
+                    pa.x = x; pa.top_idx = a.top_idx; pa.top_w = a.top_w; pa.ypart = ypart; pa.D = c.D; pa.topk = c.TOPK; pa.B = B; pa.E = c.E;
+                    pa.world = ep_world; pa.rank = ep_rank; pa.seq = d_ep_seq; pa.rows_sent = d_ep_rows; pa.err = d_err;
+                    const int nb0 = std::min(B, EP_MAX_BLOCKS);
+                    launch_k(k_ep_push_records, dim3(nb0), dim3(256), 0, st, pa);
+                    launch_k(k_ep_wait, dim3(1), dim3(EP_MAX_WORLD * EP_MAX_BLOCKS), 0, st, EpWaitArgs{nullptr, (int*)ep_block + ep_flag_off, d_ep_seq, 0, ep_world, ep_rank, nb0, 1 << 21, d_err});
+                } else {
+                    launch_k(k_ep_pack, dim3(B), dim3(256), 0, st, ep);
+                    if (ep_exchange_records(st)) return 1;
+                }
                 x2.x = rec_all; x2.x_stride = rw; x2.top_idx = (const int*)(rec_all + c.D); x2.top_w = rec_all + c.D + c.TOPK; x2.idx_stride = rw;
                 x2.combine = 0; x2.local0 = ep_rank * B; x2.nlocal = B;
                 if (grouped) {
@@ -1304,7 +1329,10 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count, int chunk_T, bool chunk
                 } else {
                     launch_experts(x2, Tg, nsm, st, this);
                 }
-                if (ep_exchange_outputs(st)) return 1;
+                if (ep_peer_ready) {
+                    launch_k(k_ep_push_outputs, dim3(EP_MAX_BLOCKS), dim3(256), 0, st, pa);
+                    launch_k(k_ep_wait, dim3(1), dim3(EP_MAX_WORLD * EP_MAX_BLOCKS), 0, st, EpWaitArgs{nullptr, (int*)ep_block + ep_flag_off, d_ep_seq, 1, ep_world, ep_rank, EP_MAX_BLOCKS, 1 << 21, d_err});
+                } else if (ep_exchange_outputs(st)) return 1;
                 launch_k(k_ep_combine, dim3(std::max(1, (c.D + 255) / 256), B), dim3(256), 0, st, ep);
                 n += 2;
             }
@@ -1440,6 +1468,7 @@ int b2_engine::check_device_error() {
         if (h == 1) return fail("a token id is outside the vocabulary (%d)", c.V);
         if (h == 3) return fail("a bulk copy into shared memory did not complete (bounded wait gave up)");
         if (h == 4) return fail("a block waited too long for another block's results (bounded wait gave up)");
+        if (h == 5) return fail("another rank's part of the expert exchange did not arrive (bounded wait gave up)");
         return fail("router returned an expert outside 0..%d", c.E - 1);
     }
     return 0;
@@ -1447,6 +1476,7 @@ int b2_engine::check_device_error() {
 
 int b2_engine::run_steps(int n) {
     for (int i = 0; i < n; i++) CU(cudaGraphLaunch(graph, stream));
+    if (ep_world > 1) ep_steps += n;
     length += n;
     hits += (uint64_t)n * B * c.TOPK * c.L;
     return 0;
@@ -1592,6 +1622,44 @@ int b2_ep_init(b2_engine* e, const void* id_in, size_t len) {
     ce = cudaStreamSynchronize(e->stream);
     if (ce != cudaSuccess) return e->fail("first exchange: %s", cudaGetErrorString(ce));
     return e->build_graph();
+}
+
+int b2_ep_ipc_handle(b2_engine* e, void* out, size_t len) {
+    if (!e || !e->finished) return 1;
+    if (e->ep_world <= 1 || !e->ep_block) return e->fail("this engine was created for a single GPU");
+    if (len < sizeof(cudaIpcMemHandle_t)) return e->fail("the handle buffer needs %zu bytes", sizeof(cudaIpcMemHandle_t));
+    cudaIpcMemHandle_t h;
+    cudaError_t ce = cudaSetDevice(e->device);
+    if (ce == cudaSuccess) ce = cudaIpcGetMemHandle(&h, e->ep_block);
+    if (ce != cudaSuccess) return e->fail("cudaIpcGetMemHandle: %s", cudaGetErrorString(ce));
+    memcpy(out, &h, sizeof(h));
+    return 0;
+}
+
+int b2_ep_ipc_attach(b2_engine* e, const void* handles, size_t len_each, int n) {
+    if (!e || !e->finished) return 1;
+    if (e->ep_world <= 1 || !e->ep_block) return e->fail("this engine was created for a single GPU");
+    if (n != e->ep_world || n > EP_MAX_WORLD || len_each < sizeof(cudaIpcMemHandle_t))
+        return e->fail("expected %d handles of %zu bytes (at most %d ranks)", e->ep_world, sizeof(cudaIpcMemHandle_t), EP_MAX_WORLD);
+    if (e->ep_peer_ready) return e->fail("the peers' blocks are mapped already");
+    if (e->c.D % 4 != 0 || (2 * e->c.TOPK) % 4 != 0) return e->fail("the peer-store exchange needs d_model and 2 x experts_active to be multiples of 4 (16-byte rows)");
+    cudaError_t ce = cudaSetDevice(e->device);
+    if (ce != cudaSuccess) return e->fail("cudaSetDevice: %s", cudaGetErrorString(ce));
+    for (int p = 0; p < n; p++) {
+        if (p == e->ep_rank) { e->ep_peer[p] = e->ep_block; continue; }
+        cudaIpcMemHandle_t h;
+        memcpy(&h, (const char*)handles + (size_t)p * len_each, sizeof(h));
+        void* ptr = nullptr;
+        ce = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+        if (ce != cudaSuccess) {
+            for (int q = 0; q < p; q++) if (q != e->ep_rank && e->ep_peer[q]) { cudaIpcCloseMemHandle(e->ep_peer[q]); e->ep_peer[q] = nullptr; }
+            cudaGetLastError();
+            return e->fail("cudaIpcOpenMemHandle (rank %d): %s", p, cudaGetErrorString(ce));
+        }
+        e->ep_peer[p] = (float*)ptr;
+    }
+    e->ep_peer_ready = true;
+    return e->comm ? e->build_graph() : 0;          // the step graph holds the exchange's launches
 }
 
 int b2_open(const char* nx_path, int max_context, int device, int batch, int kv_dtype, b2_engine** out) {
@@ -2007,6 +2075,12 @@ double b2_ep_bytes_per_step(const b2_engine* e) {
     const Cfg& c = e->c;
     const double peers = e->ep_world - 1;
     const double gather = peers * e->B * (c.D + 2.0 * c.TOPK) * 4;       // this GPU's records, to every peer
+    if (e->ep_peer_ready) {
+        // peer stores: only the rows of picks computed here for other ranks' tokens travel; counted on the device
+        unsigned long long rows = 0;
+        cudaMemcpy(&rows, e->d_ep_rows, sizeof(rows), cudaMemcpyDeviceToHost);
+        return c.L * gather + (e->ep_steps > 0 ? (double)rows * c.D * 4 / e->ep_steps : 0.0);
+    }
     const double back = peers * e->B * (c.TOPK + 1.0) * c.D * 4;         // pick outputs computed here, to their owners
     return c.L * (gather + back);
 }

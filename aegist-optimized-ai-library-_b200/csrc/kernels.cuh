@@ -1186,6 +1186,140 @@ __global__ void k_ep_combine(const EpArgs a) {
     trace_out(a.trace);
 }
 
+// The same exchange without a library call: every GPU maps every other GPU's exchange block (cudaIpc) and writes
+// its records, and afterwards the outputs of the picks it computed, straight into their places there with plain
+// peer stores. Every sending block then raises a flag of its own in each receiver's block (one system-scope fence by
+// one thread after the block's barrier, then relaxed stores of the exchange's number: fences of all threads, or a
+// last-block counter with three fences in a row, cost 15 us per launch). The receiver's one-block kernel polls its
+// flags with acquire loads, for a bounded number of polls (then error 5 and on with whatever is there), and the
+// kernels after it read the data. Only rows of picks whose expert lives on the sender travel (1 / world of the dense
+// block on average). A block is written again only after its reader has answered (records -> outputs -> next
+// layer's records), so one buffer does.
+constexpr int EP_MAX_WORLD = 8;
+constexpr int EP_MAX_BLOCKS = 64;                    // sending blocks per launch, each with its own flag
+struct EpPeers {
+    float* base[EP_MAX_WORLD];   // every rank's exchange block as this GPU addresses it (its own included)
+    size_t rec_off, y_off;       // floats from the base: records [world * B][D + 2 topk], outputs [world][B][topk + 1][D]
+    size_t flag_off;             // ints from the base: flags [2 kinds][EP_MAX_WORLD senders][EP_MAX_BLOCKS]
+};
+struct EpPushArgs {
+    unsigned long long* trace;
+    EpPeers peers;
+    const float* x;              // [B][D]
+    const int* top_idx;          // [B][topk]
+    const float* top_w;
+    const float* ypart;          // [world * B][topk + 1][D] (outputs kind)
+    int D, topk, B, E, world, rank;
+    const int* seq;              // [2] number of the last completed exchange of each kind
+    unsigned long long* rows_sent;
+    int* err;
+};
+
+// one thread of a block, after the block's stores and a barrier
+__device__ __forceinline__ void ep_signal(const EpPushArgs& a, int kind) {
+    __threadfence_system();
+    const int v = a.seq[kind] + 1;
+    for (int p = 0; p < a.world; p++) {
+        if (p == a.rank) continue;
+        int* f = reinterpret_cast<int*>(a.peers.base[p]) + a.peers.flag_off + (kind * EP_MAX_WORLD + a.rank) * EP_MAX_BLOCKS + blockIdx.x;
+        asm volatile("st.relaxed.sys.global.s32 [%0], %1;" ::"l"(f), "r"(v) : "memory");
+    }
+}
+
+// records: block b takes the local sequences b, b + gridDim.x, .. and writes each one's record into slot
+// rank * B + sequence of every rank's block
+__global__ void __launch_bounds__(256) k_ep_push_records(const EpPushArgs a) {
+    grid_dep_launch();
+    trace_in(a.trace, 18, gridDim.x);
+    grid_dep_wait();
+    const int rw = a.D + 2 * a.topk;
+    for (int b = blockIdx.x; b < a.B; b += gridDim.x) {
+        const size_t slot = (size_t)(a.rank * a.B + b) * rw;
+        for (int k = threadIdx.x * 4; k < a.D; k += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(a.x + (size_t)b * a.D + k);
+            for (int p = 0; p < a.world; p++) *reinterpret_cast<float4*>(a.peers.base[p] + a.peers.rec_off + slot + k) = v;
+        }
+        if ((int)threadIdx.x < a.topk) {
+            const float fi = __int_as_float(a.top_idx[b * a.topk + threadIdx.x]), fw = a.top_w[b * a.topk + threadIdx.x];
+            for (int p = 0; p < a.world; p++) {
+                float* r = a.peers.base[p] + a.peers.rec_off + slot;
+                r[a.D + threadIdx.x] = fi;
+                r[a.D + a.topk + threadIdx.x] = fw;
+            }
+        }
+    }
+    __syncthreads();                                 // the block's stores happen before thread 0's fence (bar.sync, then a cumulative fence)
+    if (threadIdx.x == 0) ep_signal(a, 0);
+    trace_out(a.trace);
+}
+
+// outputs: a row per (token, rank of the pick) of all world * B tokens, then one per local sequence for the shared
+// expert's slot; a row travels only if its expert lives here, to the rank that owns the token. Block b takes the rows
+// b, b + gridDim.x, ..
+__global__ void __launch_bounds__(256) k_ep_push_outputs(const EpPushArgs a) {
+    grid_dep_launch();
+    trace_in(a.trace, 19, gridDim.x);
+    grid_dep_wait();
+    const int T = a.world * a.B, rw = a.D + 2 * a.topk, per = a.E / a.world;
+    const float* rec = a.peers.base[a.rank] + a.peers.rec_off;
+    unsigned sent = 0;
+    for (int row = blockIdx.x; row < T * a.topk + a.B; row += gridDim.x) {
+        int t, r, owner;
+        bool go;
+        if (row < T * a.topk) {
+            t = row / a.topk; r = row - t * a.topk;
+            const int e = __float_as_int(rec[(size_t)t * rw + a.D + r]);
+            go = min(max(e, 0), a.E - 1) / per == a.rank;
+            owner = t / a.B;
+        } else {
+            t = a.rank * a.B + (row - T * a.topk); r = a.topk;         // the shared expert's output of a local sequence
+            go = true;
+            owner = a.rank;
+        }
+        if (!go) continue;
+        const float* src = a.ypart + ((size_t)t * (a.topk + 1) + r) * a.D;
+        float* dst = a.peers.base[owner] + a.peers.y_off + ((size_t)(a.rank * a.B + (t - owner * a.B)) * (a.topk + 1) + r) * a.D;
+        for (int k = threadIdx.x * 4; k < a.D; k += blockDim.x * 4) *reinterpret_cast<float4*>(dst + k) = *reinterpret_cast<const float4*>(src + k);
+        sent += owner != a.rank;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (sent) atomicAdd(a.rows_sent, (unsigned long long)sent);
+        ep_signal(a, 1);
+    }
+    trace_out(a.trace);
+}
+
+// one block: thread (p, b) waits for block b of rank p's launch of this kind; then the exchange's number is kept
+struct EpWaitArgs {
+    unsigned long long* trace;
+    int* flags;                  // this rank's [2][EP_MAX_WORLD][EP_MAX_BLOCKS]
+    int* seq;                    // [2]
+    int kind, world, rank, nblocks, polls;
+    int* err;
+};
+__global__ void __launch_bounds__(EP_MAX_WORLD * EP_MAX_BLOCKS) k_ep_wait(const EpWaitArgs a) {
+    trace_in(a.trace, 20, a.kind);
+    grid_dep_wait();                                 // keeps the chain: what follows this kernel also follows what came before it
+    trace_pt(a.trace, 1);
+    const int want = a.seq[a.kind] + 1;
+    const int p = threadIdx.x / EP_MAX_BLOCKS, b = threadIdx.x % EP_MAX_BLOCKS;
+    const bool failed = a.err && *reinterpret_cast<volatile int*>(a.err) != 0;     // an earlier wait of this step gave up: do not wait again
+    if (!failed && p < a.world && p != a.rank && b < a.nblocks) {
+        const int* f = a.flags + (a.kind * EP_MAX_WORLD + p) * EP_MAX_BLOCKS + b;
+        bool ok = false;
+        for (int i = 0; i < a.polls && !ok; i++) {
+            int v;
+            asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(f) : "memory");
+            ok = v - want >= 0;
+        }
+        if (!ok && a.err) atomicExch(a.err, 5);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) { __threadfence_system(); a.seq[a.kind] = want; }
+    trace_out(a.trace);
+}
+
 // ------------------------------------------------------------------------------------------
 // Small helpers for the host: fill and copy.
 // next_tok[b] = arg-max of logits[b][0..rows) (the first of equal maxima), pos[b] += 1: the greedy step of a batch

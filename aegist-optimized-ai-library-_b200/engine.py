@@ -50,6 +50,8 @@ SYMBOLS = {
     "b2_finish": (_I, [_P]),
     "b2_ep_unique_id": (_I, [_P, _P, C.c_size_t]),
     "b2_ep_init": (_I, [_P, _P, C.c_size_t]),
+    "b2_ep_ipc_handle": (_I, [_P, _P, C.c_size_t]),
+    "b2_ep_ipc_attach": (_I, [_P, _P, C.c_size_t, _I]),
     "b2_verify_file": (_I, [C.c_char_p, C.POINTER(_I), C.c_char_p, C.c_size_t]),
     "b2_close": (None, [_P]),
     "b2_feed": (_I, [_P, _P, _I, _P]),
@@ -183,6 +185,18 @@ class HybridEngine:
     def ep_init(self, unique_id: bytes):
         buf = C.create_string_buffer(unique_id, 128)
         self._check(self._lib.b2_ep_init(self._h, buf, 128))
+
+    def ep_ipc_handle(self) -> bytes:
+        """The handle of this rank's exchange block, for the other ranks to map (b2_ep_ipc_handle)."""
+        buf = C.create_string_buffer(64)
+        self._check(self._lib.b2_ep_ipc_handle(self._h, buf, 64))
+        return buf.raw
+
+    def ep_ipc_attach(self, handles):
+        """Map every rank's exchange block (handles in rank order): the exchange then runs on peer stores."""
+        blob = b"".join(bytes(h).ljust(64, b"\0")[:64] for h in handles)
+        buf = C.create_string_buffer(blob, len(blob))
+        self._check(self._lib.b2_ep_ipc_attach(self._h, buf, 64, len(handles)))
 
     def _check(self, rc):
         if rc:

@@ -26,13 +26,37 @@ def expert_owner(expert: int, n_experts: int, world: int) -> int:
     return int(expert) // (n_experts // world)
 
 
-def attach(engine, rank: int, world: int):
+def attach(engine, rank: int, world: int, peer_stores: bool = True) -> str:
     """Create the engine's NCCL communicator: rank 0 makes the id, everyone receives it through the
-    default torch.distributed group, then all ranks initialise together."""
+    default torch.distributed group, then all ranks initialise together. With `peer_stores` the ranks
+    then map each other's exchange blocks and the per-layer exchange runs on plain peer stores with
+    bounded flag waits instead of NCCL calls; if any rank cannot map a peer (no peer access between
+    the GPUs, IPC closed in the container), all ranks stay on NCCL. Returns "peer-stores" or "nccl"."""
     import torch.distributed as dist
     box = [engine.ep_unique_id() if rank == 0 else None]
     dist.broadcast_object_list(box, src=0)
     engine.ep_init(box[0])
+    if not peer_stores:
+        return "nccl"
+    try:
+        mine = engine.ep_ipc_handle()
+    except Exception:
+        mine = None
+    handles = [None] * world
+    dist.all_gather_object(handles, mine)
+    ok = all(h is not None for h in handles)
+    if ok:
+        try:
+            engine.ep_ipc_attach(handles)
+        except Exception:
+            ok = False
+    votes = [None] * world
+    dist.all_gather_object(votes, ok)
+    if all(votes):
+        return "peer-stores"
+    if ok:
+        raise RuntimeError("this rank mapped its peers but another rank could not: rebuild the engines with peer_stores=False")
+    return "nccl"
 
 
 def load_per_rank(picks: np.ndarray, n_experts: int, world: int) -> np.ndarray:

@@ -247,37 +247,54 @@ def run_profile_case(args):
     cfg = pkg.HybridConfig.full(n_layers=args.profile_case)
     b64 = args.workload == "b64"             # the batched kernels: 64 sequences at context 8192, Zipf(1.1) expert popularity
     batch, ctx = (64, B64_PROMPT) if b64 else (1, PROMPT)
-    eng = E.HybridEngine.from_tensors(cfg.to_dict(), brain.random_brain(cfg, seed=0, device="cuda:0"),
-                                      max_context=ctx + 64, device=0, batch=batch, kv_dtype=E.KV_BF16)
+    # under torchrun (batched workload only): expert parallel as in the bench, rank 0 prints
+    world, rank, local = (int(os.environ.get(k, d)) for k, d in (("WORLD_SIZE", "1"), ("RANK", "0"), ("LOCAL_RANK", "0")))
+    if world > 1:
+        import torch.distributed as dist
+        from b200moe import ep
+        assert b64, "--profile-case on several GPUs needs --workload b64"
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    eng = E.HybridEngine.from_tensors(cfg.to_dict(), brain.random_brain(cfg, seed=0, device=f"cuda:{local}"),
+                                      max_context=ctx + 64, device=local, batch=batch // world, kv_dtype=E.KV_BF16,
+                                      ep_rank=rank, ep_world=world)
+    if world > 1:
+        ep.attach(eng, rank, world, peer_stores=not args.nccl_exchange)
     if b64:
         for layer in range(cfg.n_layers):
             eng.set_router_bias(layer, brain.router_popularity_bias(cfg, layer, 0, 1.1).numpy())
     eng.seek(ctx)
-    toks, ms = eng.decode_greedy(np.arange(1, batch + 1), max(args.warmup, 1))
+    toks, ms = eng.decode_greedy(np.arange(1, batch + 1)[rank * (batch // world):(rank + 1) * (batch // world)], max(args.warmup, 1))
     toks, ms = eng.decode_greedy(toks[-1], args.steps)
-    print(json.dumps({"profile_case": True, "layers": args.profile_case, "batch": batch, "context": ctx, "steps": args.steps,
-                      "ms_per_step": ms / args.steps, "launches_per_step": eng.launches_per_step(), "note": "not a bench value"}), flush=True)
+    if rank == 0:
+        print(json.dumps({"profile_case": True, "layers": args.profile_case, "batch": batch, "gpus": world, "context": ctx, "steps": args.steps,
+                          "ms_per_step": ms / args.steps, "launches_per_step": eng.launches_per_step(), "note": "not a bench value"}), flush=True)
     if args.timeline:
         # the step as the CUDA graph runs it: per launch, microseconds on the device global timer relative to the
         # first launch, and block 0's own progress (SM cycle counter at the sampled clock) at its points 1..7
         names = {1: "k_tcgemv", 3: "k_delta_step", 5: "k_moe_gu1", 6: "k_moe_down1", 7: "k_attn(_mma)", 8: "k_attn_merge", 9: "k_prep_x",
                  10: "k_mma_i8", 11: "k_group_picks", 12: "k_mma_q4", 13: "k_ep_combine", 14: "k_umma", 15: "k_prep_q", 16: "k_umma_q4",
-                 17: "k_prep_q_slots"}
-        eng.trace_step()
+                 17: "k_prep_q_slots", 18: "k_ep_push_records", 19: "k_ep_push_outputs", 20: "k_ep_wait"}
+        eng.trace_step()                     # every rank steps (the exchange is collective); rank 0 prints its own timeline
         t = eng.trace_step().astype(np.int64)
         ghz = args.timeline_ghz
-        live = t[t[:, 5] > 0]
-        t0 = live[:, 0].min()
+        live = t[t[:, 5] > 0] if rank == 0 else t[:0]
+        t0 = live[:, 0].min() if len(live) else 0
         prev = None
-        print("kernel hint | first block in, last block in, last block out | since previous kernel's end | block 0: us after it came in, at points 1..7")
+        if rank == 0:
+            print("kernel hint | first block in, last block in, last block out | since previous kernel's end (includes NCCL's kernels, "
+                  "which do not stamp) | block 0: us after it came in, at points 1..7")
         for r in live:
             s, li, e = (r[0] - t0) / 1e3, (r[7] - t0) / 1e3, (r[4] - t0) / 1e3
             pts = " ".join(f"{(r[8 + j] - r[8]) / ghz / 1e3:6.2f}" if r[8 + j] > 0 else "     -" for j in range(1, 8))
             print(f"{names.get(int(r[5]), '?'):13s} {int(r[6]):6d} | {s:7.2f} {li:7.2f} {e:7.2f} | {e - (prev if prev is not None else s):6.2f} | {pts}")
             prev = e
+    if world > 1:
+        eng.close()
+        dist.destroy_process_group()
 
 
-def b64_measure(pkg, K: int, W: int, world: int, rank: int, local: int, dist):
+def b64_measure(pkg, K: int, W: int, world: int, rank: int, local: int, dist, peer_stores: bool = True):
     """Batched decode of 64 sequences at context 8192 with Zipf(1.1) expert popularity, expert-parallel over `world`
     ranks (256/world experts of every layer per GPU, the routed tokens exchanged by NCCL). Returns rank 0's line."""
     import hashlib
@@ -293,8 +310,7 @@ def b64_measure(pkg, K: int, W: int, world: int, rank: int, local: int, dist):
     eng = E.HybridEngine.from_tensors(cfg.to_dict(), brain.random_brain(cfg, seed=0, device=f"cuda:{local}"),
                                       max_context=cap, device=local, batch=B, kv_dtype=E.KV_BF16, ep_rank=rank, ep_world=world)
     torch.cuda.empty_cache()
-    if world > 1:
-        ep.attach(eng, rank, world)
+    exchange = ep.attach(eng, rank, world, peer_stores=peer_stores) if world > 1 else "none"
     for layer in range(cfg.n_layers):
         eng.set_router_bias(layer, brain.router_popularity_bias(cfg, layer, 0, 1.1).numpy())
     t_build = time.perf_counter() - t0
@@ -368,7 +384,9 @@ def b64_measure(pkg, K: int, W: int, world: int, rank: int, local: int, dist):
                        "batch": Bt, "sequences_per_gpu": B, "context": B64_PROMPT,
                        "context_note": f"length set to {B64_PROMPT - fed} directly, then {fed} real tokens fed",
                        "kv_cache": "bf16", "parallelism": f"ep{world}: {cfg.n_experts // world} experts of every layer per GPU, "
-                                                          "sequences split over the GPUs, NCCL all-gather + all-to-all per layer",
+                                                          "sequences split over the GPUs, per layer the records of all sequences to every GPU and the "
+                                                          "pick outputs back to their owners, by " + {"peer-stores": "plain peer stores over NVLink with bounded flag waits (rows of owned picks only)", "nccl": "NCCL all-gather + grouped send/recv (dense blocks)", "none": "no exchange (one GPU)"}[exchange],
+                       "exchange": exchange,
                        "l2": "per-step traffic exceeds L2 (126 MB); no flush needed"},
             "e2e": {"value": Bt * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 4 * B, "d2h_bytes_per_step": 4 * B,
                     "timing": "host wall clock around K feed_batch() calls (ids in, arg-max out), max over ranks"},
@@ -393,7 +411,7 @@ def run_b64(args):
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    line = b64_measure(pkg, args.steps, max(args.warmup, 3), world, rank, local, dist)
+    line = b64_measure(pkg, args.steps, max(args.warmup, 3), world, rank, local, dist, peer_stores=not args.nccl_exchange)
     if rank == 0:
         print(json.dumps(line, default=lambda o: o.item() if hasattr(o, 'item') else str(o)), flush=True)
     if world > 1:
@@ -570,6 +588,8 @@ if __name__ == "__main__":
     ap.add_argument("--no-b64", action="store_true", help="one GPU: skip the batch-64 point of the expert-parallel series")
     ap.add_argument("--workload", default="auto", choices=["auto", "b1", "b64"],
                     help="b1: batch-1 decode (the default on one GPU); b64: 64 sequences, expert-parallel (the default on several)")
+    ap.add_argument("--nccl-exchange", action="store_true",
+                    help="several GPUs: keep the per-layer expert exchange on NCCL calls (default: plain peer stores with bounded flag waits)")
     ap.add_argument("--timeline", action="store_true",
                     help="with --profile-case: also print the device-side timeline of one graph-run step (b2_debug_trace_step)")
     ap.add_argument("--timeline-ghz", type=float, default=1.965, help="SM clock for converting block 0's cycle counts")

@@ -53,6 +53,16 @@ int b2_finish(b2_engine* e);
 int b2_ep_unique_id(b2_engine* e, void* id_out, size_t len);
 int b2_ep_init(b2_engine* e, const void* id_in, size_t len);
 
+/* The same exchange by plain peer stores instead of NCCL calls (optional, after b2_ep_init): every rank gets the
+ * 64-byte handle of its exchange block (cudaIpc), the handles of all ranks in rank order travel to every rank by any
+ * means, and b2_ep_ipc_attach maps them. From then on a rank writes its records, and the outputs of the picks it
+ * computed (only those: 1 / ep_world of the dense block on average), straight into the other ranks' blocks and raises
+ * a flag there; the receiving rank waits for the flags a bounded number of polls (about a second; then the step
+ * fails with a message, it does not hang). Results are the same sums in the same order as with NCCL and as on one
+ * GPU. All ranks attach, or none. No counterpart in the reference. */
+int b2_ep_ipc_handle(b2_engine* e, void* handle_out, size_t len);
+int b2_ep_ipc_attach(b2_engine* e, const void* handles, size_t len_each, int n);
+
 /* NxFile::verify (aegist_rs/src/nx.rs:164-184): recompute the per-group SHA-256 of a brain file.
  * ok[0..2] = base, engine, cores (1 = matches the header). */
 int b2_verify_file(const char* nx_path, int ok[3], char* err, size_t err_len);

@@ -1,5 +1,6 @@
-"""Expert-parallel decode on two GPUs through the C ABI + NCCL: identical to the single-GPU engine
-and within tolerance of the reference's stored batch rows. Skipped with fewer than two GPUs."""
+"""Expert-parallel decode on two GPUs through the C ABI, with the exchange on plain peer stores and on NCCL:
+identical to the single-GPU engine and within tolerance of the reference's stored batch rows. Skipped with fewer
+than two GPUs."""
 import os
 import socket
 
@@ -21,7 +22,7 @@ def _tensors(micro_path):
     return nx, [(n, nx.info(n)["dtype"], np.array(nx.tensor(n))) for n in nx.header["tensors"]]
 
 
-def _worker(rank, world, port, micro_path, ids, steps, out_dir):
+def _worker(rank, world, port, micro_path, ids, steps, out_dir, peer_stores):
     import torch.distributed as dist
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     torch.cuda.set_device(rank)
@@ -32,7 +33,8 @@ def _worker(rank, world, port, micro_path, ids, steps, out_dir):
     B = ids.shape[0] // world
     e = E.HybridEngine.from_tensors(nx.config, tensors, max_context=32, device=rank, batch=B, kv_dtype=E.KV_F32,
                                     ep_rank=rank, ep_world=world)
-    ep.attach(e, rank, world)
+    how = ep.attach(e, rank, world, peer_stores=peer_stores)
+    assert how == ("peer-stores" if peer_stores else "nccl"), how
     mine = ids[rank * B:(rank + 1) * B]
     rows = []
     for t in range(mine.shape[1]):
@@ -42,13 +44,15 @@ def _worker(rank, world, port, micro_path, ids, steps, out_dir):
         nxt, lg = e.feed_batch(rows[-1].argmax(-1))
         rows.append(lg)
     np.save(os.path.join(out_dir, f"rows{rank}.npy"), np.stack(rows))
+    assert (e.ep_bytes_per_step() > 0)
     e.close()
     dist.barrier()
     dist.destroy_process_group()
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_two_gpus_equal_one_gpu(pkg, micro_path, golden_dir, tmp_path):
+@pytest.mark.parametrize("peer_stores", [True, False])
+def test_two_gpus_equal_one_gpu(pkg, micro_path, golden_dir, tmp_path, peer_stores):
     import torch.multiprocessing as mp
     from b200moe import engine as E
     g = np.load(os.path.join(golden_dir, "micro_golden.npz"))
@@ -57,7 +61,7 @@ def test_two_gpus_equal_one_gpu(pkg, micro_path, golden_dir, tmp_path):
     s.bind(("127.0.0.1", 0))
     port = s.getsockname()[1]
     s.close()
-    mp.spawn(_worker, args=(2, port, micro_path, ids, 8, str(tmp_path)), nprocs=2, join=True)
+    mp.spawn(_worker, args=(2, port, micro_path, ids, 8, str(tmp_path), peer_stores), nprocs=2, join=True)
     two = np.concatenate([np.load(tmp_path / f"rows{r}.npy") for r in range(2)], 1)      # [T, 4, V]
     e = E.HybridEngine.load(micro_path, max_context=32, batch=4)
     rows = []
@@ -69,3 +73,48 @@ def test_two_gpus_equal_one_gpu(pkg, micro_path, golden_dir, tmp_path):
     e.close()
     assert np.array_equal(two, one)                          # same sums in the same order
     assert np.abs(two - g["batch_logits"]).max() < 3e-4       # and the reference's rows
+
+
+def _worker_absent(rank, world, port, micro_path, ids, out_dir):
+    """Both ranks take three steps together; then rank 1 stays away and rank 0 steps alone."""
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    nx, tensors = _tensors(micro_path)
+    from b200moe import engine as E
+    from b200moe import ep
+    B = ids.shape[0] // world
+    e = E.HybridEngine.from_tensors(nx.config, tensors, max_context=32, device=rank, batch=B, kv_dtype=E.KV_F32,
+                                    ep_rank=rank, ep_world=world)
+    assert ep.attach(e, rank, world, peer_stores=True) == "peer-stores"
+    mine = ids[rank * B:(rank + 1) * B]
+    for t in range(3):
+        e.feed_batch(mine[:, t])
+    torch.cuda.synchronize()
+    dist.barrier()                      # nothing of either rank is in flight from here on
+    msg = ""
+    if rank == 0:
+        try:
+            e.feed_batch(mine[:, 3])
+        except E.EngineError as err:
+            msg = str(err)
+        with open(os.path.join(out_dir, "absent.txt"), "w") as f:
+            f.write(msg)
+    dist.barrier()                      # rank 1 keeps its block mapped until rank 0 has given up
+    e.close()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_absent_rank_ends_the_step_with_an_error(pkg, micro_path, golden_dir, tmp_path):
+    """A rank that does not take part (it left between steps, on the host): the other rank's bounded flag waits run out,
+    its kernels end normally and the step returns an error that names the exchange; nothing hangs."""
+    import torch.multiprocessing as mp
+    g = np.load(os.path.join(golden_dir, "micro_golden.npz"))
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mp.spawn(_worker_absent, args=(2, port, micro_path, g["batch_prompt"], str(tmp_path)), nprocs=2, join=True)
+    assert "did not arrive" in (tmp_path / "absent.txt").read_text()
