@@ -1285,7 +1285,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count, int chunk_T, bool chunk
             x2.shd_w = l.sh_down.w; x2.shd_s = l.sh_down.s; x2.SH = c.SH; x2.xout = x; x2.err = d_err;
             x2.ypart = ypart; x2.counter = d_dcounter; x2.null_is_error = ep_world == 1;
             const int Tg = B * ep_world;
-            const bool grouped = xh && Tg >= 16 && Tg * c.TOPK <= GQ_MAXP && c.D % MM_KC == 0 && c.I % MM_KC == 0 &&
+            const bool grouped = xh && Tg >= 8 && Tg * c.TOPK <= GQ_MAXP && c.D % MM_KC == 0 && c.I % MM_KC == 0 &&
                                  c.SH % MM_KC == 0 && c.D <= 2048 && c.I <= 2048 && c.E <= 256;
             const ExpertMmaCtx mctx{g_list, g_chunk, cap_small, cap_big, xh, acth, xsum_tok, xsum_act,
                                     chunk ? pc.sq : sq, chunk ? pc.sq_scale : sq_scale, chunk ? pc.sq_sum : sq_sum, Tg * c.TOPK,
