@@ -34,6 +34,11 @@ namespace b2 {
         if (e_ != cudaSuccess) return fail("%s: %s", #call, cudaGetErrorString(e_));                   \
     } while (0)
 
+// From this many sequences (or prompt tokens) on a step runs on the tcgen05 GEMM family; below it on the GEMV family,
+// which re-reads the weights once per pair of sequences. Measured on the 4-layer full-width case at context 8192:
+// 0.53 ms per step at 4 sequences, 0.92 at 7 on the GEMV family; 0.74 at 8 on the GEMM family.
+constexpr int BATCH_GEMM_MIN = 6;
+
 struct Cfg {
     int V = 0, D = 0, L = 0;
     std::vector<int> attn;
@@ -560,7 +565,7 @@ int b2_engine::finish() {
     if (const char* v = getenv("B2_ATTN_SPLITS")) nsplit = std::max(1, std::min(64, atoi(v)));   // for tests: long slices at short contexts
     attn_tiles = ((cap + nsplit - 1) / nsplit + AM_TILE - 1) / AM_TILE;
     CU(dalloc(&attn_part, (size_t)B * c.KV * nsplit * (c.H / c.KV) * (c.HD + 2)));
-    if (B >= 8) {
+    if ((int)Bg >= BATCH_GEMM_MIN) {
         xh_tpad = ((int)Bg + MM_TOK - 1) / MM_TOK * MM_TOK;
         CU(dalloc((uint16_t**)&xh, (size_t)xh_tpad * 2 * 4096));
         uq_passes = ((int)Bg + UM_TOK - 1) / UM_TOK;
@@ -742,7 +747,7 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
     GemvArgs a = a0;
     if (a.x_stride == 0) a.x_stride = a.K;
     cudaError_t e;
-    if (bc && B >= 8 && launch_umma(a, B, nsm, st, *bc, &e)) {
+    if (bc && B >= BATCH_GEMM_MIN && launch_umma(a, B, nsm, st, *bc, &e)) {
         // every matrix of the group went to the tcgen05 GEMM; the head's arg-max and the router's top-8 are launches of their own
         if (e != cudaSuccess) return e;
         for (int i = 0; i < a.nseg; i++)
@@ -755,7 +760,7 @@ static cudaError_t launch_gemv(const GemvArgs& a0, int B, int nsm, cudaStream_t 
                          a.top_idx, a.top_w, B, a.core);
         return e;
     }
-    if (bc && bc->xh && B >= 8 && B <= bc->Tpad && a.K % MM_KC == 0) {
+    if (bc && bc->xh && B >= BATCH_GEMM_MIN && B <= bc->Tpad && a.K % MM_KC == 0) {
         // int8 matrices (except the head with its arg-max) go to the tensor cores; bf16 rows stay on k_rowgemv
         MmaArgs m{};
         GemvArgs rest = a;
@@ -1259,7 +1264,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count, int chunk_T, bool chunk
             };
             a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D; a.err = d_err;
             // fewer than 8 tokens on one GPU: the top-8 moves into the expert kernel and the experts are spread over all SMs
-            const bool moe1 = ep_world == 1 && B < 8 && moe1_shape_ok(c);
+            const bool moe1 = ep_world == 1 && B < BATCH_GEMM_MIN && moe1_shape_ok(c);
             a.finisher = moe1 ? FIN_NONE : FIN_TOPK; a.counter = d_counter; a.E = c.E; a.topk = c.TOPK;
             // a chunk's picks live in its own scratch; the last token's are kept where a decode step's are (b2_debug_router)
             a.top_idx = chunk ? pc.top_idx : top_idx + (size_t)li * B * c.TOPK;
@@ -1285,7 +1290,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count, int chunk_T, bool chunk
             x2.shd_w = l.sh_down.w; x2.shd_s = l.sh_down.s; x2.SH = c.SH; x2.xout = x; x2.err = d_err;
             x2.ypart = ypart; x2.counter = d_dcounter; x2.null_is_error = ep_world == 1;
             const int Tg = B * ep_world;
-            const bool grouped = xh && Tg >= 8 && Tg * c.TOPK <= GQ_MAXP && c.D % MM_KC == 0 && c.I % MM_KC == 0 &&
+            const bool grouped = xh && Tg >= BATCH_GEMM_MIN && Tg * c.TOPK <= GQ_MAXP && c.D % MM_KC == 0 && c.I % MM_KC == 0 &&
                                  c.SH % MM_KC == 0 && c.D <= 2048 && c.I <= 2048 && c.E <= 256;
             const ExpertMmaCtx mctx{g_list, g_chunk, cap_small, cap_big, xh, acth, xsum_tok, xsum_act,
                                     chunk ? pc.sq : sq, chunk ? pc.sq_scale : sq_scale, chunk ? pc.sq_sum : sq_sum, Tg * c.TOPK,
