@@ -667,7 +667,7 @@ static cudaError_t launch_mma_i8(const MmaArgs& m, int passes, int nsm, cudaStre
     return e;
 }
 
-// Tensor-core paths for 8 or more tokens: scratch for the fp16 activations of k_mma_i8, and for the activation planes of
+// Tensor-core paths for BATCH_GEMM_MIN or more tokens: scratch for the fp16 activations of k_mma_i8, and for the activation planes of
 // the tcgen05 GEMM (k_umma: int8 digit planes qi, bf16 planes qb, per-token scales; `passes_max` groups of 64 tokens).
 struct BatchCtx { __half* xh; int Tpad; int8_t* qi; uint16_t* qb; float* xscale; int passes_max; };
 
@@ -1080,7 +1080,7 @@ static cudaError_t launch_attn(const AttnArgs& a, int HD, bool f32, int B, cudaS
     return cudaSuccess;
 }
 
-// The expert kernels for fewer than 8 tokens (moe1.cuh): shapes they take, and their two launches. `x_in` rows are
+// The expert kernels for fewer than BATCH_GEMM_MIN tokens (moe1.cuh): shapes they take, and their two launches. `x_in` rows are
 // normalised with `norm_w` when it is given; the result is added into `xout`.
 static bool moe1_shape_ok(const Cfg& c) {
     return (c.D == 512 || c.D == 1024 || c.D == 2048 || c.D == 4096) && c.I >= 128 && c.I <= 2048 && (c.I & (c.I - 1)) == 0 &&
@@ -1263,7 +1263,7 @@ int b2_engine::enqueue_step(cudaStream_t st, bool count, int chunk_T, bool chunk
                 if (has_live) launch_k(k_cores_live, dim3(B), dim3(256), (size_t)(c.D + c.rank) * 4, st, cl);
             };
             a.x = x; a.norm_w = l.norm2; a.eps = c.eps; a.K = c.D; a.err = d_err;
-            // fewer than 8 tokens on one GPU: the top-8 moves into the expert kernel and the experts are spread over all SMs
+            // fewer than BATCH_GEMM_MIN tokens on one GPU: the top-8 moves into the expert kernel and the experts are spread over all SMs
             const bool moe1 = ep_world == 1 && B < BATCH_GEMM_MIN && moe1_shape_ok(c);
             a.finisher = moe1 ? FIN_NONE : FIN_TOPK; a.counter = d_counter; a.E = c.E; a.topk = c.TOPK;
             // a chunk's picks live in its own scratch; the last token's are kept where a decode step's are (b2_debug_router)

@@ -13,10 +13,11 @@
 //   GEMV group    norm2 + router logits + shared gate/up(+SiLU) + shared_gate (+ top-8)
 //   expert gate/up, expert down + shared down, += residual
 //
-// A GEMV group is k_tcgemv (tcgemv.cuh; k_rowgemv, rowgemv.cuh, for shapes it does not take) up to 7
-// sequences and k_prep_x + k_mma_i8 (mmagemm.cuh) from 8 on; the experts are k_moe_gu1 / k_moe_down1
-// (moe1.cuh) up to 7 sequences, k_expert_gu / k_expert_down (this file) for 8 to 15 tokens and wherever
-// the faster kernels do not take the shape, and the grouped GEMM (mmaexperts.cuh, ummaq4.cuh) from 8 tokens on.
+// A GEMV group is k_tcgemv (tcgemv.cuh; k_rowgemv, rowgemv.cuh, for shapes it does not take) up to 5
+// sequences and k_prep_q + k_umma (ummagemm.cuh; k_prep_x + k_mma_i8, mmagemm.cuh, for shapes it does not take)
+// from 6 on; the experts are k_moe_gu1 / k_moe_down1 (moe1.cuh) up to 5 sequences, the grouped GEMM
+// (k_group_picks, mmaexperts.cuh + k_umma_q4, ummaq4.cuh; k_mma_q4 for shapes it does not take) from 6 tokens
+// on, and k_expert_gu / k_expert_down (this file) wherever none of the faster kernels takes the shape.
 //
 // All arithmetic is fp32 with fp32 accumulation or exact integer products (the reference's kernels
 // are fp32, aegist_rs/kernels/aegist.cu:1-6). Weights stream from HBM exactly once per step.

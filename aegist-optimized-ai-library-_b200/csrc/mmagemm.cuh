@@ -1,4 +1,4 @@
-// Batched decode (8 or more sequences per GPU): the int8 linears as a tensor-core contraction.
+// Batched decode (6 or more sequences per GPU): the int8 linears as a tensor-core contraction.
 //
 // With B sequences the linears are [rows x K] x [K x B] products: real dense contractions, and on
 // CUDA cores they are bound by the FMA rate, not by HBM (64 sequences x 1.7 G weights = 110 GFMA per

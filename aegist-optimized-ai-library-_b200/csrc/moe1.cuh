@@ -1,4 +1,4 @@
-// The routed experts of one layer for a handful of tokens (fewer than 8), as two kernels whose work
+// The routed experts of one layer for a handful of tokens (fewer than 6 in the engine, up to 7), as two kernels whose work
 // is spread evenly over the GPU instead of one block per pick:
 //
 //   k_moe_gu1    every block: router softmax + top-8 from the logits (redundantly, which replaces a

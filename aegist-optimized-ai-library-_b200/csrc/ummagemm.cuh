@@ -2,7 +2,7 @@
 //
 //   out[t][row] = epilogue(scale[row] * sum_k W[row][k] x[t][k])        rows x K weights, T tokens
 //
-// With 8 or more tokens (batched decode, prompt chunks) the linears are dense contractions. The fifth-generation
+// With 6 or more tokens (batched decode, prompt chunks) the linears are dense contractions. The fifth-generation
 // tensor cores take both operands straight from shared memory and keep the accumulator in tensor memory, so no
 // warp touches a weight byte:
 //

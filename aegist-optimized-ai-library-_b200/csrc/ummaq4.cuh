@@ -1,4 +1,4 @@
-// k_umma_q4: the 4-bit experts of a step (8 or more tokens) as a grouped Blackwell tensor-core GEMM
+// k_umma_q4: the 4-bit experts of a step (6 or more tokens) as a grouped Blackwell tensor-core GEMM
 // (the reference's expert GEMMs for more than 8 tokens, aegist_rs/kernels/hybrid.cu:461-549).
 //
 // k_group_picks has sorted the step's picks by expert and cut every expert's list into chunks of at most 16 picks. A

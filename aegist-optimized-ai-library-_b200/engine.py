@@ -351,9 +351,8 @@ class HybridEngine:
         return self._lib.b2_ep_bytes_per_step(self._h)
 
     # roles of the launches of a decode step; which kernel fills a role depends on the batch:
-    #   1-7 sequences: k_tcgemv (in_proj, out_proj, head), k_moe_gu1, k_moe_down1
-    #   8+ sequences:  k_prep_x + k_mma_i8 (+ k_tcgemv for bf16 rows and the head), k_expert_gu / k_expert_down,
-    #                  or k_group_picks + k_mma_q4 from 16 tokens on
+    #   1-5 sequences: k_tcgemv (in_proj, out_proj, head), k_moe_gu1, k_moe_down1
+    #   6+ sequences:  k_prep_q + k_umma (tcgen05 GEMMs), k_group_picks + k_prep_q_slots + k_umma_q4 for the experts
     KERNEL_CLASSES = ("embed", "in_proj", "delta_step", "attention", "out_proj", "expert_gate_up", "expert_down", "head")
     KERNELS_SMALL_BATCH = {"embed": "k_embed", "in_proj": "k_tcgemv", "delta_step": "k_delta_step",
                            "attention": "k_attn + k_attn_merge", "out_proj": "k_tcgemv", "expert_gate_up": "k_moe_gu1",
