@@ -724,7 +724,8 @@ static bool launch_umma(const GemvArgs& a, int T, int nsm, cudaStream_t st, cons
     u.nseg = a.nseg;
     // tokens per unit: a block pulls about 110 GB/s out of L2, so few row blocks are split over the tokens too
     int tt = UM_TOK;
-    while (tt > 16 && u.total_units * passes * (UM_TOK / tt) * 2 <= nsm && T > tt / 2) tt /= 2;
+    while (tt > 16 && tt / 2 >= T) tt /= 2;      // no wider than the tokens need: narrow tiles move two K chunks per stage
+    while (tt > 16 && u.total_units * passes * ((std::min(T, (int)UM_TOK) + tt - 1) / tt) * 2 <= nsm && T > tt / 2) tt /= 2;
     u.tt = tt;
     if (!byte_matrix_map(&u.xmap_i8, bc.qi, (uint64_t)passes * UM_PI * UM_TOK, a.K, tt)) return false;
     if (!byte_matrix_map(&u.xmap_bf, bc.qb, (uint64_t)passes * UM_PB * UM_TOK, 2ull * a.K, tt)) return false;
@@ -735,7 +736,8 @@ static bool launch_umma(const GemvArgs& a, int T, int nsm, cudaStream_t st, cons
     u.K = a.K; u.T = T; u.passes = passes; u.xscale = bc.xscale;
     u.conv_w = a.conv_w; u.conv_state = a.conv_state; u.a_log = a.a_log; u.dt_bias = a.dt_bias; u.err = a.err;
     if ((*err = opt_in_smem(k_umma, UM_SMEM)) != cudaSuccess) return true;
-    const int grid = std::max(1, std::min(u.total_units * passes * (UM_TOK / tt), nsm));
+    const int nsub = passes == 1 ? (std::min(T, (int)UM_TOK) + tt - 1) / tt : UM_TOK / tt;      // as the kernel counts them
+    const int grid = std::max(1, std::min(u.total_units * passes * nsub, nsm));
     *err = launch_k(k_umma, dim3(grid), dim3(UM_THREADS), UM_SMEM, st, u);
     g_umma_launches++;
     return true;

@@ -148,7 +148,9 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_umma(const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem = tmem_slot;
     const int NST = um_stages(a.tt), STAGE = um_stage_bytes(a.tt), KC = um_kc(a.tt), CHUNK = um_chunk_bytes(a.tt);
-    const int nsub = UM_TOK / a.tt;                  // token groups of a pass
+    // token groups of a pass; with a single pass only the groups that hold tokens are counted, so that the work items
+    // that exist spread over all blocks
+    const int nsub = a.passes == 1 ? (min(a.T, UM_TOK) + a.tt - 1) / a.tt : UM_TOK / a.tt;
     const int nwork = a.total_units * a.passes * nsub;       // (row block, pass of 64 tokens, token group), token groups innermost
     // work item w -> unit, pass, first token; false when the group holds no token at all (every role skips it alike)
     auto decode = [&](int w, int& unit, int& pass, int& sub) {
