@@ -85,3 +85,61 @@ def test_ownership_and_load(pkg):
     picks = np.array([[0, 1, 100, 255], [33, 34, 35, 36]])
     assert ep.load_per_rank(picks, 256, 8).tolist() == [2, 4, 0, 1, 0, 0, 0, 1]
     assert ep.load_per_rank(picks, 256, 1).tolist() == [8]
+
+
+class _FakeEngine:
+    """Stands in for HybridEngine in ep.attach: records the calls, fails where told to."""
+
+    def __init__(self, rank, fail_handle=False, fail_attach=False):
+        self.rank, self.fail_handle, self.fail_attach, self.calls = rank, fail_handle, fail_attach, []
+
+    def ep_unique_id(self):
+        return b"\x07" * 128
+
+    def ep_init(self, uid):
+        assert uid == b"\x07" * 128
+        self.calls.append("init")
+
+    def ep_ipc_handle(self):
+        if self.fail_handle:
+            raise RuntimeError("cudaIpcGetMemHandle: not supported")
+        return bytes([self.rank]) * 64
+
+    def ep_ipc_attach(self, handles):
+        assert [h[0] for h in handles] == list(range(len(handles)))      # every rank's handle, in rank order
+        if self.fail_attach:
+            raise RuntimeError("cudaIpcOpenMemHandle: peer access is not available")
+        self.calls.append("attach")
+
+
+def _attach_worker(rank, world, port, case, out_dir):
+    import sys
+    sys.path.insert(0, ROOT)
+    from __graft_entry__ import load_package
+    load_package()
+    from b200moe import ep
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    e = _FakeEngine(rank, fail_handle=(case == "no-handle" and rank == 1), fail_attach=(case == "no-attach" and rank == 1))
+    try:
+        how = ep.attach(e, rank, world, peer_stores=(case != "off"))
+    except RuntimeError as err:
+        how = "raised: " + str(err)[:40]
+    with open(os.path.join(out_dir, f"attach{rank}.txt"), "w") as f:
+        f.write(how + "|" + ",".join(e.calls))
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("case,want", [("ok", ["peer-stores|init,attach"] * 2), ("off", ["nccl|init"] * 2),
+                                       ("no-handle", ["nccl|init"] * 2),
+                                       ("no-attach", ["raised: this rank mapped its peers but another r|init,attach", "nccl|init"])])
+def test_attach_agrees_on_the_exchange(tmp_path, case, want):
+    """ep.attach: all ranks end on the same exchange. A rank without a handle keeps everyone on NCCL before anything is
+    mapped; a rank that cannot map a peer after the others did makes the others raise instead of running mixed."""
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mp.spawn(_attach_worker, args=(2, port, case, str(tmp_path)), nprocs=2, join=True)
+    assert [(tmp_path / f"attach{r}.txt").read_text() for r in range(2)] == want
