@@ -160,14 +160,15 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_umma(const __grid_constant__ 
         unit = r / a.passes;
         return pass * UM_TOK + sub * a.tt < a.T;
     };
-    grid_dep_wait();                                 // activations (and residuals, conv state) are earlier launches' results
+    // activations (and residuals, conv state) are earlier launches' results; the weights are not, so the producer warp
+    // sends the weight copies of its first stages before it waits
+    if (warp != 0) grid_dep_wait();
 
     // step-timeline points of block 0 (any thread may stamp): 1 past the dependency wait, 2 the producer has issued its
     // last copy, 3 the MMA lane has committed its last unit, 4 the epilogue got its first accumulator, 5 the epilogue is done
     auto stamp = [&](int i) {
         if (a.trace && blockIdx.x == 0) a.trace[8 + i] = (unsigned long long)clock64();
     };
-    if (threadIdx.x == 0) stamp(1);
     // A bounded wait. `dead` is the caller's own flag: after one of its waits has given up, a thread skips the rest
     // and runs to the end of its loops; the other roles' waits then give up the same way.
     auto wait = [&](uint64_t* bar, uint32_t parity, bool& dead) {
@@ -186,27 +187,61 @@ __global__ void __launch_bounds__(UM_THREADS, 1) k_umma(const __grid_constant__ 
         bool dead = false;
         uint32_t armed_mask = 0, armed_par = 0;     // stages with a copy group sent, and the parity of the latest one
         const int ck = lane / 5, which = lane - ck * 5;      // this lane's chunk of the stage and its copy within the chunk
-        for (int w = blockIdx.x; w < nwork; w += gridDim.x) {
+        // what a lane copies for a work item: its tensor map, row coordinate and place in the stage
+        struct Item { const CUtensorMap* map; int y, off, nk; bool ok; };
+        auto item = [&](int w) {
+            Item it{nullptr, 0, 0, 0, false};
             int unit, pass, sub;
-            if (!decode(w, unit, pass, sub)) continue;
+            if (!decode(w, unit, pass, sub)) return it;
             int s, blk;
             locate(unit, s, blk);
             const int kind = a.seg[s].kind;
             const bool isbf = kind == SEG_BF || kind == SEG_BF_SIGMOID || kind == SEG_BF_DECAY;
             const bool pair = kind == SEG_I8_GATEUP;
-            const int nk = (isbf ? 2 * a.K : a.K) / UM_BK;             // K chunks of the unit
-            const CUtensorMap* map = which >= 2 ? (isbf ? &a.xmap_bf : &a.xmap_i8) : (pair && which == 1 ? &a.wmap2[s] : &a.wmap[s]);
-            const int y = which >= 2 ? (pass * UM_PI + (which - 2)) * UM_TOK + sub * a.tt : (pair ? blk * 64 : blk * UM_M + which * 64);
-            const int off = ck * CHUNK + (which >= 2 ? UM_A_BYTES + (which - 2) * a.tt * UM_BK : which * 64 * UM_BK);
-            for (int k0 = 0; k0 < nk; k0 += KC) {
-                const int nch = min(KC, nk - k0);                       // chunks in this stage
+            it.nk = (isbf ? 2 * a.K : a.K) / UM_BK;                   // K chunks of the unit
+            it.map = which >= 2 ? (isbf ? &a.xmap_bf : &a.xmap_i8) : (pair && which == 1 ? &a.wmap2[s] : &a.wmap[s]);
+            it.y = which >= 2 ? (pass * UM_PI + (which - 2)) * UM_TOK + sub * a.tt : (pair ? blk * 64 : blk * UM_M + which * 64);
+            it.off = ck * CHUNK + (which >= 2 ? UM_A_BYTES + (which - 2) * a.tt * UM_BK : which * 64 * UM_BK);
+            it.ok = true;
+            return it;
+        };
+        // before the wait: the weight copies (lanes with which < 2) of the first work item's first stages, whose barriers
+        // are armed for the whole stage; after it, the plane copies of the same stages. The loop below goes on from there.
+        int w_first = blockIdx.x, pre = 0;
+        while (w_first < nwork && !item(w_first).ok) w_first += gridDim.x;
+        if (w_first < nwork) {
+            const Item it = item(w_first);
+            for (int k0 = 0; k0 < it.nk && pre < NST; k0 += KC, pre++) {
+                const int nch = min(KC, it.nk - k0);
+                if (lane == 0) mbar_expect_tx(&full_bar[pre], (uint32_t)nch * CHUNK);
+                __syncwarp();
+                if (lane < 5 * nch && which < 2) tma_load_2d(ring + (size_t)pre * STAGE + it.off, it.map, (k0 + ck) * UM_BK, it.y, &full_bar[pre]);
+            }
+            grid_dep_wait();
+            if (lane == 0) stamp(1);
+            for (int j = 0; j < pre; j++) {
+                const int k0 = j * KC, nch = min(KC, it.nk - k0);
+                if (lane < 5 * nch && which >= 2) tma_load_2d(ring + (size_t)j * STAGE + it.off, it.map, (k0 + ck) * UM_BK, it.y, &full_bar[j]);
+                armed_mask |= 1u << j;                                  // parity 0: the first use of these stages
+            }
+            st = pre == NST ? 0 : pre;
+            ph = pre == NST ? 1 : 0;
+        } else {
+            grid_dep_wait();
+            if (lane == 0) stamp(1);
+        }
+        for (int w = w_first; w < nwork; w += gridDim.x) {
+            const Item it = item(w);
+            if (!it.ok) continue;
+            for (int k0 = (w == w_first ? pre * KC : 0); k0 < it.nk; k0 += KC) {
+                const int nch = min(KC, it.nk - k0);                    // chunks in this stage
                 if (lane == 0) {
                     wait(&empty_bar[st], ph ^ 1, dead);
                     if (!dead) mbar_expect_tx(&full_bar[st], (uint32_t)nch * CHUNK);
                 }
                 dead = __shfl_sync(0xffffffffu, (int)dead, 0) != 0;
                 if (dead) break;
-                if (lane < 5 * nch) tma_load_2d(ring + (size_t)st * STAGE + off, map, (k0 + ck) * UM_BK, y, &full_bar[st]);
+                if (lane < 5 * nch) tma_load_2d(ring + (size_t)st * STAGE + it.off, it.map, (k0 + ck) * UM_BK, it.y, &full_bar[st]);
                 armed_mask |= 1u << st;
                 armed_par = (armed_par & ~(1u << st)) | ((uint32_t)ph << st);
                 if (++st == NST) { st = 0; ph ^= 1; }
