@@ -118,3 +118,55 @@ def test_absent_rank_ends_the_step_with_an_error(pkg, micro_path, golden_dir, tm
     s.close()
     mp.spawn(_worker_absent, args=(2, port, micro_path, g["batch_prompt"], str(tmp_path)), nprocs=2, join=True)
     assert "did not arrive" in (tmp_path / "absent.txt").read_text()
+
+
+def _worker_full(rank, world, port, out_dir, steps):
+    """Four full-width layers (hidden 2048, 256 experts, expert hidden 512): the tcgen05 GEMMs and the grouped 4-bit
+    expert GEMM over this rank's half of the experts, exchange on peer stores."""
+    import sys
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    from __graft_entry__ import load_package
+    pkg = load_package()
+    from b200moe import brain, ep
+    from b200moe import engine as E
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    cfg = pkg.HybridConfig.full(n_layers=4)
+    B = 16 // world
+    e = E.HybridEngine.from_tensors(cfg.to_dict(), brain.random_brain(cfg, seed=0, device=f"cuda:{rank}"), max_context=64,
+                                    device=rank, batch=B, kv_dtype=E.KV_BF16, ep_rank=rank, ep_world=world)
+    assert ep.attach(e, rank, world) == "peer-stores"
+    first = np.arange(100, 116, dtype=np.uint32)[rank * B:(rank + 1) * B]
+    toks, _ = e.decode_greedy(first, steps)
+    nxt, logits = e.feed_batch(toks[-1])
+    np.save(os.path.join(out_dir, f"full{rank}.npy"), logits)
+    np.save(os.path.join(out_dir, f"toks{rank}.npy"), toks)
+    e.close()
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_gpus_equal_one_gpu_at_full_width(pkg, tmp_path):
+    """The benchmark's expert-parallel kernels at the benchmark's widths: 16 sequences on two GPUs give bit for bit the
+    tokens and logits of 16 sequences on one GPU."""
+    import torch.multiprocessing as mp
+    from b200moe import brain
+    from b200moe import engine as E
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    port = s.getsockname()[1]
+    s.close()
+    mp.spawn(_worker_full, args=(2, port, str(tmp_path), 6), nprocs=2, join=True)
+    two_t = np.concatenate([np.load(tmp_path / f"toks{r}.npy") for r in range(2)], 1)
+    two_l = np.concatenate([np.load(tmp_path / f"full{r}.npy") for r in range(2)], 0)
+    cfg = pkg.HybridConfig.full(n_layers=4)
+    e = E.HybridEngine.from_tensors(cfg.to_dict(), brain.random_brain(cfg, seed=0, device="cuda:0"), max_context=64, device=0,
+                                    batch=16, kv_dtype=E.KV_BF16)
+    toks, _ = e.decode_greedy(np.arange(100, 116, dtype=np.uint32), 6)
+    nxt, logits = e.feed_batch(toks[-1])
+    e.close()
+    assert np.array_equal(two_t, toks)
+    assert np.array_equal(two_l, logits)
