@@ -1,14 +1,25 @@
-"""Decode throughput of the hybrid-MoE engine on B200, next to the CPU port of the reference path.
+"""Decode throughput of the hybrid-MoE engine on B200, next to the reference's CPU implementation of the same path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload auto|b1|b64]
 
 N = 1 (the headline): the full 35B-A3B-shaped model (40 layers, hidden 2048, vocab 151936, 256
 experts top-8 + shared, int8 linears, 4-bit experts), random-init and quantised with the repo's
-quantisers, all experts resident; batch-1 greedy decode after a 4096-token uniform-random prompt.
-A step is one decoded token. `value` is tokens/s of the device-resident greedy loop (CUDA events on
-the engine's stream); `e2e` is the same loop driven through the reference-facing call
-`feed(&[id]) -> logits` with host buffers (id host->device, 608 KB of logits device->host, arg-max by
-the host sampler, every token).
+quantisers, all experts resident; batch-1 greedy decode after a 4096-token uniform-random prompt
+(fed through the engine's chunked feed, untimed). A step is one decoded token. `value` is tokens/s of the
+device-resident greedy loop (CUDA events on the engine's stream); `e2e` is the same loop driven through the
+reference-facing call `feed(&[id]) -> logits` with host buffers (id host->device, 608 KB of logits
+device->host, arg-max by the host sampler, every token). `roofline`: every kernel class timed inside the CUDA
+graph with the device timer, the dominant one against the measured copy bandwidth. `parity`: a 4-layer
+full-width sample brain against the CPU oracle (picks, greedy tokens, logits). `cpu_baseline`: the reference's
+own Python model on the host cores over a bounded sample. `b64`: the one-GPU point of the batched series.
+
+N > 1 under torchrun (or `--workload b64`): 64 sequences at context 8192 with Zipf(1.1) expert popularity, split
+over the ranks, experts sharded (expert parallel); the per-layer exchange runs on plain peer stores
+(`--nccl-exchange`: on NCCL calls). `tokens_sha1` of the first greedy steps must not depend on N.
+`--workload b1` on several GPUs runs independent replicas of the batch-1 workload.
+
+`--profile-case L [--workload b64] [--timeline]`: a short run of the first L layers at full width for profiler
+captures and for the in-graph step timeline; its line is not a bench value.
 
 One JSON line on stdout (rank 0).
 """
